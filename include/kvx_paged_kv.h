@@ -1,0 +1,142 @@
+/*
+ * Launch layer of the paged KV-cache hot path: the entry points that move K/V bytes on
+ * the GPU.  Same names and signatures as the reference launch header
+ * (reference: kernels/kvx_paged_kv.h:11-57), implemented by hand-written sm_100a kernels.
+ *
+ * Every launcher:
+ *   - takes host-resident descriptors whose data / slots / indices / lengths / scale
+ *     pointers address memory of the CURRENT device;
+ *   - enqueues its kernel on `stream` (an opaque cudaStream_t; NULL = the legacy default
+ *     stream) and returns without synchronising;
+ *   - allocates nothing and keeps no pointer after returning;
+ *   - returns KVX_STATUS_OK without launching when there is nothing to move;
+ *   - reports a failed launch as KVX_STATUS_INTERNAL_ERROR;
+ *   - treats bad DATA as "skip": a token whose slot is negative or addresses a block
+ *     >= num_blocks is not written; a sequence position >= seq_lens[s], a logical block
+ *     >= max_blocks_per_seq, or a block id that is negative (or >= num_blocks) is not
+ *     gathered and the corresponding output bytes stay untouched.
+ *
+ * Descriptor checks and their status codes follow the reference launchers in evaluation
+ * order (reference: kernels/kvx_paged_kv.cu:315-376, :493-559, :763-829).
+ */
+#ifndef KVX_PAGED_KV_H
+#define KVX_PAGED_KV_H
+
+#include "kvx_abi.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------ write ------------
+ * cache[slot / block_size][slot % block_size][h][d] = key[t][h][d] (and value), for every
+ * token t with a valid slot, honouring the cache tensors' own strides and layout
+ * (NHD, HND, HND_PACKED).  Bits are copied unchanged.
+ *
+ * kvx_launch_write_kv dispatches on cache->k.dtype: F16 / BF16 / F32 need IO tensors of
+ * the same type; F8_E4M3 (ABI 1.2) quantises 16/32-bit IO on the fly, see below.
+ * reference: kernels/kvx_paged_kv.h:11-13, kernels/kvx_paged_kv.cu:472-491 */
+KVX_API kvx_status_t kvx_launch_write_kv(const kvx_cache_desc_t *cache,
+                                         const kvx_write_desc_t *write, void *stream);
+
+/* Same result as kvx_launch_write_kv.  `tokens_per_seq` must be > 0 and divide
+ * io.num_tokens; it is validated, never used for scheduling.
+ * reference: kernels/kvx_paged_kv.h:15-17, kernels/kvx_paged_kv.cu:739-761 */
+KVX_API kvx_status_t kvx_launch_write_kv_prefill(const kvx_cache_desc_t *cache,
+                                                 const kvx_write_desc_t *write,
+                                                 int32_t tokens_per_seq, void *stream);
+
+/* Type-pinned variants: UNSUPPORTED unless cache AND io tensors have exactly this dtype.
+ * reference: kernels/kvx_paged_kv.h:23-45, kernels/kvx_paged_kv.cu:453-470, :718-737 */
+KVX_API kvx_status_t kvx_launch_write_kv_f32(const kvx_cache_desc_t *cache,
+                                             const kvx_write_desc_t *write, void *stream);
+KVX_API kvx_status_t kvx_launch_write_kv_f16(const kvx_cache_desc_t *cache,
+                                             const kvx_write_desc_t *write, void *stream);
+KVX_API kvx_status_t kvx_launch_write_kv_bf16(const kvx_cache_desc_t *cache,
+                                              const kvx_write_desc_t *write, void *stream);
+KVX_API kvx_status_t kvx_launch_write_kv_prefill_f32(const kvx_cache_desc_t *cache,
+                                                     const kvx_write_desc_t *write,
+                                                     int32_t tokens_per_seq, void *stream);
+KVX_API kvx_status_t kvx_launch_write_kv_prefill_f16(const kvx_cache_desc_t *cache,
+                                                     const kvx_write_desc_t *write,
+                                                     int32_t tokens_per_seq, void *stream);
+KVX_API kvx_status_t kvx_launch_write_kv_prefill_bf16(const kvx_cache_desc_t *cache,
+                                                      const kvx_write_desc_t *write,
+                                                      int32_t tokens_per_seq, void *stream);
+
+/* ------------------------------------------------------------------ gather -----------
+ * out[s][tok][h][d] = cache[table[s][tok / block_size]][tok % block_size][h][d] for
+ * tok < seq_lens[s]; PACKED block tables only; table and seq_lens share one index type.
+ * reference: kernels/kvx_paged_kv.h:19-21, kernels/kvx_paged_kv.cu:891-910 */
+KVX_API kvx_status_t kvx_launch_gather_kv(const kvx_cache_desc_t *cache,
+                                          const kvx_gather_desc_t *gather, void *stream);
+
+/* reference: kernels/kvx_paged_kv.h:47-57, kernels/kvx_paged_kv.cu:872-889 */
+KVX_API kvx_status_t kvx_launch_gather_kv_f32(const kvx_cache_desc_t *cache,
+                                              const kvx_gather_desc_t *gather, void *stream);
+KVX_API kvx_status_t kvx_launch_gather_kv_f16(const kvx_cache_desc_t *cache,
+                                              const kvx_gather_desc_t *gather, void *stream);
+KVX_API kvx_status_t kvx_launch_gather_kv_bf16(const kvx_cache_desc_t *cache,
+                                               const kvx_gather_desc_t *gather, void *stream);
+
+/* ------------------------------------------------------------------ fp8-e4m3 ---------
+ * The reference declares the fp8 dtype and the scale descriptors (kvx_abi.h:47,154-180)
+ * but its launchers answer UNSUPPORTED for them (kernels/kvx_paged_kv.cu:488,907); the
+ * entry points below have no data-moving counterpart there.
+ *
+ * Cache tensors are KVX_DTYPE_F8_E4M3 (1 byte per element, any of the three layouts); IO
+ * tensors are F16, BF16 or F32 (K and V alike).
+ *   write : q = e4m3_rn_satfinite((float)x / scale)      one IEEE f32 division, one
+ *           rounding to E4M3 (ties to even), |y| > 448 and +-inf -> +-448, NaN -> 0x7F.
+ *   gather: out = io_type_rn((float)e4m3(q) * scale)     one f32 multiply, then round to
+ *           the IO type (ties to even); NaN comes out as the canonical quiet NaN.
+ * Scale selection, separately for K and V:
+ *   *_scale_desc.data != NULL : dtype F32, granularity PER_TENSOR (one value) or PER_HEAD
+ *                               (ndim 1, shape[0] = num_kv_heads, stride[0] in elements);
+ *   otherwise                 : the device scalar k_scale / v_scale (per tensor);
+ *   neither                   : KVX_STATUS_UNSUPPORTED.
+ * kvx_launch_write_kv / kvx_launch_gather_kv route here when cache->k.dtype is F8_E4M3.
+ * A gather descriptor has no scale fields, so the dequantising gather takes them as
+ * arguments. */
+KVX_API kvx_status_t kvx_launch_write_kv_f8e4m3(const kvx_cache_desc_t *cache,
+                                                const kvx_write_desc_t *write, void *stream);
+
+KVX_API kvx_status_t kvx_launch_gather_kv_f8e4m3(const kvx_cache_desc_t *cache,
+                                                 const kvx_gather_desc_t *gather,
+                                                 const kvx_scale_desc_t *k_scale,
+                                                 const kvx_scale_desc_t *v_scale, void *stream);
+
+/* Per-head (or per-tensor) scales of one write batch: scale = absmax / 448, absmax taken
+ * over every token and dim of the head (PER_HEAD) or of the tensor (PER_TENSOR), K and V
+ * separately; an absmax of zero (or NaN) yields 1.0f.  Outputs are F32 device arrays of
+ * num_kv_heads (PER_HEAD) or 1 (PER_TENSOR) elements.
+ * `workspace` is device scratch of at least kvx_kv_scales_workspace_bytes(num_kv_heads)
+ * bytes, 256-byte aligned, that MUST be zero before the first call; each call leaves it
+ * zeroed again.  Calls sharing one workspace must not overlap on the GPU.
+ * No counterpart in the reference. */
+KVX_API size_t kvx_kv_scales_workspace_bytes(uint32_t num_kv_heads);
+
+KVX_API kvx_status_t kvx_launch_kv_scales(const kvx_kv_io_desc_t *io,
+                                          kvx_scale_granularity_t granularity, float *k_scale_out,
+                                          float *v_scale_out, void *workspace,
+                                          size_t workspace_bytes, void *stream);
+
+/* ------------------------------------------------------------------ introspection ----
+ * Number of kernels this library has launched in this process since load (or since the
+ * last reset).  Lets a benchmark state how many of its timed launches were these kernels.
+ * No counterpart in the reference. */
+KVX_API uint64_t kvx_b200_launch_count(void);
+KVX_API void kvx_b200_reset_launch_count(void);
+
+/* Tuning knobs for experiments: name = "write_vecs_per_cta", "gather_path" (0 = registers,
+ * 1 = bulk-async staging), ...; returns 0 when the name is known.  Defaults are the
+ * measured-best values; production callers never need this.  No counterpart in the
+ * reference. */
+KVX_API int kvx_b200_set_option(const char *name, int64_t value);
+KVX_API int64_t kvx_b200_get_option(const char *name);
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+
+#endif /* KVX_PAGED_KV_H */

@@ -1,0 +1,63 @@
+"""Builds the C-ABI shared library ``kvx_b200/lib/libkvx_b200.so`` in-tree with nvcc + gcc.
+
+The library holds the CUDA-free validators (``csrc/kvx_abi.c``), the launch layer and
+kernels (``csrc/kvx_paged_kv.cu``) and the host-buffer pipeline (``csrc/kvx_host.cu``),
+compiled for sm_100a only.  Run ``python -m kvx_b200.build`` or call :func:`build`.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CSRC = os.path.join(ROOT, "kvx_b200", "csrc")
+LIB_DIR = os.path.join(ROOT, "kvx_b200", "lib")
+LIB_PATH = os.path.join(LIB_DIR, "libkvx_b200.so")
+INCLUDE = os.path.join(ROOT, "include")
+BUILD_DIR = os.path.join(ROOT, "build")
+
+NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+              "-Xcompiler", "-fPIC", "-I" + INCLUDE]
+CU_SOURCES = ["kvx_paged_kv.cu", "kvx_host.cu"]
+
+
+def _nvcc() -> str:
+    for cand in (shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    raise RuntimeError("nvcc not found: the CUDA library cannot be built")
+
+
+def _stale(target: str, sources: list[str]) -> bool:
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    return any(os.path.getmtime(s) > t for s in sources)
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile the library if any source is newer than it; returns the library path."""
+    os.makedirs(LIB_DIR, exist_ok=True)
+    os.makedirs(BUILD_DIR, exist_ok=True)
+    cu = [os.path.join(CSRC, f) for f in CU_SOURCES if os.path.exists(os.path.join(CSRC, f))]
+    c_src = os.path.join(CSRC, "kvx_abi.c")
+    headers = [os.path.join(INCLUDE, f) for f in os.listdir(INCLUDE)]
+    if not force and not _stale(LIB_PATH, cu + [c_src] + headers):
+        return LIB_PATH
+    c_obj = os.path.join(BUILD_DIR, "kvx_abi.o")
+    run = lambda cmd: subprocess.run(cmd, check=True, stdout=None if verbose else subprocess.PIPE,
+                                     stderr=subprocess.STDOUT)
+    run(["gcc", "-std=c11", "-O2", "-fPIC", "-Wall", "-I" + INCLUDE, "-c", c_src, "-o", c_obj])
+    objs = []
+    for src in cu:
+        obj = os.path.join(BUILD_DIR, os.path.basename(src) + ".o")
+        run([_nvcc(), *NVCC_FLAGS, "-c", src, "-o", obj])
+        objs.append(obj)
+    run([_nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", *objs, c_obj, "-o", LIB_PATH])
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose=True))

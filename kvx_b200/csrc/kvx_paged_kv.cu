@@ -1,0 +1,1721 @@
+/*
+ * Paged KV-cache write / gather for NVIDIA B200 (sm_100a): launch layer + kernels, one
+ * self-contained translation unit with C linkage (needs only kvx_abi.h, kvx_paged_kv.h
+ * and the CUDA runtime, so it can be added to another project's source list as is).
+ *
+ * The work is pure data movement bounded by HBM bandwidth, so the kernels are organised
+ * around three things only: 16-byte coalesced accesses, many independent loads in flight
+ * per thread before the first store, and no wasted threads on padding.
+ *
+ *   write, vector tier   kvx_write_rows_kernel     one CTA = a tile of consecutive tokens;
+ *                        slot -> destination byte offsets are resolved once per token into
+ *                        shared memory, then all threads stream the tile's 16-byte vectors
+ *                        (4 K + 4 V loads in flight per thread, streaming cache hints).
+ *   gather, vector tier  kvx_gather_pages_kernel   persistent CTAs; every CTA compacts the
+ *                        ragged (sequence, page) rectangle with a shared-memory prefix sum
+ *                        over ceil(len / block_size), then each warp copies whole page
+ *                        chunks (contiguous on both sides for NHD) 8 vectors deep.
+ *   gather, bulk tier    kvx_gather_bulk_kernel    same decomposition, but a page chunk is
+ *                        staged global -> shared -> global with cp.async.bulk (the TMA
+ *                        engine), one elected thread per ring of stages.
+ *   fp8-e4m3             quantise-on-write / dequantise-on-gather variants of the above
+ *                        plus the absmax -> scale reduction.
+ *   generic tier         one element per thread for layouts, head sizes or alignments the
+ *                        vector tiers cannot take (HND_PACKED, odd head_dim, ...).
+ *
+ * Semantics (which element goes where, what is skipped) follow the reference kernels:
+ * kernels/kvx_paged_kv.cu:54-75 (offsets), :98-123 (write), :232-266 (gather).
+ */
+#include "kvx_paged_kv.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+
+#include <atomic>
+
+namespace {
+
+// ------------------------------------------------------------------ tunables ----------
+
+struct Options {
+  int64_t write_vecs_per_cta = 1024;  // 16-byte vectors of K (and of V) one write CTA moves
+  int64_t write_unroll = 4;           // vectors of K and of V in flight per thread (1,2,4)
+  int64_t gather_path = 0;            // 0 = register copy, 1 = cp.async.bulk staging
+  int64_t gather_ctas_per_sm = 4;     // persistent CTAs per SM (register path)
+  int64_t gather_part_bytes = 32768;  // largest span one warp copies per work item
+  int64_t bulk_stage_bytes = 16384;   // bytes per shared-memory stage (bulk path)
+  int64_t bulk_stages = 4;            // stages per pipe (bulk path)
+  int64_t bulk_pipes = 3;             // pipes (elected threads) per CTA (bulk path)
+  int64_t bulk_lag = 2;               // loads a pipe keeps in flight ahead of its stores
+  int64_t bulk_ctas_per_sm = 1;
+  int64_t force_generic = 0;          // 1 = always take the one-element-per-thread tier
+};
+Options g_opt;
+std::atomic<uint64_t> g_launches{0};
+
+struct OptionName {
+  const char *name;
+  int64_t Options::*field;
+};
+const OptionName kOptionNames[] = {
+    {"write_vecs_per_cta", &Options::write_vecs_per_cta},
+    {"write_unroll", &Options::write_unroll},
+    {"gather_path", &Options::gather_path},
+    {"gather_ctas_per_sm", &Options::gather_ctas_per_sm},
+    {"gather_part_bytes", &Options::gather_part_bytes},
+    {"bulk_stage_bytes", &Options::bulk_stage_bytes},
+    {"bulk_stages", &Options::bulk_stages},
+    {"bulk_pipes", &Options::bulk_pipes},
+    {"bulk_lag", &Options::bulk_lag},
+    {"bulk_ctas_per_sm", &Options::bulk_ctas_per_sm},
+    {"force_generic", &Options::force_generic},
+};
+
+// Per-device facts, looked up once (never per launch).
+struct DeviceInfo {
+  int sm_count = 0;
+  int max_smem_optin = 0;
+};
+DeviceInfo g_dev[64];
+std::atomic<int> g_dev_ready[64];
+
+const DeviceInfo &device_info() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (g_dev_ready[dev].load(std::memory_order_acquire) == 0) {
+    DeviceInfo info;
+    cudaDeviceGetAttribute(&info.sm_count, cudaDevAttrMultiProcessorCount, dev);
+    cudaDeviceGetAttribute(&info.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    if (info.sm_count <= 0) info.sm_count = 148;
+    g_dev[dev] = info;
+    g_dev_ready[dev].store(1, std::memory_order_release);
+  }
+  return g_dev[dev];
+}
+
+// ------------------------------------------------------------------ geometry ----------
+
+// A page tensor with its axes renamed (block, token-in-block, head, dim) whatever the
+// layout, strides in BYTES.  The offset of element (b, o, h, d) is
+//   b*blk + o*tok + h*head + (d / pack)*dhi + (d % pack)*dlo
+// which restates the reference's per-layout switch (kernels/kvx_paged_kv.cu:54-75):
+//   NHD        strides (s0,s1,s2,s3)     -> blk=s0 tok=s1 head=s2 dhi=s3 pack=1
+//   HND        strides (s0,s1,s2,s3)     -> blk=s0 head=s1 tok=s2 dhi=s3 pack=1
+//   HND_PACKED strides (s0,s1,s2,s3,s4)  -> blk=s0 head=s1 dhi=s2 tok=s3 dlo=s4 pack=shape[4]
+struct PageView {
+  char *base;
+  int64_t blk, tok, head, dhi, dlo;
+  int32_t pack;
+};
+
+struct Geometry {
+  int32_t num_blocks, block_size, heads, dim;
+  int32_t elem;  // bytes per cache element
+};
+
+kvx_status_t make_page_view(const kvx_cache_desc_t *c, const kvx_tensor_desc_t *t, int64_t elem,
+                            PageView *out) {
+  const int64_t *s = t->stride;
+  out->base = static_cast<char *>(t->data);
+  out->pack = 1;
+  out->dlo = 0;
+  switch (t->layout) {
+    case KVX_LAYOUT_BLOCK_NHD:
+      out->blk = s[0] * elem, out->tok = s[1] * elem, out->head = s[2] * elem, out->dhi = s[3] * elem;
+      return KVX_STATUS_OK;
+    case KVX_LAYOUT_BLOCK_HND:
+      out->blk = s[0] * elem, out->head = s[1] * elem, out->tok = s[2] * elem, out->dhi = s[3] * elem;
+      return KVX_STATUS_OK;
+    case KVX_LAYOUT_BLOCK_HND_PACKED: {
+      const int64_t pack = t->shape[4];
+      if (pack <= 0 || (static_cast<int64_t>(c->head_dim) % pack) != 0 || pack > INT32_MAX)
+        return KVX_STATUS_INVALID_ARGUMENT;
+      out->blk = s[0] * elem, out->head = s[1] * elem, out->dhi = s[2] * elem, out->tok = s[3] * elem;
+      out->dlo = s[4] * elem;
+      out->pack = static_cast<int32_t>(pack);
+      return KVX_STATUS_OK;
+    }
+    default:
+      return KVX_STATUS_UNSUPPORTED;
+  }
+}
+
+int64_t dtype_bytes(kvx_dtype_t t) {
+  switch (t) {
+    case KVX_DTYPE_F16:
+    case KVX_DTYPE_BF16:
+      return 2;
+    case KVX_DTYPE_F32:
+      return 4;
+    case KVX_DTYPE_F8_E4M3:
+      return 1;
+    default:
+      return 0;
+  }
+}
+
+bool aligned(const void *p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+bool is_pow2(int64_t v) { return v > 0 && (v & (v - 1)) == 0; }
+int shift_of(int64_t v) {  // log2 for powers of two, -1 otherwise
+  if (!is_pow2(v)) return -1;
+  int s = 0;
+  while ((int64_t{1} << s) < v) ++s;
+  return s;
+}
+
+// `dim` is contiguous (d -> d*elem bytes) in this view?
+bool dim_contiguous(const PageView &v, int64_t elem, int64_t dim) {
+  if (v.pack == 1) return v.dhi == elem;
+  return v.pack == dim && v.dlo == elem;
+}
+
+// Can this view be addressed with `vec`-byte vectors along dim?
+bool view_vectorisable(const PageView &v, int64_t elem, int64_t dim, int64_t vec) {
+  return dim_contiguous(v, elem, dim) && (dim * elem) % vec == 0 && aligned(v.base, vec) &&
+         v.blk % vec == 0 && v.tok % vec == 0 && v.head % vec == 0 && v.blk >= 0 && v.tok >= 0 &&
+         v.head >= 0;
+}
+
+// ------------------------------------------------------------------ device helpers ----
+
+__device__ int g_device_error;  // set when a bounded wait gives up; read by the host on demand
+
+__device__ __forceinline__ uint4 load_stream(const void *p) {
+  // Read-once data: bypass L1 allocation.
+  uint4 r;
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p));
+  return r;
+}
+__device__ __forceinline__ void store_stream(void *p, const uint4 &r) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(r.x), "r"(r.y), "r"(r.z),
+               "r"(r.w)
+               : "memory");
+}
+
+// n / d and n % d for a runtime d with a known power-of-two shift (or -1).
+__device__ __forceinline__ int div_by(int n, int d, int shift) {
+  return shift >= 0 ? (n >> shift) : (n / d);
+}
+
+__device__ __forceinline__ void split_slot(int64_t slot, int32_t block_size, int bs_shift,
+                                           int64_t *block, int64_t *off) {
+  if (bs_shift >= 0) {
+    *block = slot >> bs_shift;
+    *off = slot & (block_size - 1);
+  } else if ((slot >> 31) == 0) {  // fits 32 bits: cheap division
+    const uint32_t s = static_cast<uint32_t>(slot);
+    const uint32_t b = s / static_cast<uint32_t>(block_size);
+    *block = b;
+    *off = s - b * static_cast<uint32_t>(block_size);
+  } else {
+    *block = slot / block_size;
+    *off = slot - *block * block_size;
+  }
+}
+
+// ------------------------------------------------------------------ write: vector tier -
+
+constexpr int kWriteThreads = 256;
+constexpr int kMaxTokTile = 128;
+
+struct WriteRowsParams {
+  const char *key, *value;  // dense [T, row_bytes]
+  char *k_base, *v_base;
+  int64_t k_blk, k_tok, k_head;  // bytes
+  int64_t v_blk, v_tok, v_head;
+  const void *slots;
+  int64_t row_bytes;
+  int32_t num_tokens, num_blocks, block_size, bs_shift;
+  int32_t vpr, vpr_shift;  // 16-byte vectors per token row
+  int32_t vps, vps_shift;  // 16-byte vectors per head segment
+  int32_t tok_tile;        // tokens per CTA (<= kMaxTokTile)
+};
+
+// kSeg = false: every token row is one contiguous span in both page tensors.
+// kSeg = true : a row is num_heads spans of head_dim elements (HND pages, or NHD pages whose
+//               head stride is not head_dim).
+template <typename SlotT, bool kSeg, int kUnroll>
+__global__ void __launch_bounds__(kWriteThreads) kvx_write_rows_kernel(const WriteRowsParams p) {
+  __shared__ int64_t s_k[kMaxTokTile];
+  __shared__ int64_t s_v[kMaxTokTile];
+  const int tid = threadIdx.x;
+  const int64_t tok0 = static_cast<int64_t>(blockIdx.x) * p.tok_tile;
+  const int ntok = static_cast<int>(min(static_cast<int64_t>(p.tok_tile), p.num_tokens - tok0));
+
+  if (tid < ntok) {
+    const int64_t slot = static_cast<int64_t>(static_cast<const SlotT *>(p.slots)[tok0 + tid]);
+    int64_t ko = -1, vo = -1;
+    if (slot >= 0) {  // negative = padding (reference: kernels/kvx_paged_kv.cu:137-140)
+      int64_t b, o;
+      split_slot(slot, p.block_size, p.bs_shift, &b, &o);
+      if (b < p.num_blocks) {  // out-of-range block: skipped, not an error (:143-145)
+        ko = b * p.k_blk + o * p.k_tok;
+        vo = b * p.v_blk + o * p.v_tok;
+      }
+    }
+    s_k[tid] = ko;
+    s_v[tid] = vo;
+  }
+  __syncthreads();
+
+  const char *ksrc = p.key + tok0 * p.row_bytes;
+  const char *vsrc = p.value + tok0 * p.row_bytes;
+  const int nvec = ntok * p.vpr;
+  for (int f0 = tid; f0 < nvec; f0 += kWriteThreads * kUnroll) {
+    uint4 kr[kUnroll], vr[kUnroll];
+    int64_t kd[kUnroll], vd[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int f = f0 + u * kWriteThreads;
+      kd[u] = -1;
+      if (f < nvec) {
+        const int tok = div_by(f, p.vpr, p.vpr_shift);
+        const int64_t ko = s_k[tok];
+        if (ko >= 0) {
+          const int v = f - tok * p.vpr;
+          if (kSeg) {
+            const int h = div_by(v, p.vps, p.vps_shift);
+            const int64_t w = static_cast<int64_t>(v - h * p.vps) * 16;
+            kd[u] = ko + h * p.k_head + w;
+            vd[u] = s_v[tok] + h * p.v_head + w;
+          } else {
+            kd[u] = ko + static_cast<int64_t>(v) * 16;
+            vd[u] = s_v[tok] + static_cast<int64_t>(v) * 16;
+          }
+          kr[u] = load_stream(ksrc + static_cast<int64_t>(f) * 16);
+          vr[u] = load_stream(vsrc + static_cast<int64_t>(f) * 16);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      if (kd[u] >= 0) {
+        store_stream(p.k_base + kd[u], kr[u]);
+        store_stream(p.v_base + vd[u], vr[u]);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ element converters -
+
+struct F16 {
+  uint16_t bits;
+};
+struct BF16 {
+  uint16_t bits;
+};
+struct F32 {
+  uint32_t bits;
+};
+struct F8 {
+  uint8_t bits;
+};
+
+__device__ __forceinline__ float to_f32(F16 x) { return __half2float(__ushort_as_half(x.bits)); }
+__device__ __forceinline__ float to_f32(BF16 x) {
+  return __uint_as_float(static_cast<uint32_t>(x.bits) << 16);
+}
+__device__ __forceinline__ float to_f32(F32 x) { return __uint_as_float(x.bits); }
+
+// Two f32 -> two E4M3 bytes with one rounding each (nearest even, saturating to +-448);
+// `lo` lands in bits 0-7.  A NaN input yields 0x7F whatever its sign.
+__device__ __forceinline__ uint32_t e4m3x2_from_f32(float lo, float hi) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  uint32_t q = r;
+  if (lo != lo) q = (q & 0xFF00u) | 0x7Fu;
+  if (hi != hi) q = (q & 0x00FFu) | 0x7F00u;
+  return q;
+}
+
+// Quantise: one IEEE division, then one rounding to E4M3.
+__device__ __forceinline__ uint32_t quant2(float lo, float hi, float scale) {
+  return e4m3x2_from_f32(__fdiv_rn(lo, scale), __fdiv_rn(hi, scale));
+}
+
+// Two E4M3 bytes (bits 0-15) -> two f32, exact.
+__device__ __forceinline__ float2 e4m3x2_to_f32(uint32_t q) {
+  uint32_t h2;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(static_cast<uint16_t>(q)));
+  return __half22float2(*reinterpret_cast<__half2 *>(&h2));
+}
+
+// Round f32 to the IO element type (nearest even); NaN becomes the canonical quiet NaN.
+__device__ __forceinline__ F16 from_f32(float z, F16) {
+  return F16{__half_as_ushort(__float2half_rn(z))};
+}
+__device__ __forceinline__ BF16 from_f32(float z, BF16) {
+  return BF16{__bfloat16_as_ushort(__float2bfloat16_rn(z))};
+}
+__device__ __forceinline__ F32 from_f32(float z, F32) {
+  return F32{(z != z) ? 0x7FFFFFFFu : __float_as_uint(z)};
+}
+
+template <typename T>
+struct ElemTraits;
+template <>
+struct ElemTraits<F16> {
+  static constexpr int per_vec = 8;  // elements in 16 bytes
+};
+template <>
+struct ElemTraits<BF16> {
+  static constexpr int per_vec = 8;
+};
+template <>
+struct ElemTraits<F32> {
+  static constexpr int per_vec = 4;
+};
+
+// 16 bytes of IO elements -> per_vec E4M3 bytes (8 or 4), packed little-endian.
+__device__ __forceinline__ uint2 quant_vec(const uint4 &x, float scale, BF16) {
+  const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+  uint32_t q[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    q[i] = quant2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xFFFF0000u), scale);
+  return make_uint2(q[0] | (q[1] << 16), q[2] | (q[3] << 16));
+}
+__device__ __forceinline__ uint2 quant_vec(const uint4 &x, float scale, F16) {
+  const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+  uint32_t q[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+    q[i] = quant2(f.x, f.y, scale);
+  }
+  return make_uint2(q[0] | (q[1] << 16), q[2] | (q[3] << 16));
+}
+__device__ __forceinline__ uint2 quant_vec(const uint4 &x, float scale, F32) {
+  const uint32_t a = quant2(__uint_as_float(x.x), __uint_as_float(x.y), scale);
+  const uint32_t b = quant2(__uint_as_float(x.z), __uint_as_float(x.w), scale);
+  return make_uint2(a | (b << 16), 0u);
+}
+
+// per_vec E4M3 bytes -> 16 bytes of IO elements.
+__device__ __forceinline__ uint4 dequant_vec(uint2 q, float scale, BF16) {
+  const uint32_t w[4] = {q.x & 0xFFFFu, q.x >> 16, q.y & 0xFFFFu, q.y >> 16};
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = e4m3x2_to_f32(w[i]);
+    o[i] = static_cast<uint32_t>(from_f32(f.x * scale, BF16{}).bits) |
+           (static_cast<uint32_t>(from_f32(f.y * scale, BF16{}).bits) << 16);
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+__device__ __forceinline__ uint4 dequant_vec(uint2 q, float scale, F16) {
+  const uint32_t w[4] = {q.x & 0xFFFFu, q.x >> 16, q.y & 0xFFFFu, q.y >> 16};
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = e4m3x2_to_f32(w[i]);
+    o[i] = static_cast<uint32_t>(from_f32(f.x * scale, F16{}).bits) |
+           (static_cast<uint32_t>(from_f32(f.y * scale, F16{}).bits) << 16);
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+__device__ __forceinline__ uint4 dequant_vec(uint2 q, float scale, F32) {
+  const float2 a = e4m3x2_to_f32(q.x & 0xFFFFu);
+  const float2 b = e4m3x2_to_f32(q.x >> 16);
+  return make_uint4(from_f32(a.x * scale, F32{}).bits, from_f32(a.y * scale, F32{}).bits,
+                    from_f32(b.x * scale, F32{}).bits, from_f32(b.y * scale, F32{}).bits);
+}
+
+struct ScaleView {
+  const float *base;  // device
+  int64_t stride;     // elements between heads; 0 = one scale per tensor
+};
+
+// ------------------------------------------------------------------ write: fp8 vector --
+
+struct WriteF8Params {
+  WriteRowsParams w;  // vpr / vps count 16-byte INPUT vectors; k_*/v_* strides are cache bytes
+  ScaleView ks, vs;
+  int32_t dim;  // head_dim
+};
+
+// Same token tiling as kvx_write_rows_kernel; each 16-byte input vector (8 or 4 elements,
+// all of one head) becomes 8 or 4 cache bytes.
+template <typename IoT, typename SlotT, int kUnroll>
+__global__ void __launch_bounds__(kWriteThreads) kvx_write_f8_kernel(const WriteF8Params q) {
+  constexpr int kPer = ElemTraits<IoT>::per_vec;
+  const WriteRowsParams &p = q.w;
+  __shared__ int64_t s_k[kMaxTokTile];
+  __shared__ int64_t s_v[kMaxTokTile];
+  const int tid = threadIdx.x;
+  const int64_t tok0 = static_cast<int64_t>(blockIdx.x) * p.tok_tile;
+  const int ntok = static_cast<int>(min(static_cast<int64_t>(p.tok_tile), p.num_tokens - tok0));
+  if (tid < ntok) {
+    const int64_t slot = static_cast<int64_t>(static_cast<const SlotT *>(p.slots)[tok0 + tid]);
+    int64_t ko = -1, vo = -1;
+    if (slot >= 0) {
+      int64_t b, o;
+      split_slot(slot, p.block_size, p.bs_shift, &b, &o);
+      if (b < p.num_blocks) {
+        ko = b * p.k_blk + o * p.k_tok;
+        vo = b * p.v_blk + o * p.v_tok;
+      }
+    }
+    s_k[tid] = ko;
+    s_v[tid] = vo;
+  }
+  __syncthreads();
+
+  const char *ksrc = p.key + tok0 * p.row_bytes;
+  const char *vsrc = p.value + tok0 * p.row_bytes;
+  const int nvec = ntok * p.vpr;
+  for (int f0 = tid; f0 < nvec; f0 += kWriteThreads * kUnroll) {
+    uint4 kr[kUnroll], vr[kUnroll];
+    int64_t kd[kUnroll], vd[kUnroll];
+    int hh[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int f = f0 + u * kWriteThreads;
+      kd[u] = -1;
+      if (f < nvec) {
+        const int tok = div_by(f, p.vpr, p.vpr_shift);
+        const int64_t ko = s_k[tok];
+        if (ko >= 0) {
+          const int v = f - tok * p.vpr;
+          const int h = div_by(v, p.vps, p.vps_shift);
+          const int64_t w = static_cast<int64_t>(v - h * p.vps) * kPer;  // cache bytes into the head
+          hh[u] = h;
+          kd[u] = ko + h * p.k_head + w;
+          vd[u] = s_v[tok] + h * p.v_head + w;
+          kr[u] = load_stream(ksrc + static_cast<int64_t>(f) * 16);
+          vr[u] = load_stream(vsrc + static_cast<int64_t>(f) * 16);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      if (kd[u] >= 0) {
+        const float sk = __ldg(q.ks.base + hh[u] * q.ks.stride);
+        const float sv = __ldg(q.vs.base + hh[u] * q.vs.stride);
+        const uint2 a = quant_vec(kr[u], sk, IoT{});
+        const uint2 b = quant_vec(vr[u], sv, IoT{});
+        if (kPer == 8) {
+          *reinterpret_cast<uint2 *>(p.k_base + kd[u]) = a;
+          *reinterpret_cast<uint2 *>(p.v_base + vd[u]) = b;
+        } else {
+          *reinterpret_cast<uint32_t *>(p.k_base + kd[u]) = a.x;
+          *reinterpret_cast<uint32_t *>(p.v_base + vd[u]) = b.x;
+        }
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ generic tier ------
+
+struct GenericParams {
+  PageView k, v;  // byte strides
+  Geometry g;
+  ScaleView ks, vs;
+};
+
+template <typename T>
+__device__ __forceinline__ T load_elem(const char *p) {
+  return *reinterpret_cast<const T *>(p);
+}
+
+__device__ __forceinline__ int64_t page_byte_offset(const PageView &v, int64_t b, int64_t o, int64_t h,
+                                                    int32_t d) {
+  const int32_t hi = d / v.pack;
+  return b * v.blk + o * v.tok + h * v.head + hi * v.dhi + (d - hi * v.pack) * v.dlo;
+}
+
+// Element conversion between IO type and cache type.  Same type = bit copy.
+template <typename SrcT, typename DstT>
+struct Convert {
+  static __device__ __forceinline__ DstT apply(SrcT x, float) {
+    DstT r;
+    r.bits = x.bits;
+    return r;
+  }
+};
+template <typename SrcT>
+struct Convert<SrcT, F8> {  // quantise
+  static __device__ __forceinline__ F8 apply(SrcT x, float scale) {
+    return F8{static_cast<uint8_t>(e4m3x2_from_f32(__fdiv_rn(to_f32(x), scale), 0.f) & 0xFFu)};
+  }
+};
+// One (token, head, dim) element per thread, any layout / stride / alignment.
+template <typename IoT, typename CacheT, typename SlotT>
+__global__ void __launch_bounds__(256)
+    kvx_write_generic_kernel(const IoT *key, const IoT *value, const void *slots, int64_t num_tokens,
+                             const GenericParams p) {
+  const int64_t hd = static_cast<int64_t>(p.g.heads) * p.g.dim;
+  const int64_t total = num_tokens * hd;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int64_t t = idx / hd;
+  const int32_t rem = static_cast<int32_t>(idx - t * hd);
+  const int32_t h = rem / p.g.dim;
+  const int32_t d = rem - h * p.g.dim;
+  const int64_t slot = static_cast<int64_t>(static_cast<const SlotT *>(slots)[t]);
+  if (slot < 0) return;
+  const int64_t b = slot / p.g.block_size;
+  const int64_t o = slot - b * p.g.block_size;
+  if (b >= p.g.num_blocks) return;
+  const float sk = p.ks.base ? __ldg(p.ks.base + h * p.ks.stride) : 1.f;
+  const float sv = p.vs.base ? __ldg(p.vs.base + h * p.vs.stride) : 1.f;
+  *reinterpret_cast<CacheT *>(p.k.base + page_byte_offset(p.k, b, o, h, d)) =
+      Convert<IoT, CacheT>::apply(key[idx], sk);
+  *reinterpret_cast<CacheT *>(p.v.base + page_byte_offset(p.v, b, o, h, d)) =
+      Convert<IoT, CacheT>::apply(value[idx], sv);
+}
+
+struct GatherShape {
+  const void *table, *lens;
+  int32_t seq_count, max_blocks, max_seq_len;
+};
+
+template <typename IdxT>
+__device__ __forceinline__ int64_t read_idx(const void *p, int64_t i) {
+  return static_cast<int64_t>(static_cast<const IdxT *>(p)[i]);
+}
+
+// One output element per thread over the padded [S, Lmax, H, D] rectangle.
+template <typename IoT, typename CacheT, typename IdxT, bool kDequant>
+__global__ void __launch_bounds__(256)
+    kvx_gather_generic_kernel(IoT *key_out, IoT *value_out, const GatherShape s, const GenericParams p) {
+  const int64_t hd = static_cast<int64_t>(p.g.heads) * p.g.dim;
+  const int64_t total = static_cast<int64_t>(s.seq_count) * s.max_seq_len * hd;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int64_t row = idx / hd;
+  const int32_t rem = static_cast<int32_t>(idx - row * hd);
+  const int32_t h = rem / p.g.dim;
+  const int32_t d = rem - h * p.g.dim;
+  const int32_t seq = static_cast<int32_t>(row / s.max_seq_len);
+  const int32_t tok = static_cast<int32_t>(row - static_cast<int64_t>(seq) * s.max_seq_len);
+  if (tok >= read_idx<IdxT>(s.lens, seq)) return;
+  const int32_t lb = tok / p.g.block_size;
+  if (lb >= s.max_blocks) return;
+  const int64_t b = read_idx<IdxT>(s.table, static_cast<int64_t>(seq) * s.max_blocks + lb);
+  if (b < 0 || b >= p.g.num_blocks) return;
+  const int64_t o = tok - static_cast<int64_t>(lb) * p.g.block_size;
+  const CacheT kq = load_elem<CacheT>(p.k.base + page_byte_offset(p.k, b, o, h, d));
+  const CacheT vq = load_elem<CacheT>(p.v.base + page_byte_offset(p.v, b, o, h, d));
+  if (kDequant) {
+    const float sk = __ldg(p.ks.base + h * p.ks.stride);
+    const float sv = __ldg(p.vs.base + h * p.vs.stride);
+    key_out[idx] = from_f32(e4m3x2_to_f32(kq.bits).x * sk, IoT{});
+    value_out[idx] = from_f32(e4m3x2_to_f32(vq.bits).x * sv, IoT{});
+  } else {
+    IoT a, c;
+    a.bits = kq.bits;
+    c.bits = vq.bits;
+    key_out[idx] = a;
+    value_out[idx] = c;
+  }
+}
+
+// ------------------------------------------------------------------ gather: vector tier -
+
+constexpr int kGatherThreads = 256;
+constexpr int kGatherWarps = kGatherThreads / 32;
+
+struct GatherPagesParams {
+  const char *k_base, *v_base;
+  int64_t k_blk, k_tok, k_head;  // bytes
+  int64_t v_blk, v_tok, v_head;
+  char *key_out, *value_out;
+  GatherShape s;
+  int64_t out_row_bytes;  // bytes of one output token row
+  int32_t num_blocks, block_size;
+  int32_t vpr, vpr_shift;  // 16-byte OUTPUT vectors per token row
+  int32_t vps, vps_shift;  // 16-byte output vectors per head segment
+  int32_t part_vecs;       // output vectors one work item covers
+  int32_t parts;           // work items per full page chunk
+  int32_t use_prefix;      // 1: prefix[] in shared memory holds compacted page counts
+  int32_t dim;             // head_dim (fp8 variant)
+  ScaleView ks, vs;        // fp8 variant
+};
+
+// Pages sequence s really has: ceil(min(len, Lmax) / bs), clamped to the table width.
+template <typename IdxT>
+__device__ __forceinline__ int32_t pages_of(const GatherPagesParams &p, int32_t seq) {
+  int64_t len = read_idx<IdxT>(p.s.lens, seq);
+  if (len <= 0) return 0;
+  if (len > p.s.max_seq_len) len = p.s.max_seq_len;
+  const int64_t n = (len + p.block_size - 1) / p.block_size;
+  return static_cast<int32_t>(min(n, static_cast<int64_t>(p.s.max_blocks)));
+}
+
+// Exclusive prefix sum of pages_of() over all sequences into prefix[0..S]; returns prefix[S].
+template <typename IdxT>
+__device__ int32_t build_page_prefix(const GatherPagesParams &p, int32_t *prefix, int32_t *warp_tot) {
+  const int tid = threadIdx.x;
+  const int S = p.s.seq_count;
+  const int per = (S + kGatherThreads - 1) / kGatherThreads;
+  const int begin = min(tid * per, S), end = min(begin + per, S);
+  int32_t local = 0;
+  for (int s = begin; s < end; ++s) local += pages_of<IdxT>(p, s);
+  // inclusive scan of `local` across the CTA
+  int32_t incl = local;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int32_t n = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+    if ((tid & 31) >= d) incl += n;
+  }
+  if ((tid & 31) == 31) warp_tot[tid >> 5] = incl;
+  __syncthreads();
+  int32_t base = 0;
+  for (int w = 0; w < (tid >> 5); ++w) base += warp_tot[w];
+  int32_t run = base + incl - local;  // exclusive prefix of this thread's first sequence
+  for (int s = begin; s < end; ++s) {
+    prefix[s] = run;
+    run += pages_of<IdxT>(p, s);
+  }
+  if (tid == kGatherThreads - 1) prefix[S] = run;
+  __syncthreads();
+  return prefix[S];
+}
+
+struct ChunkRef {
+  int32_t seq, lb;
+};
+
+// Compact chunk index -> (sequence, logical block): last s with prefix[s] <= c.
+__device__ __forceinline__ ChunkRef find_chunk(const int32_t *prefix, int32_t S, int32_t c) {
+  int lo = 0, hi = S;  // prefix[lo] <= c < prefix[hi]
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (prefix[mid] <= c)
+      lo = mid;
+    else
+      hi = mid;
+  }
+  return ChunkRef{lo, c - prefix[lo]};
+}
+
+// Everything a copy loop needs to know about one (sequence, page) chunk.
+struct ChunkInfo {
+  int64_t block;    // physical page, -1 = skip
+  int32_t tokens;   // valid tokens in the chunk
+  int64_t out_off;  // byte offset of the chunk's first row in the output tensors
+};
+
+template <typename IdxT>
+__device__ __forceinline__ ChunkInfo resolve_chunk(const GatherPagesParams &p, int32_t seq, int32_t lb) {
+  ChunkInfo c;
+  c.block = -1;
+  c.tokens = 0;
+  c.out_off = 0;
+  int64_t len = read_idx<IdxT>(p.s.lens, seq);
+  if (len > p.s.max_seq_len) len = p.s.max_seq_len;
+  const int64_t first = static_cast<int64_t>(lb) * p.block_size;
+  if (first >= len || lb >= p.s.max_blocks) return c;  // (reference: kernels/kvx_paged_kv.cu:247-253)
+  const int64_t b = read_idx<IdxT>(p.s.table, static_cast<int64_t>(seq) * p.s.max_blocks + lb);
+  if (b < 0 || b >= p.num_blocks) return c;  // negative id: skipped (:256-258); too large: skipped too
+  c.block = b;
+  c.tokens = static_cast<int32_t>(min(len - first, static_cast<int64_t>(p.block_size)));
+  c.out_off = (static_cast<int64_t>(seq) * p.s.max_seq_len + first) * p.out_row_bytes;
+  return c;
+}
+
+// Persistent CTAs; warp-granular work items (chunk, part, K|V).
+//   kSeg = false : page rows are contiguous -> a chunk is one contiguous span on both sides.
+//   kSeg = true  : per-head segments (HND pages or padded strides).
+template <typename IdxT, bool kSeg, int kUnroll>
+__global__ void __launch_bounds__(kGatherThreads) kvx_gather_pages_kernel(const GatherPagesParams p) {
+  extern __shared__ int32_t s_prefix[];
+  __shared__ int32_t s_warp_tot[kGatherWarps];
+  int64_t chunks;
+  if (p.use_prefix)
+    chunks = build_page_prefix<IdxT>(p, s_prefix, s_warp_tot);
+  else
+    chunks = static_cast<int64_t>(p.s.seq_count) * p.s.max_blocks;
+
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = static_cast<int64_t>(blockIdx.x) * kGatherWarps + (threadIdx.x >> 5);
+  const int64_t warps = static_cast<int64_t>(gridDim.x) * kGatherWarps;
+  const int64_t items = chunks * p.parts * 2;
+
+  for (int64_t item = warp; item < items; item += warps) {
+    const int kv = static_cast<int>(item & 1);
+    const int64_t rest = item >> 1;
+    const int64_t c = rest / p.parts;
+    const int part = static_cast<int>(rest - c * p.parts);
+    ChunkRef ref;
+    if (p.use_prefix) {
+      ref = find_chunk(s_prefix, p.s.seq_count, static_cast<int32_t>(c));
+    } else {
+      ref.seq = static_cast<int32_t>(c / p.s.max_blocks);
+      ref.lb = static_cast<int32_t>(c - static_cast<int64_t>(ref.seq) * p.s.max_blocks);
+    }
+    const ChunkInfo ci = resolve_chunk<IdxT>(p, ref.seq, ref.lb);
+    if (ci.block < 0) continue;
+    const int nvec = ci.tokens * p.vpr;
+    const int vbeg = part * p.part_vecs;
+    const int vend = min(vbeg + p.part_vecs, nvec);
+    const char *src = kv ? p.v_base + ci.block * p.v_blk : p.k_base + ci.block * p.k_blk;
+    char *dst = (kv ? p.value_out : p.key_out) + ci.out_off;
+    const int64_t tok_b = kv ? p.v_tok : p.k_tok;
+    const int64_t head_b = kv ? p.v_head : p.k_head;
+
+    for (int f0 = vbeg + lane; f0 < vend; f0 += 32 * kUnroll) {
+      uint4 r[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int f = f0 + u * 32;
+        if (f < vend) {
+          int64_t so;
+          if (kSeg) {
+            const int tok = div_by(f, p.vpr, p.vpr_shift);
+            const int v = f - tok * p.vpr;
+            const int h = div_by(v, p.vps, p.vps_shift);
+            so = tok * tok_b + h * head_b + static_cast<int64_t>(v - h * p.vps) * 16;
+          } else {
+            so = static_cast<int64_t>(f) * 16;
+          }
+          r[u] = load_stream(src + so);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int f = f0 + u * 32;
+        if (f < vend) store_stream(dst + static_cast<int64_t>(f) * 16, r[u]);
+      }
+    }
+  }
+}
+
+// Dequantising gather: same decomposition; each 16-byte OUTPUT vector (8 or 4 elements of
+// one head) is produced from 8 or 4 cache bytes.
+template <typename IoT, typename IdxT, int kUnroll>
+__global__ void __launch_bounds__(kGatherThreads) kvx_gather_f8_kernel(const GatherPagesParams p) {
+  constexpr int kPer = ElemTraits<IoT>::per_vec;
+  extern __shared__ int32_t s_prefix[];
+  __shared__ int32_t s_warp_tot[kGatherWarps];
+  int64_t chunks;
+  if (p.use_prefix)
+    chunks = build_page_prefix<IdxT>(p, s_prefix, s_warp_tot);
+  else
+    chunks = static_cast<int64_t>(p.s.seq_count) * p.s.max_blocks;
+
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = static_cast<int64_t>(blockIdx.x) * kGatherWarps + (threadIdx.x >> 5);
+  const int64_t warps = static_cast<int64_t>(gridDim.x) * kGatherWarps;
+  const int64_t items = chunks * p.parts * 2;
+
+  for (int64_t item = warp; item < items; item += warps) {
+    const int kv = static_cast<int>(item & 1);
+    const int64_t rest = item >> 1;
+    const int64_t c = rest / p.parts;
+    const int part = static_cast<int>(rest - c * p.parts);
+    ChunkRef ref;
+    if (p.use_prefix) {
+      ref = find_chunk(s_prefix, p.s.seq_count, static_cast<int32_t>(c));
+    } else {
+      ref.seq = static_cast<int32_t>(c / p.s.max_blocks);
+      ref.lb = static_cast<int32_t>(c - static_cast<int64_t>(ref.seq) * p.s.max_blocks);
+    }
+    const ChunkInfo ci = resolve_chunk<IdxT>(p, ref.seq, ref.lb);
+    if (ci.block < 0) continue;
+    const int nvec = ci.tokens * p.vpr;
+    const int vbeg = part * p.part_vecs;
+    const int vend = min(vbeg + p.part_vecs, nvec);
+    const char *src = kv ? p.v_base + ci.block * p.v_blk : p.k_base + ci.block * p.k_blk;
+    char *dst = (kv ? p.value_out : p.key_out) + ci.out_off;
+    const int64_t tok_b = kv ? p.v_tok : p.k_tok;
+    const int64_t head_b = kv ? p.v_head : p.k_head;
+    const ScaleView sc = kv ? p.vs : p.ks;
+
+    for (int f0 = vbeg + lane; f0 < vend; f0 += 32 * kUnroll) {
+      uint2 r[kUnroll];
+      int hh[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int f = f0 + u * 32;
+        if (f < vend) {
+          const int tok = div_by(f, p.vpr, p.vpr_shift);
+          const int v = f - tok * p.vpr;
+          const int h = div_by(v, p.vps, p.vps_shift);
+          const char *a = src + tok * tok_b + h * head_b + static_cast<int64_t>(v - h * p.vps) * kPer;
+          hh[u] = h;
+          if (kPer == 8)
+            r[u] = *reinterpret_cast<const uint2 *>(a);
+          else
+            r[u] = make_uint2(*reinterpret_cast<const uint32_t *>(a), 0u);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int f = f0 + u * 32;
+        if (f < vend) {
+          const float scale = __ldg(sc.base + hh[u] * sc.stride);
+          store_stream(dst + static_cast<int64_t>(f) * 16, dequant_vec(r[u], scale, IoT{}));
+        }
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ gather: bulk tier --
+// cp.async.bulk staging of contiguous page chunks: global -> shared (completion on an
+// mbarrier) -> global (bulk group).  One elected thread ("pipe") owns a ring of stages and
+// walks its share of the work items; the copy engine moves the bytes.
+
+constexpr int kBulkMaxPipes = 8;
+constexpr int kBulkMaxStages = 8;
+constexpr uint32_t kBulkWaitLimit = 1u << 22;  // polls before a wait is abandoned
+
+__device__ __forceinline__ uint32_t smem_addr(const void *p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes)
+               : "memory");
+}
+// Bounded wait for the phase with the given parity; false = gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+  const uint32_t a = smem_addr(bar);
+  for (uint32_t i = 0; i < kBulkWaitLimit; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(a), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void bulk_load(void *smem_dst, const void *gsrc, uint32_t bytes, uint64_t *bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_addr(smem_dst)),
+      "l"(gsrc), "r"(bytes), "r"(smem_addr(bar))
+      : "memory");
+}
+__device__ __forceinline__ void bulk_store(void *gdst, const void *smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst),
+               "r"(smem_addr(smem_src)), "r"(bytes)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+template <int kPending>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPending) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
+struct BulkParams {
+  GatherPagesParams g;  // kSeg = false geometry; part_vecs * 16 <= stage_bytes
+  int32_t stage_bytes, stages, pipes, lag;
+};
+
+template <typename IdxT>
+__global__ void __launch_bounds__(kGatherThreads) kvx_gather_bulk_kernel(const BulkParams bp) {
+  const GatherPagesParams &p = bp.g;
+  extern __shared__ __align__(128) unsigned char s_raw[];
+  __shared__ int32_t s_warp_tot[kGatherWarps];
+  __shared__ __align__(8) uint64_t s_bar[kBulkMaxPipes * kBulkMaxStages];
+  // layout of dynamic shared memory: [stages of all pipes][prefix]
+  unsigned char *stage_mem = s_raw;
+  int32_t *s_prefix =
+      reinterpret_cast<int32_t *>(s_raw + static_cast<size_t>(bp.pipes) * bp.stages * bp.stage_bytes);
+
+  if (threadIdx.x < kBulkMaxPipes * kBulkMaxStages) mbar_init(&s_bar[threadIdx.x], 1);
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  int64_t chunks;
+  if (p.use_prefix)
+    chunks = build_page_prefix<IdxT>(p, s_prefix, s_warp_tot);  // ends with __syncthreads()
+  else {
+    chunks = static_cast<int64_t>(p.s.seq_count) * p.s.max_blocks;
+    __syncthreads();
+  }
+
+  const int warp_in_cta = threadIdx.x >> 5;
+  if ((threadIdx.x & 31) != 0 || warp_in_cta >= bp.pipes) return;  // one elected thread per pipe
+
+  const int64_t pipe = static_cast<int64_t>(blockIdx.x) * bp.pipes + warp_in_cta;
+  const int64_t npipes = static_cast<int64_t>(gridDim.x) * bp.pipes;
+  const int64_t items = chunks * p.parts * 2;
+  unsigned char *my_stage = stage_mem + static_cast<size_t>(warp_in_cta) * bp.stages * bp.stage_bytes;
+  uint64_t *my_bar = &s_bar[warp_in_cta * kBulkMaxStages];
+
+  // Ring bookkeeping.  Item n of this pipe uses stage n % stages; its load completes phase
+  // (n / stages) & 1 of that stage's barrier.  Loads run `lag` items ahead of stores, so a
+  // pipe has `lag` loads and up to `stages - lag` stores in flight.
+  char *dst_q[kBulkMaxStages] = {};
+  uint32_t bytes_q[kBulkMaxStages] = {};
+  int64_t issued = 0, retired = 0;
+  bool failed = false;
+
+  auto retire_one = [&]() {
+    const int st = static_cast<int>(retired % bp.stages);
+    const uint32_t parity = static_cast<uint32_t>((retired / bp.stages) & 1);
+    if (!mbar_wait(&my_bar[st], parity)) {
+      failed = true;
+      return;
+    }
+    bulk_store(dst_q[st], my_stage + static_cast<size_t>(st) * bp.stage_bytes, bytes_q[st]);
+    ++retired;
+  };
+
+  for (int64_t item = pipe; item < items && !failed; item += npipes) {
+    const int kv = static_cast<int>(item & 1);
+    const int64_t rest = item >> 1;
+    const int64_t c = rest / p.parts;
+    const int part = static_cast<int>(rest - c * p.parts);
+    ChunkRef ref;
+    if (p.use_prefix) {
+      ref = find_chunk(s_prefix, p.s.seq_count, static_cast<int32_t>(c));
+    } else {
+      ref.seq = static_cast<int32_t>(c / p.s.max_blocks);
+      ref.lb = static_cast<int32_t>(c - static_cast<int64_t>(ref.seq) * p.s.max_blocks);
+    }
+    const ChunkInfo ci = resolve_chunk<IdxT>(p, ref.seq, ref.lb);
+    if (ci.block < 0) continue;
+    const int64_t nbytes = static_cast<int64_t>(ci.tokens) * p.out_row_bytes;
+    const int64_t bbeg = static_cast<int64_t>(part) * p.part_vecs * 16;
+    if (bbeg >= nbytes) continue;
+    const uint32_t bytes = static_cast<uint32_t>(min(static_cast<int64_t>(p.part_vecs) * 16, nbytes - bbeg));
+    const char *src = (kv ? p.v_base + ci.block * p.v_blk : p.k_base + ci.block * p.k_blk) + bbeg;
+    char *dst = (kv ? p.value_out : p.key_out) + ci.out_off + bbeg;
+
+    // Keep at most `lag` loads outstanding: drain the oldest into a store first.
+    if (issued - retired >= bp.lag) retire_one();
+    if (failed) break;
+    const int st = static_cast<int>(issued % bp.stages);
+    // The stage was last read by the store of item `issued - stages`.  Stores are committed
+    // in item order and `issued - lag + 1` of them exist now, so `stages - lag` groups were
+    // committed after that one: once at most that many are still reading, it is done.
+    switch (bp.stages - bp.lag) {
+      case 0: bulk_wait_read<0>(); break;
+      case 1: bulk_wait_read<1>(); break;
+      case 2: bulk_wait_read<2>(); break;
+      case 3: bulk_wait_read<3>(); break;
+      case 4: bulk_wait_read<4>(); break;
+      case 5: bulk_wait_read<5>(); break;
+      case 6: bulk_wait_read<6>(); break;
+      default: bulk_wait_read<7>(); break;
+    }
+    mbar_expect_tx(&my_bar[st], bytes);
+    bulk_load(my_stage + static_cast<size_t>(st) * bp.stage_bytes, src, bytes, &my_bar[st]);
+    dst_q[st] = dst;
+    bytes_q[st] = bytes;
+    ++issued;
+  }
+  while (retired < issued && !failed) retire_one();
+  if (failed) atomicExch(&g_device_error, 1);
+  bulk_wait_all();  // stores must complete before shared memory is released
+}
+
+// ------------------------------------------------------------------ absmax -> scale ----
+
+constexpr int kScaleThreads = 256;
+
+struct ScalesParams {
+  const char *key, *value;
+  int64_t total_vecs;  // 16-byte vectors per tensor
+  int32_t vpr, vpr_shift, vps, vps_shift;
+  int32_t heads;
+  int32_t group;       // lanes that share one head in every iteration (power of two <= 32)
+  int32_t per_tensor;  // 1: one scale per tensor
+  float *k_out, *v_out;
+  uint32_t *work;  // [2 * heads] running maxima (magnitude bits) + [1] CTA ticket
+};
+
+// |x| as f32 bits, maximum over the elements of one 16-byte vector.
+__device__ __forceinline__ uint32_t absmax_vec(const uint4 &x, BF16) {
+  const uint32_t a = __vmaxu2(__vmaxu2(x.x & 0x7FFF7FFFu, x.y & 0x7FFF7FFFu),
+                              __vmaxu2(x.z & 0x7FFF7FFFu, x.w & 0x7FFF7FFFu));
+  return max(a & 0xFFFFu, a >> 16) << 16;
+}
+__device__ __forceinline__ uint32_t absmax_vec(const uint4 &x, F16) {
+  const uint32_t a = __vmaxu2(__vmaxu2(x.x & 0x7FFF7FFFu, x.y & 0x7FFF7FFFu),
+                              __vmaxu2(x.z & 0x7FFF7FFFu, x.w & 0x7FFF7FFFu));
+  const uint16_t m = static_cast<uint16_t>(max(a & 0xFFFFu, a >> 16));  // order-preserving on |f16|
+  return __float_as_uint(__half2float(__ushort_as_half(m))) & 0x7FFFFFFFu;
+}
+__device__ __forceinline__ uint32_t absmax_vec(const uint4 &x, F32) {
+  return max(max(x.x & 0x7FFFFFFFu, x.y & 0x7FFFFFFFu), max(x.z & 0x7FFFFFFFu, x.w & 0x7FFFFFFFu));
+}
+
+template <typename IoT>
+__global__ void __launch_bounds__(kScaleThreads) kvx_kv_scales_kernel(const ScalesParams p) {
+  extern __shared__ uint32_t s_max[];  // [2 * heads]
+  __shared__ int s_last;
+  const int tid = threadIdx.x;
+  for (int i = tid; i < 2 * p.heads; i += kScaleThreads) s_max[i] = 0;
+  __syncthreads();
+
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kScaleThreads;
+  // total_vecs is rounded up to a multiple of the CTA size by the loop bound so that every
+  // lane of a warp takes part in the shuffles.
+  const int64_t bound = (p.total_vecs + kScaleThreads - 1) / kScaleThreads * kScaleThreads;
+  for (int64_t f = static_cast<int64_t>(blockIdx.x) * kScaleThreads + tid; f < bound; f += stride) {
+    uint32_t mk = 0, mv = 0;
+    int h = 0;
+    if (f < p.total_vecs) {
+      mk = absmax_vec(load_stream(p.key + f * 16), IoT{});
+      mv = absmax_vec(load_stream(p.value + f * 16), IoT{});
+      const int v = static_cast<int>(p.vpr_shift >= 0 ? (f & (p.vpr - 1)) : (f % p.vpr));
+      h = div_by(v, p.vps, p.vps_shift);
+    }
+    for (int d = 1; d < p.group; d <<= 1) {
+      mk = max(mk, __shfl_xor_sync(0xFFFFFFFFu, mk, d));
+      mv = max(mv, __shfl_xor_sync(0xFFFFFFFFu, mv, d));
+    }
+    if ((tid & (p.group - 1)) == 0 && f < p.total_vecs) {
+      if (mk) atomicMax(&s_max[h], mk);
+      if (mv) atomicMax(&s_max[p.heads + h], mv);
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < 2 * p.heads; i += kScaleThreads)
+    if (s_max[i]) atomicMax(&p.work[i], s_max[i]);
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) s_last = (atomicAdd(&p.work[2 * p.heads], 1u) == gridDim.x - 1);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  // Last CTA: turn the maxima into scales and leave the workspace zeroed for the next call.
+  if (p.per_tensor) {
+    if (tid < 2) {
+      uint32_t m = 0;
+      for (int hh = 0; hh < p.heads; ++hh) m = max(m, __ldcg(&p.work[tid * p.heads + hh]));
+      const float s = __fdiv_rn(__uint_as_float(m), 448.0f);
+      (tid == 0 ? p.k_out : p.v_out)[0] = (s > 0.0f) ? s : 1.0f;
+    }
+  } else {
+    for (int i = tid; i < 2 * p.heads; i += kScaleThreads) {
+      const float s = __fdiv_rn(__uint_as_float(__ldcg(&p.work[i])), 448.0f);
+      (i < p.heads ? p.k_out : p.v_out)[i < p.heads ? i : i - p.heads] = (s > 0.0f) ? s : 1.0f;
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i <= 2 * p.heads; i += kScaleThreads) p.work[i] = 0;
+}
+
+// ------------------------------------------------------------------ host: validation ---
+
+// IO tensor shape / stride checks of the launchers (reference: kernels/kvx_paged_kv.cu:269-313).
+kvx_status_t check_io_tensor(const kvx_tensor_desc_t *t, uint32_t ndim, const int64_t *dims) {
+  if (t->ndim != ndim) return KVX_STATUS_INVALID_ARGUMENT;
+  for (uint32_t i = 0; i < ndim; ++i)
+    if (t->shape[i] != dims[i]) return KVX_STATUS_INVALID_ARGUMENT;
+  int64_t run = 1;
+  for (uint32_t i = ndim; i-- > 0;) {
+    if (t->stride[i] != run) return KVX_STATUS_UNSUPPORTED;
+    run *= dims[i];
+  }
+  return KVX_STATUS_OK;
+}
+
+bool resolve_scale(const kvx_scale_desc_t *d, const void *scalar, uint32_t heads, ScaleView *out) {
+  if (d != nullptr && d->size >= sizeof(kvx_scale_desc_t) && d->data != nullptr) {
+    if (d->dtype != KVX_DTYPE_F32) return false;
+    if (d->granularity == KVX_SCALE_PER_TENSOR) {
+      *out = ScaleView{static_cast<const float *>(d->data), 0};
+      return true;
+    }
+    if (d->granularity == KVX_SCALE_PER_HEAD && d->ndim == 1 && d->shape[0] == static_cast<int64_t>(heads)) {
+      *out = ScaleView{static_cast<const float *>(d->data), d->stride[0]};
+      return true;
+    }
+    return false;
+  }
+  if (scalar != nullptr) {
+    *out = ScaleView{static_cast<const float *>(scalar), 0};
+    return true;
+  }
+  return false;
+}
+
+bool io_dtype_quantisable(kvx_dtype_t t) {
+  return t == KVX_DTYPE_F16 || t == KVX_DTYPE_BF16 || t == KVX_DTYPE_F32;
+}
+
+cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
+
+kvx_status_t finish_launch() {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? KVX_STATUS_OK : KVX_STATUS_INTERNAL_ERROR;
+}
+
+// ------------------------------------------------------------------ host: write --------
+
+template <typename SlotT, bool kSeg>
+void launch_write_rows(const WriteRowsParams &p, int grid, int unroll, cudaStream_t st) {
+  if (unroll >= 4)
+    kvx_write_rows_kernel<SlotT, kSeg, 4><<<grid, kWriteThreads, 0, st>>>(p);
+  else if (unroll >= 2)
+    kvx_write_rows_kernel<SlotT, kSeg, 2><<<grid, kWriteThreads, 0, st>>>(p);
+  else
+    kvx_write_rows_kernel<SlotT, kSeg, 1><<<grid, kWriteThreads, 0, st>>>(p);
+}
+
+template <typename IoT, typename CacheT>
+kvx_status_t launch_write_generic(const kvx_write_desc_t *w, const GenericParams &gp, cudaStream_t st) {
+  const int64_t total = static_cast<int64_t>(w->io.num_tokens) * gp.g.heads * gp.g.dim;
+  const int64_t grid = (total + 255) / 256;
+  if (grid > INT32_MAX) return KVX_STATUS_UNSUPPORTED;
+  const IoT *k = static_cast<const IoT *>(w->io.key.data);
+  const IoT *v = static_cast<const IoT *>(w->io.value.data);
+  if (w->slots.dtype == KVX_DTYPE_S32)
+    kvx_write_generic_kernel<IoT, CacheT, int32_t>
+        <<<static_cast<unsigned>(grid), 256, 0, st>>>(k, v, w->slots.slots, w->io.num_tokens, gp);
+  else
+    kvx_write_generic_kernel<IoT, CacheT, int64_t>
+        <<<static_cast<unsigned>(grid), 256, 0, st>>>(k, v, w->slots.slots, w->io.num_tokens, gp);
+  return finish_launch();
+}
+
+// Tokens per CTA: aim at `write_vecs_per_cta` vectors of K per CTA, but never fewer CTAs
+// than fill the machine twice when the batch is small.
+int pick_tok_tile(int64_t tokens, int64_t vpr, int sm_count) {
+  int64_t tile = g_opt.write_vecs_per_cta / vpr;
+  if (tile < 1) tile = 1;
+  if (tile > kMaxTokTile) tile = kMaxTokTile;
+  const int64_t want_ctas = static_cast<int64_t>(sm_count) * 4;
+  while (tile > 1 && (tokens + tile - 1) / tile < want_ctas) tile >>= 1;
+  return static_cast<int>(tile);
+}
+
+/*
+ * Shared body of every write entry point.  `expected` is the cache dtype the entry point
+ * is pinned to; for F8_E4M3 the IO tensors may be F16 / BF16 / F32.
+ * Check order: reference kernels/kvx_paged_kv.cu:320-376 (write), :497-559 (prefill).
+ */
+kvx_status_t write_impl(const kvx_cache_desc_t *cache, const kvx_write_desc_t *write, void *stream,
+                        kvx_dtype_t expected, bool prefill, int32_t tokens_per_seq) {
+  if (cache == nullptr || write == nullptr) return KVX_STATUS_INVALID_ARGUMENT;
+  if (prefill && tokens_per_seq <= 0) return KVX_STATUS_INVALID_ARGUMENT;
+  if (write->size < sizeof(kvx_write_desc_t) || write->io.size < sizeof(kvx_kv_io_desc_t) ||
+      write->slots.size < sizeof(kvx_slot_mapping_t))
+    return KVX_STATUS_INVALID_ARGUMENT;
+  if (prefill && (write->io.num_tokens % static_cast<uint32_t>(tokens_per_seq)) != 0)
+    return KVX_STATUS_INVALID_ARGUMENT;
+  if (cache->k.dtype != expected || cache->v.dtype != expected) return KVX_STATUS_UNSUPPORTED;
+  const bool fp8 = (expected == KVX_DTYPE_F8_E4M3);
+  const kvx_dtype_t io_dtype = write->io.key.dtype;
+  ScaleView ks{nullptr, 0}, vs{nullptr, 0};
+  if (fp8) {
+    if (!io_dtype_quantisable(io_dtype) || write->io.value.dtype != io_dtype) return KVX_STATUS_UNSUPPORTED;
+    if (!resolve_scale(&write->k_scale_desc, write->k_scale, cache->num_kv_heads, &ks) ||
+        !resolve_scale(&write->v_scale_desc, write->v_scale, cache->num_kv_heads, &vs))
+      return KVX_STATUS_UNSUPPORTED;
+  } else if (io_dtype != expected || write->io.value.dtype != expected) {
+    return KVX_STATUS_UNSUPPORTED;
+  }
+  if (write->io.num_kv_heads != cache->num_kv_heads || write->io.head_dim != cache->head_dim)
+    return KVX_STATUS_INVALID_ARGUMENT;
+  const int64_t dims[3] = {write->io.num_tokens, write->io.num_kv_heads, write->io.head_dim};
+  kvx_status_t st = check_io_tensor(&write->io.key, 3, dims);
+  if (st != KVX_STATUS_OK) return st;
+  st = check_io_tensor(&write->io.value, 3, dims);
+  if (st != KVX_STATUS_OK) return st;
+  if (write->slots.token_count != write->io.num_tokens) return KVX_STATUS_INVALID_ARGUMENT;
+
+  const int64_t elem = dtype_bytes(expected);
+  const int64_t io_elem = dtype_bytes(io_dtype);
+  GenericParams gp;
+  st = make_page_view(cache, &cache->k, elem, &gp.k);
+  if (st != KVX_STATUS_OK) return st;
+  st = make_page_view(cache, &cache->v, elem, &gp.v);
+  if (st != KVX_STATUS_OK) return st;
+  gp.g = Geometry{static_cast<int32_t>(cache->num_blocks), static_cast<int32_t>(cache->block_size),
+                  static_cast<int32_t>(cache->num_kv_heads), static_cast<int32_t>(cache->head_dim),
+                  static_cast<int32_t>(elem)};
+  gp.ks = ks;
+  gp.vs = vs;
+
+  const int64_t T = write->io.num_tokens, H = cache->num_kv_heads, D = cache->head_dim;
+  if (T * H * D == 0) return KVX_STATUS_OK;
+  if (write->slots.dtype != KVX_DTYPE_S32 && write->slots.dtype != KVX_DTYPE_S64)
+    return KVX_STATUS_INVALID_ARGUMENT;
+  // Stricter than the reference, which would fault on the device instead.
+  if (write->io.key.data == nullptr || write->io.value.data == nullptr || write->slots.slots == nullptr ||
+      cache->k.data == nullptr || cache->v.data == nullptr || cache->block_size == 0 ||
+      cache->num_blocks > static_cast<uint32_t>(INT32_MAX) || T > INT32_MAX)
+    return KVX_STATUS_INVALID_ARGUMENT;
+
+  const cudaStream_t cs = as_stream(stream);
+  const DeviceInfo &dev = device_info();
+  const bool s32 = (write->slots.dtype == KVX_DTYPE_S32);
+
+  // ---- vector tier: 16-byte input vectors, each inside one head -------------------------
+  const int64_t row_bytes = H * D * io_elem;
+  const int64_t out_vec = fp8 ? 16 / io_elem : 16;  // cache bytes produced per input vector
+  const bool vec_ok = !g_opt.force_generic && (D * io_elem) % 16 == 0 &&
+                      aligned(write->io.key.data, 16) && aligned(write->io.value.data, 16) &&
+                      view_vectorisable(gp.k, elem, D, out_vec) && view_vectorisable(gp.v, elem, D, out_vec) &&
+                      row_bytes / 16 <= (1 << 20);
+  if (vec_ok) {
+    WriteRowsParams p;
+    p.key = static_cast<const char *>(write->io.key.data);
+    p.value = static_cast<const char *>(write->io.value.data);
+    p.k_base = gp.k.base, p.k_blk = gp.k.blk, p.k_tok = gp.k.tok, p.k_head = gp.k.head;
+    p.v_base = gp.v.base, p.v_blk = gp.v.blk, p.v_tok = gp.v.tok, p.v_head = gp.v.head;
+    p.slots = write->slots.slots;
+    p.row_bytes = row_bytes;
+    p.num_tokens = static_cast<int32_t>(T);
+    p.num_blocks = gp.g.num_blocks;
+    p.block_size = gp.g.block_size;
+    p.bs_shift = shift_of(p.block_size);
+    p.vpr = static_cast<int32_t>(row_bytes / 16);
+    p.vpr_shift = shift_of(p.vpr);
+    p.vps = static_cast<int32_t>(D * io_elem / 16);
+    p.vps_shift = shift_of(p.vps);
+    p.tok_tile = pick_tok_tile(T, p.vpr, dev.sm_count);
+    const int grid = static_cast<int>((T + p.tok_tile - 1) / p.tok_tile);
+    const int unroll = static_cast<int>(g_opt.write_unroll);
+    if (fp8) {
+      WriteF8Params q{p, ks, vs, static_cast<int32_t>(D)};
+#define KVX_F8_WRITE(IoT)                                                                  \
+  do {                                                                                     \
+    if (s32)                                                                               \
+      kvx_write_f8_kernel<IoT, int32_t, 2><<<grid, kWriteThreads, 0, cs>>>(q);             \
+    else                                                                                   \
+      kvx_write_f8_kernel<IoT, int64_t, 2><<<grid, kWriteThreads, 0, cs>>>(q);             \
+  } while (0)
+      if (io_dtype == KVX_DTYPE_BF16)
+        KVX_F8_WRITE(BF16);
+      else if (io_dtype == KVX_DTYPE_F16)
+        KVX_F8_WRITE(F16);
+      else
+        KVX_F8_WRITE(F32);
+#undef KVX_F8_WRITE
+      return finish_launch();
+    }
+    const bool seg = !(gp.k.head == D * elem && gp.v.head == D * elem);
+    if (s32) {
+      if (seg)
+        launch_write_rows<int32_t, true>(p, grid, unroll, cs);
+      else
+        launch_write_rows<int32_t, false>(p, grid, unroll, cs);
+    } else {
+      if (seg)
+        launch_write_rows<int64_t, true>(p, grid, unroll, cs);
+      else
+        launch_write_rows<int64_t, false>(p, grid, unroll, cs);
+    }
+    return finish_launch();
+  }
+
+  // ---- generic tier ---------------------------------------------------------------------
+  if (fp8) {
+    if (io_dtype == KVX_DTYPE_BF16) return launch_write_generic<BF16, F8>(write, gp, cs);
+    if (io_dtype == KVX_DTYPE_F16) return launch_write_generic<F16, F8>(write, gp, cs);
+    return launch_write_generic<F32, F8>(write, gp, cs);
+  }
+  if (elem == 2) return launch_write_generic<BF16, BF16>(write, gp, cs);  // 16-bit copy, either type
+  return launch_write_generic<F32, F32>(write, gp, cs);
+}
+
+// ------------------------------------------------------------------ host: gather -------
+
+template <typename IoT, typename CacheT, bool kDequant>
+kvx_status_t launch_gather_generic(const kvx_gather_desc_t *g, const GatherShape &s, const GenericParams &gp,
+                                   cudaStream_t st) {
+  const int64_t total = static_cast<int64_t>(s.seq_count) * s.max_seq_len * gp.g.heads * gp.g.dim;
+  const int64_t grid = (total + 255) / 256;
+  if (grid > INT32_MAX) return KVX_STATUS_UNSUPPORTED;
+  IoT *k = static_cast<IoT *>(g->io.key.data);
+  IoT *v = static_cast<IoT *>(g->io.value.data);
+  if (g->seq_lens.dtype == KVX_DTYPE_S32)
+    kvx_gather_generic_kernel<IoT, CacheT, int32_t, kDequant>
+        <<<static_cast<unsigned>(grid), 256, 0, st>>>(k, v, s, gp);
+  else
+    kvx_gather_generic_kernel<IoT, CacheT, int64_t, kDequant>
+        <<<static_cast<unsigned>(grid), 256, 0, st>>>(k, v, s, gp);
+  return finish_launch();
+}
+
+// Largest sequence count whose page-count prefix fits in shared memory next to everything
+// else; beyond it the kernels walk the padded (sequence, page) rectangle instead.
+constexpr int kMaxPrefixSeqs = 10240;
+
+/*
+ * Shared body of every gather entry point.
+ * Check order: reference kernels/kvx_paged_kv.cu:768-829, :837-863.
+ */
+kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t *gather,
+                         const kvx_scale_desc_t *k_scale, const kvx_scale_desc_t *v_scale, void *stream,
+                         kvx_dtype_t expected) {
+  if (cache == nullptr || gather == nullptr) return KVX_STATUS_INVALID_ARGUMENT;
+  if (gather->size < sizeof(kvx_gather_desc_t) || gather->io.size < sizeof(kvx_kv_io_desc_t) ||
+      gather->block_table.size < sizeof(kvx_block_table_t) || gather->seq_lens.size < sizeof(kvx_seq_lens_t))
+    return KVX_STATUS_INVALID_ARGUMENT;
+  if (cache->k.dtype != expected || cache->v.dtype != expected) return KVX_STATUS_UNSUPPORTED;
+  const bool fp8 = (expected == KVX_DTYPE_F8_E4M3);
+  const kvx_dtype_t io_dtype = gather->io.key.dtype;
+  ScaleView ks{nullptr, 0}, vs{nullptr, 0};
+  if (fp8) {
+    if (!io_dtype_quantisable(io_dtype) || gather->io.value.dtype != io_dtype) return KVX_STATUS_UNSUPPORTED;
+    if (!resolve_scale(k_scale, nullptr, cache->num_kv_heads, &ks) ||
+        !resolve_scale(v_scale, nullptr, cache->num_kv_heads, &vs))
+      return KVX_STATUS_UNSUPPORTED;
+  } else if (io_dtype != expected || gather->io.value.dtype != expected) {
+    return KVX_STATUS_UNSUPPORTED;
+  }
+  if (gather->block_table.format != KVX_BLOCK_TABLE_PACKED) return KVX_STATUS_UNSUPPORTED;
+  if (gather->io.num_kv_heads != cache->num_kv_heads || gather->io.head_dim != cache->head_dim)
+    return KVX_STATUS_INVALID_ARGUMENT;
+  if (gather->seq_lens.seq_count != gather->block_table.seq_count) return KVX_STATUS_INVALID_ARGUMENT;
+  const int64_t dims[4] = {gather->block_table.seq_count, gather->max_seq_len, gather->io.num_kv_heads,
+                           gather->io.head_dim};
+  kvx_status_t st = check_io_tensor(&gather->io.key, 4, dims);
+  if (st != KVX_STATUS_OK) return st;
+  st = check_io_tensor(&gather->io.value, 4, dims);
+  if (st != KVX_STATUS_OK) return st;
+
+  const int64_t elem = dtype_bytes(expected);
+  const int64_t io_elem = dtype_bytes(io_dtype);
+  GenericParams gp;
+  st = make_page_view(cache, &cache->k, elem, &gp.k);
+  if (st != KVX_STATUS_OK) return st;
+  st = make_page_view(cache, &cache->v, elem, &gp.v);
+  if (st != KVX_STATUS_OK) return st;
+  gp.g = Geometry{static_cast<int32_t>(cache->num_blocks), static_cast<int32_t>(cache->block_size),
+                  static_cast<int32_t>(cache->num_kv_heads), static_cast<int32_t>(cache->head_dim),
+                  static_cast<int32_t>(elem)};
+  gp.ks = ks;
+  gp.vs = vs;
+
+  const int64_t S = gather->block_table.seq_count, L = gather->max_seq_len;
+  const int64_t H = cache->num_kv_heads, D = cache->head_dim;
+  if (S * L * H * D == 0) return KVX_STATUS_OK;
+  const bool s32 = gather->block_table.index_dtype == KVX_DTYPE_S32 && gather->seq_lens.dtype == KVX_DTYPE_S32;
+  const bool s64 = gather->block_table.index_dtype == KVX_DTYPE_S64 && gather->seq_lens.dtype == KVX_DTYPE_S64;
+  if (!s32 && !s64) return KVX_STATUS_INVALID_ARGUMENT;
+  // Stricter than the reference, which would fault on the device instead.
+  if (gather->io.key.data == nullptr || gather->io.value.data == nullptr ||
+      gather->block_table.indices == nullptr || gather->seq_lens.lengths == nullptr ||
+      cache->k.data == nullptr || cache->v.data == nullptr || cache->block_size == 0 ||
+      gather->block_table.max_blocks_per_seq == 0 || cache->num_blocks > static_cast<uint32_t>(INT32_MAX) ||
+      S > INT32_MAX || L > INT32_MAX || gather->block_table.max_blocks_per_seq > static_cast<uint32_t>(INT32_MAX))
+    return KVX_STATUS_INVALID_ARGUMENT;
+
+  GatherShape gs;
+  gs.table = gather->block_table.indices;
+  gs.lens = gather->seq_lens.lengths;
+  gs.seq_count = static_cast<int32_t>(S);
+  gs.max_blocks = static_cast<int32_t>(gather->block_table.max_blocks_per_seq);
+  gs.max_seq_len = static_cast<int32_t>(L);
+
+  const cudaStream_t cs = as_stream(stream);
+  const DeviceInfo &dev = device_info();
+
+  // ---- vector tier: 16-byte output vectors, each inside one head ------------------------
+  const int64_t out_row = H * D * io_elem;
+  const int64_t in_vec = fp8 ? 16 / io_elem : 16;  // cache bytes consumed per output vector
+  const int64_t chunk_vecs = static_cast<int64_t>(cache->block_size) * (out_row / 16);
+  const bool vec_ok = !g_opt.force_generic && (D * io_elem) % 16 == 0 && aligned(gather->io.key.data, 16) &&
+                      aligned(gather->io.value.data, 16) && view_vectorisable(gp.k, elem, D, in_vec) &&
+                      view_vectorisable(gp.v, elem, D, in_vec) && chunk_vecs < (int64_t{1} << 30) &&
+                      S * static_cast<int64_t>(gs.max_blocks) < (int64_t{1} << 31);
+  if (vec_ok) {
+    GatherPagesParams p;
+    p.k_base = gp.k.base, p.k_blk = gp.k.blk, p.k_tok = gp.k.tok, p.k_head = gp.k.head;
+    p.v_base = gp.v.base, p.v_blk = gp.v.blk, p.v_tok = gp.v.tok, p.v_head = gp.v.head;
+    p.key_out = static_cast<char *>(gather->io.key.data);
+    p.value_out = static_cast<char *>(gather->io.value.data);
+    p.s = gs;
+    p.out_row_bytes = out_row;
+    p.num_blocks = gp.g.num_blocks;
+    p.block_size = gp.g.block_size;
+    p.vpr = static_cast<int32_t>(out_row / 16);
+    p.vpr_shift = shift_of(p.vpr);
+    p.vps = static_cast<int32_t>(D * io_elem / 16);
+    p.vps_shift = shift_of(p.vps);
+    p.use_prefix = (S <= kMaxPrefixSeqs) ? 1 : 0;
+    p.dim = static_cast<int32_t>(D);
+    p.ks = ks;
+    p.vs = vs;
+    const bool contiguous_pages = !fp8 && gp.k.head == D * elem && gp.v.head == D * elem &&
+                                  gp.k.tok == H * D * elem && gp.v.tok == H * D * elem;
+    const size_t prefix_bytes = p.use_prefix ? static_cast<size_t>(S + 1) * sizeof(int32_t) : 0;
+
+    if (contiguous_pages && g_opt.gather_path == 1) {
+      // ---- bulk tier ----
+      BulkParams bp;
+      bp.g = p;
+      int64_t stage = g_opt.bulk_stage_bytes / 16 * 16;
+      if (stage < 1024) stage = 1024;
+      bp.stages = static_cast<int32_t>(g_opt.bulk_stages < 2 ? 2 : (g_opt.bulk_stages > kBulkMaxStages ? kBulkMaxStages : g_opt.bulk_stages));
+      bp.pipes = static_cast<int32_t>(g_opt.bulk_pipes < 1 ? 1 : (g_opt.bulk_pipes > kBulkMaxPipes ? kBulkMaxPipes : g_opt.bulk_pipes));
+      bp.lag = static_cast<int32_t>(g_opt.bulk_lag < 1 ? 1 : (g_opt.bulk_lag > bp.stages - 1 ? bp.stages - 1 : g_opt.bulk_lag));
+      const int64_t chunk_bytes = chunk_vecs * 16;
+      if (stage > chunk_bytes) stage = chunk_bytes;
+      bp.stage_bytes = static_cast<int32_t>(stage);
+      bp.g.part_vecs = static_cast<int32_t>(stage / 16);
+      bp.g.parts = static_cast<int32_t>((chunk_vecs + bp.g.part_vecs - 1) / bp.g.part_vecs);
+      const size_t smem = static_cast<size_t>(bp.pipes) * bp.stages * bp.stage_bytes + prefix_bytes;
+      if (smem <= static_cast<size_t>(dev.max_smem_optin) - 1024) {
+        const int64_t max_items = S * gs.max_blocks * bp.g.parts * 2;
+        int64_t grid = static_cast<int64_t>(dev.sm_count) * (g_opt.bulk_ctas_per_sm < 1 ? 1 : g_opt.bulk_ctas_per_sm);
+        const int64_t need = (max_items + bp.pipes - 1) / bp.pipes;
+        if (grid > need) grid = need;
+        if (s32) {
+          cudaFuncSetAttribute(kvx_gather_bulk_kernel<int32_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(smem));
+          kvx_gather_bulk_kernel<int32_t><<<static_cast<unsigned>(grid), kGatherThreads, smem, cs>>>(bp);
+        } else {
+          cudaFuncSetAttribute(kvx_gather_bulk_kernel<int64_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(smem));
+          kvx_gather_bulk_kernel<int64_t><<<static_cast<unsigned>(grid), kGatherThreads, smem, cs>>>(bp);
+        }
+        return finish_launch();
+      }
+    }
+
+    // ---- register tier ----
+    int64_t part_vecs = g_opt.gather_part_bytes / 16;
+    if (part_vecs < 32) part_vecs = 32;
+    if (part_vecs > chunk_vecs) part_vecs = chunk_vecs;
+    p.part_vecs = static_cast<int32_t>(part_vecs);
+    p.parts = static_cast<int32_t>((chunk_vecs + part_vecs - 1) / part_vecs);
+    const int64_t max_items = S * gs.max_blocks * p.parts * 2;
+    int64_t grid = static_cast<int64_t>(dev.sm_count) * (g_opt.gather_ctas_per_sm < 1 ? 1 : g_opt.gather_ctas_per_sm);
+    const int64_t need = (max_items + kGatherWarps - 1) / kGatherWarps;
+    if (grid > need) grid = need;
+    const unsigned ug = static_cast<unsigned>(grid);
+    if (fp8) {
+#define KVX_F8_GATHER(IoT)                                                                     \
+  do {                                                                                         \
+    if (s32)                                                                                   \
+      kvx_gather_f8_kernel<IoT, int32_t, 4><<<ug, kGatherThreads, prefix_bytes, cs>>>(p);      \
+    else                                                                                       \
+      kvx_gather_f8_kernel<IoT, int64_t, 4><<<ug, kGatherThreads, prefix_bytes, cs>>>(p);      \
+  } while (0)
+      if (io_dtype == KVX_DTYPE_BF16)
+        KVX_F8_GATHER(BF16);
+      else if (io_dtype == KVX_DTYPE_F16)
+        KVX_F8_GATHER(F16);
+      else
+        KVX_F8_GATHER(F32);
+#undef KVX_F8_GATHER
+      return finish_launch();
+    }
+    if (s32) {
+      if (contiguous_pages)
+        kvx_gather_pages_kernel<int32_t, false, 8><<<ug, kGatherThreads, prefix_bytes, cs>>>(p);
+      else
+        kvx_gather_pages_kernel<int32_t, true, 8><<<ug, kGatherThreads, prefix_bytes, cs>>>(p);
+    } else {
+      if (contiguous_pages)
+        kvx_gather_pages_kernel<int64_t, false, 8><<<ug, kGatherThreads, prefix_bytes, cs>>>(p);
+      else
+        kvx_gather_pages_kernel<int64_t, true, 8><<<ug, kGatherThreads, prefix_bytes, cs>>>(p);
+    }
+    return finish_launch();
+  }
+
+  // ---- generic tier ---------------------------------------------------------------------
+  if (fp8) {
+    if (io_dtype == KVX_DTYPE_BF16) return launch_gather_generic<BF16, F8, true>(gather, gs, gp, cs);
+    if (io_dtype == KVX_DTYPE_F16) return launch_gather_generic<F16, F8, true>(gather, gs, gp, cs);
+    return launch_gather_generic<F32, F8, true>(gather, gs, gp, cs);
+  }
+  if (elem == 2) return launch_gather_generic<BF16, BF16, false>(gather, gs, gp, cs);
+  return launch_gather_generic<F32, F32, false>(gather, gs, gp, cs);
+}
+
+}  // namespace
+
+// ====================================================================== C entry points ==
+
+extern "C" {
+
+KVX_API kvx_status_t kvx_launch_write_kv_f32(const kvx_cache_desc_t *cache, const kvx_write_desc_t *write,
+                                             void *stream) {
+  return write_impl(cache, write, stream, KVX_DTYPE_F32, false, 0);
+}
+KVX_API kvx_status_t kvx_launch_write_kv_f16(const kvx_cache_desc_t *cache, const kvx_write_desc_t *write,
+                                             void *stream) {
+  return write_impl(cache, write, stream, KVX_DTYPE_F16, false, 0);
+}
+KVX_API kvx_status_t kvx_launch_write_kv_bf16(const kvx_cache_desc_t *cache, const kvx_write_desc_t *write,
+                                              void *stream) {
+  return write_impl(cache, write, stream, KVX_DTYPE_BF16, false, 0);
+}
+KVX_API kvx_status_t kvx_launch_write_kv_f8e4m3(const kvx_cache_desc_t *cache, const kvx_write_desc_t *write,
+                                                void *stream) {
+  return write_impl(cache, write, stream, KVX_DTYPE_F8_E4M3, false, 0);
+}
+
+KVX_API kvx_status_t kvx_launch_write_kv(const kvx_cache_desc_t *cache, const kvx_write_desc_t *write,
+                                         void *stream) {
+  if (cache == nullptr || write == nullptr) return KVX_STATUS_INVALID_ARGUMENT;
+  if (cache->k.dtype != cache->v.dtype) return KVX_STATUS_INVALID_ARGUMENT;
+  switch (cache->k.dtype) {
+    case KVX_DTYPE_F16:
+    case KVX_DTYPE_BF16:
+    case KVX_DTYPE_F32:
+    case KVX_DTYPE_F8_E4M3:
+      return write_impl(cache, write, stream, cache->k.dtype, false, 0);
+    default:
+      return KVX_STATUS_UNSUPPORTED;
+  }
+}
+
+KVX_API kvx_status_t kvx_launch_write_kv_prefill_f32(const kvx_cache_desc_t *cache,
+                                                     const kvx_write_desc_t *write, int32_t tokens_per_seq,
+                                                     void *stream) {
+  return write_impl(cache, write, stream, KVX_DTYPE_F32, true, tokens_per_seq);
+}
+KVX_API kvx_status_t kvx_launch_write_kv_prefill_f16(const kvx_cache_desc_t *cache,
+                                                     const kvx_write_desc_t *write, int32_t tokens_per_seq,
+                                                     void *stream) {
+  return write_impl(cache, write, stream, KVX_DTYPE_F16, true, tokens_per_seq);
+}
+KVX_API kvx_status_t kvx_launch_write_kv_prefill_bf16(const kvx_cache_desc_t *cache,
+                                                      const kvx_write_desc_t *write, int32_t tokens_per_seq,
+                                                      void *stream) {
+  return write_impl(cache, write, stream, KVX_DTYPE_BF16, true, tokens_per_seq);
+}
+
+KVX_API kvx_status_t kvx_launch_write_kv_prefill(const kvx_cache_desc_t *cache, const kvx_write_desc_t *write,
+                                                 int32_t tokens_per_seq, void *stream) {
+  if (cache == nullptr || write == nullptr) return KVX_STATUS_INVALID_ARGUMENT;
+  if (cache->k.dtype != cache->v.dtype) return KVX_STATUS_INVALID_ARGUMENT;
+  switch (cache->k.dtype) {
+    case KVX_DTYPE_F16:
+    case KVX_DTYPE_BF16:
+    case KVX_DTYPE_F32:
+    case KVX_DTYPE_F8_E4M3:
+      return write_impl(cache, write, stream, cache->k.dtype, true, tokens_per_seq);
+    default:
+      return KVX_STATUS_UNSUPPORTED;
+  }
+}
+
+KVX_API kvx_status_t kvx_launch_gather_kv_f32(const kvx_cache_desc_t *cache, const kvx_gather_desc_t *gather,
+                                              void *stream) {
+  return gather_impl(cache, gather, nullptr, nullptr, stream, KVX_DTYPE_F32);
+}
+KVX_API kvx_status_t kvx_launch_gather_kv_f16(const kvx_cache_desc_t *cache, const kvx_gather_desc_t *gather,
+                                              void *stream) {
+  return gather_impl(cache, gather, nullptr, nullptr, stream, KVX_DTYPE_F16);
+}
+KVX_API kvx_status_t kvx_launch_gather_kv_bf16(const kvx_cache_desc_t *cache, const kvx_gather_desc_t *gather,
+                                               void *stream) {
+  return gather_impl(cache, gather, nullptr, nullptr, stream, KVX_DTYPE_BF16);
+}
+KVX_API kvx_status_t kvx_launch_gather_kv_f8e4m3(const kvx_cache_desc_t *cache,
+                                                 const kvx_gather_desc_t *gather,
+                                                 const kvx_scale_desc_t *k_scale,
+                                                 const kvx_scale_desc_t *v_scale, void *stream) {
+  return gather_impl(cache, gather, k_scale, v_scale, stream, KVX_DTYPE_F8_E4M3);
+}
+
+KVX_API kvx_status_t kvx_launch_gather_kv(const kvx_cache_desc_t *cache, const kvx_gather_desc_t *gather,
+                                          void *stream) {
+  if (cache == nullptr || gather == nullptr) return KVX_STATUS_INVALID_ARGUMENT;
+  if (cache->k.dtype != cache->v.dtype) return KVX_STATUS_INVALID_ARGUMENT;
+  switch (cache->k.dtype) {
+    case KVX_DTYPE_F16:
+    case KVX_DTYPE_BF16:
+    case KVX_DTYPE_F32:
+      return gather_impl(cache, gather, nullptr, nullptr, stream, cache->k.dtype);
+    default:
+      // An fp8 cache needs scales, which a gather descriptor cannot carry: use
+      // kvx_launch_gather_kv_f8e4m3.
+      return KVX_STATUS_UNSUPPORTED;
+  }
+}
+
+KVX_API size_t kvx_kv_scales_workspace_bytes(uint32_t num_kv_heads) {
+  const size_t raw = (2 * static_cast<size_t>(num_kv_heads) + 1) * sizeof(uint32_t);
+  return (raw + 255) / 256 * 256;
+}
+
+KVX_API kvx_status_t kvx_launch_kv_scales(const kvx_kv_io_desc_t *io, kvx_scale_granularity_t granularity,
+                                          float *k_scale_out, float *v_scale_out, void *workspace,
+                                          size_t workspace_bytes, void *stream) {
+  if (io == nullptr || k_scale_out == nullptr || v_scale_out == nullptr || workspace == nullptr)
+    return KVX_STATUS_INVALID_ARGUMENT;
+  if (io->size < sizeof(kvx_kv_io_desc_t)) return KVX_STATUS_INVALID_ARGUMENT;
+  if (granularity != KVX_SCALE_PER_HEAD && granularity != KVX_SCALE_PER_TENSOR) return KVX_STATUS_UNSUPPORTED;
+  if (!io_dtype_quantisable(io->key.dtype) || io->value.dtype != io->key.dtype) return KVX_STATUS_UNSUPPORTED;
+  if (io->num_kv_heads == 0 || io->head_dim == 0) return KVX_STATUS_INVALID_ARGUMENT;
+  const int64_t dims[3] = {io->num_tokens, io->num_kv_heads, io->head_dim};
+  kvx_status_t st = check_io_tensor(&io->key, 3, dims);
+  if (st != KVX_STATUS_OK) return st;
+  st = check_io_tensor(&io->value, 3, dims);
+  if (st != KVX_STATUS_OK) return st;
+  if (workspace_bytes < kvx_kv_scales_workspace_bytes(io->num_kv_heads) || !aligned(workspace, 256))
+    return KVX_STATUS_INVALID_ARGUMENT;
+  const int64_t elem = dtype_bytes(io->key.dtype);
+  const int64_t T = io->num_tokens, H = io->num_kv_heads, D = io->head_dim;
+  if (T > 0 && (io->key.data == nullptr || io->value.data == nullptr)) return KVX_STATUS_INVALID_ARGUMENT;
+  // Vector loads need whole 16-byte vectors inside one head.
+  if ((D * elem) % 16 != 0 || !aligned(io->key.data, 16) || !aligned(io->value.data, 16) ||
+      2 * H * sizeof(uint32_t) > 40960)
+    return KVX_STATUS_UNSUPPORTED;
+
+  ScalesParams p;
+  p.key = static_cast<const char *>(io->key.data);
+  p.value = static_cast<const char *>(io->value.data);
+  p.vpr = static_cast<int32_t>(H * D * elem / 16);
+  p.vpr_shift = shift_of(p.vpr);
+  p.vps = static_cast<int32_t>(D * elem / 16);
+  p.vps_shift = shift_of(p.vps);
+  p.total_vecs = T * p.vpr;
+  p.heads = static_cast<int32_t>(H);
+  int group = 1;
+  while (group < 32 && p.vps % (group * 2) == 0) group *= 2;
+  p.group = group;
+  p.per_tensor = (granularity == KVX_SCALE_PER_TENSOR) ? 1 : 0;
+  p.k_out = k_scale_out;
+  p.v_out = v_scale_out;
+  p.work = static_cast<uint32_t *>(workspace);
+
+  const DeviceInfo &dev = device_info();
+  int64_t grid = (p.total_vecs + kScaleThreads * 8 - 1) / (kScaleThreads * 8);
+  const int64_t cap = static_cast<int64_t>(dev.sm_count) * 8;
+  if (grid > cap) grid = cap;
+  if (grid < 1) grid = 1;
+  const size_t smem = 2 * static_cast<size_t>(H) * sizeof(uint32_t);
+  const cudaStream_t cs = as_stream(stream);
+  if (io->key.dtype == KVX_DTYPE_BF16)
+    kvx_kv_scales_kernel<BF16><<<static_cast<unsigned>(grid), kScaleThreads, smem, cs>>>(p);
+  else if (io->key.dtype == KVX_DTYPE_F16)
+    kvx_kv_scales_kernel<F16><<<static_cast<unsigned>(grid), kScaleThreads, smem, cs>>>(p);
+  else
+    kvx_kv_scales_kernel<F32><<<static_cast<unsigned>(grid), kScaleThreads, smem, cs>>>(p);
+  return finish_launch();
+}
+
+KVX_API uint64_t kvx_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+KVX_API void kvx_b200_reset_launch_count(void) { g_launches.store(0, std::memory_order_relaxed); }
+
+KVX_API int kvx_b200_set_option(const char *name, int64_t value) {
+  if (name == nullptr) return -1;
+  for (const OptionName &o : kOptionNames)
+    if (strcmp(o.name, name) == 0) {
+      g_opt.*(o.field) = value;
+      return 0;
+    }
+  return -1;
+}
+KVX_API int64_t kvx_b200_get_option(const char *name) {
+  if (name == nullptr) return -1;
+  for (const OptionName &o : kOptionNames)
+    if (strcmp(o.name, name) == 0) return g_opt.*(o.field);
+  return -1;
+}
+
+}  // extern "C"

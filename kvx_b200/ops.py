@@ -1,0 +1,202 @@
+"""Torch-tensor front end of the C-ABI library.
+
+The write operator keeps the name, argument order and checks of the operator the
+reference's vLLM patch registers (``reshape_and_cache_flash_kvx``, reference:
+patches/vllm/kvx.patch:176-275): it fills the ABI descriptors from tensor sizes and strides
+without canonicalising them, passes torch's current CUDA stream and raises when the status
+is not OK.  Torch is used for device memory and streams only; all data movement happens in
+``libkvx_b200.so``.  Nothing here falls back to PyTorch indexing.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import abi
+from ._lib import lib
+
+_FLOAT_CODES = {torch.float16: abi.DTYPE_F16, torch.bfloat16: abi.DTYPE_BF16,
+                torch.float32: abi.DTYPE_F32}
+_INDEX_CODES = {torch.int32: abi.DTYPE_S32, torch.int64: abi.DTYPE_S64}
+_FP8_TORCH = (torch.float8_e4m3fn, torch.uint8)
+
+
+class KvxError(RuntimeError):
+    """A launcher returned a status other than ``KVX_STATUS_OK``."""
+
+    def __init__(self, what: str, status: int):
+        super().__init__(f"{what} failed with status={status} ({abi.STATUS_NAMES.get(status, '?')})")
+        self.status = status
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _cache_code(t: torch.Tensor, kv_cache_dtype: str) -> int:
+    if kv_cache_dtype in ("fp8", "fp8_e4m3"):
+        if t.dtype not in _FP8_TORCH:
+            raise TypeError("an fp8 cache must be a float8_e4m3fn or uint8 tensor")
+        return abi.DTYPE_F8_E4M3
+    if kv_cache_dtype != "auto":
+        raise ValueError(f"unsupported kv_cache_dtype {kv_cache_dtype!r}")
+    if t.dtype not in _FLOAT_CODES:
+        raise TypeError(f"unsupported cache dtype {t.dtype}")
+    return _FLOAT_CODES[t.dtype]
+
+
+def cache_desc_from_tensors(key_cache: torch.Tensor, value_cache: torch.Tensor,
+                            kv_cache_dtype: str = "auto", head_dim: Optional[int] = None,
+                            layout: Optional[int] = None) -> abi.CacheDesc:
+    """Describe a pair of 4-D (NHD / HND) or 5-D (HND_PACKED) page tensors.
+
+    For 4-D tensors the layout is inferred as the patch does: NHD when the stride of axis 2
+    equals head_dim, else HND (reference: patches/vllm/kvx.patch:132-135, :222-229).
+    """
+    if key_cache.shape != value_cache.shape:
+        raise ValueError("key/value cache shape mismatch")
+    code = _cache_code(key_cache, kv_cache_dtype)
+    if key_cache.dim() == 5:
+        layout = abi.LAYOUT_HND_PACKED
+        nb, heads, dhi, bs, pack = key_cache.shape
+        dim = dhi * pack
+    else:
+        dim = key_cache.shape[3]
+        if layout is None:
+            layout = abi.LAYOUT_NHD if key_cache.stride(2) == dim else abi.LAYOUT_HND
+        if layout == abi.LAYOUT_NHD:
+            nb, bs, heads, _ = key_cache.shape
+        else:
+            nb, heads, bs, _ = key_cache.shape
+    c = abi.CacheDesc()
+    c.size = C.sizeof(abi.CacheDesc)
+    c.num_blocks, c.block_size, c.num_kv_heads, c.head_dim = nb, bs, heads, dim
+    c.k = abi.tensor_desc(key_cache.data_ptr(), code, key_cache.shape, key_cache.stride(), layout)
+    c.v = abi.tensor_desc(value_cache.data_ptr(), code, value_cache.shape, value_cache.stride(), layout)
+    c.pool.size = C.sizeof(abi.PoolDesc)
+    return c
+
+
+def _scale_desc(scale: Optional[torch.Tensor], heads: int) -> abi.ScaleDesc:
+    if scale is None:
+        return abi.scale_desc(None, abi.SCALE_NONE, heads)
+    if scale.dtype != torch.float32 or not scale.is_cuda:
+        raise TypeError("scales must be float32 CUDA tensors")
+    if scale.numel() == 1:
+        return abi.scale_desc(scale.data_ptr(), abi.SCALE_PER_TENSOR, heads)
+    if scale.dim() == 1 and scale.numel() == heads:
+        return abi.scale_desc(scale.data_ptr(), abi.SCALE_PER_HEAD, heads, scale.stride(0))
+    raise ValueError("a scale must have 1 or num_kv_heads elements")
+
+
+def reshape_and_cache_flash_kvx(key: torch.Tensor, value: torch.Tensor, key_cache: torch.Tensor,
+                                value_cache: torch.Tensor, slot_mapping: torch.Tensor,
+                                kv_cache_dtype: str = "auto", k_scale: Optional[torch.Tensor] = None,
+                                v_scale: Optional[torch.Tensor] = None,
+                                tokens_per_seq: Optional[int] = None) -> None:
+    """Scatter ``key`` / ``value`` ``[num_tokens, heads, dim]`` into the paged caches.
+
+    ``slot_mapping[t] = block * block_size + offset``; negative slots are padding and are
+    skipped.  ``kv_cache_dtype="auto"`` copies bits; ``"fp8"`` quantises to e4m3 with
+    ``k_scale`` / ``v_scale`` (1 or ``heads`` float32 values).  ``tokens_per_seq`` selects
+    the prefill entry point, whose result is identical.
+    """
+    if not (key.is_cuda and value.is_cuda and key_cache.is_cuda and value_cache.is_cuda):
+        raise ValueError("key/value and cache tensors must be CUDA tensors")
+    if key.dtype != value.dtype or key.dtype not in _FLOAT_CODES:
+        raise TypeError("key/value dtype mismatch or unsupported")
+    if key.dim() != 3 or value.shape != key.shape:
+        raise ValueError("key/value must be [num_tokens, num_heads, head_dim]")
+    if slot_mapping.dtype not in _INDEX_CODES or slot_mapping.dim() != 1:
+        raise TypeError("slot_mapping must be a 1-D int32 or int64 tensor")
+    num_tokens = slot_mapping.shape[0]
+    heads, dim = key.shape[1], key.shape[2]
+    cache = cache_desc_from_tensors(key_cache, value_cache, kv_cache_dtype)
+    w = abi.WriteDesc()
+    w.size = C.sizeof(abi.WriteDesc)
+    w.io.size = C.sizeof(abi.KvIoDesc)
+    w.io.num_tokens, w.io.num_kv_heads, w.io.head_dim = num_tokens, heads, dim
+    code = _FLOAT_CODES[key.dtype]
+    shape = (num_tokens, heads, dim)  # the patch sizes the batch by slot_mapping (kvx.patch:208)
+    w.io.key = abi.tensor_desc(key.data_ptr(), code, shape, key.stride(), abi.LAYOUT_INVALID)
+    w.io.value = abi.tensor_desc(value.data_ptr(), code, shape, value.stride(), abi.LAYOUT_INVALID)
+    w.slots.size = C.sizeof(abi.SlotMapping)
+    w.slots.dtype, w.slots.token_count = _INDEX_CODES[slot_mapping.dtype], num_tokens
+    w.slots.invalid_slot = -1
+    w.slots.slots = slot_mapping.data_ptr()
+    w.k_scale_desc = _scale_desc(k_scale, heads)
+    w.v_scale_desc = _scale_desc(v_scale, heads)
+    if tokens_per_seq is None:
+        status = lib().kvx_launch_write_kv(C.byref(cache), C.byref(w), _stream())
+    else:
+        status = lib().kvx_launch_write_kv_prefill(C.byref(cache), C.byref(w), int(tokens_per_seq), _stream())
+    if status != abi.STATUS_OK:
+        raise KvxError("kvx cache write", status)
+
+
+def gather_kv(key_cache: torch.Tensor, value_cache: torch.Tensor, block_table: torch.Tensor,
+              seq_lens: torch.Tensor, key_out: torch.Tensor, value_out: torch.Tensor,
+              kv_cache_dtype: str = "auto", k_scale: Optional[torch.Tensor] = None,
+              v_scale: Optional[torch.Tensor] = None) -> None:
+    """Materialise ``out[s, tok] = cache[block_table[s, tok // bs], tok % bs]`` for
+    ``tok < seq_lens[s]``; other positions of ``key_out`` / ``value_out`` stay untouched.
+
+    ``block_table`` is ``[seq_count, max_blocks_per_seq]`` (int32 or int64, same dtype as
+    ``seq_lens``); outputs are dense ``[seq_count, max_seq_len, heads, dim]``.
+    """
+    if block_table.dim() != 2 or not block_table.is_contiguous():
+        raise ValueError("block_table must be a contiguous [seq_count, max_blocks_per_seq] tensor")
+    if block_table.dtype not in _INDEX_CODES or seq_lens.dtype != block_table.dtype:
+        raise TypeError("block_table and seq_lens must share an int32 or int64 dtype")
+    if key_out.dim() != 4 or key_out.shape != value_out.shape or key_out.dtype not in _FLOAT_CODES:
+        raise ValueError("outputs must be [seq_count, max_seq_len, heads, dim] float tensors")
+    seqs, max_len, heads, dim = key_out.shape
+    cache = cache_desc_from_tensors(key_cache, value_cache, kv_cache_dtype)
+    g = abi.gather_desc(seqs, max_len, heads, dim, _FLOAT_CODES[key_out.dtype], key_out.data_ptr(),
+                        value_out.data_ptr(), _INDEX_CODES[block_table.dtype], block_table.data_ptr(),
+                        block_table.shape[1], seq_lens.data_ptr())
+    for t, src in ((g.io.key, key_out), (g.io.value, value_out)):
+        for i, s in enumerate(src.stride()):
+            t.stride[i] = s
+    g.block_table.seq_count = block_table.shape[0]
+    g.seq_lens.seq_count = seq_lens.shape[0]
+    if cache.k.dtype == abi.DTYPE_F8_E4M3:
+        ks, vs = _scale_desc(k_scale, heads), _scale_desc(v_scale, heads)
+        status = lib().kvx_launch_gather_kv_f8e4m3(C.byref(cache), C.byref(g), C.byref(ks), C.byref(vs), _stream())
+    else:
+        status = lib().kvx_launch_gather_kv(C.byref(cache), C.byref(g), _stream())
+    if status != abi.STATUS_OK:
+        raise KvxError("kvx cache gather", status)
+
+
+def scales_workspace(heads: int, device: torch.device) -> torch.Tensor:
+    """Zeroed scratch for :func:`compute_kv_scales`; reusable across calls on one stream."""
+    n = lib().kvx_kv_scales_workspace_bytes(heads)
+    return torch.zeros(n, dtype=torch.uint8, device=device)
+
+
+def compute_kv_scales(key: torch.Tensor, value: torch.Tensor, per_head: bool = True,
+                      workspace: Optional[torch.Tensor] = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """``absmax / 448`` of K and of V per head (or per tensor), as float32 CUDA tensors."""
+    if key.dim() != 3 or key.shape != value.shape or key.dtype != value.dtype:
+        raise ValueError("key/value must be matching [num_tokens, heads, dim] tensors")
+    tokens, heads, dim = key.shape
+    n = heads if per_head else 1
+    k_out = torch.empty(n, dtype=torch.float32, device=key.device)
+    v_out = torch.empty(n, dtype=torch.float32, device=key.device)
+    if workspace is None:
+        workspace = scales_workspace(heads, key.device)
+    io = abi.KvIoDesc()
+    io.size = C.sizeof(abi.KvIoDesc)
+    io.num_tokens, io.num_kv_heads, io.head_dim = tokens, heads, dim
+    code = _FLOAT_CODES[key.dtype]
+    io.key = abi.tensor_desc(key.data_ptr(), code, key.shape, key.stride(), abi.LAYOUT_INVALID)
+    io.value = abi.tensor_desc(value.data_ptr(), code, value.shape, value.stride(), abi.LAYOUT_INVALID)
+    status = lib().kvx_launch_kv_scales(C.byref(io), abi.SCALE_PER_HEAD if per_head else abi.SCALE_PER_TENSOR,
+                                        k_out.data_ptr(), v_out.data_ptr(), workspace.data_ptr(),
+                                        workspace.numel(), _stream())
+    if status != abi.STATUS_OK:
+        raise KvxError("kvx scale reduction", status)
+    return k_out, v_out
