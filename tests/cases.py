@@ -1,0 +1,164 @@
+"""Seeded builders of write/gather cases for the parity tests."""
+from __future__ import annotations
+
+import numpy as np
+
+from kvx_b200 import abi
+
+from harness import NP_OF, Case, canonical_strides, extent, f32_to_bits, random_bits
+
+SENTINEL = {1: 0xA5, 2: 0xA5C3, 4: 0xA5C3F00D}
+
+
+def sentinel_fill(n: int, code: int) -> np.ndarray:
+    dt = NP_OF[code]
+    return np.full(n, SENTINEL[np.dtype(dt).itemsize], dtype=dt)
+
+
+def make_case(seed: int, *, layout=abi.LAYOUT_NHD, dtype=abi.DTYPE_BF16, num_blocks=8, block_size=4,
+              heads=2, dim=8, pack=1, seqs=2, lens=None, max_seq_len=None, max_blocks=None,
+              slot_dtype=np.int64, index_dtype=np.int32, pad_frac=0.0, oob_slots=0, bad_blocks=0,
+              stride_pad=None, real_values=False, cache_dtype=None, scale_gran=abi.SCALE_NONE,
+              write_all=True, tokens=None) -> Case:
+    """One case.  Sequences own disjoint pages drawn from a seeded permutation; the write
+    batch holds every token of every sequence (sequence-major) unless ``tokens`` caps it.
+
+    pad_frac    fraction of slots replaced by -1 (and a few by other negatives)
+    oob_slots   slots pointing past the pool (block >= num_blocks): must be skipped
+    bad_blocks  block-table entries replaced by -1 / >= num_blocks inside valid ranges
+    stride_pad  (blk, tok, head) extra elements added to those strides (non-canonical pool)
+    """
+    rng = np.random.default_rng(seed)
+    geom = abi.CacheGeometry(num_blocks, block_size, heads, dim, layout, pack)
+    cache_dtype = dtype if cache_dtype is None else cache_dtype
+    if lens is None:
+        lens = [int(rng.integers(0, 3 * block_size + 1)) for _ in range(seqs)]
+    lens = list(lens)
+    seqs = len(lens)
+    need = [-(-n // block_size) for n in lens]
+    if max_blocks is None:
+        max_blocks = max(1, max(need, default=1))
+    if max_seq_len is None:
+        max_seq_len = max(1, max(lens, default=1))
+    assert sum(need) <= num_blocks, "pool too small"
+    perm = rng.permutation(num_blocks)
+    table = np.full((seqs, max_blocks), -1, dtype=index_dtype)
+    slots, p = [], 0
+    for s, n in enumerate(lens):
+        for lb in range(need[s]):
+            if lb < max_blocks:
+                table[s, lb] = perm[p]
+            for o in range(min(block_size, n - lb * block_size)):
+                slots.append(int(perm[p]) * block_size + o)
+            p += 1
+    slots = np.array(slots, dtype=np.int64)
+    if tokens is not None:
+        slots = slots[:tokens]
+    T = slots.shape[0]
+    if pad_frac > 0 and T:
+        mask = rng.random(T) < pad_frac
+        slots[mask] = -1
+        neg = np.flatnonzero(mask)[:2]
+        slots[neg] = [-7, -(2 ** 40)][: len(neg)] if slot_dtype == np.int64 else [-7, -12345][: len(neg)]
+    for i in range(min(oob_slots, T)):
+        slots[(i * 7919) % T] = num_blocks * block_size + i * block_size + (i % block_size)
+    slots = slots.astype(slot_dtype)
+    for i in range(bad_blocks):
+        s = i % seqs
+        if need[s] > 0:
+            table[s, i % min(need[s], max_blocks)] = -1 if i % 2 == 0 else num_blocks + i
+
+    if real_values:
+        key = f32_to_bits(rng.standard_normal((T, heads, dim)).astype(np.float32), dtype)
+        value = f32_to_bits(rng.standard_normal((T, heads, dim)).astype(np.float32), dtype)
+    else:
+        key, value = random_bits(rng, (T, heads, dim), dtype), random_bits(rng, (T, heads, dim), dtype)
+
+    k_stride = v_stride = None
+    n_elems = geom.elems
+    if stride_pad is not None:
+        k_stride = _padded_strides(geom, stride_pad)
+        v_stride = _padded_strides(geom, tuple(2 * x for x in stride_pad))
+        n_k, n_v = extent(geom.shape, k_stride), extent(geom.shape, v_stride)
+    else:
+        n_k = n_v = n_elems
+    case = Case(geom=geom, cache_dtype=cache_dtype, io_dtype=dtype, key=key, value=value, slots=slots,
+                cache_k=sentinel_fill(n_k, cache_dtype), cache_v=sentinel_fill(n_v, cache_dtype),
+                k_stride=k_stride, v_stride=v_stride, table=table,
+                lens=np.array(lens, dtype=index_dtype), max_seq_len=max_seq_len,
+                out_k=sentinel_fill(seqs * max_seq_len * heads * dim, dtype).reshape(seqs, max_seq_len, heads, dim),
+                out_v=sentinel_fill(seqs * max_seq_len * heads * dim, dtype).reshape(seqs, max_seq_len, heads, dim))
+    if cache_dtype == abi.DTYPE_F8_E4M3:
+        n = heads if scale_gran == abi.SCALE_PER_HEAD else 1
+        case.scale_gran = scale_gran
+        case.k_scale = (0.01 + rng.random(n) * 0.05).astype(np.float32)
+        case.v_scale = (0.01 + rng.random(n) * 0.05).astype(np.float32)
+    return case
+
+
+def _padded_strides(geom: abi.CacheGeometry, pad) -> list[int]:
+    """Strides of an NHD/HND pool whose head, token and block pitches are padded (multiples
+    given in elements), keeping dim contiguous."""
+    blk_pad, tok_pad, head_pad = pad
+    D, H, bs = geom.head_dim, geom.num_kv_heads, geom.block_size
+    if geom.layout == abi.LAYOUT_NHD:
+        s_head = D + head_pad
+        s_tok = H * s_head + tok_pad
+        s_blk = bs * s_tok + blk_pad
+        return [s_blk, s_tok, s_head, 1]
+    if geom.layout == abi.LAYOUT_HND:
+        s_tok = D + tok_pad
+        s_head = bs * s_tok + head_pad
+        s_blk = H * s_head + blk_pad
+        return [s_blk, s_head, s_tok, 1]
+    raise ValueError("padded strides: NHD / HND only")
+
+
+def expected_write_numpy(case: Case):
+    """Independent numpy statement of the canonical-stride write, used to cross-check the C
+    checker itself (follows the expected-value loops of the reference's kernel test,
+    tests/kvx_kernel_test.cu:264-301 for NHD and :415-446 for HND)."""
+    g = case.geom
+    assert case.k_stride is None and case.cache_dtype == case.io_dtype
+    k = case.cache_k.copy().reshape(g.shape)
+    v = case.cache_v.copy().reshape(g.shape)
+    for t, slot in enumerate(case.slots.tolist()):
+        if slot < 0:
+            continue
+        b, o = divmod(slot, g.block_size)
+        if b >= g.num_blocks:
+            continue
+        for dst, src in ((k, case.key), (v, case.value)):
+            if g.layout == abi.LAYOUT_NHD:
+                dst[b, o] = src[t]
+            elif g.layout == abi.LAYOUT_HND:
+                dst[b, :, o, :] = src[t]
+            else:
+                dst[b, :, :, o, :] = src[t].reshape(g.num_kv_heads, g.head_dim // g.pack, g.pack)
+    return k.reshape(-1), v.reshape(-1)
+
+
+def expected_gather_numpy(case: Case, cache_k: np.ndarray, cache_v: np.ndarray):
+    """Independent numpy statement of the gather (tests/kvx_kernel_test.cu:749-777)."""
+    g = case.geom
+    assert case.k_stride is None and case.cache_dtype == case.io_dtype
+    outs = []
+    for pool, out0 in ((cache_k, case.out_k), (cache_v, case.out_v)):
+        pool = pool.reshape(g.shape)
+        out = out0.copy()
+        for s in range(case.table.shape[0]):
+            for tok in range(min(int(case.lens[s]), case.max_seq_len)):
+                lb, o = divmod(tok, g.block_size)
+                if lb >= case.table.shape[1]:
+                    continue
+                b = int(case.table[s, lb])
+                if b < 0 or b >= g.num_blocks:
+                    continue
+                if g.layout == abi.LAYOUT_NHD:
+                    out[s, tok] = pool[b, o]
+                elif g.layout == abi.LAYOUT_HND:
+                    out[s, tok] = pool[b, :, o, :]
+                else:
+                    out[s, tok] = pool[b, :, :, o, :].reshape(g.num_kv_heads, g.head_dim)
+        outs.append(out)
+    return outs[0], outs[1]

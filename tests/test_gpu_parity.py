@@ -1,0 +1,203 @@
+"""Parity tests proper: the CUDA library, called through its C ABI on a B200, against the
+CPU checker on the same seeded inputs -- byte for byte, untouched bytes included."""
+import ctypes as C
+import dataclasses
+
+import numpy as np
+import pytest
+
+import kvx_b200
+from kvx_b200 import abi
+
+import cases
+from harness import (Case, device_buffers, descriptors, f32_to_bits, gpu_gather, gpu_write, oracle_gather,
+                     oracle_write)
+
+pytestmark = pytest.mark.gpu
+
+OK = abi.STATUS_OK
+DTYPES = [abi.DTYPE_F32, abi.DTYPE_F16, abi.DTYPE_BF16]
+LAYOUTS = [(abi.LAYOUT_NHD, 1), (abi.LAYOUT_HND, 1), (abi.LAYOUT_HND_PACKED, 4)]
+
+
+@pytest.fixture(autouse=True)
+def _defaults():
+    """Every test starts from the library's default tuning."""
+    saved = {n: kvx_b200.get_option(n) for n in ("gather_path", "force_generic", "write_unroll",
+                                                  "write_vecs_per_cta", "gather_part_bytes")}
+    yield
+    for n, v in saved.items():
+        kvx_b200.set_option(n, v)
+
+
+def check_write(case: Case, entry="dispatch", tps=1):
+    st, ek, ev = oracle_write(case)
+    assert st == OK
+    st, k, v = gpu_write(case, entry, tps)
+    assert st == OK, (entry, st)
+    assert np.array_equal(k, ek), f"K cache differs ({case.note}, {entry})"
+    assert np.array_equal(v, ev), f"V cache differs ({case.note}, {entry})"
+    return ek, ev
+
+
+def check_gather(case: Case, k, v, entry="dispatch"):
+    st, ek, ev = oracle_gather(case, k, v)
+    assert st == OK
+    st, gk, gv = gpu_gather(case, k, v, entry)
+    assert st == OK, (entry, st)
+    assert np.array_equal(gk, ek), f"K out differs ({case.note}, {entry})"
+    assert np.array_equal(gv, ev), f"V out differs ({case.note}, {entry})"
+
+
+# ------------------------------------------------------------------ reference's own cases -
+
+def _toy(dtype, heads, dim, tps, layout):
+    geom = abi.CacheGeometry(2, 4, heads, dim, layout)
+    n = 2 * tps * heads * dim
+    val = np.float32(0.1) + np.float32(0.01) * np.arange(n, dtype=np.float32)
+    key = f32_to_bits(val, dtype).reshape(-1, heads, dim)
+    value = f32_to_bits(val + np.float32(0.5), dtype).reshape(-1, heads, dim)
+    slots = np.array([s * 4 + (4 - tps) + t for s in range(2) for t in range(tps)], np.int64)
+    zeros = np.zeros(geom.elems, dtype=key.dtype)
+    return Case(geom=geom, cache_dtype=dtype, io_dtype=dtype, key=key, value=value, slots=slots,
+                cache_k=zeros.copy(), cache_v=zeros.copy(), note=f"toy h{heads} d{dim} tps{tps}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,dim,tps,layout", [
+    (2, 4, 1, abi.LAYOUT_NHD), (1, 7, 1, abi.LAYOUT_NHD), (2, 4, 2, abi.LAYOUT_NHD),
+    (2, 4, 1, abi.LAYOUT_HND), (1, 7, 2, abi.LAYOUT_HND)])
+def test_reference_write_cases(dtype, heads, dim, tps, layout):
+    """tests/kvx_kernel_test.cu:456-466 and :621-627, every entry point, exact."""
+    case = _toy(dtype, heads, dim, tps, layout)
+    for entry in ("dispatch", "typed", "prefill", "prefill_typed"):
+        check_write(case, entry, tps)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_reference_gather_case(dtype):
+    """tests/kvx_kernel_test.cu:629-786."""
+    geom = abi.CacheGeometry(2, 4, 2, 4)
+    val = np.float32(0.05) + np.float32(0.01) * np.arange(geom.elems, dtype=np.float32)
+    ck, cv = f32_to_bits(val, dtype), f32_to_bits(val + np.float32(0.5), dtype)
+    empty = np.zeros((0, 2, 4), ck.dtype)
+    out = np.zeros((2, 4, 2, 4), ck.dtype)
+    case = Case(geom=geom, cache_dtype=dtype, io_dtype=dtype, key=empty, value=empty,
+                slots=np.zeros(0, np.int64), cache_k=ck, cache_v=cv, table=np.array([[0], [1]], np.int32),
+                lens=np.array([4, 4], np.int32), max_seq_len=4, out_k=out.copy(), out_v=out.copy())
+    for entry in ("dispatch", "typed"):
+        check_gather(case, ck, cv, entry)
+
+
+# ------------------------------------------------------------------ the matrix ------------
+
+VARIANTS = [
+    dict(),
+    dict(pad_frac=0.3, slot_dtype=np.int32),
+    dict(oob_slots=3, bad_blocks=3, index_dtype=np.int64),
+    dict(lens=[0, 9, 4, 1], num_blocks=16),
+    dict(lens=[5, 12], max_seq_len=7, max_blocks=2),
+    dict(heads=1, dim=7, lens=[9, 2]),                       # odd head_dim -> generic tier
+    dict(heads=3, dim=24, block_size=5, lens=[11, 5, 0, 3], num_blocks=9),  # nothing is a power of two
+]
+
+
+@pytest.mark.parametrize("layout,pack", LAYOUTS)
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_matrix_small(layout, pack, dtype):
+    for i, kw in enumerate(VARIANTS):
+        if layout == abi.LAYOUT_HND_PACKED and kw.get("dim", 8) % pack:
+            continue
+        case = cases.make_case(200 + i, layout=layout, pack=pack, dtype=dtype, **kw)
+        case.note = f"variant {i}"
+        k, v = check_write(case)
+        check_write(case, "prefill", 1)
+        check_gather(case, k, v)
+
+
+@pytest.mark.parametrize("layout", [abi.LAYOUT_NHD, abi.LAYOUT_HND])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_vector_tier_shapes(layout, dtype):
+    """Shapes whose rows are whole 16-byte vectors: the vector tiers, ragged lengths,
+    padding, out-of-range ids, both index widths."""
+    for i, kw in enumerate([
+        dict(heads=8, dim=128, block_size=16, num_blocks=40, lens=[100, 17, 256, 1, 0, 33], pad_frac=0.1),
+        dict(heads=1, dim=128, block_size=16, num_blocks=40, lens=[64, 200], slot_dtype=np.int32, index_dtype=np.int64,
+             oob_slots=5, bad_blocks=4),
+        dict(heads=4, dim=64, block_size=32, num_blocks=20, lens=[31, 33, 160], pad_frac=0.5),
+        dict(heads=3, dim=40, block_size=6, num_blocks=50, lens=[7, 100, 13], pad_frac=0.05),
+        dict(heads=2, dim=8, block_size=4, num_blocks=64, lens=[50, 70], max_seq_len=40, max_blocks=9),
+    ]):
+        case = cases.make_case(300 + i, layout=layout, dtype=dtype, **kw)
+        case.note = f"vec {i}"
+        k, v = check_write(case)
+        check_gather(case, k, v)
+        kvx_b200.set_option("force_generic", 1)
+        check_write(case)
+        check_gather(case, k, v)
+        kvx_b200.set_option("force_generic", 0)
+
+
+@pytest.mark.parametrize("layout", [abi.LAYOUT_NHD, abi.LAYOUT_HND])
+def test_noncanonical_strides(layout):
+    """Padded block / token / head pitches (what views of a fused [blocks, 2, ...] allocation
+    look like): still the vector tier, K and V with different strides."""
+    for pad in ((16, 8, 8), (4096, 0, 0), (0, 8, 0), (3, 1, 1)):  # the last one is misaligned -> generic
+        case = cases.make_case(41, layout=layout, dtype=abi.DTYPE_BF16, heads=4, dim=64, block_size=8,
+                               num_blocks=12, lens=[20, 8, 31], pad_frac=0.1, stride_pad=pad)
+        case.note = f"pad {pad}"
+        k, v = check_write(case)
+        check_gather(case, k, v)
+
+
+def test_tuning_knobs_do_not_change_results():
+    case = cases.make_case(77, dtype=abi.DTYPE_BF16, heads=8, dim=128, block_size=16, num_blocks=80,
+                           lens=[300, 77, 512, 9], pad_frac=0.1)
+    _, ek, ev = oracle_write(case)
+    for unroll in (1, 2, 4):
+        for vecs in (128, 1024, 8192):
+            kvx_b200.set_option("write_unroll", unroll)
+            kvx_b200.set_option("write_vecs_per_cta", vecs)
+            check_write(case)
+    for part in (512, 4096, 65536):
+        kvx_b200.set_option("gather_part_bytes", part)
+        check_gather(case, ek, ev)
+
+
+def test_bulk_gather_path_matches():
+    """cp.async.bulk staging tier of the gather."""
+    kvx_b200.set_option("gather_path", 1)
+    for i, kw in enumerate([
+        dict(heads=8, dim=128, block_size=16, num_blocks=60, lens=[100, 17, 256, 1, 0, 333], bad_blocks=3),
+        dict(heads=2, dim=64, block_size=32, num_blocks=30, lens=[31, 33, 160], index_dtype=np.int64),
+        dict(heads=8, dim=128, block_size=32, num_blocks=12, lens=[300, 5]),  # chunk larger than a stage
+        dict(heads=1, dim=8, block_size=4, num_blocks=64, lens=[50, 70], max_seq_len=40, max_blocks=9),
+    ]):
+        case = cases.make_case(500 + i, dtype=abi.DTYPE_BF16, **kw)
+        _, k, v = oracle_write(case)
+        check_gather(case, k, v)
+
+
+def test_empty_and_degenerate_batches():
+    case = cases.make_case(3, dtype=abi.DTYPE_F16, heads=2, dim=64, lens=[0, 0], num_blocks=4)
+    assert case.T == 0
+    st, k, v = gpu_write(case)
+    assert st == OK and np.array_equal(k, case.cache_k) and np.array_equal(v, case.cache_v)
+    st, gk, gv = gpu_gather(case, k, v)
+    assert st == OK and np.array_equal(gk, case.out_k) and np.array_equal(gv, case.out_v)
+    # every slot padded
+    case = cases.make_case(4, dtype=abi.DTYPE_F16, heads=2, dim=64, lens=[9, 3], num_blocks=4, pad_frac=1.1)
+    st, k, v = gpu_write(case)
+    assert st == OK and np.array_equal(k, case.cache_k)
+
+
+def test_non_default_stream():
+    import torch
+    case = cases.make_case(8, dtype=abi.DTYPE_BF16, heads=4, dim=64, block_size=16, num_blocks=16, lens=[100, 50])
+    _, ek, ev = oracle_write(case)
+    s = torch.cuda.Stream()
+    st, k, v = gpu_write(case, stream=s.cuda_stream)
+    assert st == OK and np.array_equal(k, ek) and np.array_equal(v, ev)
+    _, eok, _ = oracle_gather(case, ek, ev)
+    st, gk, _ = gpu_gather(case, ek, ev, stream=s.cuda_stream)
+    assert st == OK and np.array_equal(gk, eok)
