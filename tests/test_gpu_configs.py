@@ -231,5 +231,10 @@ def test_config5_fp8_shape_with_outliers():
     check_gather(case, k, v)
     # dequantised values stay within half an e4m3 step of the input
     _, gk, _ = gpu_gather(case, k, v)
-    err = np.abs(bits_to_f32(gk.reshape(case.key.shape), abi.DTYPE_BF16) - bits_to_f32(case.key, abi.DTYPE_BF16))
-    assert float(err.max()) <= float(want.max()) * 32 + 1e-3
+    t = 0
+    for s, n in enumerate(case.lens.tolist()):
+        got = bits_to_f32(gk[s, :n], abi.DTYPE_BF16)
+        ref = bits_to_f32(case.key[t:t + n], abi.DTYPE_BF16)
+        # e4m3 keeps 3 mantissa bits: relative error <= 2^-4 (+ the subnormal step)
+        assert np.all(np.abs(got - ref) <= np.abs(ref) * 0.0625 + want[None, :, None] * 2.0 ** -9 * 1.01)
+        t += n
