@@ -1,0 +1,381 @@
+#!/usr/bin/env python
+"""Benchmark of the paged KV-cache write + gather hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--impl reference]
+
+One step = one pass of the hot path over the configuration: `layers` prefill writes (one per
+layer, each into its own page tensors) followed by `layers` full gathers.  Default workload
+is the Llama-3-8B prefill configuration (bf16, 8 KV heads x 128, block 16, 64 sequences of
+512..4096 tokens, ~10 % of slots = -1, pages drawn from a pool of up to 150 GB).  With N > 1
+(launched by torch.distributed.run, one process per GPU) the cache is sharded by KV head:
+rank r owns heads [r*8/N, (r+1)*8/N), index metadata is replicated, and no collective runs
+on the data path (one barrier + one max-reduction of the measured time).
+
+Prints ONE JSON line:  value = whole-job GB/s of algorithmic HBM bytes with inputs resident
+in HBM; e2e = the same metric through the host-buffer C-ABI entry points (pinned host K/V in,
+gathered K/V out, copies inside the timed region); roofline = dominant kernel against the
+measured HBM copy peak; cpu_baseline = the CPU restatement timed on this box's cores.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peak() -> tuple[float, str]:
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="kvx_b200", choices=["kvx_b200", "reference"])
+    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
+    ap.add_argument("--layers", type=int, default=None, help="override the configuration's layer count")
+    ap.add_argument("--pool-gb", type=float, default=None, help="cap the page pool (per device)")
+    ap.add_argument("--e2e-steps", type=int, default=None, help="steps of the host-buffer leg (default: min(steps, 3))")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-reference-kernels", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU baseline budget")
+    ap.add_argument("--option", action="append", default=[], help="tuning knob name=value")
+    return ap.parse_args()
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+# ------------------------------------------------------------------ CPU baseline ---------
+
+def cpu_baseline(spec, seconds: float, threads: int | None = None) -> dict:
+    """Times the CPU restatement (row memcpy per valid token, page-chunk memcpy per gathered
+    page, pthreads) on ONE layer of the configuration with a pool of twice the needed pages,
+    repeated until about `seconds` have passed.  This is test infrastructure timed as a
+    baseline; the product never calls it."""
+    import numpy as np
+    from kvx_b200 import abi, workloads
+    from kvx_b200.bench_support import DTYPE_CODE
+    from oracle.kvx_oracle import oracle
+
+    threads = threads or len(os.sched_getaffinity(0))
+    cpu_spec = spec
+    if spec.cache_dtype == "f8e4m3":
+        return {"value": None, "unit": "GB/s", "cores": threads, "kind": "port",
+                "sample": "not timed: the threaded CPU form covers the copy path only"}
+    meta = workloads.build_metadata(cpu_spec, num_blocks=None, pool_budget_bytes=0)  # pool = needed pages
+    meta = workloads.build_metadata(cpu_spec, num_blocks=2 * meta.gather_pages)
+    H, D, bs = spec.heads, spec.dim, spec.block_size
+    e = workloads.ELEM[spec.io_dtype]
+    rng = np.random.default_rng(7)
+    T, S, Lmax = meta.write_tokens, spec.seqs, meta.max_seq_len
+    np_t = np.uint16 if e == 2 else np.uint32
+    key = rng.integers(0, 65535, size=(T, H, D), dtype=np.uint16).astype(np_t) if e == 2 else rng.integers(0, 2 ** 32 - 1, size=(T, H, D), dtype=np.uint32)
+    value = key[::-1].copy()
+    geom = abi.CacheGeometry(meta.num_blocks, bs, H, D)
+    ck, cv = np.zeros(geom.elems, np_t), np.zeros(geom.elems, np_t)
+    ok_, ov_ = np.zeros((S, Lmax, H, D), np_t), np.zeros((S, Lmax, H, D), np_t)
+    code = DTYPE_CODE[spec.io_dtype]
+    cache = abi.cache_desc(geom, code, ck.ctypes.data, cv.ctypes.data, abi.MEMORY_HOST)
+    w = abi.write_desc(T, H, D, code, key.ctypes.data, value.ctypes.data, abi.DTYPE_S64, meta.slots.ctypes.data, abi.MEMORY_HOST)
+    g = abi.gather_desc(S, Lmax, H, D, code, ok_.ctypes.data, ov_.ctypes.data, abi.DTYPE_S32, meta.table.ctypes.data,
+                        meta.table.shape[1], meta.lens.ctypes.data, abi.MEMORY_HOST)
+    L = oracle()
+    for _ in range(1):  # warm-up: touches every page once
+        assert L.kvx_cpu_baseline_write_kv(C.byref(cache), C.byref(w), threads) == 0
+        assert L.kvx_cpu_baseline_gather_kv(C.byref(cache), C.byref(g), threads) == 0
+    reps, t_w, t_g = 0, 0.0, 0.0
+    t_end = time.perf_counter() + seconds
+    while reps < 3 or time.perf_counter() < t_end:
+        t0 = time.perf_counter(); L.kvx_cpu_baseline_write_kv(C.byref(cache), C.byref(w), threads)
+        t1 = time.perf_counter(); L.kvx_cpu_baseline_gather_kv(C.byref(cache), C.byref(g), threads)
+        t2 = time.perf_counter()
+        t_w += t1 - t0; t_g += t2 - t1; reps += 1
+        if reps >= 200:
+            break
+    wb, gb = meta.write_bytes(H), meta.gather_bytes(H)
+    return {"value": round((wb + gb) * reps / (t_w + t_g) / 1e9, 2), "unit": "GB/s", "cores": threads, "kind": "port",
+            "write_gbs": round(wb * reps / t_w / 1e9, 2), "gather_gbs": round(gb * reps / t_g / 1e9, 2),
+            "ms_per_layer": round((t_w + t_g) / reps * 1e3, 3),
+            "sample": f"1 of {spec.layers} layers (all {H} heads), {T} write tokens / {meta.gather_tokens} gathered, "
+                      f"pool = 2x needed pages in host RAM, {reps} repetitions; the reference has no CPU data "
+                      f"path, this is the CPU restatement of its kernels"}
+
+
+def reference_arm(args) -> None:
+    """`--impl reference`: the reference's hot path on this box's host cores.  The reference
+    moves data only in CUDA (its C entry points validate and return), so the CPU arm is the
+    CPU restatement of its kernels, all host threads, one layer of the workload per step."""
+    from kvx_b200 import workloads
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    spec = workloads.SPECS[args.workload]
+    threads = len(os.sched_getaffinity(0))
+    per_step = 1.0
+    t0 = time.perf_counter()
+    res = cpu_baseline(spec, seconds=max(2.0, min(60.0, per_step * (args.steps + args.warmup))), threads=threads)
+    line = {"impl": "reference", "metric": "kv_write_gather_hbm_gbs", "value": res["value"], "unit": "GB/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": res.get("ms_per_layer"), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+            "config": {"workload": spec.name, "layers_per_step": 1, "heads": spec.heads, "head_dim": spec.dim,
+                       "block_size": spec.block_size, "seqs": spec.seqs, "l2": "inputs larger than host caches"},
+            "cpu_baseline": res,
+            "e2e": {"value": res["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "wall_s": round(time.perf_counter() - t0, 1)}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------ GPU arm --------------
+
+def main() -> None:
+    args = parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+
+    import torch
+    import kvx_b200
+    from kvx_b200 import abi, bench_support as bs, workloads
+
+    rank, world, local = dist_env()
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    for opt in args.option:
+        name, val = opt.split("=")
+        kvx_b200.set_option(name, int(val))
+    L = kvx_b200.lib()
+    spec = workloads.SPECS[args.workload]
+    peak, peak_kind = measured_peak()
+
+    dw = bs.setup_device_workload(spec, rank, world, layers=args.layers, pool_gb=args.pool_gb)
+    layers, meta = dw.layers, dw.meta
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def step(events=None):
+        if events:
+            events[0].record()
+        for l in range(layers):
+            bs.launch_write(dw, l, stream)
+        if events:
+            events[1].record()
+        for l in range(layers):
+            bs.launch_gather(dw, l, stream)
+        if events:
+            events[2].record()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = bs.ClockSampler(local, period_ms=20)
+    sampler.start()  # sampled from the warm-up on: the timed region alone can be shorter than one period
+    for _ in range(max(args.warmup, 3)):
+        step()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    barrier()
+    launches0 = L.kvx_b200_launch_count()
+    for i in range(args.steps):
+        step(ev[i])
+    barrier()
+    launches = L.kvx_b200_launch_count() - launches0
+    clocks = sampler.stop()
+
+    total_ms = ev[0][0].elapsed_time(ev[-1][2])
+    write_ms = sum(e[0].elapsed_time(e[1]) for e in ev)
+    gather_ms = sum(e[1].elapsed_time(e[2]) for e in ev)
+    t = torch.tensor([total_ms, write_ms, gather_ms], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, write_ms, gather_ms = [float(x) for x in t.tolist()]
+
+    # ---- host-buffer leg (the call a user of the C ABI with host buffers makes) -------------
+    e2e = None
+    if not args.no_e2e:
+        e2e = run_e2e(args, dw, dist)
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    wb_all, gb_all = meta.write_bytes(spec.heads), meta.gather_bytes(spec.heads)  # all heads = all ranks
+    steps = args.steps
+    value = (wb_all + gb_all) * layers * steps / (total_ms * 1e-3) / 1e9
+    write_gbs_rank = dw.write_bytes * layers * steps / (write_ms * 1e-3) / 1e9
+    gather_gbs_rank = dw.gather_bytes * layers * steps / (gather_ms * 1e-3) / 1e9
+    dom, dom_gbs, dom_bytes, dom_ms = ("gather", gather_gbs_rank, dw.gather_bytes, gather_ms) \
+        if dw.gather_bytes >= dw.write_bytes else ("write", write_gbs_rank, dw.write_bytes, write_ms)
+    line = {
+        "metric": "kv_write_gather_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
+        "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": round(total_ms / steps, 4),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+        "config": {"workload": spec.name, "layers": layers, "heads_global": spec.heads, "heads_per_gpu": dw.heads,
+                   "head_dim": spec.dim, "block_size": spec.block_size, "seqs": spec.seqs,
+                   "write_tokens": meta.write_tokens, "valid_tokens": meta.valid_tokens,
+                   "gather_tokens": meta.gather_tokens, "pool_blocks_per_tensor": meta.num_blocks,
+                   "pool_gb_per_gpu": round(dw.pool.numel() / 1e9, 2), "parallelism": f"kv_head_shard{world}",
+                   "l2": "inputs (K+V batch, page pool) larger than L2; every layer has its own pages"},
+        "pct_of_nominal_8tbs": round(100 * value / world / NOMINAL_HBM_GBS, 1),
+        "write": {"gbs_per_gpu": round(write_gbs_rank, 1), "us_per_launch": round(write_ms * 1e3 / (layers * steps), 2),
+                  "tokens_per_s": round(meta.valid_tokens * layers * steps / (write_ms * 1e-3)),
+                  "frac_of_peak": round(write_gbs_rank / peak, 4)},
+        "gather": {"gbs_per_gpu": round(gather_gbs_rank, 1), "us_per_launch": round(gather_ms * 1e3 / (layers * steps), 2),
+                   "tokens_per_s": round(meta.gather_tokens * layers * steps / (gather_ms * 1e-3)),
+                   "frac_of_peak": round(gather_gbs_rank / peak, 4)},
+        "roofline": {"bound": "hbm", "kernel": dom, "achieved": round(dom_gbs, 1), "peak": peak, "unit": "GB/s",
+                     "frac": round(dom_gbs / peak, 4), "peak_kind": peak_kind,
+                     "bytes_per_launch": dom_bytes, "us_per_launch": round(dom_ms * 1e3 / (layers * steps), 2),
+                     "traffic": TRAFFIC_PER_LAUNCH.get((args.workload, dom, world))},
+        "gpu_launches": int(launches), "clocks": clocks,
+    }
+    if e2e is not None:
+        line["e2e"] = e2e
+    if world == 1 and not args.no_reference_kernels:
+        line["reference_kernels"] = time_reference_kernels(dw, peak)
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(spec, args.cpu_seconds)
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
+# captures summarised under profiles/ (bytes); filled in as captures are taken.
+TRAFFIC_PER_LAUNCH: dict = {}
+
+
+def run_e2e(args, dw, dist) -> dict:
+    """Same workload through kvx_host_write_kv / kvx_host_gather_kv: K/V batch, slots, block
+    table and lengths in pinned host memory, gathered K/V back to pinned host memory, every
+    step, copies inside the timed region."""
+    import torch
+    import kvx_b200
+    from kvx_b200 import abi, bench_support as bs
+    L = kvx_b200.lib()
+    meta, spec = dw.meta, dw.meta.spec
+    steps = args.e2e_steps or min(args.steps, 3)
+    hk = torch.empty(dw.key.shape, dtype=dw.key.dtype).pin_memory(); hk.copy_(dw.key)
+    hv = torch.empty(dw.value.shape, dtype=dw.value.dtype).pin_memory(); hv.copy_(dw.value)
+    hs = torch.from_numpy(meta.slots).pin_memory()
+    ht = torch.from_numpy(meta.table).pin_memory()
+    hl = torch.from_numpy(meta.lens).pin_memory()
+    hok = torch.empty(dw.out_k.shape, dtype=dw.out_k.dtype).pin_memory()
+    hov = torch.empty(dw.out_v.shape, dtype=dw.out_v.dtype).pin_memory()
+    seq_bytes = dw.out_k[0].numel() * dw.out_k.element_size()
+    chunk = max(64 << 20, seq_bytes)
+    pipe = C.c_void_p()
+    st = L.kvx_host_pipe_create(chunk, spec.seqs, meta.table.shape[1], C.byref(pipe))
+    if st != abi.STATUS_OK:
+        return {"value": None, "unit": "GB/s", "error": f"kvx_host_pipe_create status {st}"}
+    code = bs.DTYPE_CODE[spec.io_dtype]
+    w = abi.write_desc(meta.write_tokens, dw.heads, spec.dim, code, hk.data_ptr(), hv.data_ptr(), abi.DTYPE_S64,
+                       hs.data_ptr(), abi.MEMORY_HOST, dw.ks_desc, dw.vs_desc)
+    g = abi.gather_desc(spec.seqs, meta.max_seq_len, dw.heads, spec.dim, code, hok.data_ptr(), hov.data_ptr(),
+                        abi.DTYPE_S32, ht.data_ptr(), meta.table.shape[1], hl.data_ptr(), abi.MEMORY_HOST)
+    ks = C.byref(dw.ks_desc) if dw.ks_desc is not None else None
+    vs = C.byref(dw.vs_desc) if dw.vs_desc is not None else None
+
+    def step():
+        for l in range(dw.layers):
+            a = L.kvx_host_write_kv(pipe, C.byref(dw.caches[l]), C.byref(w))
+            b = L.kvx_host_gather_kv(pipe, C.byref(dw.caches[l]), C.byref(g), ks, vs)
+            if a != 0 or b != 0:
+                raise RuntimeError(f"host pipeline status write={a} gather={b}")
+        if L.kvx_host_pipe_sync(pipe) != 0:
+            raise RuntimeError("host pipeline failed")
+
+    step()  # warm-up
+    h0, d0 = C.c_uint64(), C.c_uint64()
+    L.kvx_host_pipe_traffic(pipe, C.byref(h0), C.byref(d0))
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    tt = torch.tensor([dt], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    dt = float(tt.item())
+    h1, d1 = C.c_uint64(), C.c_uint64()
+    L.kvx_host_pipe_traffic(pipe, C.byref(h1), C.byref(d1))
+    # the last layer's gathered bytes must equal what the device-resident path produces
+    check = bool(torch.equal(hok[0, : int(meta.lens[0])].cuda(), dw.out_k[0, : int(meta.lens[0])])) if dw.layers else True
+    L.kvx_host_pipe_destroy(pipe)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    bytes_all = (meta.write_bytes(spec.heads) + meta.gather_bytes(spec.heads)) * dw.layers * steps
+    return {"value": round(bytes_all / dt / 1e9, 2), "unit": "GB/s", "steps": steps,
+            "ms_per_step": round(dt / steps * 1e3, 2),
+            "h2d_bytes_per_step": int((h1.value - h0.value) // steps),
+            "d2h_bytes_per_step": int((d1.value - d0.value) // steps),
+            "pcie_gbs_per_gpu": round(((h1.value - h0.value) + (d1.value - d0.value)) / dt / 1e9, 2),
+            "matches_device_path": check, "n_gpus": world,
+            "api": "kvx_host_write_kv + kvx_host_gather_kv (pinned host buffers, staged in chunks)"}
+
+
+def time_reference_kernels(dw, peak: float) -> dict:
+    """The reference project's own CUDA kernels (compiled unmodified for sm_100a) on the same
+    device-resident inputs, a few layers, CUDA-event timed.  Context for the numbers above."""
+    import torch
+    from oracle.kvx_oracle import reference
+    try:
+        R = reference()
+    except Exception as exc:  # library missing or unloadable
+        return {"unavailable": str(exc)[:120]}
+    if R is None or dw.meta.spec.cache_dtype == "f8e4m3":
+        return {"unavailable": "oracle/_ref/libkvx_ref.so not present" if R is None else "no fp8 path in the reference"}
+    stream = torch.cuda.current_stream().cuda_stream
+    n = min(dw.layers, 4)
+    out = {}
+    for name, fn, desc, nbytes in (("write", R.kvx_launch_write_kv, dw.write, dw.write_bytes),
+                                   ("gather", R.kvx_launch_gather_kv, dw.gather, dw.gather_bytes)):
+        for l in range(n):
+            assert fn(C.byref(dw.caches[l]), C.byref(desc), stream) == 0
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(3):
+            for l in range(n):
+                fn(C.byref(dw.caches[l]), C.byref(desc), stream)
+        b.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) * 1e3 / (3 * n)
+        out[name] = {"us_per_launch": round(us, 2), "gbs": round(nbytes / us / 1e3, 1),
+                     "frac_of_peak": round(nbytes / us / 1e3 / peak, 4)}
+    return out
+
+
+if __name__ == "__main__":
+    main()

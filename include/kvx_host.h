@@ -1,0 +1,62 @@
+/*
+ * Host-buffer front end of the paged KV write / gather: K/V batches, slot mappings, block
+ * tables and gathered outputs live in HOST memory (ideally page-locked), the page pools
+ * live on the device.  A pipe owns the device staging buffers, streams and events needed
+ * to overlap host<->device copies with the kernels; nothing is allocated per call.
+ *
+ * The reference's kvx_write_kv / kvx_gather_kv (kvx_abi.h:194-199, kvx_abi.c:354-466)
+ * accept descriptors whose buffers are KVX_MEMORY_HOST -- its ABI test calls them on stack
+ * arrays (tests/kvx_abi_test.c:257-261, :284-295) -- but only validate them.  These entry
+ * points take the same descriptors and move the data.
+ */
+#ifndef KVX_HOST_H
+#define KVX_HOST_H
+
+#include "kvx_abi.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct kvx_host_pipe kvx_host_pipe_t;
+
+/* Creates a pipe on the current device.  `chunk_bytes` bounds one staged K (or V) chunk;
+ * three chunk sets are allocated (about 6 * chunk_bytes of device memory plus slots).
+ * `max_seqs * max_blocks_per_seq` bounds the block tables it can stage.
+ * OUT_OF_RANGE when device memory cannot be had. */
+KVX_API kvx_status_t kvx_host_pipe_create(size_t chunk_bytes, uint32_t max_seqs,
+                                          uint32_t max_blocks_per_seq, kvx_host_pipe_t **out_pipe);
+
+KVX_API void kvx_host_pipe_destroy(kvx_host_pipe_t *pipe);
+
+/* write->io.key/value.data and write->slots.slots are HOST pointers; cache->k/v.data are
+ * DEVICE pointers.  Tokens are staged chunk by chunk (host->device copy of chunk i+1
+ * overlaps the kernel of chunk i).  Asynchronous: returns once everything is enqueued; the
+ * host buffers must stay valid until kvx_host_pipe_sync.  Semantics and status codes are
+ * those of kvx_launch_write_kv. */
+KVX_API kvx_status_t kvx_host_write_kv(kvx_host_pipe_t *pipe, const kvx_cache_desc_t *cache,
+                                       const kvx_write_desc_t *write);
+
+/* gather->io.key/value.data, block_table.indices and seq_lens.lengths are HOST pointers.
+ * Sequences are gathered into device staging a group at a time and only the bytes the
+ * gather defines (positions below the sequence length whose page id is valid) are copied
+ * back, so every other byte of the host outputs stays untouched, as with
+ * kvx_launch_gather_kv.  Ordered after earlier kvx_host_write_kv calls on the same pipe.
+ * k_scale / v_scale (host descriptors with DEVICE data) are needed for an fp8 cache only. */
+KVX_API kvx_status_t kvx_host_gather_kv(kvx_host_pipe_t *pipe, const kvx_cache_desc_t *cache,
+                                        const kvx_gather_desc_t *gather,
+                                        const kvx_scale_desc_t *k_scale,
+                                        const kvx_scale_desc_t *v_scale);
+
+/* Blocks until every copy and kernel enqueued through the pipe has finished.
+ * INTERNAL_ERROR if any of them failed. */
+KVX_API kvx_status_t kvx_host_pipe_sync(kvx_host_pipe_t *pipe);
+
+/* Bytes moved host->device and device->host through the pipe since creation. */
+KVX_API void kvx_host_pipe_traffic(const kvx_host_pipe_t *pipe, uint64_t *h2d_bytes,
+                                   uint64_t *d2h_bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KVX_HOST_H */

@@ -20,6 +20,8 @@ EXPORTS = [
     "kvx_launch_gather_kv_bf16", "kvx_launch_write_kv_f8e4m3", "kvx_launch_gather_kv_f8e4m3",
     "kvx_kv_scales_workspace_bytes", "kvx_launch_kv_scales", "kvx_b200_launch_count",
     "kvx_b200_reset_launch_count", "kvx_b200_set_option", "kvx_b200_get_option",
+    "kvx_host_pipe_create", "kvx_host_pipe_destroy", "kvx_host_write_kv", "kvx_host_gather_kv",
+    "kvx_host_pipe_sync", "kvx_host_pipe_traffic",
 ]
 
 
@@ -63,6 +65,15 @@ def lib() -> C.CDLL:
     L.kvx_b200_reset_launch_count.argtypes, L.kvx_b200_reset_launch_count.restype = [], None
     L.kvx_b200_set_option.argtypes, L.kvx_b200_set_option.restype = [C.c_char_p, C.c_int64], C.c_int
     L.kvx_b200_get_option.argtypes, L.kvx_b200_get_option.restype = [C.c_char_p], C.c_int64
+    L.kvx_host_pipe_create.argtypes = [C.c_size_t, C.c_uint32, C.c_uint32, P(C.c_void_p)]
+    L.kvx_host_pipe_create.restype = st
+    L.kvx_host_pipe_destroy.argtypes, L.kvx_host_pipe_destroy.restype = [C.c_void_p], None
+    L.kvx_host_write_kv.argtypes, L.kvx_host_write_kv.restype = [C.c_void_p, P(abi.CacheDesc), P(abi.WriteDesc)], st
+    L.kvx_host_gather_kv.argtypes = [C.c_void_p, P(abi.CacheDesc), P(abi.GatherDesc), P(abi.ScaleDesc), P(abi.ScaleDesc)]
+    L.kvx_host_gather_kv.restype = st
+    L.kvx_host_pipe_sync.argtypes, L.kvx_host_pipe_sync.restype = [C.c_void_p], st
+    L.kvx_host_pipe_traffic.argtypes = [C.c_void_p, P(C.c_uint64), P(C.c_uint64)]
+    L.kvx_host_pipe_traffic.restype = None
     _lib = L
     return L
 

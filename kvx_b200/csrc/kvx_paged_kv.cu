@@ -868,7 +868,7 @@ __global__ void __launch_bounds__(kGatherThreads) kvx_gather_f8_kernel(const Gat
 
 constexpr int kBulkMaxPipes = 8;
 constexpr int kBulkMaxStages = 8;
-constexpr uint32_t kBulkWaitLimit = 1u << 22;  // polls before a wait is abandoned
+constexpr uint64_t kBulkWaitNs = 1000000000ull;  // a wait on a copy is abandoned after one second
 
 __device__ __forceinline__ uint32_t smem_addr(const void *p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -880,21 +880,35 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes)
                : "memory");
 }
-// Bounded wait for the phase with the given parity; false = gave up.
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Wait for the phase with the given parity, for at most kBulkWaitNs of wall time (a copy that
+// has not landed after that long never will); false = gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
   const uint32_t a = smem_addr(bar);
-  for (uint32_t i = 0; i < kBulkWaitLimit; ++i) {
+  uint64_t deadline = 0;
+  for (uint32_t i = 0;; ++i) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(done)
         : "r"(a), "r"(parity)
         : "memory");
     if (done) return true;
+    if (i >= 64) {  // past the common latency: back off and watch the clock
+      __nanosleep(64);
+      const uint64_t now = global_timer_ns();
+      if (deadline == 0)
+        deadline = now + kBulkWaitNs;
+      else if (now > deadline)
+        return false;
+    }
   }
-  return false;
 }
 __device__ __forceinline__ void bulk_load(void *smem_dst, const void *gsrc, uint32_t bytes, uint64_t *bar) {
   asm volatile(
