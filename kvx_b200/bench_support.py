@@ -83,6 +83,10 @@ def setup_device_workload(spec: workloads.Spec, rank: int = 0, world: int = 1, l
     meta = workloads.build_metadata(spec, seed=seed, num_blocks=num_blocks,
                                     pool_budget_bytes=max(budget, 0) / scale_layers, shards=world)
     page_local = spec.block_size * heads * spec.dim * e_c
+    # A configuration whose pages for all layers cannot fit (the decode step's full contexts)
+    # runs on as many layers as do fit; the count is reported with the result.
+    while layers > 1 and 2 * layers * meta.num_blocks * page_local > budget:
+        layers -= 1
     pool_bytes = 2 * layers * meta.num_blocks * page_local
     if pool_bytes > budget + 1:
         raise RuntimeError(f"page pool of {pool_bytes / 1e9:.1f} GB does not fit ({budget / 1e9:.1f} GB available)")

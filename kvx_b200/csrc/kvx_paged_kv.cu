@@ -43,8 +43,9 @@ namespace {
 struct Options {
   int64_t write_vecs_per_cta = 1024;  // 16-byte vectors of K (and of V) one write CTA moves
   int64_t write_unroll = 4;           // vectors of K and of V in flight per thread (1,2,4)
-  int64_t gather_path = 0;            // 0 = register copy, 1 = cp.async.bulk staging
-  int64_t gather_ctas_per_sm = 4;     // persistent CTAs per SM (register path)
+  int64_t gather_path = 2;            // 0 = CTA-granular register copy, 1 = cp.async.bulk staging, 2 = warp-granular
+  int64_t gather_tile_bytes = 16384;  // bytes of K (and of V) one CTA moves per work item (path 0)
+  int64_t gather_ctas_per_sm = 8;     // CTAs launched per SM (register paths; 4 are resident)
   int64_t gather_part_bytes = 32768;  // largest span one warp copies per work item
   int64_t bulk_stage_bytes = 16384;   // bytes per shared-memory stage (bulk path)
   int64_t bulk_stages = 4;            // stages per pipe (bulk path)
@@ -64,6 +65,7 @@ const OptionName kOptionNames[] = {
     {"write_vecs_per_cta", &Options::write_vecs_per_cta},
     {"write_unroll", &Options::write_unroll},
     {"gather_path", &Options::gather_path},
+    {"gather_tile_bytes", &Options::gather_tile_bytes},
     {"gather_ctas_per_sm", &Options::gather_ctas_per_sm},
     {"gather_part_bytes", &Options::gather_part_bytes},
     {"bulk_stage_bytes", &Options::bulk_stage_bytes},
@@ -787,6 +789,91 @@ __global__ void __launch_bounds__(kGatherThreads) kvx_gather_pages_kernel(const 
         if (f < vend) store_stream(dst + static_cast<int64_t>(f) * 16, r[u]);
       }
     }
+  }
+}
+
+// CTA-granular variant: one work item = one part of a page chunk, K AND V, moved by the
+// whole CTA with kUnroll K loads + kUnroll V loads in flight per thread before the first
+// store (the same shape as one tile of the write kernel).  The next item's page id is
+// resolved before the current item is copied, so the lens -> table -> page dependency chain
+// never sits in front of the data loads.
+template <typename IdxT, bool kSeg, int kUnroll>
+__global__ void __launch_bounds__(kGatherThreads, 4) kvx_gather_tiles_kernel(const GatherPagesParams p) {
+  extern __shared__ int32_t s_prefix[];
+  __shared__ int32_t s_warp_tot[kGatherWarps];
+  int64_t chunks;
+  if (p.use_prefix)
+    chunks = build_page_prefix<IdxT>(p, s_prefix, s_warp_tot);
+  else
+    chunks = static_cast<int64_t>(p.s.seq_count) * p.s.max_blocks;
+  const int tid = threadIdx.x;
+  const int64_t items = chunks * p.parts;
+
+  auto resolve_item = [&](int64_t item, int *part) {
+    const int64_t c = item / p.parts;
+    *part = static_cast<int>(item - c * p.parts);
+    ChunkRef ref;
+    if (p.use_prefix) {
+      ref = find_chunk(s_prefix, p.s.seq_count, static_cast<int32_t>(c));
+    } else {
+      ref.seq = static_cast<int32_t>(c / p.s.max_blocks);
+      ref.lb = static_cast<int32_t>(c - static_cast<int64_t>(ref.seq) * p.s.max_blocks);
+    }
+    return resolve_chunk<IdxT>(p, ref.seq, ref.lb);
+  };
+
+  int64_t item = blockIdx.x;
+  if (item >= items) return;
+  int part = 0;
+  ChunkInfo cur = resolve_item(item, &part);
+  while (true) {
+    const int64_t next = item + gridDim.x;
+    int next_part = 0;
+    ChunkInfo nxt;
+    nxt.block = -1, nxt.tokens = 0, nxt.out_off = 0;
+    if (next < items) nxt = resolve_item(next, &next_part);
+
+    if (cur.block >= 0) {
+      const int nvec = cur.tokens * p.vpr;
+      const int vbeg = part * p.part_vecs;
+      const int vend = min(vbeg + p.part_vecs, nvec);
+      const char *ksrc = p.k_base + cur.block * p.k_blk;
+      const char *vsrc = p.v_base + cur.block * p.v_blk;
+      char *kdst = p.key_out + cur.out_off;
+      char *vdst = p.value_out + cur.out_off;
+      for (int f0 = vbeg + tid; f0 < vend; f0 += kGatherThreads * kUnroll) {
+        uint4 kr[kUnroll], vr[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          const int f = f0 + u * kGatherThreads;
+          if (f < vend) {
+            int64_t ko, vo;
+            if (kSeg) {
+              const int tok = div_by(f, p.vpr, p.vpr_shift);
+              const int v = f - tok * p.vpr;
+              const int h = div_by(v, p.vps, p.vps_shift);
+              const int64_t w = static_cast<int64_t>(v - h * p.vps) * 16;
+              ko = tok * p.k_tok + h * p.k_head + w;
+              vo = tok * p.v_tok + h * p.v_head + w;
+            } else {
+              ko = vo = static_cast<int64_t>(f) * 16;
+            }
+            kr[u] = load_stream(ksrc + ko);
+            vr[u] = load_stream(vsrc + vo);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          const int f = f0 + u * kGatherThreads;
+          if (f < vend) {
+            store_stream(kdst + static_cast<int64_t>(f) * 16, kr[u]);
+            store_stream(vdst + static_cast<int64_t>(f) * 16, vr[u]);
+          }
+        }
+      }
+    }
+    if (next >= items) break;
+    item = next, part = next_part, cur = nxt;
   }
 }
 
@@ -1523,18 +1610,44 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
 #undef KVX_F8_GATHER
       return finish_launch();
     }
-    if (s32) {
-      if (contiguous_pages)
-        kvx_gather_pages_kernel<int32_t, false, 8><<<ug, kGatherThreads, prefix_bytes, cs>>>(p);
-      else
-        kvx_gather_pages_kernel<int32_t, true, 8><<<ug, kGatherThreads, prefix_bytes, cs>>>(p);
-    } else {
-      if (contiguous_pages)
-        kvx_gather_pages_kernel<int64_t, false, 8><<<ug, kGatherThreads, prefix_bytes, cs>>>(p);
-      else
-        kvx_gather_pages_kernel<int64_t, true, 8><<<ug, kGatherThreads, prefix_bytes, cs>>>(p);
+    if (g_opt.gather_path == 2) {  // warp-granular items
+      if (s32) {
+        if (contiguous_pages)
+          kvx_gather_pages_kernel<int32_t, false, 8><<<ug, kGatherThreads, prefix_bytes, cs>>>(p);
+        else
+          kvx_gather_pages_kernel<int32_t, true, 8><<<ug, kGatherThreads, prefix_bytes, cs>>>(p);
+      } else {
+        if (contiguous_pages)
+          kvx_gather_pages_kernel<int64_t, false, 8><<<ug, kGatherThreads, prefix_bytes, cs>>>(p);
+        else
+          kvx_gather_pages_kernel<int64_t, true, 8><<<ug, kGatherThreads, prefix_bytes, cs>>>(p);
+      }
+      return finish_launch();
     }
-    return finish_launch();
+    // CTA-granular items (default): one item = K and V of one part.
+    {
+      int64_t tile_vecs = g_opt.gather_tile_bytes / 16;
+      if (tile_vecs < kGatherThreads) tile_vecs = kGatherThreads;
+      if (tile_vecs > chunk_vecs) tile_vecs = chunk_vecs;
+      p.part_vecs = static_cast<int32_t>(tile_vecs);
+      p.parts = static_cast<int32_t>((chunk_vecs + tile_vecs - 1) / tile_vecs);
+      const int64_t tile_items = S * gs.max_blocks * p.parts;
+      int64_t tgrid = static_cast<int64_t>(dev.sm_count) * (g_opt.gather_ctas_per_sm < 1 ? 1 : g_opt.gather_ctas_per_sm);
+      if (tgrid > tile_items) tgrid = tile_items;
+      const unsigned tg = static_cast<unsigned>(tgrid);
+      if (s32) {
+        if (contiguous_pages)
+          kvx_gather_tiles_kernel<int32_t, false, 4><<<tg, kGatherThreads, prefix_bytes, cs>>>(p);
+        else
+          kvx_gather_tiles_kernel<int32_t, true, 4><<<tg, kGatherThreads, prefix_bytes, cs>>>(p);
+      } else {
+        if (contiguous_pages)
+          kvx_gather_tiles_kernel<int64_t, false, 4><<<tg, kGatherThreads, prefix_bytes, cs>>>(p);
+        else
+          kvx_gather_tiles_kernel<int64_t, true, 4><<<tg, kGatherThreads, prefix_bytes, cs>>>(p);
+      }
+      return finish_launch();
+    }
   }
 
   // ---- generic tier ---------------------------------------------------------------------

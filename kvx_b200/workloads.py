@@ -36,17 +36,18 @@ class Spec:
     pool_bytes: float = 0.0    # K+V, all layers, all heads; 0 = twice the needed pages
     decode: bool = False       # write = one new token per sequence (at position len-1)
     outlier_frac: float = 0.0  # fraction of elements multiplied by 50 (fp8 config)
+    fixed_blocks: int = 0      # pool size in pages when the configuration states it
     index: int = 0
 
 
 SPECS = {
-    "c1": Spec("c1_tinyllama_1.1b", "f16", "f16", 22, 4, 64, 16, 8, 128, 128, index=1),
+    "c1": Spec("c1_tinyllama_1.1b", "f16", "f16", 22, 4, 64, 16, 8, 128, 128, fixed_blocks=512, index=1),
     "c2": Spec("c2_llama3_8b_prefill", "bf16", "bf16", 32, 8, 128, 16, 64, 512, 4096, pad_frac=0.10,
                pool_bytes=150e9, index=2),
     "c3": Spec("c3_decode_step", "bf16", "bf16", 32, 8, 128, 32, 512, 1, 32768, log_uniform=True, decode=True,
                index=3),
     "c4": Spec("c4_llama3_70b_head_sharded", "f16", "f16", 80, 8, 128, 16, 32, 8192, 8192, index=4),
-    "c5": Spec("c5_fp8_e4m3", "bf16", "f8e4m3", 1, 16, 256, 64, 128, 2048, 2048, outlier_frac=0.001, index=5),
+    "c5": Spec("c5_fp8_e4m3", "bf16", "f8e4m3", 4, 16, 256, 64, 128, 2048, 2048, outlier_frac=0.001, index=5),
 }
 
 ELEM = {"bf16": 2, "f16": 2, "f32": 4, "f8e4m3": 1}
@@ -99,6 +100,8 @@ def build_metadata(spec: Spec, seed: Optional[int] = None, num_blocks: Optional[
     bs = spec.block_size
     need = (lens.astype(np.int64) + bs - 1) // bs
     pages_needed = int(need.sum())
+    if num_blocks is None and spec.fixed_blocks:
+        num_blocks = spec.fixed_blocks
     if num_blocks is None:
         page_bytes_all_heads = bs * spec.heads * spec.dim * ELEM[spec.cache_dtype]
         pool = spec.pool_bytes if spec.pool_bytes > 0 else 2.0 * pages_needed * page_bytes_all_heads * 2 * spec.layers
