@@ -121,6 +121,27 @@ KVX_API kvx_status_t kvx_launch_kv_scales(const kvx_kv_io_desc_t *io,
                                           float *v_scale_out, void *workspace,
                                           size_t workspace_bytes, void *stream);
 
+/* The same reduction for callers that cannot hand over device scratch.  Serving engines that
+ * give every free byte of HBM to their page pool at start-up, or that forbid driver
+ * allocations on the request path because cudaMalloc / cudaFree synchronise the whole device,
+ * have nowhere to take a workspace from; for them the scratch lives inside the library, in a
+ * fixed device array sized for KVX_KV_SCALES_STATIC_MAX_HEADS heads (8 448 bytes held by every
+ * GPU that loads the library, until the process exits).
+ *   - io->num_kv_heads above the maximum returns KVX_STATUS_OUT_OF_RANGE and does nothing.
+ *   - No allocation of any kind happens here, on the device or through a library.
+ *   - The first call on each device looks up the array's device address (one runtime query,
+ *     cached per device); make that first call before any stream capture starts.
+ *   - All calls on one device share the one array.  It is cleared on `stream` before every
+ *     reduction, so calls issued one after the other are independent, but two calls whose
+ *     kernels overlap on the GPU (different streams, no ordering) race on it and produce
+ *     wrong scales: order them.
+ * Results are identical to kvx_launch_kv_scales.  No counterpart in the reference. */
+#define KVX_KV_SCALES_STATIC_MAX_HEADS 1024
+
+KVX_API kvx_status_t kvx_launch_kv_scales_static(const kvx_kv_io_desc_t *io,
+                                                 kvx_scale_granularity_t granularity,
+                                                 float *k_scale_out, float *v_scale_out, void *stream);
+
 /* ------------------------------------------------------------------ introspection ----
  * Number of kernels this library has launched in this process since load (or since the
  * last reset).  Lets a benchmark state how many of its timed launches were these kernels.

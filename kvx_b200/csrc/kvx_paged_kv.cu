@@ -1826,6 +1826,51 @@ KVX_API kvx_status_t kvx_launch_kv_scales(const kvx_kv_io_desc_t *io, kvx_scale_
   return finish_launch();
 }
 
+// ---------------------------------------------------------------- scales, no allocation --
+// Scratch for kvx_launch_kv_scales_static: the running maxima and the CTA ticket of the scale
+// reduction, sized for KVX_KV_SCALES_STATIC_MAX_HEADS heads.  It is part of the loaded module,
+// so every device that loads this library holds these 8 448 bytes until the process exits.
+constexpr size_t kScalesStaticWords = (2 * KVX_KV_SCALES_STATIC_MAX_HEADS + 1 + 63) / 64 * 64;  // whole 256-byte lines
+static __device__ __align__(256) uint32_t g_scales_static_scratch[kScalesStaticWords];
+
+namespace {
+// Device address of g_scales_static_scratch per device.  In host code the array's name is only
+// a handle for the runtime, never an address a kernel may use, so the address is asked for
+// once per device (with that device current) and cached.
+uint32_t *g_scales_static_ptr[64];
+std::atomic<int> g_scales_static_ready[64];
+}  // namespace
+
+KVX_API kvx_status_t kvx_launch_kv_scales_static(const kvx_kv_io_desc_t *io,
+                                                 kvx_scale_granularity_t granularity, float *k_scale_out,
+                                                 float *v_scale_out, void *stream) {
+  if (io == nullptr) return KVX_STATUS_INVALID_ARGUMENT;
+  if (io->size < sizeof(kvx_kv_io_desc_t)) return KVX_STATUS_INVALID_ARGUMENT;
+  if (io->num_kv_heads > KVX_KV_SCALES_STATIC_MAX_HEADS) return KVX_STATUS_OUT_OF_RANGE;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return KVX_STATUS_INTERNAL_ERROR;
+  if (g_scales_static_ready[dev].load(std::memory_order_acquire) == 0) {
+    void *addr = nullptr;
+    if (cudaGetSymbolAddress(&addr, g_scales_static_scratch) != cudaSuccess || addr == nullptr) {
+      cudaGetLastError();
+      return KVX_STATUS_INTERNAL_ERROR;
+    }
+    g_scales_static_ptr[dev] = static_cast<uint32_t *>(addr);
+    g_scales_static_ready[dev].store(1, std::memory_order_release);
+  }
+  uint32_t *scratch = g_scales_static_ptr[dev];
+  const size_t bytes = sizeof(uint32_t) * kScalesStaticWords;
+  // The array is shared by every call and keeps whatever the last one left; the reduction
+  // needs zeros, so clear the part it uses on the caller's stream first.
+  const size_t used = kvx_kv_scales_workspace_bytes(io->num_kv_heads);
+  if (cudaMemsetAsync(scratch, 0, used < bytes ? used : bytes, reinterpret_cast<cudaStream_t>(stream)) !=
+      cudaSuccess) {
+    cudaGetLastError();
+    return KVX_STATUS_INTERNAL_ERROR;
+  }
+  return kvx_launch_kv_scales(io, granularity, k_scale_out, v_scale_out, scratch, bytes, stream);
+}
+
 KVX_API uint64_t kvx_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 KVX_API void kvx_b200_reset_launch_count(void) { g_launches.store(0, std::memory_order_relaxed); }
 
