@@ -49,6 +49,7 @@ def parse_args():
     ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
     ap.add_argument("--layers", type=int, default=None, help="override the configuration's layer count")
     ap.add_argument("--pool-gb", type=float, default=None, help="cap the page pool (per device)")
+    ap.add_argument("--seqs", type=int, default=None, help="override the number of sequences (small profiling cases)")
     ap.add_argument("--e2e-steps", type=int, default=None, help="steps of the host-buffer leg (default: min(steps, 3))")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -167,12 +168,25 @@ def main() -> None:
     dist = None
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        # NCCL announces its version on stdout at start-up; stdout carries the one JSON line only.
+        sys.stdout.flush()
+        saved_fd = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            os.dup2(saved_fd, 1)
+            os.close(saved_fd)
     for opt in args.option:
         name, val = opt.split("=")
         kvx_b200.set_option(name, int(val))
     L = kvx_b200.lib()
     spec = workloads.SPECS[args.workload]
+    if args.seqs is not None:
+        import dataclasses
+        spec = dataclasses.replace(spec, seqs=args.seqs, name=f"{spec.name}_seqs{args.seqs}")
     peak, peak_kind = measured_peak()
 
     dw = bs.setup_device_workload(spec, rank, world, layers=args.layers, pool_gb=args.pool_gb)
