@@ -144,7 +144,28 @@ def reference_arm(args) -> None:
             "cpu_baseline": res,
             "e2e": {"value": res["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "wall_s": round(time.perf_counter() - t0, 1)}
+    if not args.no_reference_kernels:
+        line["reference_cuda"] = reference_cuda_column(args, spec)
     print(json.dumps(line), flush=True)
+
+
+def reference_cuda_column(args, spec) -> dict:
+    """Extra column of the reference arm: the reference project's own CUDA kernels (compiled
+    unmodified for sm_100a) on device-resident inputs of the same workload, a few layers,
+    CUDA-event timed.  Not the arm's headline value (that is the host-core run above)."""
+    try:
+        import torch
+        if not torch.cuda.is_available():
+            return {"unavailable": "no CUDA device"}
+        from kvx_b200 import bench_support as bs
+        torch.cuda.set_device(dist_env()[2])
+        dw = bs.setup_device_workload(spec, 0, 1, layers=min(spec.layers, 4), pool_gb=args.pool_gb)
+        res = time_reference_kernels(dw, measured_peak()[0])
+        del dw
+        torch.cuda.empty_cache()
+        return res
+    except Exception as exc:
+        return {"unavailable": repr(exc)[:160]}
 
 
 # ------------------------------------------------------------------ GPU arm --------------
@@ -274,8 +295,6 @@ def main() -> None:
     }
     if e2e is not None:
         line["e2e"] = e2e
-    if world == 1 and not args.no_reference_kernels:
-        line["reference_kernels"] = time_reference_kernels(dw, peak)
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(spec, args.cpu_seconds)
     print(json.dumps(line), flush=True)

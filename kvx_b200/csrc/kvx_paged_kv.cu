@@ -342,6 +342,36 @@ __device__ __forceinline__ uint32_t quant2(float lo, float hi, float scale) {
   return e4m3x2_from_f32(__fdiv_rn(lo, scale), __fdiv_rn(hi, scale));
 }
 
+// Division-free quantisation that is still bit-identical to the division.
+// The reference result is e4m3(RN(x / s)).  RN(x / s) itself is rebuilt from the correctly
+// rounded reciprocal r = RN(1 / s) with two residual corrections (Markstein): q0 = RN(x r) is
+// within 2 ulp of x / s, q1 = RN(q0 + r (x - s q0)) is a faithful rounding, and one more step
+// from a faithful start is the correctly rounded quotient.  The residuals are exact because
+// they are formed by fused multiply-adds.  Five float-pipe operations replace a division that
+// costs twice as many issue slots plus two trips through the conversion unit.
+//   * -0 would come out as +0, so the sign of x is copied onto the result.
+//   * +-inf, NaN and quotients beyond the f32 range turn into NaN inside the chain; a NaN
+//     anywhere in a vector sends that vector to the division route, which handles them.
+//   * a quotient too small for exact residuals is far below 2^-11 and rounds to zero anyway,
+//     provided the scale is within 2^-60 .. 2^60; other scales take the division route.
+__device__ __forceinline__ float fast_reciprocal(float s) {  // 0 = this scale must use the division
+  const bool ok = (s >= 8.673617379884035e-19f) && (s <= 1.152921504606847e18f);  // 2^-60 .. 2^60; NaN fails
+  return ok ? __frcp_rn(s) : 0.f;
+}
+__device__ __forceinline__ float quotient_rn(float x, float s, float r) {
+  const float q0 = __fmul_rn(x, r);
+  const float q1 = __fmaf_rn(__fmaf_rn(-s, q0, x), r, q0);
+  const float q2 = __fmaf_rn(__fmaf_rn(-s, q1, x), r, q1);
+  return __uint_as_float((__float_as_uint(q2) & 0x7FFFFFFFu) | (__float_as_uint(x) & 0x80000000u));
+}
+__device__ __forceinline__ uint32_t quant2_fast(float lo, float hi, float s, float r, float &nan_acc) {
+  const float qlo = quotient_rn(lo, s, r), qhi = quotient_rn(hi, s, r);
+  nan_acc = __fmaf_rn(qlo, 0.f, __fmaf_rn(qhi, 0.f, nan_acc));  // becomes NaN if either is inf or NaN
+  uint16_t c;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(c) : "f"(qhi), "f"(qlo));
+  return c;
+}
+
 // Two E4M3 bytes (bits 0-15) -> two f32, exact.
 __device__ __forceinline__ float2 e4m3x2_to_f32(uint32_t q) {
   uint32_t h2;
@@ -376,28 +406,56 @@ struct ElemTraits<F32> {
 };
 
 // 16 bytes of IO elements -> per_vec E4M3 bytes (8 or 4), packed little-endian.
-__device__ __forceinline__ uint2 quant_vec(const uint4 &x, float scale, BF16) {
+__device__ __forceinline__ void unpack_vec(const uint4 &x, float (&f)[8], BF16) {
   const uint32_t w[4] = {x.x, x.y, x.z, x.w};
-  uint32_t q[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-    q[i] = quant2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xFFFF0000u), scale);
-  return make_uint2(q[0] | (q[1] << 16), q[2] | (q[3] << 16));
-}
-__device__ __forceinline__ uint2 quant_vec(const uint4 &x, float scale, F16) {
-  const uint32_t w[4] = {x.x, x.y, x.z, x.w};
-  uint32_t q[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
-    q[i] = quant2(f.x, f.y, scale);
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
   }
+}
+__device__ __forceinline__ void unpack_vec(const uint4 &x, float (&f)[8], F16) {
+  const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ void unpack_vec(const uint4 &x, float (&f)[8], F32) {
+  f[0] = __uint_as_float(x.x), f[1] = __uint_as_float(x.y);
+  f[2] = __uint_as_float(x.z), f[3] = __uint_as_float(x.w);
+  f[4] = f[5] = f[6] = f[7] = 0.f;
+}
+
+// The IEEE-division route for one vector.  Kept out of line on purpose: it runs for a few
+// vectors in 10^4, and inlined it would be if-converted into the hot loop and issued (predicated
+// off) for every vector.
+template <typename IoT>
+__device__ __noinline__ uint2 quant_vec_exact(uint4 x, float scale) {
+  constexpr int kPairs = ElemTraits<IoT>::per_vec / 2;
+  float f[8];
+  unpack_vec(x, f, IoT{});
+  uint32_t q[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+  for (int i = 0; i < kPairs; ++i) q[i] = quant2(f[2 * i], f[2 * i + 1], scale);
   return make_uint2(q[0] | (q[1] << 16), q[2] | (q[3] << 16));
 }
-__device__ __forceinline__ uint2 quant_vec(const uint4 &x, float scale, F32) {
-  const uint32_t a = quant2(__uint_as_float(x.x), __uint_as_float(x.y), scale);
-  const uint32_t b = quant2(__uint_as_float(x.z), __uint_as_float(x.w), scale);
-  return make_uint2(a | (b << 16), 0u);
+
+// `r` = fast_reciprocal(scale), 0 when the scale rules the fast route out.
+template <typename IoT>
+__device__ __forceinline__ uint2 quant_vec(const uint4 &x, float scale, float r, IoT) {
+  constexpr int kPairs = ElemTraits<IoT>::per_vec / 2;
+  float f[8];
+  unpack_vec(x, f, IoT{});
+  uint32_t q[4] = {0u, 0u, 0u, 0u};
+  float nan_acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < kPairs; ++i) q[i] = quant2_fast(f[2 * i], f[2 * i + 1], scale, r, nan_acc);
+  if (nan_acc != nan_acc || r == 0.f)  // inf / NaN / out-of-range quotient somewhere, or an extreme scale
+    return quant_vec_exact<IoT>(x, scale);
+  return make_uint2(q[0] | (q[1] << 16), q[2] | (q[3] << 16));
 }
 
 // per_vec E4M3 bytes -> 16 bytes of IO elements.
@@ -437,10 +495,13 @@ struct ScaleView {
 
 // ------------------------------------------------------------------ write: fp8 vector --
 
+constexpr int kF8CachedHeads = 128;
+
 struct WriteF8Params {
   WriteRowsParams w;  // vpr / vps count 16-byte INPUT vectors; k_*/v_* strides are cache bytes
   ScaleView ks, vs;
-  int32_t dim;  // head_dim
+  int32_t dim;    // head_dim
+  int32_t heads;  // num_kv_heads
 };
 
 // Same token tiling as kvx_write_rows_kernel; each 16-byte input vector (8 or 4 elements,
@@ -451,9 +512,19 @@ __global__ void __launch_bounds__(kWriteThreads) kvx_write_f8_kernel(const Write
   const WriteRowsParams &p = q.w;
   __shared__ int64_t s_k[kMaxTokTile];
   __shared__ int64_t s_v[kMaxTokTile];
+  __shared__ float s_sk[kF8CachedHeads], s_sv[kF8CachedHeads];  // scale per head
+  __shared__ float s_rk[kF8CachedHeads], s_rv[kF8CachedHeads];  // fast_reciprocal per head
   const int tid = threadIdx.x;
   const int64_t tok0 = static_cast<int64_t>(blockIdx.x) * p.tok_tile;
   const int ntok = static_cast<int>(min(static_cast<int64_t>(p.tok_tile), p.num_tokens - tok0));
+  const bool cached = q.heads <= kF8CachedHeads;
+  if (cached) {
+    for (int h = tid; h < q.heads; h += kWriteThreads) {
+      const float a = __ldg(q.ks.base + h * q.ks.stride), b = __ldg(q.vs.base + h * q.vs.stride);
+      s_sk[h] = a, s_sv[h] = b;
+      s_rk[h] = fast_reciprocal(a), s_rv[h] = fast_reciprocal(b);
+    }
+  }
   if (tid < ntok) {
     const int64_t slot = static_cast<int64_t>(static_cast<const SlotT *>(p.slots)[tok0 + tid]);
     int64_t ko = -1, vo = -1;
@@ -499,10 +570,12 @@ __global__ void __launch_bounds__(kWriteThreads) kvx_write_f8_kernel(const Write
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       if (kd[u] >= 0) {
-        const float sk = __ldg(q.ks.base + hh[u] * q.ks.stride);
-        const float sv = __ldg(q.vs.base + hh[u] * q.vs.stride);
-        const uint2 a = quant_vec(kr[u], sk, IoT{});
-        const uint2 b = quant_vec(vr[u], sv, IoT{});
+        const float sk = cached ? s_sk[hh[u]] : __ldg(q.ks.base + hh[u] * q.ks.stride);
+        const float sv = cached ? s_sv[hh[u]] : __ldg(q.vs.base + hh[u] * q.vs.stride);
+        const float rk = cached ? s_rk[hh[u]] : fast_reciprocal(sk);
+        const float rv = cached ? s_rv[hh[u]] : fast_reciprocal(sv);
+        const uint2 a = quant_vec(kr[u], sk, rk, IoT{});
+        const uint2 b = quant_vec(vr[u], sv, rv, IoT{});
         if (kPer == 8) {
           *reinterpret_cast<uint2 *>(p.k_base + kd[u]) = a;
           *reinterpret_cast<uint2 *>(p.v_base + vd[u]) = b;
@@ -1383,7 +1456,7 @@ kvx_status_t write_impl(const kvx_cache_desc_t *cache, const kvx_write_desc_t *w
     const int grid = static_cast<int>((T + p.tok_tile - 1) / p.tok_tile);
     const int unroll = static_cast<int>(g_opt.write_unroll);
     if (fp8) {
-      WriteF8Params q{p, ks, vs, static_cast<int32_t>(D)};
+      WriteF8Params q{p, ks, vs, static_cast<int32_t>(D), static_cast<int32_t>(H)};
 #define KVX_F8_WRITE(IoT)                                                                  \
   do {                                                                                     \
     if (s32)                                                                               \

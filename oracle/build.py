@@ -59,6 +59,33 @@ def build_reference(force: bool = False) -> str | None:
     return REF_LIB
 
 
+def build_reference_programs(force: bool = False) -> dict:
+    """Compile the reference's own GPU test and micro-benchmark, unmodified, twice: linked
+    against the reference's kernels (``*_ref``) and against this repository's library
+    (``*_ours``).  Outputs go to _ref/ only.  Returns {name: path} of what exists."""
+    out = {}
+    tests_cu = os.path.join(REFERENCE_ROOT, "tests", "kvx_kernel_test.cu")
+    bench_cu = os.path.join(REFERENCE_ROOT, "benchmarks", "kvx_bench.cu")
+    ours = os.path.join(ROOT, "kvx_b200", "lib", "libkvx_b200.so")
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    have_src = os.path.exists(tests_cu) and os.path.exists(bench_cu) and os.path.exists(nvcc)
+    os.makedirs(REF_DIR, exist_ok=True)
+    for name, src, lib in (("kvx_kernel_test_ref", tests_cu, REF_LIB), ("kvx_kernel_test_ours", tests_cu, ours),
+                           ("kvx_bench_ref", bench_cu, REF_LIB), ("kvx_bench_ours", bench_cu, ours)):
+        exe = os.path.join(REF_DIR, name)
+        if have_src and os.path.exists(lib) and (force or _stale(exe, [src, lib])):
+            libdir, libname = os.path.dirname(lib), os.path.basename(lib)[3:-3]
+            inc = REFERENCE_ROOT if lib == REF_LIB else os.path.join(ROOT, "include")
+            subprocess.run([nvcc, "-std=c++17", "-O2", "-gencode", "arch=compute_100a,code=sm_100a", "-I" + inc, src, "-o", exe,
+                            "-L" + libdir, "-l" + libname, "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/" +
+                            os.path.relpath(libdir, REF_DIR)], check=True, stdout=subprocess.PIPE,
+                           stderr=subprocess.STDOUT)
+        if os.path.exists(exe):
+            out[name] = exe
+    return out
+
+
 if __name__ == "__main__":
     print(build_oracle(force="--force" in sys.argv))
     print(build_reference(force="--force" in sys.argv))
+    print(build_reference_programs(force="--force" in sys.argv))

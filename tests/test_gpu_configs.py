@@ -176,6 +176,41 @@ def test_fp8_quantise_every_bf16_value():
         check_gather(case, codes.copy(), codes[::-1].copy())
 
 
+def test_fp8_quantise_boundary_and_special_values_f32_io():
+    """f32 inputs built to sit on and next to every e4m3 rounding boundary after the
+    division (midpoints +- a few ulps, subnormal midpoints, +-448, +-464), plus infinities,
+    NaNs with arbitrary payloads, +-0 and denormals, at awkward scales."""
+    H, D = 2, 64
+    rng = np.random.default_rng(77)
+    codes = np.arange(0x7F, dtype=np.uint8)
+    import ml_dtypes
+    grid = codes.view(ml_dtypes.float8_e4m3fn).astype(np.float64)
+    mids = np.concatenate([(grid[:-1] + grid[1:]) / 2, [464.0, 448.0, 2.0 ** -10, 2.0 ** -11]])
+    for scales in ([1.0, 0.3], [0.0123, 7.7], [2.0 ** -30, 3e7]):
+        vals = []
+        for h, s in enumerate(scales):
+            base = (mids * s).astype(np.float32)
+            near = np.concatenate([np.nextafter(base, np.float32(np.inf)), np.nextafter(base, np.float32(-np.inf)), base,
+                                   base * np.float32(1 + 3e-7), base * np.float32(1 - 3e-7)])
+            near = np.concatenate([near, -near, [np.inf, -np.inf, 0.0, -0.0, 1e-45, -1e-45, 3e38]]).astype(np.float32)
+            vals.append(near)
+        n = max(len(v) for v in vals)
+        T = -(-n // D) + 2
+        x = rng.standard_normal((T, H, D)).astype(np.float32)
+        bits = x.view(np.uint32).copy()
+        for h, v in enumerate(vals):
+            flat = bits[:, h, :].reshape(-1)
+            flat[: len(v)] = v.view(np.uint32)
+            flat[len(v): len(v) + 4] = [0x7FC00000, 0xFFC00001, 0x7F800001, 0xFFFFFFFF]  # NaNs
+            bits[:, h, :] = flat.reshape(T, D)
+        case = cases.make_case(9, dtype=abi.DTYPE_F32, cache_dtype=abi.DTYPE_F8_E4M3, heads=H, dim=D, block_size=16,
+                               num_blocks=T // 16 + 1, lens=[T], scale_gran=abi.SCALE_PER_HEAD)
+        case.key, case.value = bits.copy(), bits[::-1].copy()
+        case.k_scale = np.array(scales, np.float32)
+        case.v_scale = np.array(scales[::-1], np.float32)
+        check_write(case)
+
+
 @pytest.mark.parametrize("io", [abi.DTYPE_BF16, abi.DTYPE_F16, abi.DTYPE_F32])
 @pytest.mark.parametrize("gran", [abi.SCALE_PER_HEAD, abi.SCALE_PER_TENSOR])
 def test_scales_kernel_matches_oracle(io, gran):
