@@ -304,7 +304,12 @@ def main() -> None:
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
 # captures summarised under profiles/ (bytes); filled in as captures are taken.
-TRAFFIC_PER_LAUNCH: dict = {}
+TRAFFIC_PER_LAUNCH: dict = {
+    # profiles/gather_write_c2_ncu_full.md: kvx_gather_pages_kernel, c2 token counts (2-layer case,
+    # same tokens per launch): 582.1 MB read + 534.2 MB written (the rest still dirty in L2)
+    ("c2", "gather", 1): 1_116_300_000,
+    ("c2", "write", 1): 999_200_000,
+}
 
 
 def run_e2e(args, dw, dist) -> dict:
