@@ -53,6 +53,7 @@ struct Options {
   int64_t bulk_lag = 2;               // loads a pipe keeps in flight ahead of its stores
   int64_t bulk_ctas_per_sm = 1;
   int64_t force_generic = 0;          // 1 = always take the one-element-per-thread tier
+  int64_t pdl = 1;                    // 1 = launch with programmatic stream serialization
 };
 Options g_opt;
 std::atomic<uint64_t> g_launches{0};
@@ -74,6 +75,7 @@ const OptionName kOptionNames[] = {
     {"bulk_lag", &Options::bulk_lag},
     {"bulk_ctas_per_sm", &Options::bulk_ctas_per_sm},
     {"force_generic", &Options::force_generic},
+    {"pdl", &Options::pdl},
 };
 
 // Per-device facts, looked up once (never per launch).
@@ -200,6 +202,17 @@ __device__ __forceinline__ void store_stream(void *p, const uint4 &r) {
                : "memory");
 }
 
+// Programmatic dependent launch.  Every streaming kernel starts with pdl_prologue(): it lets
+// the NEXT kernel in the stream begin scheduling its CTAs while this one is still running,
+// then waits until everything that was enqueued BEFORE this kernel has completed and its
+// writes are visible.  No global memory is touched before that wait, so stream order is kept;
+// what is gained is the launch latency and CTA ramp-up between back-to-back per-layer calls
+// (a no-op when the kernel was launched without the attribute).
+__device__ __forceinline__ void pdl_prologue() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // n / d and n % d for a runtime d with a known power-of-two shift (or -1).
 __device__ __forceinline__ int div_by(int n, int d, int shift) {
   return shift >= 0 ? (n >> shift) : (n / d);
@@ -244,6 +257,7 @@ struct WriteRowsParams {
 //               head stride is not head_dim).
 template <typename SlotT, bool kSeg, int kUnroll>
 __global__ void __launch_bounds__(kWriteThreads) kvx_write_rows_kernel(const WriteRowsParams p) {
+  pdl_prologue();
   __shared__ int64_t s_k[kMaxTokTile];
   __shared__ int64_t s_v[kMaxTokTile];
   const int tid = threadIdx.x;
@@ -545,6 +559,7 @@ struct WriteF8Params {
 // all of one head) becomes 8 or 4 cache bytes.
 template <typename IoT, typename SlotT, int kUnroll>
 __global__ void __launch_bounds__(kWriteThreads) kvx_write_f8_kernel(const WriteF8Params q) {
+  pdl_prologue();
   constexpr int kPer = ElemTraits<IoT>::per_vec;
   const WriteRowsParams &p = q.w;
   __shared__ int64_t s_k[kMaxTokTile];
@@ -840,6 +855,7 @@ __device__ __forceinline__ ChunkInfo resolve_chunk(const GatherPagesParams &p, i
 //   kSeg = true  : per-head segments (HND pages or padded strides).
 template <typename IdxT, bool kSeg, int kUnroll>
 __global__ void __launch_bounds__(kGatherThreads) kvx_gather_pages_kernel(const GatherPagesParams p) {
+  pdl_prologue();
   extern __shared__ int32_t s_prefix[];
   __shared__ int32_t s_warp_tot[kGatherWarps];
   int64_t chunks;
@@ -909,6 +925,7 @@ __global__ void __launch_bounds__(kGatherThreads) kvx_gather_pages_kernel(const 
 // never sits in front of the data loads.
 template <typename IdxT, bool kSeg, int kUnroll>
 __global__ void __launch_bounds__(kGatherThreads, 4) kvx_gather_tiles_kernel(const GatherPagesParams p) {
+  pdl_prologue();
   extern __shared__ int32_t s_prefix[];
   __shared__ int32_t s_warp_tot[kGatherWarps];
   int64_t chunks;
@@ -991,6 +1008,7 @@ __global__ void __launch_bounds__(kGatherThreads, 4) kvx_gather_tiles_kernel(con
 // one head) is produced from 8 or 4 cache bytes.
 template <typename IoT, typename IdxT, int kUnroll>
 __global__ void __launch_bounds__(kGatherThreads) kvx_gather_f8_kernel(const GatherPagesParams p) {
+  pdl_prologue();
   constexpr int kPer = ElemTraits<IoT>::per_vec;
   extern __shared__ int32_t s_prefix[];
   __shared__ int32_t s_warp_tot[kGatherWarps];
@@ -1365,16 +1383,33 @@ kvx_status_t finish_launch() {
   return cudaGetLastError() == cudaSuccess ? KVX_STATUS_OK : KVX_STATUS_INTERNAL_ERROR;
 }
 
+// Launch with (or without) the programmatic-stream-serialization attribute.
+template <typename Params>
+void launch_streaming(void (*kernel)(Params), unsigned grid, unsigned block, size_t smem, cudaStream_t st,
+                      const Params &p) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_opt.pdl ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
 // ------------------------------------------------------------------ host: write --------
 
 template <typename SlotT, bool kSeg>
 void launch_write_rows(const WriteRowsParams &p, int grid, int unroll, cudaStream_t st) {
   if (unroll >= 4)
-    kvx_write_rows_kernel<SlotT, kSeg, 4><<<grid, kWriteThreads, 0, st>>>(p);
+    launch_streaming(kvx_write_rows_kernel<SlotT, kSeg, 4>, grid, kWriteThreads, 0, st, p);
   else if (unroll >= 2)
-    kvx_write_rows_kernel<SlotT, kSeg, 2><<<grid, kWriteThreads, 0, st>>>(p);
+    launch_streaming(kvx_write_rows_kernel<SlotT, kSeg, 2>, grid, kWriteThreads, 0, st, p);
   else
-    kvx_write_rows_kernel<SlotT, kSeg, 1><<<grid, kWriteThreads, 0, st>>>(p);
+    launch_streaming(kvx_write_rows_kernel<SlotT, kSeg, 1>, grid, kWriteThreads, 0, st, p);
 }
 
 template <typename IoT, typename CacheT>
@@ -1497,9 +1532,9 @@ kvx_status_t write_impl(const kvx_cache_desc_t *cache, const kvx_write_desc_t *w
 #define KVX_F8_WRITE(IoT)                                                                  \
   do {                                                                                     \
     if (s32)                                                                               \
-      kvx_write_f8_kernel<IoT, int32_t, 2><<<grid, kWriteThreads, 0, cs>>>(q);             \
+      launch_streaming(kvx_write_f8_kernel<IoT, int32_t, 2>, grid, kWriteThreads, 0, cs, q);             \
     else                                                                                   \
-      kvx_write_f8_kernel<IoT, int64_t, 2><<<grid, kWriteThreads, 0, cs>>>(q);             \
+      launch_streaming(kvx_write_f8_kernel<IoT, int64_t, 2>, grid, kWriteThreads, 0, cs, q);             \
   } while (0)
       if (io_dtype == KVX_DTYPE_BF16)
         KVX_F8_WRITE(BF16);
@@ -1707,9 +1742,9 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
 #define KVX_F8_GATHER(IoT)                                                                     \
   do {                                                                                         \
     if (s32)                                                                                   \
-      kvx_gather_f8_kernel<IoT, int32_t, 4><<<ug, kGatherThreads, prefix_bytes, cs>>>(p);      \
+      launch_streaming(kvx_gather_f8_kernel<IoT, int32_t, 4>, ug, kGatherThreads, prefix_bytes, cs, p);      \
     else                                                                                       \
-      kvx_gather_f8_kernel<IoT, int64_t, 4><<<ug, kGatherThreads, prefix_bytes, cs>>>(p);      \
+      launch_streaming(kvx_gather_f8_kernel<IoT, int64_t, 4>, ug, kGatherThreads, prefix_bytes, cs, p);      \
   } while (0)
       if (io_dtype == KVX_DTYPE_BF16)
         KVX_F8_GATHER(BF16);
@@ -1723,14 +1758,14 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
     if (g_opt.gather_path == 2) {  // warp-granular items
       if (s32) {
         if (contiguous_pages)
-          kvx_gather_pages_kernel<int32_t, false, 8><<<ug, kGatherThreads, prefix_bytes, cs>>>(p);
+          launch_streaming(kvx_gather_pages_kernel<int32_t, false, 8>, ug, kGatherThreads, prefix_bytes, cs, p);
         else
-          kvx_gather_pages_kernel<int32_t, true, 8><<<ug, kGatherThreads, prefix_bytes, cs>>>(p);
+          launch_streaming(kvx_gather_pages_kernel<int32_t, true, 8>, ug, kGatherThreads, prefix_bytes, cs, p);
       } else {
         if (contiguous_pages)
-          kvx_gather_pages_kernel<int64_t, false, 8><<<ug, kGatherThreads, prefix_bytes, cs>>>(p);
+          launch_streaming(kvx_gather_pages_kernel<int64_t, false, 8>, ug, kGatherThreads, prefix_bytes, cs, p);
         else
-          kvx_gather_pages_kernel<int64_t, true, 8><<<ug, kGatherThreads, prefix_bytes, cs>>>(p);
+          launch_streaming(kvx_gather_pages_kernel<int64_t, true, 8>, ug, kGatherThreads, prefix_bytes, cs, p);
       }
       return finish_launch();
     }
@@ -1747,14 +1782,14 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
       const unsigned tg = static_cast<unsigned>(tgrid);
       if (s32) {
         if (contiguous_pages)
-          kvx_gather_tiles_kernel<int32_t, false, 4><<<tg, kGatherThreads, prefix_bytes, cs>>>(p);
+          launch_streaming(kvx_gather_tiles_kernel<int32_t, false, 4>, tg, kGatherThreads, prefix_bytes, cs, p);
         else
-          kvx_gather_tiles_kernel<int32_t, true, 4><<<tg, kGatherThreads, prefix_bytes, cs>>>(p);
+          launch_streaming(kvx_gather_tiles_kernel<int32_t, true, 4>, tg, kGatherThreads, prefix_bytes, cs, p);
       } else {
         if (contiguous_pages)
-          kvx_gather_tiles_kernel<int64_t, false, 4><<<tg, kGatherThreads, prefix_bytes, cs>>>(p);
+          launch_streaming(kvx_gather_tiles_kernel<int64_t, false, 4>, tg, kGatherThreads, prefix_bytes, cs, p);
         else
-          kvx_gather_tiles_kernel<int64_t, true, 4><<<tg, kGatherThreads, prefix_bytes, cs>>>(p);
+          launch_streaming(kvx_gather_tiles_kernel<int64_t, true, 4>, tg, kGatherThreads, prefix_bytes, cs, p);
       }
       return finish_launch();
     }
