@@ -21,7 +21,8 @@ extern "C" {
 typedef struct kvx_host_pipe kvx_host_pipe_t;
 
 /* Creates a pipe on the current device.  `chunk_bytes` bounds one staged K (or V) chunk;
- * three chunk sets are allocated (about 6 * chunk_bytes of device memory plus slots).
+ * two rings of three chunk sets are allocated, one for writes and one for gathers (about
+ * 12 * chunk_bytes of device memory plus slots).
  * `max_seqs * max_blocks_per_seq` bounds the block tables it can stage.
  * OUT_OF_RANGE when device memory cannot be had. */
 KVX_API kvx_status_t kvx_host_pipe_create(size_t chunk_bytes, uint32_t max_seqs,

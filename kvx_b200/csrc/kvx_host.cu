@@ -15,7 +15,8 @@
 
 namespace {
 
-constexpr int kSets = 3;  // staging sets in rotation
+constexpr int kSets = 3;   // staging sets in rotation, per ring
+constexpr int kRings = 2;  // ring 0 stages write batches, ring 1 stages gathered sequences
 
 int64_t elem_bytes(kvx_dtype_t t) {
   switch (t) {
@@ -42,18 +43,20 @@ struct kvx_host_pipe {
   size_t chunk_bytes = 0;
   size_t table_cap = 0;  // index entries
   uint32_t max_seqs = 0;
-  char *k_stage[kSets] = {};
-  char *v_stage[kSets] = {};
+  // Writes and gathers use separate rings so that host->device copies of the next write never
+  // wait for device->host copies of the previous gather: both PCIe directions stay busy.
+  char *k_stage[kRings * kSets] = {};
+  char *v_stage[kRings * kSets] = {};
   char *slot_stage[kSets] = {};
   size_t slot_cap = 0;  // bytes per slot staging buffer
   char *table_dev = nullptr;
   char *lens_dev = nullptr;
   cudaStream_t h2d = nullptr, exec = nullptr, d2h = nullptr;
-  cudaEvent_t ready[kSets] = {};  // staging set filled (h2d) / gathered (exec)
-  cudaEvent_t freed[kSets] = {};  // staging set consumed (exec) / copied back (d2h)
+  cudaEvent_t ready[kRings * kSets] = {};  // staging set filled (h2d) / gathered (exec)
+  cudaEvent_t freed[kRings * kSets] = {};  // staging set consumed (exec) / copied back (d2h)
   cudaEvent_t meta_done = nullptr;   // kernels of the last gather are done with table_dev / lens_dev
   cudaEvent_t meta_ready = nullptr;  // table_dev / lens_dev hold the current call's metadata
-  uint64_t uses = 0;  // staging sets handed out so far
+  uint64_t uses[kRings] = {};  // staging sets handed out so far, per ring
   uint64_t h2d_bytes = 0, d2h_bytes = 0;
   bool failed = false;
 };
@@ -67,10 +70,10 @@ bool ok(kvx_host_pipe *p, cudaError_t e) {
 
 // Next staging set; the stream that will fill it first waits until its previous contents
 // were consumed.
-int acquire_set(kvx_host_pipe *p, cudaStream_t filler) {
-  const int s = static_cast<int>(p->uses % kSets);
-  if (p->uses >= kSets) ok(p, cudaStreamWaitEvent(filler, p->freed[s], 0));
-  ++p->uses;
+int acquire_set(kvx_host_pipe *p, int ring, cudaStream_t filler) {
+  const int s = ring * kSets + static_cast<int>(p->uses[ring] % kSets);
+  if (p->uses[ring] >= kSets) ok(p, cudaStreamWaitEvent(filler, p->freed[s], 0));
+  ++p->uses[ring];
   return s;
 }
 
@@ -89,10 +92,10 @@ KVX_API kvx_status_t kvx_host_pipe_create(size_t chunk_bytes, uint32_t max_seqs,
   p->table_cap = static_cast<size_t>(max_seqs) * max_blocks_per_seq;
   p->max_seqs = max_seqs;
   bool good = true;
-  for (int i = 0; i < kSets && good; ++i) {
+  for (int i = 0; i < kRings * kSets && good; ++i) {
     good = cudaMalloc(&p->k_stage[i], p->chunk_bytes) == cudaSuccess &&
            cudaMalloc(&p->v_stage[i], p->chunk_bytes) == cudaSuccess &&
-           cudaMalloc(&p->slot_stage[i], p->slot_cap) == cudaSuccess &&
+           (i >= kSets || cudaMalloc(&p->slot_stage[i], p->slot_cap) == cudaSuccess) &&
            cudaEventCreateWithFlags(&p->ready[i], cudaEventDisableTiming) == cudaSuccess &&
            cudaEventCreateWithFlags(&p->freed[i], cudaEventDisableTiming) == cudaSuccess;
   }
@@ -117,10 +120,10 @@ KVX_API void kvx_host_pipe_destroy(kvx_host_pipe_t *p) {
   if (p->h2d) cudaStreamSynchronize(p->h2d);
   if (p->exec) cudaStreamSynchronize(p->exec);
   if (p->d2h) cudaStreamSynchronize(p->d2h);
-  for (int i = 0; i < kSets; ++i) {
+  for (int i = 0; i < kRings * kSets; ++i) {
     cudaFree(p->k_stage[i]);
     cudaFree(p->v_stage[i]);
-    cudaFree(p->slot_stage[i]);
+    if (i < kSets) cudaFree(p->slot_stage[i]);
     if (p->ready[i]) cudaEventDestroy(p->ready[i]);
     if (p->freed[i]) cudaEventDestroy(p->freed[i]);
   }
@@ -150,7 +153,7 @@ KVX_API kvx_status_t kvx_host_write_kv(kvx_host_pipe_t *p, const kvx_cache_desc_
 
   for (int64_t t0 = 0; t0 < T; t0 += per_chunk) {
     const int64_t n = std::min(per_chunk, T - t0);
-    const int s = acquire_set(p, p->h2d);
+    const int s = acquire_set(p, 0, p->h2d);
     const char *hk = static_cast<const char *>(write->io.key.data) + t0 * row;
     const char *hv = static_cast<const char *>(write->io.value.data) + t0 * row;
     const char *hs = static_cast<const char *>(write->slots.slots) + t0 * slot_b;
@@ -217,7 +220,7 @@ KVX_API kvx_status_t kvx_host_gather_kv(kvx_host_pipe_t *p, const kvx_cache_desc
   kvx_status_t status = KVX_STATUS_OK;
   for (int64_t s0 = 0; s0 < S && status == KVX_STATUS_OK; s0 += per_chunk) {
     const int64_t n = std::min(per_chunk, S - s0);
-    const int set = acquire_set(p, p->exec);
+    const int set = acquire_set(p, 1, p->exec);
     kvx_gather_desc_t g = *gather;
     g.io.num_tokens = static_cast<uint32_t>(n * L);
     g.io.key.shape[0] = g.io.value.shape[0] = n;
