@@ -54,6 +54,7 @@ struct Options {
   int64_t bulk_ctas_per_sm = 1;
   int64_t force_generic = 0;          // 1 = always take the one-element-per-thread tier
   int64_t pdl = 1;                    // 1 = launch with programmatic stream serialization
+  int64_t wide = 1;                   // 1 = 256-bit accesses where alignment allows
 };
 Options g_opt;
 std::atomic<uint64_t> g_launches{0};
@@ -76,6 +77,7 @@ const OptionName kOptionNames[] = {
     {"bulk_ctas_per_sm", &Options::bulk_ctas_per_sm},
     {"force_generic", &Options::force_generic},
     {"pdl", &Options::pdl},
+    {"wide", &Options::wide},
 };
 
 // Per-device facts, looked up once (never per launch).
@@ -199,6 +201,25 @@ __device__ __forceinline__ uint4 load_stream(const void *p) {
 __device__ __forceinline__ void store_stream(void *p, const uint4 &r) {
   asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(r.x), "r"(r.y), "r"(r.z),
                "r"(r.w)
+               : "memory");
+}
+
+// 256-bit global accesses (sm_100): half the memory instructions of the 128-bit form for the
+// same bytes; addresses must be 32-byte aligned.
+struct Vec32 {
+  uint32_t w[8];
+};
+__device__ __forceinline__ Vec32 load_stream32(const void *p) {
+  Vec32 r;
+  asm volatile("ld.global.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r.w[0]), "=r"(r.w[1]), "=r"(r.w[2]), "=r"(r.w[3]), "=r"(r.w[4]), "=r"(r.w[5]), "=r"(r.w[6]),
+                 "=r"(r.w[7])
+               : "l"(p));
+  return r;
+}
+__device__ __forceinline__ void store_stream32(void *p, const Vec32 &r) {
+  asm volatile("st.global.cs.v8.u32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(r.w[0]), "r"(r.w[1]),
+               "r"(r.w[2]), "r"(r.w[3]), "r"(r.w[4]), "r"(r.w[5]), "r"(r.w[6]), "r"(r.w[7])
                : "memory");
 }
 
@@ -913,6 +934,61 @@ __global__ void __launch_bounds__(kGatherThreads) kvx_gather_pages_kernel(const 
       for (int u = 0; u < kUnroll; ++u) {
         const int f = f0 + u * 32;
         if (f < vend) store_stream(dst + static_cast<int64_t>(f) * 16, r[u]);
+      }
+    }
+  }
+}
+
+// Warp-granular gather of contiguous page chunks with 256-bit accesses: identical work
+// decomposition to kvx_gather_pages_kernel<IdxT, false, *>, counted in 32-byte units.
+// Needs 32-byte aligned bases, block strides and rows, and an even part_vecs.
+template <typename IdxT, int kUnroll>
+__global__ void __launch_bounds__(kGatherThreads) kvx_gather_pages_wide_kernel(const GatherPagesParams p) {
+  pdl_prologue();
+  extern __shared__ int32_t s_prefix[];
+  __shared__ int32_t s_warp_tot[kGatherWarps];
+  int64_t chunks;
+  if (p.use_prefix)
+    chunks = build_page_prefix<IdxT>(p, s_prefix, s_warp_tot);
+  else
+    chunks = static_cast<int64_t>(p.s.seq_count) * p.s.max_blocks;
+
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = static_cast<int64_t>(blockIdx.x) * kGatherWarps + (threadIdx.x >> 5);
+  const int64_t warps = static_cast<int64_t>(gridDim.x) * kGatherWarps;
+  const int64_t items = chunks * p.parts * 2;
+  const int part_units = p.part_vecs >> 1, row_units = p.vpr >> 1;
+
+  for (int64_t item = warp; item < items; item += warps) {
+    const int kv = static_cast<int>(item & 1);
+    const int64_t rest = item >> 1;
+    const int64_t c = rest / p.parts;
+    const int part = static_cast<int>(rest - c * p.parts);
+    ChunkRef ref;
+    if (p.use_prefix) {
+      ref = find_chunk(s_prefix, p.s.seq_count, static_cast<int32_t>(c));
+    } else {
+      ref.seq = static_cast<int32_t>(c / p.s.max_blocks);
+      ref.lb = static_cast<int32_t>(c - static_cast<int64_t>(ref.seq) * p.s.max_blocks);
+    }
+    const ChunkInfo ci = resolve_chunk<IdxT>(p, ref.seq, ref.lb);
+    if (ci.block < 0) continue;
+    const int nunit = ci.tokens * row_units;
+    const int ubeg = part * part_units;
+    const int uend = min(ubeg + part_units, nunit);
+    const char *src = kv ? p.v_base + ci.block * p.v_blk : p.k_base + ci.block * p.k_blk;
+    char *dst = (kv ? p.value_out : p.key_out) + ci.out_off;
+    for (int f0 = ubeg + lane; f0 < uend; f0 += 32 * kUnroll) {
+      Vec32 r[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int f = f0 + u * 32;
+        if (f < uend) r[u] = load_stream32(src + static_cast<int64_t>(f) * 32);
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int f = f0 + u * 32;
+        if (f < uend) store_stream32(dst + static_cast<int64_t>(f) * 32, r[u]);
       }
     }
   }
@@ -1731,6 +1807,15 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
     int64_t part_vecs = g_opt.gather_part_bytes / 16;
     if (part_vecs < 32) part_vecs = 32;
     if (part_vecs > chunk_vecs) part_vecs = chunk_vecs;
+    // Small gathers: one warp moving a whole page serially would leave the machine idle, so
+    // shrink the parts (down to one unrolled iteration of a warp) until the padded
+    // (sequence, page) rectangle yields about two items per warp of the persistent grid.
+    {
+      const int64_t warps = static_cast<int64_t>(dev.sm_count) * kGatherWarps *
+                            (g_opt.gather_ctas_per_sm < 1 ? 1 : g_opt.gather_ctas_per_sm);
+      while (part_vecs > 256 && S * gs.max_blocks * ((chunk_vecs + part_vecs - 1) / part_vecs) * 2 < 2 * warps)
+        part_vecs = (part_vecs + 1) / 2;
+    }
     p.part_vecs = static_cast<int32_t>(part_vecs);
     p.parts = static_cast<int32_t>((chunk_vecs + part_vecs - 1) / part_vecs);
     const int64_t max_items = S * gs.max_blocks * p.parts * 2;
@@ -1756,6 +1841,16 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
       return finish_launch();
     }
     if (g_opt.gather_path == 2) {  // warp-granular items
+      const bool wide_ok = g_opt.wide && contiguous_pages && (p.part_vecs % 2) == 0 && (p.vpr % 2) == 0 &&
+                           aligned(p.k_base, 32) && aligned(p.v_base, 32) && aligned(p.key_out, 32) &&
+                           aligned(p.value_out, 32) && p.k_blk % 32 == 0 && p.v_blk % 32 == 0;
+      if (wide_ok) {
+        if (s32)
+          launch_streaming(kvx_gather_pages_wide_kernel<int32_t, 4>, ug, kGatherThreads, prefix_bytes, cs, p);
+        else
+          launch_streaming(kvx_gather_pages_wide_kernel<int64_t, 4>, ug, kGatherThreads, prefix_bytes, cs, p);
+        return finish_launch();
+      }
       if (s32) {
         if (contiguous_pages)
           launch_streaming(kvx_gather_pages_kernel<int32_t, false, 8>, ug, kGatherThreads, prefix_bytes, cs, p);

@@ -24,7 +24,7 @@ LAYOUTS = [(abi.LAYOUT_NHD, 1), (abi.LAYOUT_HND, 1), (abi.LAYOUT_HND_PACKED, 4)]
 def _defaults():
     """Every test starts from the library's default tuning."""
     saved = {n: kvx_b200.get_option(n) for n in ("gather_path", "force_generic", "write_unroll",
-                                                  "write_vecs_per_cta", "gather_part_bytes", "gather_tile_bytes")}
+                                                  "write_vecs_per_cta", "gather_part_bytes", "gather_tile_bytes", "wide", "pdl")}
     yield
     for n, v in saved.items():
         kvx_b200.set_option(n, v)
@@ -163,9 +163,14 @@ def test_tuning_knobs_do_not_change_results():
         kvx_b200.set_option("gather_tile_bytes", tile)
         check_gather(case, ek, ev)
     kvx_b200.set_option("gather_path", 2)  # warp-granular items
-    for part in (512, 4096, 65536):
-        kvx_b200.set_option("gather_part_bytes", part)
-        check_gather(case, ek, ev)
+    for wide in (0, 1):                    # 128-bit and 256-bit accesses
+        for pdl in (0, 1):                 # with and without programmatic dependent launch
+            kvx_b200.set_option("wide", wide)
+            kvx_b200.set_option("pdl", pdl)
+            for part in (512, 4096, 65536):
+                kvx_b200.set_option("gather_part_bytes", part)
+                check_gather(case, ek, ev)
+            check_write(case)
 
 
 def test_bulk_gather_path_matches():
