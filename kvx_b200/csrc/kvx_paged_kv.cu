@@ -496,10 +496,20 @@ __device__ __forceinline__ uint2 quant_vec(const uint4 &x, float scale, float r,
   return out;
 }
 
-// per_vec E4M3 bytes -> 16 bytes of IO elements, reference route: hardware e4m3 -> f16 -> f32
-// (exact), one multiply, one rounding to the IO type.
+// per_vec E4M3 bytes -> 16 bytes of IO elements: hardware e4m3x2 -> f16x2 (exact), widen to
+// f32, one multiply, one rounding to the IO type.  (Building the f32 directly from the byte
+// with integer operations was measured slower: it moves the work onto the integer pipe, which
+// then becomes the limiter.)
+__device__ __forceinline__ uint32_t pack2(float lo, float hi, BF16) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t *>(&v);
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi, F16) {
+  const __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t *>(&v);
+}
 template <typename IoT>
-__device__ __noinline__ uint4 dequant_vec_exact(uint2 q, float scale) {
+__device__ __forceinline__ uint4 dequant_vec(uint2 q, float scale, IoT) {
   const uint32_t w[4] = {q.x & 0xFFFFu, q.x >> 16, q.y & 0xFFFFu, q.y >> 16};
   if constexpr (ElemTraits<IoT>::per_vec == 4) {
     const float2 a = e4m3x2_to_f32(w[0]), b = e4m3x2_to_f32(w[1]);
@@ -510,55 +520,10 @@ __device__ __noinline__ uint4 dequant_vec_exact(uint2 q, float scale) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const float2 f = e4m3x2_to_f32(w[i]);
-      o[i] = static_cast<uint32_t>(from_f32(f.x * scale, IoT{}).bits) |
-             (static_cast<uint32_t>(from_f32(f.y * scale, IoT{}).bits) << 16);
+      o[i] = pack2(f.x * scale, f.y * scale, IoT{});  // NaN packs as the canonical 0x7FFF
     }
     return make_uint4(o[0], o[1], o[2], o[3]);
   }
-}
-
-// Fast route.  An E4M3 byte c, placed as sign | (c & 0x7F) << 20, is the f32 whose value is
-// e4m3(c) * 2^-120 for normal AND subnormal codes (the exponent fields differ by exactly the
-// bias difference 120, and an f32 with a zero exponent field is a denormal with the same
-// meaning as an E4M3 subnormal).  Multiplying it by scale * 2^120 -- exact power-of-two
-// scaling of the scale, valid while that product is finite -- is the same real product
-// e4m3(c) * scale rounded once.  Only the NaN codes 0x7F / 0xFF have no f32 image: a vector
-// holding one takes the reference route.  `big_scale` = scale * 2^120, or 0 when not usable.
-__device__ __forceinline__ float e4m3_as_scaled_f32(uint32_t word, int byte) {
-  // byte -> bits 31..24, arithmetic shift smears the sign over bits 30..27, mask them off
-  const int32_t top = static_cast<int32_t>(__byte_perm(word, 0u, 0x0444 | (byte << 12)));
-  return __uint_as_float(static_cast<uint32_t>(top >> 4) & 0x87FFFFFFu);
-}
-__device__ __forceinline__ uint32_t pack2(float lo, float hi, BF16) {
-  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<const uint32_t *>(&v);
-}
-__device__ __forceinline__ uint32_t pack2(float lo, float hi, F16) {
-  const __half2 v = __floats2half2_rn(lo, hi);
-  return *reinterpret_cast<const uint32_t *>(&v);
-}
-template <typename IoT>
-__device__ __forceinline__ uint4 dequant_vec(uint2 q, float scale, float big_scale, IoT) {
-  constexpr int kPer = ElemTraits<IoT>::per_vec;
-  uint32_t nan_bytes = __vcmpeq4(q.x & 0x7F7F7F7Fu, 0x7F7F7F7Fu);
-  if (kPer == 8) nan_bytes |= __vcmpeq4(q.y & 0x7F7F7F7Fu, 0x7F7F7F7Fu);
-  if (nan_bytes != 0u || big_scale == 0.f) return dequant_vec_exact<IoT>(q, scale);
-  float z[8];
-#pragma unroll
-  for (int i = 0; i < kPer; ++i) z[i] = __fmul_rn(e4m3_as_scaled_f32(i < 4 ? q.x : q.y, i & 3), big_scale);
-  if constexpr (kPer == 4) {
-    return make_uint4(__float_as_uint(z[0]), __float_as_uint(z[1]), __float_as_uint(z[2]), __float_as_uint(z[3]));
-  } else {
-    uint32_t o[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) o[i] = pack2(z[2 * i], z[2 * i + 1], IoT{});
-    return make_uint4(o[0], o[1], o[2], o[3]);
-  }
-}
-// scale * 2^120 when that is a finite positive number the fast route can use, else 0.
-__device__ __forceinline__ float big_scale_of(float s) {
-  const bool ok = (s > 0.f) && (s < 128.f);  // NaN fails
-  return ok ? __fmul_rn(s, 1.329227995784916e36f) : 0.f;  // 2^120
 }
 
 struct ScaleView {
@@ -1146,7 +1111,7 @@ __global__ void __launch_bounds__(kGatherThreads) kvx_gather_f8_kernel(const Gat
         const int f = f0 + u * 32;
         if (f < vend) {
           const float scale = __ldg(sc.base + hh[u] * sc.stride);
-          store_stream(dst + static_cast<int64_t>(f) * 16, dequant_vec(r[u], scale, big_scale_of(scale), IoT{}));
+          store_stream(dst + static_cast<int64_t>(f) * 16, dequant_vec(r[u], scale, IoT{}));
         }
       }
     }
