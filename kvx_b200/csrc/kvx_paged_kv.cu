@@ -690,7 +690,16 @@ __global__ void __launch_bounds__(256)
 struct GatherShape {
   const void *table, *lens;
   int32_t seq_count, max_blocks, max_seq_len;
+  // RAGGED tables: table[indptr[s] + tok] is the page of token `tok` of sequence s, for
+  // tok < indptr[s + 1] - indptr[s] (one entry per cached token).
+  const void *indptr;  // NULL = PACKED
+  int32_t indptr64;    // indptr entries are 64-bit
 };
+
+__device__ __forceinline__ int64_t read_indptr(const GatherShape &s, int64_t i) {
+  return s.indptr64 ? static_cast<const int64_t *>(s.indptr)[i]
+                    : static_cast<int64_t>(static_cast<const int32_t *>(s.indptr)[i]);
+}
 
 template <typename IdxT>
 __device__ __forceinline__ int64_t read_idx(const void *p, int64_t i) {
@@ -713,8 +722,15 @@ __global__ void __launch_bounds__(256)
   const int32_t tok = static_cast<int32_t>(row - static_cast<int64_t>(seq) * s.max_seq_len);
   if (tok >= read_idx<IdxT>(s.lens, seq)) return;
   const int32_t lb = tok / p.g.block_size;
-  if (lb >= s.max_blocks) return;
-  const int64_t b = read_idx<IdxT>(s.table, static_cast<int64_t>(seq) * s.max_blocks + lb);
+  int64_t b;
+  if (s.indptr != nullptr) {
+    const int64_t first = read_indptr(s, seq);
+    if (tok >= read_indptr(s, seq + 1) - first) return;
+    b = read_idx<IdxT>(s.table, first + tok);
+  } else {
+    if (lb >= s.max_blocks) return;
+    b = read_idx<IdxT>(s.table, static_cast<int64_t>(seq) * s.max_blocks + lb);
+  }
   if (b < 0 || b >= p.g.num_blocks) return;
   const int64_t o = tok - static_cast<int64_t>(lb) * p.g.block_size;
   const CacheT kq = load_elem<CacheT>(p.k.base + page_byte_offset(p.k, b, o, h, d));
@@ -1043,6 +1059,72 @@ __global__ void __launch_bounds__(kGatherThreads, 4) kvx_gather_tiles_kernel(con
     }
     if (next >= items) break;
     item = next, part = next_part, cur = nxt;
+  }
+}
+
+// RAGGED block tables (one page id per cached token).  CTA = a tile of consecutive tokens of
+// one sequence: the first threads resolve each token's page row into a source byte offset in
+// shared memory, then all threads stream the tile's 16-byte vectors into the (contiguous)
+// output rows -- the write kernel's shape with the indirection on the source side.
+constexpr int kRaggedTile = 64;
+template <typename IdxT, int kUnroll>
+__global__ void __launch_bounds__(kGatherThreads) kvx_gather_ragged_kernel(const GatherPagesParams p) {
+  pdl_prologue();
+  __shared__ int64_t s_k[kRaggedTile];
+  __shared__ int64_t s_v[kRaggedTile];
+  const int tid = threadIdx.x;
+  const int seq = blockIdx.y;
+  const int t0 = blockIdx.x * p.part_vecs;  // part_vecs = tokens per CTA here
+  int64_t len = read_idx<IdxT>(p.s.lens, seq);
+  const int64_t first = read_indptr(p.s, seq);
+  len = min(len, min(static_cast<int64_t>(p.s.max_seq_len), read_indptr(p.s, seq + 1) - first));
+  if (t0 >= len) return;
+  const int ntok = static_cast<int>(min(static_cast<int64_t>(p.part_vecs), len - t0));
+  if (tid < ntok) {
+    const int tok = t0 + tid;
+    const int64_t b = read_idx<IdxT>(p.s.table, first + tok);
+    int64_t ko = -1, vo = -1;
+    if (b >= 0 && b < p.num_blocks) {
+      const int64_t o = tok % p.block_size;
+      ko = b * p.k_blk + o * p.k_tok;
+      vo = b * p.v_blk + o * p.v_tok;
+    }
+    s_k[tid] = ko;
+    s_v[tid] = vo;
+  }
+  __syncthreads();
+  const int64_t out_off = (static_cast<int64_t>(seq) * p.s.max_seq_len + t0) * p.out_row_bytes;
+  char *kdst = p.key_out + out_off;
+  char *vdst = p.value_out + out_off;
+  const int nvec = ntok * p.vpr;
+  for (int f0 = tid; f0 < nvec; f0 += kGatherThreads * kUnroll) {
+    uint4 kr[kUnroll], vr[kUnroll];
+    bool live[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int f = f0 + u * kGatherThreads;
+      live[u] = false;
+      if (f < nvec) {
+        const int tok = div_by(f, p.vpr, p.vpr_shift);
+        const int64_t ko = s_k[tok];
+        if (ko >= 0) {
+          const int v = f - tok * p.vpr;
+          const int h = div_by(v, p.vps, p.vps_shift);
+          const int64_t w = static_cast<int64_t>(v - h * p.vps) * 16;
+          kr[u] = load_stream(p.k_base + ko + h * p.k_head + w);
+          vr[u] = load_stream(p.v_base + s_v[tok] + h * p.v_head + w);
+          live[u] = true;
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int f = f0 + u * kGatherThreads;
+      if (live[u]) {
+        store_stream(kdst + static_cast<int64_t>(f) * 16, kr[u]);
+        store_stream(vdst + static_cast<int64_t>(f) * 16, vr[u]);
+      }
+    }
   }
 }
 
@@ -1658,7 +1740,10 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
   } else if (io_dtype != expected || gather->io.value.dtype != expected) {
     return KVX_STATUS_UNSUPPORTED;
   }
-  if (gather->block_table.format != KVX_BLOCK_TABLE_PACKED) return KVX_STATUS_UNSUPPORTED;
+  // PACKED as in the reference; RAGGED (one page id per cached token, KVX_SPEC.md:108-114) is
+  // executed here, the reference answers UNSUPPORTED for it (kernels/kvx_paged_kv.cu:788-790).
+  const bool ragged = gather->block_table.format == KVX_BLOCK_TABLE_RAGGED;
+  if (gather->block_table.format != KVX_BLOCK_TABLE_PACKED && !ragged) return KVX_STATUS_UNSUPPORTED;
   if (gather->io.num_kv_heads != cache->num_kv_heads || gather->io.head_dim != cache->head_dim)
     return KVX_STATUS_INVALID_ARGUMENT;
   if (gather->seq_lens.seq_count != gather->block_table.seq_count) return KVX_STATUS_INVALID_ARGUMENT;
@@ -1702,6 +1787,16 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
   gs.seq_count = static_cast<int32_t>(S);
   gs.max_blocks = static_cast<int32_t>(gather->block_table.max_blocks_per_seq);
   gs.max_seq_len = static_cast<int32_t>(L);
+  gs.indptr = nullptr;
+  gs.indptr64 = 0;
+  if (ragged) {  // same rules as the validate-only entry point (reference: kvx_abi.c:142-160)
+    const kvx_block_table_t &bt = gather->block_table;
+    if ((bt.indptr_dtype != KVX_DTYPE_S32 && bt.indptr_dtype != KVX_DTYPE_S64) || bt.beam_width != 1 ||
+        bt.indptr == nullptr || bt.indptr_count != bt.seq_count + 1)
+      return KVX_STATUS_INVALID_ARGUMENT;
+    gs.indptr = bt.indptr;
+    gs.indptr64 = bt.indptr_dtype == KVX_DTYPE_S64;
+  }
 
   const cudaStream_t cs = as_stream(stream);
   const DeviceInfo &dev = device_info();
@@ -1714,7 +1809,7 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
                       aligned(gather->io.value.data, 16) && view_vectorisable(gp.k, elem, D, in_vec) &&
                       view_vectorisable(gp.v, elem, D, in_vec) && chunk_vecs < (int64_t{1} << 30) &&
                       S * static_cast<int64_t>(gs.max_blocks) < (int64_t{1} << 31);
-  if (vec_ok) {
+  if (vec_ok && !(ragged && (fp8 || S > 65535))) {
     GatherPagesParams p;
     p.k_base = gp.k.base, p.k_blk = gp.k.blk, p.k_tok = gp.k.tok, p.k_head = gp.k.head;
     p.v_base = gp.v.base, p.v_blk = gp.v.blk, p.v_tok = gp.v.tok, p.v_head = gp.v.head;
@@ -1732,6 +1827,27 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
     p.dim = static_cast<int32_t>(D);
     p.ks = ks;
     p.vs = vs;
+    if (ragged && !fp8) {
+      p.part_vecs = kRaggedTile;  // tokens per CTA
+      while (p.part_vecs > 1 && static_cast<int64_t>(p.part_vecs) * (out_row / 16) > 4096) p.part_vecs >>= 1;
+      const dim3 rg(static_cast<unsigned>((L + p.part_vecs - 1) / p.part_vecs), static_cast<unsigned>(S));
+      {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = rg;
+        cfg.blockDim = dim3(kGatherThreads);
+        cfg.stream = cs;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = g_opt.pdl ? 1 : 0;
+        if (s32)
+          cudaLaunchKernelEx(&cfg, kvx_gather_ragged_kernel<int32_t, 4>, p);
+        else
+          cudaLaunchKernelEx(&cfg, kvx_gather_ragged_kernel<int64_t, 4>, p);
+        return finish_launch();
+      }
+    }
     const bool contiguous_pages = !fp8 && gp.k.head == D * elem && gp.v.head == D * elem &&
                                   gp.k.tok == H * D * elem && gp.v.tok == H * D * elem;
     const size_t prefix_bytes = p.use_prefix ? static_cast<size_t>(S + 1) * sizeof(int32_t) : 0;

@@ -284,8 +284,19 @@ static void gather_one(const kvx_cache_desc_t *c, const kvx_tensor_desc_t *pages
     for (int64_t tok = 0; tok < Lmax; ++tok) {
       if (tok >= len) continue;
       const int64_t lb = tok / bs;
-      if (lb >= mb) continue;
-      const int64_t block = read_index(g->block_table.indices, g->block_table.index_dtype, s * mb + lb);
+      int64_t block;
+      if (g->block_table.format == KVX_BLOCK_TABLE_RAGGED) {
+        /* One page id per cached token: indices[indptr[s] + tok] for tok below
+         * indptr[s + 1] - indptr[s]; offset in the page is tok % block_size
+         * (KVX_SPEC.md:108-114).  The reference does not execute this format. */
+        const int64_t first = read_index(g->block_table.indptr, g->block_table.indptr_dtype, s);
+        const int64_t count = read_index(g->block_table.indptr, g->block_table.indptr_dtype, s + 1) - first;
+        if (tok >= count) continue;
+        block = read_index(g->block_table.indices, g->block_table.index_dtype, first + tok);
+      } else {
+        if (lb >= mb) continue;
+        block = read_index(g->block_table.indices, g->block_table.index_dtype, s * mb + lb);
+      }
       if (block < 0 || block >= (int64_t)c->num_blocks) continue;
       const int64_t off = tok - lb * bs;
       for (int64_t h = 0; h < H; ++h) {
@@ -310,7 +321,8 @@ kvx_status_t kvx_oracle_gather_kv(const kvx_cache_desc_t *cache, const kvx_gathe
   int64_t kss = 0, vss = 0;
   if (cache == NULL || gather == NULL) return KVX_STATUS_INVALID_ARGUMENT;
   if (!layout_known(cache->k.layout) || !layout_known(cache->v.layout)) return KVX_STATUS_UNSUPPORTED;
-  if (gather->block_table.format != KVX_BLOCK_TABLE_PACKED) return KVX_STATUS_UNSUPPORTED;
+  if (gather->block_table.format != KVX_BLOCK_TABLE_PACKED && gather->block_table.format != KVX_BLOCK_TABLE_RAGGED)
+    return KVX_STATUS_UNSUPPORTED;
   if (gather->block_table.index_dtype != gather->seq_lens.dtype) return KVX_STATUS_INVALID_ARGUMENT;
   if (gather->seq_lens.dtype != KVX_DTYPE_S32 && gather->seq_lens.dtype != KVX_DTYPE_S64)
     return KVX_STATUS_INVALID_ARGUMENT;

@@ -162,3 +162,39 @@ def expected_gather_numpy(case: Case, cache_k: np.ndarray, cache_v: np.ndarray):
                     out[s, tok] = pool[b, :, :, o, :].reshape(g.num_kv_heads, g.head_dim)
         outs.append(out)
     return outs[0], outs[1]
+
+
+def to_ragged(case: Case, indptr_dtype=np.int32, truncate=()) -> Case:
+    """The same gather expressed with a RAGGED table: one page id per cached token, taken from
+    the PACKED table (KVX_SPEC.md:108-114).  ``truncate`` lists sequences whose token list is
+    cut to half their length (the gather must then stop there)."""
+    import dataclasses
+    bs = case.geom.block_size
+    ids, counts = [], []
+    for s in range(case.table.shape[0]):
+        n = int(min(max(int(case.lens[s]), 0), case.table.shape[1] * bs))
+        if s in truncate:
+            n //= 2
+        ids.extend(int(case.table[s, t // bs]) for t in range(n))
+        counts.append(n)
+    indptr = np.concatenate([[0], np.cumsum(counts)]).astype(indptr_dtype)
+    return dataclasses.replace(case, ragged=np.array(ids, dtype=case.table.dtype), indptr=indptr)
+
+
+def expected_gather_ragged_numpy(case: Case, cache_k: np.ndarray, cache_v: np.ndarray):
+    """Independent numpy statement of the RAGGED gather (NHD / HND canonical pools)."""
+    g = case.geom
+    outs = []
+    for pool, out0 in ((cache_k, case.out_k), (cache_v, case.out_v)):
+        pool = pool.reshape(g.shape)
+        out = out0.copy()
+        for s in range(case.indptr.shape[0] - 1):
+            first, count = int(case.indptr[s]), int(case.indptr[s + 1] - case.indptr[s])
+            for tok in range(min(int(case.lens[s]), case.max_seq_len, count)):
+                b = int(case.ragged[first + tok])
+                if b < 0 or b >= g.num_blocks:
+                    continue
+                o = tok % g.block_size
+                out[s, tok] = pool[b, o] if g.layout == abi.LAYOUT_NHD else pool[b, :, o, :]
+        outs.append(out)
+    return outs[0], outs[1]

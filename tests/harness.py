@@ -76,6 +76,9 @@ class Case:
     max_seq_len: int = 0
     out_k: Optional[np.ndarray] = None     # [S, Lmax, H, D] raw bits before the call
     out_v: Optional[np.ndarray] = None
+    # RAGGED form of the block table (one page id per cached token); used instead of `table`
+    ragged: Optional[np.ndarray] = None    # [sum(counts)] int32 / int64
+    indptr: Optional[np.ndarray] = None    # [S + 1] int32 / int64
     note: str = ""
     keep: list = field(default_factory=list)
 
@@ -116,10 +119,17 @@ def descriptors(case: Case, bufs: dict, memory: int):
         gather = abi.gather_desc(S, case.max_seq_len, g.num_kv_heads, g.head_dim, case.io_dtype,
                                  _addr(bufs["out_k"]), _addr(bufs["out_v"]), index_code(case.table),
                                  _addr(bufs["table"]), mb, _addr(bufs["lens"]), memory)
+        if case.ragged is not None:
+            b = gather.block_table
+            b.format = abi.TABLE_RAGGED
+            b.indptr_dtype = index_code(case.indptr)
+            b.indices, b.indices_count = _addr(bufs["ragged"]), int(case.ragged.shape[0])
+            b.indptr, b.indptr_count = _addr(bufs["indptr"]), int(case.indptr.shape[0])
     return cache, write, gather, ks, vs
 
 
-_FIELDS = ("key", "value", "slots", "cache_k", "cache_v", "k_scale", "v_scale", "table", "lens", "out_k", "out_v")
+_FIELDS = ("key", "value", "slots", "cache_k", "cache_v", "k_scale", "v_scale", "table", "lens", "out_k", "out_v",
+           "ragged", "indptr")
 
 
 def host_buffers(case: Case) -> dict:

@@ -187,6 +187,34 @@ def test_bulk_gather_path_matches():
         check_gather(case, k, v)
 
 
+@pytest.mark.parametrize("dtype", [abi.DTYPE_BF16, abi.DTYPE_F32])
+@pytest.mark.parametrize("layout", [abi.LAYOUT_NHD, abi.LAYOUT_HND])
+def test_ragged_block_table_gather(layout, dtype):
+    """RAGGED tables (one page id per cached token), which the reference validates but answers
+    UNSUPPORTED for: vector tier, generic tier (odd head_dim), both index widths, truncated
+    token lists, invalid ids."""
+    for i, kw in enumerate([
+        dict(heads=8, dim=128, block_size=16, num_blocks=60, lens=[100, 17, 256, 1, 0, 333], bad_blocks=3),
+        dict(heads=2, dim=64, block_size=32, num_blocks=30, lens=[31, 33, 160], index_dtype=np.int64),
+        dict(heads=1, dim=7, block_size=4, num_blocks=16, lens=[9, 4, 0, 6]),
+        dict(heads=3, dim=24, block_size=5, num_blocks=40, lens=[50, 70], max_seq_len=40),
+    ]):
+        packed = cases.make_case(800 + i, layout=layout, dtype=dtype, **kw)
+        _, k, v = oracle_write(packed)
+        for indptr_dtype, trunc in ((np.int32, ()), (np.int64, (0, 1))):
+            rag = cases.to_ragged(packed, indptr_dtype, truncate=trunc)
+            rag.note = f"ragged {i}"
+            check_gather(rag, k, v)
+            check_gather(rag, k, v, "typed")
+
+
+def test_ragged_block_table_gather_fp8():
+    packed = cases.make_case(850, dtype=abi.DTYPE_BF16, cache_dtype=abi.DTYPE_F8_E4M3, real_values=True, heads=4,
+                             dim=64, block_size=16, num_blocks=24, lens=[100, 40, 7], scale_gran=abi.SCALE_PER_HEAD)
+    _, k, v = oracle_write(packed)
+    check_gather(cases.to_ragged(packed), k, v)
+
+
 def test_empty_and_degenerate_batches():
     case = cases.make_case(3, dtype=abi.DTYPE_F16, heads=2, dim=64, lens=[0, 0], num_blocks=4)
     assert case.T == 0

@@ -91,6 +91,25 @@ def test_reference_kernel_test_gather_case(dtype):
     assert np.array_equal(ok_.reshape(-1), ck) and np.array_equal(ov_.reshape(-1), cv)
 
 
+@pytest.mark.parametrize("layout", [abi.LAYOUT_NHD, abi.LAYOUT_HND])
+def test_ragged_table_gather_matches_numpy_statement(layout):
+    """RAGGED tables: one page id per cached token (KVX_SPEC.md:108-114).  Same result as the
+    PACKED form of the same pages; a token list shorter than seq_lens stops the gather."""
+    for seed, kw in enumerate([dict(lens=[9, 4, 0, 13], num_blocks=16), dict(lens=[5, 12], max_seq_len=7, bad_blocks=2),
+                               dict(lens=[20, 3], index_dtype=np.int64, block_size=5, num_blocks=8)]):
+        packed = cases.make_case(400 + seed, layout=layout, dtype=abi.DTYPE_BF16, **kw)
+        _, k, v = oracle_write(packed)
+        _, pk, pv = oracle_gather(packed, k, v)
+        for indptr_dtype, trunc in ((np.int32, ()), (np.int64, (0,))):
+            rag = cases.to_ragged(packed, indptr_dtype, truncate=trunc)
+            st, rk, rv = oracle_gather(rag, k, v)
+            assert st == abi.STATUS_OK
+            ek, ev = cases.expected_gather_ragged_numpy(rag, k, v)
+            assert np.array_equal(rk, ek) and np.array_equal(rv, ev)
+            if not trunc and packed.table.shape[1] * packed.geom.block_size >= packed.max_seq_len:
+                assert np.array_equal(rk, pk) and np.array_equal(rv, pv)
+
+
 def test_noncanonical_strides_and_untouched_bytes():
     for layout in (abi.LAYOUT_NHD, abi.LAYOUT_HND):
         case = cases.make_case(7, layout=layout, stride_pad=(16, 8, 8), pad_frac=0.2, lens=[6, 3])
