@@ -66,8 +66,16 @@ KVX_API kvx_status_t kvx_launch_write_kv_prefill_bf16(const kvx_cache_desc_t *ca
 
 /* ------------------------------------------------------------------ gather -----------
  * out[s][tok][h][d] = cache[table[s][tok / block_size]][tok % block_size][h][d] for
- * tok < seq_lens[s]; PACKED block tables only; table and seq_lens share one index type.
- * reference: kernels/kvx_paged_kv.h:19-21, kernels/kvx_paged_kv.cu:891-910 */
+ * tok < seq_lens[s]; table and seq_lens share one index type.
+ * reference: kernels/kvx_paged_kv.h:19-21, kernels/kvx_paged_kv.cu:891-910
+ *
+ * Block-table formats: PACKED as in the reference.  RAGGED (ABI 1.2; the reference validates
+ * it, kvx_abi.c:142-160, but its launcher answers UNSUPPORTED, kernels/kvx_paged_kv.cu:788-790)
+ * follows KVX_SPEC.md:108-114: `indices` holds ONE PAGE ID PER CACHED TOKEN, `indptr`
+ * (seq_count + 1 entries, S32 or S64) the prefix sums of the per-sequence token counts; token
+ * tok of sequence s lives in page indices[indptr[s] + tok] at offset tok % block_size, and
+ * the gather stops at min(seq_lens[s], indptr[s + 1] - indptr[s], max_seq_len).  Outputs keep
+ * the padded [seq_count, max_seq_len, heads, dim] form.  KV_OFFSETS stays UNSUPPORTED. */
 KVX_API kvx_status_t kvx_launch_gather_kv(const kvx_cache_desc_t *cache,
                                           const kvx_gather_desc_t *gather, void *stream);
 
