@@ -164,6 +164,12 @@ class ClockSampler:
                                          stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
+            return
+        # nvidia-smi needs a moment to start; wait for its first line so that short runs are sampled too
+        import time
+        deadline = time.time() + 3.0
+        while time.time() < deadline and os.path.getsize(self.path) == 0 and self.proc.poll() is None:
+            time.sleep(0.02)
 
     def stop(self) -> dict:
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}

@@ -59,5 +59,33 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB_PATH
 
 
+TORCH_OPS_SRC = os.path.join(CSRC, "kvx_torch_ops.cpp")
+TORCH_OPS_PATH = os.path.join(LIB_DIR, "libkvx_b200_torch.so")
+
+
+def build_torch_ops(force: bool = False, verbose: bool = False) -> str:
+    """Compile the torch operator library (``torch.ops.kvx_b200.*``) against the installed
+    torch and link it to ``libkvx_b200.so`` (found at load time next to it, via $ORIGIN)."""
+    from torch.utils import cpp_extension as ext
+    import torch
+
+    build(force=False, verbose=verbose)
+    headers = [os.path.join(INCLUDE, f) for f in os.listdir(INCLUDE)]
+    if not force and not _stale(TORCH_OPS_PATH, [TORCH_OPS_SRC, LIB_PATH] + headers):
+        return TORCH_OPS_PATH
+    cuda_home = os.path.dirname(os.path.dirname(_nvcc()))
+    cmd = ["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-Wall",
+           "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI),
+           "-I" + INCLUDE, "-I" + os.path.join(cuda_home, "include")]
+    cmd += ["-isystem" + p for p in ext.include_paths()]
+    cmd += [TORCH_OPS_SRC, "-o", TORCH_OPS_PATH, "-L" + LIB_DIR, "-lkvx_b200", "-Wl,-rpath,$ORIGIN"]
+    for d in ext.library_paths():
+        cmd += ["-L" + d, "-Wl,-rpath," + d]
+    cmd += ["-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch"]
+    subprocess.run(cmd, check=True, stdout=None if verbose else subprocess.PIPE, stderr=subprocess.STDOUT)
+    return TORCH_OPS_PATH
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose=True))
+    print(build_torch_ops(force="--force" in sys.argv, verbose=True))

@@ -6,10 +6,17 @@ patches/vllm/kvx.patch:176-275): it fills the ABI descriptors from tensor sizes 
 without canonicalising them, passes torch's current CUDA stream and raises when the status
 is not OK.  Torch is used for device memory and streams only; all data movement happens in
 ``libkvx_b200.so``.  Nothing here falls back to PyTorch indexing.
+
+When ``lib/libkvx_b200_torch.so`` is built, calls on 4-D caches go through the operators it
+registers with torch's dispatcher (``torch.ops.kvx_b200.*``), which do the same descriptor
+filling in C++ and cost a few microseconds of host time per call; otherwise, and for 5-D
+packed caches and the prefill entry point, the descriptors are filled here through ctypes.
 """
 from __future__ import annotations
 
 import ctypes as C
+import os
+import re
 from typing import Optional
 
 import torch
@@ -35,6 +42,45 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+_NATIVE = None          # torch.ops.kvx_b200 once libkvx_b200_torch.so is loaded; False if it is not built
+_NO_SCALE: dict = {}    # one empty float32 tensor per device, standing for "no scale"
+_STATUS_RE = re.compile(r"(kvx cache \w+) failed with status=(\d+)")
+
+
+def native_ops():
+    """``torch.ops.kvx_b200`` (the dispatcher-registered operators of ``csrc/kvx_torch_ops.cpp``),
+    or None when that library has not been built; the ctypes route below is then used."""
+    global _NATIVE
+    if _NATIVE is None:
+        path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libkvx_b200_torch.so")
+        if os.path.exists(path):
+            lib()  # libkvx_b200.so first, so that the operator library binds to the same copy
+            torch.ops.load_library(path)
+            _NATIVE = torch.ops.kvx_b200
+        else:
+            _NATIVE = False
+    return _NATIVE or None
+
+
+def _scale_arg(scale: Optional[torch.Tensor], device: torch.device) -> torch.Tensor:
+    if scale is not None:
+        return scale
+    t = _NO_SCALE.get(device)
+    if t is None:
+        t = _NO_SCALE[device] = torch.empty(0, dtype=torch.float32, device=device)
+    return t
+
+
+def _call_native(op, *args) -> None:
+    try:
+        op(*args)
+    except RuntimeError as exc:
+        m = _STATUS_RE.search(str(exc))
+        if m is None:
+            raise
+        raise KvxError(m.group(1), int(m.group(2))) from None
+
+
 def _cache_code(t: torch.Tensor, kv_cache_dtype: str) -> int:
     if kv_cache_dtype in ("fp8", "fp8_e4m3"):
         if t.dtype not in _FP8_TORCH:
@@ -48,33 +94,50 @@ def _cache_code(t: torch.Tensor, kv_cache_dtype: str) -> int:
 
 
 def cache_desc_from_tensors(key_cache: torch.Tensor, value_cache: torch.Tensor,
-                            kv_cache_dtype: str = "auto", head_dim: Optional[int] = None,
+                            kv_cache_dtype: str = "auto", heads: Optional[int] = None,
                             layout: Optional[int] = None) -> abi.CacheDesc:
     """Describe a pair of 4-D (NHD / HND) or 5-D (HND_PACKED) page tensors.
 
-    For 4-D tensors the layout is inferred as the patch does: NHD when the stride of axis 2
-    equals head_dim, else HND (reference: patches/vllm/kvx.patch:132-135, :222-229).
+    For 4-D tensors the layout is inferred unless given.  The reference's operator decides
+    by one stride (NHD when stride(2) == head_dim, reference: patches/vllm/kvx.patch:132-135,
+    :222-229), which misreads a contiguous ``[blocks, heads, block_size, dim]`` tensor; the
+    rule here agrees with it wherever it is right and also accepts that tensor and vLLM's
+    permuted view of HND memory: ``stride(1) < stride(2)`` is a ``[blocks, block_size, heads,
+    dim]`` view of HND memory; otherwise the axis whose size equals ``heads`` names the
+    layout; when ``block_size == heads`` (or ``heads`` is not given) the reference's stride
+    rule decides.
     """
     if key_cache.shape != value_cache.shape:
         raise ValueError("key/value cache shape mismatch")
     code = _cache_code(key_cache, kv_cache_dtype)
+    k_shape, k_stride = list(key_cache.shape), list(key_cache.stride())
+    v_shape, v_stride = list(value_cache.shape), list(value_cache.stride())
     if key_cache.dim() == 5:
         layout = abi.LAYOUT_HND_PACKED
         nb, heads, dhi, bs, pack = key_cache.shape
         dim = dhi * pack
     else:
         dim = key_cache.shape[3]
-        if layout is None:
-            layout = abi.LAYOUT_NHD if key_cache.stride(2) == dim else abi.LAYOUT_HND
+        if layout is None and k_stride[1] < k_stride[2]:
+            layout = abi.LAYOUT_HND  # a logical-NHD view of HND memory: describe the memory
+            for shape, stride in ((k_shape, k_stride), (v_shape, v_stride)):
+                shape[1], shape[2] = shape[2], shape[1]
+                stride[1], stride[2] = stride[2], stride[1]
+        elif layout is None:
+            nhd, hnd = k_shape[2] == heads, k_shape[1] == heads
+            if heads is not None and nhd != hnd:
+                layout = abi.LAYOUT_NHD if nhd else abi.LAYOUT_HND
+            else:
+                layout = abi.LAYOUT_NHD if k_stride[2] == dim else abi.LAYOUT_HND
         if layout == abi.LAYOUT_NHD:
-            nb, bs, heads, _ = key_cache.shape
+            nb, bs, heads, _ = k_shape
         else:
-            nb, heads, bs, _ = key_cache.shape
+            nb, heads, bs, _ = k_shape
     c = abi.CacheDesc()
     c.size = C.sizeof(abi.CacheDesc)
     c.num_blocks, c.block_size, c.num_kv_heads, c.head_dim = nb, bs, heads, dim
-    c.k = abi.tensor_desc(key_cache.data_ptr(), code, key_cache.shape, key_cache.stride(), layout)
-    c.v = abi.tensor_desc(value_cache.data_ptr(), code, value_cache.shape, value_cache.stride(), layout)
+    c.k = abi.tensor_desc(key_cache.data_ptr(), code, k_shape, k_stride, layout)
+    c.v = abi.tensor_desc(value_cache.data_ptr(), code, v_shape, v_stride, layout)
     c.pool.size = C.sizeof(abi.PoolDesc)
     return c
 
@@ -103,6 +166,12 @@ def reshape_and_cache_flash_kvx(key: torch.Tensor, value: torch.Tensor, key_cach
     ``k_scale`` / ``v_scale`` (1 or ``heads`` float32 values).  ``tokens_per_seq`` selects
     the prefill entry point, whose result is identical.
     """
+    native = native_ops() if tokens_per_seq is None and key_cache.dim() == 4 else None
+    if native is not None:
+        dev = key.device
+        _call_native(native.reshape_and_cache_flash_kvx, key, value, key_cache, value_cache, slot_mapping,
+                     kv_cache_dtype, _scale_arg(k_scale, dev), _scale_arg(v_scale, dev))
+        return
     if not (key.is_cuda and value.is_cuda and key_cache.is_cuda and value_cache.is_cuda):
         raise ValueError("key/value and cache tensors must be CUDA tensors")
     if key.dtype != value.dtype or key.dtype not in _FLOAT_CODES:
@@ -113,7 +182,7 @@ def reshape_and_cache_flash_kvx(key: torch.Tensor, value: torch.Tensor, key_cach
         raise TypeError("slot_mapping must be a 1-D int32 or int64 tensor")
     num_tokens = slot_mapping.shape[0]
     heads, dim = key.shape[1], key.shape[2]
-    cache = cache_desc_from_tensors(key_cache, value_cache, kv_cache_dtype)
+    cache = cache_desc_from_tensors(key_cache, value_cache, kv_cache_dtype, heads)
     w = abi.WriteDesc()
     w.size = C.sizeof(abi.WriteDesc)
     w.io.size = C.sizeof(abi.KvIoDesc)
@@ -146,6 +215,12 @@ def gather_kv(key_cache: torch.Tensor, value_cache: torch.Tensor, block_table: t
     ``block_table`` is ``[seq_count, max_blocks_per_seq]`` (int32 or int64, same dtype as
     ``seq_lens``); outputs are dense ``[seq_count, max_seq_len, heads, dim]``.
     """
+    native = native_ops() if key_cache.dim() == 4 else None
+    if native is not None:
+        dev = key_out.device
+        _call_native(native.gather_kv, key_cache, value_cache, block_table, seq_lens, key_out, value_out,
+                     kv_cache_dtype, _scale_arg(k_scale, dev), _scale_arg(v_scale, dev))
+        return
     if block_table.dim() != 2 or not block_table.is_contiguous():
         raise ValueError("block_table must be a contiguous [seq_count, max_blocks_per_seq] tensor")
     if block_table.dtype not in _INDEX_CODES or seq_lens.dtype != block_table.dtype:
@@ -153,7 +228,7 @@ def gather_kv(key_cache: torch.Tensor, value_cache: torch.Tensor, block_table: t
     if key_out.dim() != 4 or key_out.shape != value_out.shape or key_out.dtype not in _FLOAT_CODES:
         raise ValueError("outputs must be [seq_count, max_seq_len, heads, dim] float tensors")
     seqs, max_len, heads, dim = key_out.shape
-    cache = cache_desc_from_tensors(key_cache, value_cache, kv_cache_dtype)
+    cache = cache_desc_from_tensors(key_cache, value_cache, kv_cache_dtype, heads)
     g = abi.gather_desc(seqs, max_len, heads, dim, _FLOAT_CODES[key_out.dtype], key_out.data_ptr(),
                         value_out.data_ptr(), _INDEX_CODES[block_table.dtype], block_table.data_ptr(),
                         block_table.shape[1], seq_lens.data_ptr())

@@ -229,3 +229,21 @@ def test_reference_abi_test_program_passes_against_this_header(tmp_path):
                     os.path.join(ROOT, "kvx_b200", "csrc", "kvx_abi.c"),
                     os.path.join(REFERENCE_ROOT, "tests", "kvx_abi_test.c"), "-o", str(exe)], check=True)
     assert subprocess.run([str(exe)]).returncode == 0
+
+
+def test_torch_operator_library_registers_its_operators(built_lib):
+    """libkvx_b200_torch.so builds against the installed torch, loads without a GPU and
+    registers the write operator under the name and schema of the reference's vLLM patch
+    (reference: patches/vllm/kvx.patch:288-296) plus the gather operator."""
+    from kvx_b200 import build, ops
+    build.build_torch_ops()
+    native = ops.native_ops()
+    assert native is not None
+    write = native.reshape_and_cache_flash_kvx.default._schema
+    names = [a.name for a in write.arguments]
+    assert names == ["key", "value", "key_cache", "value_cache", "slot_mapping", "kv_cache_dtype", "k_scale", "v_scale"]
+    assert [a.name for a in write.arguments if a.alias_info is not None and a.alias_info.is_write] == \
+        ["key_cache", "value_cache"]
+    gather = native.gather_kv.default._schema
+    assert [a.name for a in gather.arguments][:6] == ["key_cache", "value_cache", "block_table", "seq_lens",
+                                                       "key_out", "value_out"]
