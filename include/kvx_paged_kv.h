@@ -75,7 +75,21 @@ KVX_API kvx_status_t kvx_launch_write_kv_prefill_bf16(const kvx_cache_desc_t *ca
  * (seq_count + 1 entries, S32 or S64) the prefix sums of the per-sequence token counts; token
  * tok of sequence s lives in page indices[indptr[s] + tok] at offset tok % block_size, and
  * the gather stops at min(seq_lens[s], indptr[s + 1] - indptr[s], max_seq_len).  Outputs keep
- * the padded [seq_count, max_seq_len, heads, dim] form.  KV_OFFSETS stays UNSUPPORTED. */
+ * the padded [seq_count, max_seq_len, heads, dim] form.
+ *
+ * KV_OFFSETS (ABI 1.2; validated by the reference, kvx_abi.c:161-189, never executed) follows
+ * KVX_SPEC.md:116-122 and KV_CACHE_LAYOUTS.md:89-96: `indices` is an S32 table
+ * [seq_count, beam_width, 2, max_blocks_per_seq] of pool offsets, [s][0][0][lb] naming the K
+ * page and [s][0][1][lb] the V page of logical block lb.  Bit 31 of an entry selects
+ * cache->pool.secondary, otherwise cache->pool.primary; the low 31 bits count blocks:
+ *     page = pool + offset * cache->pool.bytes_per_block.
+ * Inside a page cache->k / cache->v give layout, dtype and the strides of the token, head and
+ * dim axes; their data pointers and block strides are not used.  Skipped without error: an
+ * entry for the secondary pool when there is none, and an offset that is not below
+ * cache->num_blocks (which therefore counts the blocks of one pool).  The validate-only
+ * rules apply (S32, KVCACHEINDEX flag, power-of-two block_size, indices_count, no indptr,
+ * pool with bytes_per_block and primary); beam_width must be 1 (UNSUPPORTED otherwise: the
+ * output has one row per sequence). */
 KVX_API kvx_status_t kvx_launch_gather_kv(const kvx_cache_desc_t *cache,
                                           const kvx_gather_desc_t *gather, void *stream);
 

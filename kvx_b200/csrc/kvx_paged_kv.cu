@@ -694,7 +694,27 @@ struct GatherShape {
   // tok < indptr[s + 1] - indptr[s] (one entry per cached token).
   const void *indptr;  // NULL = PACKED
   int32_t indptr64;    // indptr entries are 64-bit
+  // KV_OFFSETS tables (KVX_SPEC.md:116-122, KV_CACHE_LAYOUTS.md:89-96): int32
+  // [S, beam_width, 2, max_blocks]; entry [s][0][0][lb] names the K page and [s][0][1][lb] the V
+  // page of logical block lb.  Bit 31 of an entry selects the secondary pool, the low 31 bits
+  // count pool blocks: page = pool + offset * pool_block_bytes.
+  const char *pool[2];  // primary, secondary (may be NULL); pool[0] == NULL = not KV_OFFSETS
+  int64_t pool_block_bytes;
+  int32_t beam_width;
 };
+
+// First byte of the K (kv = 0) or V (kv = 1) page of logical block lb of sequence seq in a
+// KV_OFFSETS table, or NULL when the entry is skipped: it names the secondary pool and there
+// is none, or its offset is not below num_blocks (the bound holds for either pool).
+__device__ __forceinline__ const char *offsets_page(const GatherShape &s, int32_t num_blocks, int32_t seq,
+                                                    int32_t lb, int kv) {
+  const int64_t at = ((static_cast<int64_t>(seq) * s.beam_width) * 2 + kv) * s.max_blocks + lb;
+  const uint32_t e = static_cast<const uint32_t *>(s.table)[at];
+  const char *base = s.pool[e >> 31];
+  const uint32_t off = e & 0x7FFFFFFFu;
+  if (base == nullptr || off >= static_cast<uint32_t>(num_blocks)) return nullptr;
+  return base + static_cast<int64_t>(off) * s.pool_block_bytes;
+}
 
 __device__ __forceinline__ int64_t read_indptr(const GatherShape &s, int64_t i) {
   return s.indptr64 ? static_cast<const int64_t *>(s.indptr)[i]
@@ -722,30 +742,47 @@ __global__ void __launch_bounds__(256)
   const int32_t tok = static_cast<int32_t>(row - static_cast<int64_t>(seq) * s.max_seq_len);
   if (tok >= read_idx<IdxT>(s.lens, seq)) return;
   const int32_t lb = tok / p.g.block_size;
-  int64_t b;
-  if (s.indptr != nullptr) {
-    const int64_t first = read_indptr(s, seq);
-    if (tok >= read_indptr(s, seq + 1) - first) return;
-    b = read_idx<IdxT>(s.table, first + tok);
-  } else {
-    if (lb >= s.max_blocks) return;
-    b = read_idx<IdxT>(s.table, static_cast<int64_t>(seq) * s.max_blocks + lb);
-  }
-  if (b < 0 || b >= p.g.num_blocks) return;
   const int64_t o = tok - static_cast<int64_t>(lb) * p.g.block_size;
-  const CacheT kq = load_elem<CacheT>(p.k.base + page_byte_offset(p.k, b, o, h, d));
-  const CacheT vq = load_elem<CacheT>(p.v.base + page_byte_offset(p.v, b, o, h, d));
-  if (kDequant) {
-    const float sk = __ldg(p.ks.base + h * p.ks.stride);
-    const float sv = __ldg(p.vs.base + h * p.vs.stride);
-    key_out[idx] = from_f32(e4m3x2_to_f32(kq.bits).x * sk, IoT{});
-    value_out[idx] = from_f32(e4m3x2_to_f32(vq.bits).x * sv, IoT{});
+  const char *kp, *vp;  // the element's address in its K / V page, NULL = skipped
+  if (s.pool[0] != nullptr) {
+    if (lb >= s.max_blocks) return;
+    kp = offsets_page(s, p.g.num_blocks, seq, lb, 0);
+    vp = offsets_page(s, p.g.num_blocks, seq, lb, 1);
+    if (kp != nullptr) kp += page_byte_offset(p.k, 0, o, h, d);
+    if (vp != nullptr) vp += page_byte_offset(p.v, 0, o, h, d);
   } else {
-    IoT a, c;
-    a.bits = kq.bits;
-    c.bits = vq.bits;
-    key_out[idx] = a;
-    value_out[idx] = c;
+    int64_t b;
+    if (s.indptr != nullptr) {
+      const int64_t first = read_indptr(s, seq);
+      if (tok >= read_indptr(s, seq + 1) - first) return;
+      b = read_idx<IdxT>(s.table, first + tok);
+    } else {
+      if (lb >= s.max_blocks) return;
+      b = read_idx<IdxT>(s.table, static_cast<int64_t>(seq) * s.max_blocks + lb);
+    }
+    if (b < 0 || b >= p.g.num_blocks) return;
+    kp = p.k.base + page_byte_offset(p.k, b, o, h, d);
+    vp = p.v.base + page_byte_offset(p.v, b, o, h, d);
+  }
+  if (kp != nullptr) {
+    const CacheT q = load_elem<CacheT>(kp);
+    if (kDequant) {
+      key_out[idx] = from_f32(e4m3x2_to_f32(q.bits).x * __ldg(p.ks.base + h * p.ks.stride), IoT{});
+    } else {
+      IoT a;
+      a.bits = q.bits;
+      key_out[idx] = a;
+    }
+  }
+  if (vp != nullptr) {
+    const CacheT q = load_elem<CacheT>(vp);
+    if (kDequant) {
+      value_out[idx] = from_f32(e4m3x2_to_f32(q.bits).x * __ldg(p.vs.base + h * p.vs.stride), IoT{});
+    } else {
+      IoT a;
+      a.bits = q.bits;
+      value_out[idx] = a;
+    }
   }
 }
 
@@ -835,7 +872,7 @@ struct ChunkInfo {
   int64_t out_off;  // byte offset of the chunk's first row in the output tensors
 };
 
-template <typename IdxT>
+template <typename IdxT, bool kOffsets = false>
 __device__ __forceinline__ ChunkInfo resolve_chunk(const GatherPagesParams &p, int32_t seq, int32_t lb) {
   ChunkInfo c;
   c.block = -1;
@@ -845,9 +882,13 @@ __device__ __forceinline__ ChunkInfo resolve_chunk(const GatherPagesParams &p, i
   if (len > p.s.max_seq_len) len = p.s.max_seq_len;
   const int64_t first = static_cast<int64_t>(lb) * p.block_size;
   if (first >= len || lb >= p.s.max_blocks) return c;  // (reference: kernels/kvx_paged_kv.cu:247-253)
-  const int64_t b = read_idx<IdxT>(p.s.table, static_cast<int64_t>(seq) * p.s.max_blocks + lb);
-  if (b < 0 || b >= p.num_blocks) return c;  // negative id: skipped (:256-258); too large: skipped too
-  c.block = b;
+  if (kOffsets) {
+    c.block = 0;  // the K and the V page are looked up by the caller
+  } else {
+    const int64_t b = read_idx<IdxT>(p.s.table, static_cast<int64_t>(seq) * p.s.max_blocks + lb);
+    if (b < 0 || b >= p.num_blocks) return c;  // negative id: skipped (:256-258); too large: skipped too
+    c.block = b;
+  }
   c.tokens = static_cast<int32_t>(min(len - first, static_cast<int64_t>(p.block_size)));
   c.out_off = (static_cast<int64_t>(seq) * p.s.max_seq_len + first) * p.out_row_bytes;
   return c;
@@ -856,7 +897,8 @@ __device__ __forceinline__ ChunkInfo resolve_chunk(const GatherPagesParams &p, i
 // Persistent CTAs; warp-granular work items (chunk, part, K|V).
 //   kSeg = false : page rows are contiguous -> a chunk is one contiguous span on both sides.
 //   kSeg = true  : per-head segments (HND pages or padded strides).
-template <typename IdxT, bool kSeg, int kUnroll>
+//   kOffsets     : KV_OFFSETS table; K and V pages are resolved separately (offsets_page).
+template <typename IdxT, bool kSeg, int kUnroll, bool kOffsets = false>
 __global__ void __launch_bounds__(kGatherThreads) kvx_gather_pages_kernel(const GatherPagesParams p) {
   pdl_prologue();
   extern __shared__ int32_t s_prefix[];
@@ -884,12 +926,18 @@ __global__ void __launch_bounds__(kGatherThreads) kvx_gather_pages_kernel(const 
       ref.seq = static_cast<int32_t>(c / p.s.max_blocks);
       ref.lb = static_cast<int32_t>(c - static_cast<int64_t>(ref.seq) * p.s.max_blocks);
     }
-    const ChunkInfo ci = resolve_chunk<IdxT>(p, ref.seq, ref.lb);
+    const ChunkInfo ci = resolve_chunk<IdxT, kOffsets>(p, ref.seq, ref.lb);
     if (ci.block < 0) continue;
     const int nvec = ci.tokens * p.vpr;
     const int vbeg = part * p.part_vecs;
     const int vend = min(vbeg + p.part_vecs, nvec);
-    const char *src = kv ? p.v_base + ci.block * p.v_blk : p.k_base + ci.block * p.k_blk;
+    const char *src;
+    if (kOffsets) {
+      src = offsets_page(p.s, p.num_blocks, ref.seq, ref.lb, kv);
+      if (src == nullptr) continue;
+    } else {
+      src = kv ? p.v_base + ci.block * p.v_blk : p.k_base + ci.block * p.k_blk;
+    }
     char *dst = (kv ? p.value_out : p.key_out) + ci.out_off;
     const int64_t tok_b = kv ? p.v_tok : p.k_tok;
     const int64_t head_b = kv ? p.v_head : p.k_head;
@@ -1130,7 +1178,7 @@ __global__ void __launch_bounds__(kGatherThreads) kvx_gather_ragged_kernel(const
 
 // Dequantising gather: same decomposition; each 16-byte OUTPUT vector (8 or 4 elements of
 // one head) is produced from 8 or 4 cache bytes.
-template <typename IoT, typename IdxT, int kUnroll>
+template <typename IoT, typename IdxT, int kUnroll, bool kOffsets = false>
 __global__ void __launch_bounds__(kGatherThreads) kvx_gather_f8_kernel(const GatherPagesParams p) {
   pdl_prologue();
   constexpr int kPer = ElemTraits<IoT>::per_vec;
@@ -1159,12 +1207,18 @@ __global__ void __launch_bounds__(kGatherThreads) kvx_gather_f8_kernel(const Gat
       ref.seq = static_cast<int32_t>(c / p.s.max_blocks);
       ref.lb = static_cast<int32_t>(c - static_cast<int64_t>(ref.seq) * p.s.max_blocks);
     }
-    const ChunkInfo ci = resolve_chunk<IdxT>(p, ref.seq, ref.lb);
+    const ChunkInfo ci = resolve_chunk<IdxT, kOffsets>(p, ref.seq, ref.lb);
     if (ci.block < 0) continue;
     const int nvec = ci.tokens * p.vpr;
     const int vbeg = part * p.part_vecs;
     const int vend = min(vbeg + p.part_vecs, nvec);
-    const char *src = kv ? p.v_base + ci.block * p.v_blk : p.k_base + ci.block * p.k_blk;
+    const char *src;
+    if (kOffsets) {
+      src = offsets_page(p.s, p.num_blocks, ref.seq, ref.lb, kv);
+      if (src == nullptr) continue;
+    } else {
+      src = kv ? p.v_base + ci.block * p.v_blk : p.k_base + ci.block * p.k_blk;
+    }
     char *dst = (kv ? p.value_out : p.key_out) + ci.out_off;
     const int64_t tok_b = kv ? p.v_tok : p.k_tok;
     const int64_t head_b = kv ? p.v_head : p.k_head;
@@ -1742,8 +1796,11 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
   }
   // PACKED as in the reference; RAGGED (one page id per cached token, KVX_SPEC.md:108-114) is
   // executed here, the reference answers UNSUPPORTED for it (kernels/kvx_paged_kv.cu:788-790).
+  // KV_OFFSETS (KVX_SPEC.md:116-122), also UNSUPPORTED in the reference, is executed for
+  // beam_width 1: the output has one row per sequence, so there is no place for more beams.
   const bool ragged = gather->block_table.format == KVX_BLOCK_TABLE_RAGGED;
-  if (gather->block_table.format != KVX_BLOCK_TABLE_PACKED && !ragged) return KVX_STATUS_UNSUPPORTED;
+  const bool offsets = gather->block_table.format == KVX_BLOCK_TABLE_KV_OFFSETS;
+  if (gather->block_table.format != KVX_BLOCK_TABLE_PACKED && !ragged && !offsets) return KVX_STATUS_UNSUPPORTED;
   if (gather->io.num_kv_heads != cache->num_kv_heads || gather->io.head_dim != cache->head_dim)
     return KVX_STATUS_INVALID_ARGUMENT;
   if (gather->seq_lens.seq_count != gather->block_table.seq_count) return KVX_STATUS_INVALID_ARGUMENT;
@@ -1789,6 +1846,24 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
   gs.max_seq_len = static_cast<int32_t>(L);
   gs.indptr = nullptr;
   gs.indptr64 = 0;
+  gs.pool[0] = gs.pool[1] = nullptr;
+  gs.pool_block_bytes = 0;
+  gs.beam_width = 1;
+  if (offsets) {  // same rules as the validate-only entry point (reference: kvx_abi.c:161-189)
+    const kvx_block_table_t &bt = gather->block_table;
+    if (bt.index_dtype != KVX_DTYPE_S32 || (bt.flags & KVX_BLOCK_TABLE_FLAG_KVCACHEINDEX) == 0 ||
+        bt.beam_width == 0 || !is_pow2(cache->block_size) ||
+        static_cast<uint64_t>(bt.indices_count) !=
+            static_cast<uint64_t>(bt.seq_count) * bt.beam_width * 2 * bt.max_blocks_per_seq ||
+        bt.indptr != nullptr || bt.indptr_count != 0 || cache->pool.size < sizeof(kvx_pool_desc_t) ||
+        cache->pool.bytes_per_block == 0 || cache->pool.primary == nullptr)
+      return KVX_STATUS_INVALID_ARGUMENT;
+    if (bt.beam_width != 1) return KVX_STATUS_UNSUPPORTED;
+    gs.pool[0] = static_cast<const char *>(cache->pool.primary);
+    gs.pool[1] = static_cast<const char *>(cache->pool.secondary);
+    gs.pool_block_bytes = cache->pool.bytes_per_block;
+    gs.beam_width = 1;
+  }
   if (ragged) {  // same rules as the validate-only entry point (reference: kvx_abi.c:142-160)
     const kvx_block_table_t &bt = gather->block_table;
     if ((bt.indptr_dtype != KVX_DTYPE_S32 && bt.indptr_dtype != KVX_DTYPE_S64) || bt.beam_width != 1 ||
@@ -1808,7 +1883,9 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
   const bool vec_ok = !g_opt.force_generic && (D * io_elem) % 16 == 0 && aligned(gather->io.key.data, 16) &&
                       aligned(gather->io.value.data, 16) && view_vectorisable(gp.k, elem, D, in_vec) &&
                       view_vectorisable(gp.v, elem, D, in_vec) && chunk_vecs < (int64_t{1} << 30) &&
-                      S * static_cast<int64_t>(gs.max_blocks) < (int64_t{1} << 31);
+                      S * static_cast<int64_t>(gs.max_blocks) < (int64_t{1} << 31) &&
+                      (!offsets || (aligned(gs.pool[0], in_vec) && aligned(gs.pool[1], in_vec) &&
+                                    gs.pool_block_bytes % in_vec == 0));
   if (vec_ok && !(ragged && (fp8 || S > 65535))) {
     GatherPagesParams p;
     p.k_base = gp.k.base, p.k_blk = gp.k.blk, p.k_tok = gp.k.tok, p.k_head = gp.k.head;
@@ -1852,7 +1929,7 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
                                   gp.k.tok == H * D * elem && gp.v.tok == H * D * elem;
     const size_t prefix_bytes = p.use_prefix ? static_cast<size_t>(S + 1) * sizeof(int32_t) : 0;
 
-    if (contiguous_pages && g_opt.gather_path == 1) {
+    if (contiguous_pages && g_opt.gather_path == 1 && !offsets) {
       // ---- bulk tier ----
       BulkParams bp;
       bp.g = p;
@@ -1907,7 +1984,9 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
     if (fp8) {
 #define KVX_F8_GATHER(IoT)                                                                     \
   do {                                                                                         \
-    if (s32)                                                                                   \
+    if (offsets)                                                                               \
+      launch_streaming(kvx_gather_f8_kernel<IoT, int32_t, 4, true>, ug, kGatherThreads, prefix_bytes, cs, p); \
+    else if (s32)                                                                              \
       launch_streaming(kvx_gather_f8_kernel<IoT, int32_t, 4>, ug, kGatherThreads, prefix_bytes, cs, p);      \
     else                                                                                       \
       launch_streaming(kvx_gather_f8_kernel<IoT, int64_t, 4>, ug, kGatherThreads, prefix_bytes, cs, p);      \
@@ -1919,6 +1998,13 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
       else
         KVX_F8_GATHER(F32);
 #undef KVX_F8_GATHER
+      return finish_launch();
+    }
+    if (offsets) {  // K and V pages are looked up separately; 16-byte vectors, any in-page pitch
+      if (contiguous_pages)
+        launch_streaming(kvx_gather_pages_kernel<int32_t, false, 8, true>, ug, kGatherThreads, prefix_bytes, cs, p);
+      else
+        launch_streaming(kvx_gather_pages_kernel<int32_t, true, 8, true>, ug, kGatherThreads, prefix_bytes, cs, p);
       return finish_launch();
     }
     if (g_opt.gather_path == 2) {  // warp-granular items

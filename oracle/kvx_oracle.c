@@ -271,7 +271,7 @@ kvx_status_t kvx_oracle_write_kv(const kvx_cache_desc_t *cache, const kvx_write_
 
 /* One tensor of a gather.  kernels/kvx_paged_kv.cu:232-266; additionally a block id
  * >= num_blocks is skipped (the reference reads out of bounds there). */
-static void gather_one(const kvx_cache_desc_t *c, const kvx_tensor_desc_t *pages,
+static void gather_one(const kvx_cache_desc_t *c, const kvx_tensor_desc_t *pages, int kv,
                        const kvx_tensor_desc_t *dst, const kvx_gather_desc_t *g, const float *scale,
                        int64_t scale_stride) {
   const int64_t H = c->num_kv_heads, D = c->head_dim, bs = c->block_size;
@@ -285,7 +285,23 @@ static void gather_one(const kvx_cache_desc_t *c, const kvx_tensor_desc_t *pages
       if (tok >= len) continue;
       const int64_t lb = tok / bs;
       int64_t block;
-      if (g->block_table.format == KVX_BLOCK_TABLE_RAGGED) {
+      const char *page_base = (const char *)pages->data; /* block 0 of the tensor */
+      if (g->block_table.format == KVX_BLOCK_TABLE_KV_OFFSETS) {
+        /* TensorRT-LLM form (KVX_SPEC.md:116-122, KV_CACHE_LAYOUTS.md:89-96): int32 table
+         * [S, beam_width, 2, max_blocks]; [s][0][0][lb] names the K page, [s][0][1][lb] the V
+         * page.  Bit 31 selects the secondary pool, the low 31 bits count pool blocks:
+         * page = pool + offset * bytes_per_block; inside the page the tensor's own strides
+         * apply.  Skipped: a secondary entry without a secondary pool, an offset that is not
+         * below num_blocks.  The reference does not execute this format. */
+        uint32_t e;
+        const char *pool;
+        if (lb >= mb) continue;
+        e = ((const uint32_t *)g->block_table.indices)[((s * g->block_table.beam_width) * 2 + kv) * mb + lb];
+        pool = (const char *)((e >> 31) ? c->pool.secondary : c->pool.primary);
+        if (pool == NULL || (e & 0x7FFFFFFFu) >= c->num_blocks) continue;
+        page_base = pool + (size_t)(e & 0x7FFFFFFFu) * c->pool.bytes_per_block;
+        block = 0;
+      } else if (g->block_table.format == KVX_BLOCK_TABLE_RAGGED) {
         /* One page id per cached token: indices[indptr[s] + tok] for tok below
          * indptr[s + 1] - indptr[s]; offset in the page is tok % block_size
          * (KVX_SPEC.md:108-114).  The reference does not execute this format. */
@@ -304,10 +320,10 @@ static void gather_one(const kvx_cache_desc_t *c, const kvx_tensor_desc_t *pages
           const int64_t oi = ((s * Lmax + tok) * H + h) * D + d;
           const int64_t ci = page_offset(pages, block, off, h, d);
           if (dequant) {
-            const float f = kvx_oracle_e4m3_to_f32(((const uint8_t *)pages->data)[ci]);
+            const float f = kvx_oracle_e4m3_to_f32(((const uint8_t *)page_base)[ci]);
             store_from_f32(dst->data, dst->dtype, oi, f * scale[h * scale_stride]);
           } else {
-            memcpy((char *)dst->data + (size_t)oi * E, (const char *)pages->data + (size_t)ci * E, E);
+            memcpy((char *)dst->data + (size_t)oi * E, page_base + (size_t)ci * E, E);
           }
         }
       }
@@ -321,8 +337,13 @@ kvx_status_t kvx_oracle_gather_kv(const kvx_cache_desc_t *cache, const kvx_gathe
   int64_t kss = 0, vss = 0;
   if (cache == NULL || gather == NULL) return KVX_STATUS_INVALID_ARGUMENT;
   if (!layout_known(cache->k.layout) || !layout_known(cache->v.layout)) return KVX_STATUS_UNSUPPORTED;
-  if (gather->block_table.format != KVX_BLOCK_TABLE_PACKED && gather->block_table.format != KVX_BLOCK_TABLE_RAGGED)
+  if (gather->block_table.format != KVX_BLOCK_TABLE_PACKED && gather->block_table.format != KVX_BLOCK_TABLE_RAGGED &&
+      gather->block_table.format != KVX_BLOCK_TABLE_KV_OFFSETS)
     return KVX_STATUS_UNSUPPORTED;
+  if (gather->block_table.format == KVX_BLOCK_TABLE_KV_OFFSETS &&
+      (gather->block_table.beam_width != 1 || gather->block_table.index_dtype != KVX_DTYPE_S32 ||
+       cache->pool.primary == NULL || cache->pool.bytes_per_block == 0))
+    return gather->block_table.beam_width > 1 ? KVX_STATUS_UNSUPPORTED : KVX_STATUS_INVALID_ARGUMENT;
   if (gather->block_table.index_dtype != gather->seq_lens.dtype) return KVX_STATUS_INVALID_ARGUMENT;
   if (gather->seq_lens.dtype != KVX_DTYPE_S32 && gather->seq_lens.dtype != KVX_DTYPE_S64)
     return KVX_STATUS_INVALID_ARGUMENT;
@@ -335,8 +356,8 @@ kvx_status_t kvx_oracle_gather_kv(const kvx_cache_desc_t *cache, const kvx_gathe
   } else if (gather->io.key.dtype != cache->k.dtype || gather->io.value.dtype != cache->v.dtype) {
     return KVX_STATUS_UNSUPPORTED;
   }
-  gather_one(cache, &cache->k, &gather->io.key, gather, ks, kss);
-  gather_one(cache, &cache->v, &gather->io.value, gather, vs, vss);
+  gather_one(cache, &cache->k, 0, &gather->io.key, gather, ks, kss);
+  gather_one(cache, &cache->v, 1, &gather->io.value, gather, vs, vss);
   return KVX_STATUS_OK;
 }
 

@@ -198,3 +198,65 @@ def expected_gather_ragged_numpy(case: Case, cache_k: np.ndarray, cache_v: np.nd
                 out[s, tok] = pool[b, o] if g.layout == abi.LAYOUT_NHD else pool[b, :, o, :]
         outs.append(out)
     return outs[0], outs[1]
+
+
+def to_kv_offsets(case: Case, cache_k: np.ndarray, cache_v: np.ndarray, seed: int = 0, secondary_frac: float = 0.3,
+                  with_secondary: bool = True, unused: int = 0x7FFFFFFF) -> Case:
+    """The same gather expressed the TensorRT-LLM way (KVX_SPEC.md:116-122): every K page and
+    every V page of the canonical pools ``cache_k`` / ``cache_v`` becomes one block of a
+    primary or (for a seeded fraction of the blocks) a secondary pool, at a seeded position;
+    the int32 table ``[S, 1, 2, max_blocks]`` holds the pool offsets, bit 31 set for the
+    secondary pool.  Table entries that PACKED marks invalid get ``unused`` (an offset beyond
+    the pool).  With ``with_secondary=False`` the secondary pool is withheld, so its entries
+    must be skipped.  The gather result must equal the PACKED one (where pages are present)."""
+    import dataclasses
+    g = case.geom
+    assert case.k_stride is None and g.layout in (abi.LAYOUT_NHD, abi.LAYOUT_HND)
+    rng = np.random.default_rng(seed)
+    NB = g.num_blocks
+    page = g.elems // NB                      # elements per page
+    pages = np.concatenate([cache_k.reshape(NB, page), cache_v.reshape(NB, page)])  # K pages then V pages
+    in_secondary = rng.random(2 * NB) < secondary_frac
+    pools, where = [], np.zeros(2 * NB, dtype=np.uint32)
+    for flag in (False, True):
+        ids = np.flatnonzero(in_secondary == flag)
+        spots = rng.permutation(2 * NB)[: len(ids)]     # scattered over a pool of 2 NB blocks
+        pool = sentinel_fill(2 * NB * page, case.cache_dtype).reshape(2 * NB, page)
+        pool[spots] = pages[ids]
+        where[ids] = spots.astype(np.uint32) | (np.uint32(0x80000000) if flag else np.uint32(0))
+        pools.append(pool.reshape(-1))
+    S, M = case.table.shape
+    table = np.full((S, 1, 2, M), unused, dtype=np.uint32)
+    for s in range(S):
+        for lb in range(M):
+            b = int(case.table[s, lb])
+            if 0 <= b < NB:
+                table[s, 0, 0, lb] = where[b]
+                table[s, 0, 1, lb] = where[NB + b]
+    geom = abi.CacheGeometry(2 * NB, g.block_size, g.num_kv_heads, g.head_dim, g.layout, g.pack)
+    return dataclasses.replace(case, geom=geom, kv_offsets=table.view(np.int32), pool_primary=pools[0],
+                               pool_secondary=pools[1] if with_secondary else None,
+                               pool_block_bytes=page * pools[0].dtype.itemsize,
+                               lens=case.lens.astype(np.int32), table=case.table.astype(np.int32),
+                               keep=[in_secondary])
+
+
+def expected_without_secondary(packed: Case, off: Case, packed_k: np.ndarray, packed_v: np.ndarray):
+    """Expected KV_OFFSETS gather when the secondary pool is withheld: the PACKED result, with
+    the rows whose K (resp. V) page went to the secondary pool left as they were."""
+    in_secondary = off.keep[0]
+    NB, bs = packed.geom.num_blocks, packed.geom.block_size
+    ek, ev = packed_k.copy(), packed_v.copy()
+    for s in range(packed.table.shape[0]):
+        for tok in range(min(int(packed.lens[s]), packed.max_seq_len)):
+            lb = tok // bs
+            if lb >= packed.table.shape[1]:
+                continue
+            b = int(packed.table[s, lb])
+            if not 0 <= b < NB:
+                continue
+            if in_secondary[b]:
+                ek[s, tok] = packed.out_k[s, tok]
+            if in_secondary[NB + b]:
+                ev[s, tok] = packed.out_v[s, tok]
+    return ek, ev

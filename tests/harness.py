@@ -79,6 +79,12 @@ class Case:
     # RAGGED form of the block table (one page id per cached token); used instead of `table`
     ragged: Optional[np.ndarray] = None    # [sum(counts)] int32 / int64
     indptr: Optional[np.ndarray] = None    # [S + 1] int32 / int64
+    # KV_OFFSETS form (TensorRT-LLM): K and V pages live in block pools; used instead of `table`
+    # for the lookup and instead of cache_k / cache_v for the data
+    kv_offsets: Optional[np.ndarray] = None      # [S, beam_width, 2, max_blocks] int32 (bit 31 = secondary)
+    pool_primary: Optional[np.ndarray] = None    # 1-D raw bits
+    pool_secondary: Optional[np.ndarray] = None  # 1-D raw bits or None
+    pool_block_bytes: int = 0
     note: str = ""
     keep: list = field(default_factory=list)
 
@@ -108,8 +114,16 @@ def descriptors(case: Case, bufs: dict, memory: int):
     """(cache, write, gather, k_scale, v_scale) descriptors over the buffers in ``bufs``
     (numpy arrays for the host, torch tensors for the device)."""
     g = case.geom
-    cache = abi.cache_desc(g, case.cache_dtype, _addr(bufs["cache_k"]), _addr(bufs["cache_v"]), memory,
-                           case.k_stride, case.v_stride)
+    if case.kv_offsets is not None:
+        base = _addr(bufs["pool_primary"])
+        cache = abi.cache_desc(g, case.cache_dtype, base, base, memory, case.k_stride, case.v_stride)
+        cache.pool.memory = memory
+        cache.pool.bytes_per_block = case.pool_block_bytes
+        cache.pool.primary = base
+        cache.pool.secondary = _addr(bufs["pool_secondary"]) if "pool_secondary" in bufs else None
+    else:
+        cache = abi.cache_desc(g, case.cache_dtype, _addr(bufs["cache_k"]), _addr(bufs["cache_v"]), memory,
+                               case.k_stride, case.v_stride)
     ks, vs = _scale(case, bufs.get("k_scale"), "k"), _scale(case, bufs.get("v_scale"), "v")
     write = abi.write_desc(case.T, g.num_kv_heads, g.head_dim, case.io_dtype, _addr(bufs["key"]),
                            _addr(bufs["value"]), index_code(case.slots), _addr(bufs["slots"]), memory, ks, vs)
@@ -125,11 +139,16 @@ def descriptors(case: Case, bufs: dict, memory: int):
             b.indptr_dtype = index_code(case.indptr)
             b.indices, b.indices_count = _addr(bufs["ragged"]), int(case.ragged.shape[0])
             b.indptr, b.indptr_count = _addr(bufs["indptr"]), int(case.indptr.shape[0])
+        if case.kv_offsets is not None:
+            b = gather.block_table
+            b.format, b.flags = abi.TABLE_KV_OFFSETS, abi.TABLE_FLAG_KVCACHEINDEX
+            b.beam_width, b.max_blocks_per_seq = int(case.kv_offsets.shape[1]), int(case.kv_offsets.shape[3])
+            b.indices, b.indices_count = _addr(bufs["kv_offsets"]), int(case.kv_offsets.size)
     return cache, write, gather, ks, vs
 
 
 _FIELDS = ("key", "value", "slots", "cache_k", "cache_v", "k_scale", "v_scale", "table", "lens", "out_k", "out_v",
-           "ragged", "indptr")
+           "ragged", "indptr", "kv_offsets", "pool_primary", "pool_secondary")
 
 
 def host_buffers(case: Case) -> dict:

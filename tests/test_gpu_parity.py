@@ -215,6 +215,47 @@ def test_ragged_block_table_gather_fp8():
     check_gather(cases.to_ragged(packed), k, v)
 
 
+@pytest.mark.parametrize("dtype", [abi.DTYPE_BF16, abi.DTYPE_F32])
+@pytest.mark.parametrize("layout", [abi.LAYOUT_NHD, abi.LAYOUT_HND])
+def test_kv_offsets_block_table_gather(layout, dtype):
+    """KV_OFFSETS tables (TensorRT-LLM form: separate K and V page offsets into a primary and a
+    secondary pool, bit 31 selecting the pool), which the reference validates but answers
+    UNSUPPORTED for: vector tier and generic tier (odd head_dim), entries beyond the pool,
+    a withheld secondary pool; the result must also equal the PACKED gather of the same pages."""
+    for i, kw in enumerate([
+        dict(heads=8, dim=128, block_size=16, num_blocks=60, lens=[100, 17, 256, 1, 0, 333], bad_blocks=3),
+        dict(heads=2, dim=64, block_size=32, num_blocks=30, lens=[31, 33, 160]),
+        dict(heads=1, dim=7, block_size=4, num_blocks=16, lens=[9, 4, 0, 6]),
+        dict(heads=3, dim=24, block_size=8, num_blocks=40, lens=[50, 70], max_seq_len=40),
+    ]):
+        packed = cases.make_case(900 + i, layout=layout, dtype=dtype, **kw)
+        _, k, v = oracle_write(packed)
+        _, pk, pv = oracle_gather(packed, k, v)
+        off = cases.to_kv_offsets(packed, k, v, seed=i)
+        off.note = f"kv_offsets {i}"
+        check_gather(off, k, v)
+        check_gather(off, k, v, "typed")
+        st, gk, gv = gpu_gather(off, k, v)
+        assert np.array_equal(gk, pk) and np.array_equal(gv, pv)
+        bare = cases.to_kv_offsets(packed, k, v, seed=i, with_secondary=False)
+        check_gather(bare, k, v)
+        ek, ev = cases.expected_without_secondary(packed, bare, pk, pv)
+        st, gk, gv = gpu_gather(bare, k, v)
+        assert np.array_equal(gk, ek) and np.array_equal(gv, ev)
+
+
+def test_kv_offsets_block_table_gather_fp8():
+    packed = cases.make_case(950, dtype=abi.DTYPE_BF16, cache_dtype=abi.DTYPE_F8_E4M3, real_values=True, heads=4,
+                             dim=64, block_size=16, num_blocks=24, lens=[100, 40, 7], scale_gran=abi.SCALE_PER_HEAD,
+                             layout=abi.LAYOUT_HND)
+    _, k, v = oracle_write(packed)
+    _, pk, pv = oracle_gather(packed, k, v)
+    off = cases.to_kv_offsets(packed, k, v, seed=5)
+    check_gather(off, k, v)
+    st, gk, gv = gpu_gather(off, k, v)
+    assert np.array_equal(gk, pk) and np.array_equal(gv, pv)
+
+
 def test_empty_and_degenerate_batches():
     case = cases.make_case(3, dtype=abi.DTYPE_F16, heads=2, dim=64, lens=[0, 0], num_blocks=4)
     assert case.T == 0

@@ -118,8 +118,28 @@ def test_gather_launcher_statuses(built_lib):
     assert G(L, cache(), gather(abi.DTYPE_F32)) == UNSUPPORTED
     g = gather(); g.block_table.format = abi.TABLE_RAGGED      # RAGGED is executed here; without indptr it is malformed
     assert G(L, cache(), g) == INVALID
-    g = gather(); g.block_table.format = abi.TABLE_KV_OFFSETS
-    assert G(L, cache(), g) == UNSUPPORTED
+    # KV_OFFSETS is executed here too: the validate-only entry point's rules (reference:
+    # kvx_abi.c:161-189), then UNSUPPORTED for more than one beam
+    def offsets(beams=1):
+        g = gather()
+        b = g.block_table
+        b.format, b.flags, b.beam_width = abi.TABLE_KV_OFFSETS, abi.TABLE_FLAG_KVCACHEINDEX, beams
+        b.indices_count = b.seq_count * beams * 2 * b.max_blocks_per_seq
+        c = cache()
+        c.pool.bytes_per_block, c.pool.primary = 64, FAKE
+        return c, g
+    c, g = offsets(); g.block_table.flags = 0
+    assert G(L, c, g) == INVALID
+    c, g = offsets(); c.pool.primary = None
+    assert G(L, c, g) == INVALID
+    c, g = offsets(); c.pool.bytes_per_block = 0
+    assert G(L, c, g) == INVALID
+    c, g = offsets(); g.block_table.indices_count -= 1
+    assert G(L, c, g) == INVALID
+    c, g = offsets(); c.block_size = 3; c.k.shape[1] = c.v.shape[1] = 3
+    assert G(L, c, g) == INVALID                            # block_size must be a power of two
+    c, g = offsets(2)
+    assert G(L, c, g) == UNSUPPORTED
     g = gather(); g.io.num_kv_heads = 3
     assert G(L, cache(), g) == INVALID
     g = gather(); g.seq_lens.seq_count = 1
@@ -193,7 +213,7 @@ for it in range(8000):
     c, w, g = cache(dt, layout, pack), write(dt), gather(dt)
     for _ in range(rng.choice([1, 1, 2])):
         _mutate(rng, rng.choice([c, w, g]))
-    if abi.DTYPE_F8_E4M3 in (c.k.dtype, c.v.dtype) or g.block_table.format == abi.TABLE_RAGGED:
+    if abi.DTYPE_F8_E4M3 in (c.k.dtype, c.v.dtype) or g.block_table.format in (abi.TABLE_RAGGED, abi.TABLE_KV_OFFSETS):
         continue  # this ABI's extensions
     tps = rng.choice([0, 1, 2, 3, 4])
     for name, args in (("kvx_launch_write_kv", (C.byref(c), C.byref(w), None)),

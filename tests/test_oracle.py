@@ -110,6 +110,32 @@ def test_ragged_table_gather_matches_numpy_statement(layout):
                 assert np.array_equal(rk, pk) and np.array_equal(rv, pv)
 
 
+@pytest.mark.parametrize("layout", [abi.LAYOUT_NHD, abi.LAYOUT_HND])
+def test_kv_offsets_table_gather_equals_packed(layout):
+    """KV_OFFSETS tables (KVX_SPEC.md:116-122): K and V pages scattered over a primary and a
+    secondary pool give the PACKED result of the same pages; without the secondary pool its
+    pages are skipped; more than one beam is UNSUPPORTED."""
+    for seed, kw in enumerate([dict(lens=[9, 4, 0, 13], num_blocks=16), dict(lens=[5, 12], max_seq_len=7, bad_blocks=2),
+                               dict(lens=[20, 3], block_size=8, num_blocks=8, max_blocks=2)]):
+        packed = cases.make_case(450 + seed, layout=layout, dtype=abi.DTYPE_BF16, **kw)
+        _, k, v = oracle_write(packed)
+        _, pk, pv = oracle_gather(packed, k, v)
+        off = cases.to_kv_offsets(packed, k, v, seed=seed)
+        st, ok_, ov_ = oracle_gather(off)
+        assert st == abi.STATUS_OK
+        assert np.array_equal(ok_, pk) and np.array_equal(ov_, pv)
+        bare = cases.to_kv_offsets(packed, k, v, seed=seed, with_secondary=False)
+        st, ok_, ov_ = oracle_gather(bare)
+        assert st == abi.STATUS_OK
+        ek, ev = cases.expected_without_secondary(packed, bare, pk, pv)
+        assert np.array_equal(ok_, ek) and np.array_equal(ov_, ev)
+        if seed == 0:
+            assert not np.array_equal(ek, pk), "the case should have pages in the secondary pool"
+    import dataclasses
+    beams = dataclasses.replace(off, kv_offsets=np.repeat(off.kv_offsets, 2, axis=1))
+    assert oracle_gather(beams)[0] == abi.STATUS_UNSUPPORTED
+
+
 def test_noncanonical_strides_and_untouched_bytes():
     for layout in (abi.LAYOUT_NHD, abi.LAYOUT_HND):
         case = cases.make_case(7, layout=layout, stride_pad=(16, 8, 8), pad_frac=0.2, lens=[6, 3])
