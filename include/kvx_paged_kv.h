@@ -128,6 +128,21 @@ KVX_API kvx_status_t kvx_launch_gather_kv_f8e4m3(const kvx_cache_desc_t *cache,
                                                  const kvx_scale_desc_t *k_scale,
                                                  const kvx_scale_desc_t *v_scale, void *stream);
 
+/* Un-padded gather (no reference counterpart; the reference's gather only writes the padded
+ * [seq_count, max_seq_len, heads, dim] rectangle).  gather->io.key / value are dense 3-D
+ * [rows, heads, dim] tensors with rows = gather->io.num_tokens; `out_indptr` is a DEVICE array
+ * of seq_count + 1 row numbers (S32 or S64, `out_indptr_dtype`), normally the prefix sums of
+ * the sequence lengths.  Token tok of sequence s is written to row out_indptr[s] + tok for
+ *     tok < min(seq_lens[s], max_seq_len, out_indptr[s + 1] - out_indptr[s]),
+ * and never at or beyond `rows`; a sequence with a negative out_indptr is skipped.  All block
+ * table formats and the fp8 cache are accepted; k_scale / v_scale are read only for an fp8
+ * cache (NULL otherwise).  Every other check and status is that of kvx_launch_gather_kv. */
+KVX_API kvx_status_t kvx_launch_gather_kv_varlen(const kvx_cache_desc_t *cache,
+                                                 const kvx_gather_desc_t *gather, const void *out_indptr,
+                                                 kvx_dtype_t out_indptr_dtype,
+                                                 const kvx_scale_desc_t *k_scale,
+                                                 const kvx_scale_desc_t *v_scale, void *stream);
+
 /* Per-head (or per-tensor) scales of one write batch: scale = absmax / 448, absmax taken
  * over every token and dim of the head (PER_HEAD) or of the tensor (PER_TENSOR), K and V
  * separately; an absmax of zero (or NaN) yields 1.0f.  Outputs are F32 device arrays of

@@ -18,7 +18,7 @@ EXPORTS = [
     "kvx_launch_write_kv_prefill_f32", "kvx_launch_write_kv_prefill_f16",
     "kvx_launch_write_kv_prefill_bf16", "kvx_launch_gather_kv_f32", "kvx_launch_gather_kv_f16",
     "kvx_launch_gather_kv_bf16", "kvx_launch_write_kv_f8e4m3", "kvx_launch_gather_kv_f8e4m3",
-    "kvx_kv_scales_workspace_bytes", "kvx_launch_kv_scales", "kvx_launch_kv_scales_static",
+    "kvx_launch_gather_kv_varlen", "kvx_kv_scales_workspace_bytes", "kvx_launch_kv_scales", "kvx_launch_kv_scales_static",
     "kvx_b200_launch_count",
     "kvx_b200_reset_launch_count", "kvx_b200_set_option", "kvx_b200_get_option",
     "kvx_host_pipe_create", "kvx_host_pipe_destroy", "kvx_host_write_kv", "kvx_host_gather_kv",
@@ -58,6 +58,9 @@ def lib() -> C.CDLL:
     L.kvx_launch_gather_kv_f8e4m3.argtypes = [P(abi.CacheDesc), P(abi.GatherDesc), P(abi.ScaleDesc),
                                               P(abi.ScaleDesc), C.c_void_p]
     L.kvx_launch_gather_kv_f8e4m3.restype = st
+    L.kvx_launch_gather_kv_varlen.argtypes = [P(abi.CacheDesc), P(abi.GatherDesc), C.c_void_p, C.c_int,
+                                              P(abi.ScaleDesc), P(abi.ScaleDesc), C.c_void_p]
+    L.kvx_launch_gather_kv_varlen.restype = st
     L.kvx_kv_scales_workspace_bytes.argtypes, L.kvx_kv_scales_workspace_bytes.restype = [C.c_uint32], C.c_size_t
     L.kvx_launch_kv_scales.argtypes = [P(abi.KvIoDesc), C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
                                        C.c_size_t, C.c_void_p]

@@ -701,6 +701,11 @@ struct GatherShape {
   const char *pool[2];  // primary, secondary (may be NULL); pool[0] == NULL = not KV_OFFSETS
   int64_t pool_block_bytes;
   int32_t beam_width;
+  // Un-padded output (kvx_launch_gather_kv_varlen): token tok of sequence s goes to output row
+  // out_indptr[s] + tok while that stays below out_indptr[s + 1] and below out_rows.
+  const void *out_indptr;  // NULL = padded [S, max_seq_len, H, D] output
+  int32_t out_indptr64;
+  int64_t out_rows;
 };
 
 // First byte of the K (kv = 0) or V (kv = 1) page of logical block lb of sequence seq in a
@@ -726,6 +731,24 @@ __device__ __forceinline__ int64_t read_idx(const void *p, int64_t i) {
   return static_cast<int64_t>(static_cast<const IdxT *>(p)[i]);
 }
 
+// Where sequence `seq` lands in the output: its first row, and how many of its tokens may be
+// written (seq_lens, max_seq_len and, for the un-padded form, the rows set aside for it).
+struct OutSpan {
+  int64_t first_row, tokens;
+};
+
+template <typename IdxT>
+__device__ __forceinline__ OutSpan out_span(const GatherShape &s, int32_t seq) {
+  const int64_t len = min(read_idx<IdxT>(s.lens, seq), static_cast<int64_t>(s.max_seq_len));
+  if (s.out_indptr == nullptr) return OutSpan{static_cast<int64_t>(seq) * s.max_seq_len, len};
+  const int64_t first = s.out_indptr64 ? static_cast<const int64_t *>(s.out_indptr)[seq]
+                                       : static_cast<int64_t>(static_cast<const int32_t *>(s.out_indptr)[seq]);
+  const int64_t next = s.out_indptr64 ? static_cast<const int64_t *>(s.out_indptr)[seq + 1]
+                                      : static_cast<int64_t>(static_cast<const int32_t *>(s.out_indptr)[seq + 1]);
+  if (first < 0) return OutSpan{0, 0};
+  return OutSpan{first, min(len, min(next, s.out_rows) - first)};
+}
+
 // One output element per thread over the padded [S, Lmax, H, D] rectangle.
 template <typename IoT, typename CacheT, typename IdxT, bool kDequant>
 __global__ void __launch_bounds__(256)
@@ -740,7 +763,9 @@ __global__ void __launch_bounds__(256)
   const int32_t d = rem - h * p.g.dim;
   const int32_t seq = static_cast<int32_t>(row / s.max_seq_len);
   const int32_t tok = static_cast<int32_t>(row - static_cast<int64_t>(seq) * s.max_seq_len);
-  if (tok >= read_idx<IdxT>(s.lens, seq)) return;
+  const OutSpan span = out_span<IdxT>(s, seq);
+  if (tok >= span.tokens) return;
+  const int64_t out = (span.first_row + tok) * hd + rem;  // element index in the output tensors
   const int32_t lb = tok / p.g.block_size;
   const int64_t o = tok - static_cast<int64_t>(lb) * p.g.block_size;
   const char *kp, *vp;  // the element's address in its K / V page, NULL = skipped
@@ -767,21 +792,21 @@ __global__ void __launch_bounds__(256)
   if (kp != nullptr) {
     const CacheT q = load_elem<CacheT>(kp);
     if (kDequant) {
-      key_out[idx] = from_f32(e4m3x2_to_f32(q.bits).x * __ldg(p.ks.base + h * p.ks.stride), IoT{});
+      key_out[out] = from_f32(e4m3x2_to_f32(q.bits).x * __ldg(p.ks.base + h * p.ks.stride), IoT{});
     } else {
       IoT a;
       a.bits = q.bits;
-      key_out[idx] = a;
+      key_out[out] = a;
     }
   }
   if (vp != nullptr) {
     const CacheT q = load_elem<CacheT>(vp);
     if (kDequant) {
-      value_out[idx] = from_f32(e4m3x2_to_f32(q.bits).x * __ldg(p.vs.base + h * p.vs.stride), IoT{});
+      value_out[out] = from_f32(e4m3x2_to_f32(q.bits).x * __ldg(p.vs.base + h * p.vs.stride), IoT{});
     } else {
       IoT a;
       a.bits = q.bits;
-      value_out[idx] = a;
+      value_out[out] = a;
     }
   }
 }
@@ -878,8 +903,8 @@ __device__ __forceinline__ ChunkInfo resolve_chunk(const GatherPagesParams &p, i
   c.block = -1;
   c.tokens = 0;
   c.out_off = 0;
-  int64_t len = read_idx<IdxT>(p.s.lens, seq);
-  if (len > p.s.max_seq_len) len = p.s.max_seq_len;
+  const OutSpan span = out_span<IdxT>(p.s, seq);
+  const int64_t len = span.tokens;
   const int64_t first = static_cast<int64_t>(lb) * p.block_size;
   if (first >= len || lb >= p.s.max_blocks) return c;  // (reference: kernels/kvx_paged_kv.cu:247-253)
   if (kOffsets) {
@@ -890,7 +915,7 @@ __device__ __forceinline__ ChunkInfo resolve_chunk(const GatherPagesParams &p, i
     c.block = b;
   }
   c.tokens = static_cast<int32_t>(min(len - first, static_cast<int64_t>(p.block_size)));
-  c.out_off = (static_cast<int64_t>(seq) * p.s.max_seq_len + first) * p.out_row_bytes;
+  c.out_off = (span.first_row + first) * p.out_row_bytes;
   return c;
 }
 
@@ -1123,9 +1148,9 @@ __global__ void __launch_bounds__(kGatherThreads) kvx_gather_ragged_kernel(const
   const int tid = threadIdx.x;
   const int seq = blockIdx.y;
   const int t0 = blockIdx.x * p.part_vecs;  // part_vecs = tokens per CTA here
-  int64_t len = read_idx<IdxT>(p.s.lens, seq);
+  const OutSpan span = out_span<IdxT>(p.s, seq);
   const int64_t first = read_indptr(p.s, seq);
-  len = min(len, min(static_cast<int64_t>(p.s.max_seq_len), read_indptr(p.s, seq + 1) - first));
+  const int64_t len = min(span.tokens, read_indptr(p.s, seq + 1) - first);
   if (t0 >= len) return;
   const int ntok = static_cast<int>(min(static_cast<int64_t>(p.part_vecs), len - t0));
   if (tid < ntok) {
@@ -1141,7 +1166,7 @@ __global__ void __launch_bounds__(kGatherThreads) kvx_gather_ragged_kernel(const
     s_v[tid] = vo;
   }
   __syncthreads();
-  const int64_t out_off = (static_cast<int64_t>(seq) * p.s.max_seq_len + t0) * p.out_row_bytes;
+  const int64_t out_off = (span.first_row + t0) * p.out_row_bytes;
   char *kdst = p.key_out + out_off;
   char *vdst = p.value_out + out_off;
   const int nvec = ntok * p.vpr;
@@ -1775,9 +1800,14 @@ constexpr int kMaxPrefixSeqs = 10240;
  * Shared body of every gather entry point.
  * Check order: reference kernels/kvx_paged_kv.cu:768-829, :837-863.
  */
+struct VarlenOut {  // un-padded output of kvx_launch_gather_kv_varlen
+  const void *indptr;
+  kvx_dtype_t dtype;
+};
+
 kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t *gather,
                          const kvx_scale_desc_t *k_scale, const kvx_scale_desc_t *v_scale, void *stream,
-                         kvx_dtype_t expected) {
+                         kvx_dtype_t expected, const VarlenOut *varlen = nullptr) {
   if (cache == nullptr || gather == nullptr) return KVX_STATUS_INVALID_ARGUMENT;
   if (gather->size < sizeof(kvx_gather_desc_t) || gather->io.size < sizeof(kvx_kv_io_desc_t) ||
       gather->block_table.size < sizeof(kvx_block_table_t) || gather->seq_lens.size < sizeof(kvx_seq_lens_t))
@@ -1806,10 +1836,13 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
   if (gather->seq_lens.seq_count != gather->block_table.seq_count) return KVX_STATUS_INVALID_ARGUMENT;
   const int64_t dims[4] = {gather->block_table.seq_count, gather->max_seq_len, gather->io.num_kv_heads,
                            gather->io.head_dim};
-  kvx_status_t st = check_io_tensor(&gather->io.key, 4, dims);
+  const int64_t flat[3] = {gather->io.num_tokens, gather->io.num_kv_heads, gather->io.head_dim};
+  kvx_status_t st = varlen ? check_io_tensor(&gather->io.key, 3, flat) : check_io_tensor(&gather->io.key, 4, dims);
   if (st != KVX_STATUS_OK) return st;
-  st = check_io_tensor(&gather->io.value, 4, dims);
+  st = varlen ? check_io_tensor(&gather->io.value, 3, flat) : check_io_tensor(&gather->io.value, 4, dims);
   if (st != KVX_STATUS_OK) return st;
+  if (varlen && (varlen->indptr == nullptr || (varlen->dtype != KVX_DTYPE_S32 && varlen->dtype != KVX_DTYPE_S64)))
+    return KVX_STATUS_INVALID_ARGUMENT;
 
   const int64_t elem = dtype_bytes(expected);
   const int64_t io_elem = dtype_bytes(io_dtype);
@@ -1826,7 +1859,7 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
 
   const int64_t S = gather->block_table.seq_count, L = gather->max_seq_len;
   const int64_t H = cache->num_kv_heads, D = cache->head_dim;
-  if (S * L * H * D == 0) return KVX_STATUS_OK;
+  if (S * L * H * D == 0 || (varlen && gather->io.num_tokens == 0)) return KVX_STATUS_OK;
   const bool s32 = gather->block_table.index_dtype == KVX_DTYPE_S32 && gather->seq_lens.dtype == KVX_DTYPE_S32;
   const bool s64 = gather->block_table.index_dtype == KVX_DTYPE_S64 && gather->seq_lens.dtype == KVX_DTYPE_S64;
   if (!s32 && !s64) return KVX_STATUS_INVALID_ARGUMENT;
@@ -1849,6 +1882,9 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
   gs.pool[0] = gs.pool[1] = nullptr;
   gs.pool_block_bytes = 0;
   gs.beam_width = 1;
+  gs.out_indptr = varlen ? varlen->indptr : nullptr;
+  gs.out_indptr64 = varlen && varlen->dtype == KVX_DTYPE_S64;
+  gs.out_rows = varlen ? static_cast<int64_t>(gather->io.num_tokens) : 0;
   if (offsets) {  // same rules as the validate-only entry point (reference: kvx_abi.c:161-189)
     const kvx_block_table_t &bt = gather->block_table;
     if (bt.index_dtype != KVX_DTYPE_S32 || (bt.flags & KVX_BLOCK_TABLE_FLAG_KVCACHEINDEX) == 0 ||
@@ -2167,6 +2203,23 @@ KVX_API kvx_status_t kvx_launch_gather_kv(const kvx_cache_desc_t *cache, const k
     default:
       // An fp8 cache needs scales, which a gather descriptor cannot carry: use
       // kvx_launch_gather_kv_f8e4m3.
+      return KVX_STATUS_UNSUPPORTED;
+  }
+}
+
+KVX_API kvx_status_t kvx_launch_gather_kv_varlen(const kvx_cache_desc_t *cache, const kvx_gather_desc_t *gather,
+                                                 const void *out_indptr, kvx_dtype_t out_indptr_dtype,
+                                                 const kvx_scale_desc_t *k_scale,
+                                                 const kvx_scale_desc_t *v_scale, void *stream) {
+  if (cache == nullptr) return KVX_STATUS_INVALID_ARGUMENT;
+  const VarlenOut out{out_indptr, out_indptr_dtype};
+  switch (cache->k.dtype) {
+    case KVX_DTYPE_F32:
+    case KVX_DTYPE_F16:
+    case KVX_DTYPE_BF16:
+    case KVX_DTYPE_F8_E4M3:
+      return gather_impl(cache, gather, k_scale, v_scale, stream, cache->k.dtype, &out);
+    default:
       return KVX_STATUS_UNSUPPORTED;
   }
 }

@@ -246,6 +246,40 @@ def gather_kv(key_cache: torch.Tensor, value_cache: torch.Tensor, block_table: t
         raise KvxError("kvx cache gather", status)
 
 
+def gather_kv_varlen(key_cache: torch.Tensor, value_cache: torch.Tensor, block_table: torch.Tensor,
+                     seq_lens: torch.Tensor, out_indptr: torch.Tensor, key_out: torch.Tensor,
+                     value_out: torch.Tensor, max_seq_len: int, kv_cache_dtype: str = "auto",
+                     k_scale: Optional[torch.Tensor] = None, v_scale: Optional[torch.Tensor] = None) -> None:
+    """The gather into un-padded ``[rows, heads, dim]`` outputs (the form variable-length
+    attention kernels take, with ``out_indptr`` as their cumulative sequence lengths): token
+    ``tok`` of sequence ``s`` goes to row ``out_indptr[s] + tok`` for ``tok < min(seq_lens[s],
+    max_seq_len, out_indptr[s + 1] - out_indptr[s])``; other rows stay untouched."""
+    if block_table.dim() != 2 or not block_table.is_contiguous():
+        raise ValueError("block_table must be a contiguous [seq_count, max_blocks_per_seq] tensor")
+    if block_table.dtype not in _INDEX_CODES or seq_lens.dtype != block_table.dtype:
+        raise TypeError("block_table and seq_lens must share an int32 or int64 dtype")
+    if out_indptr.dtype not in _INDEX_CODES or out_indptr.numel() != block_table.shape[0] + 1:
+        raise ValueError("out_indptr must hold seq_count + 1 int32 or int64 row numbers")
+    if key_out.dim() != 3 or key_out.shape != value_out.shape or key_out.dtype not in _FLOAT_CODES:
+        raise ValueError("outputs must be [rows, heads, dim] float tensors")
+    rows, heads, dim = key_out.shape
+    seqs = block_table.shape[0]
+    cache = cache_desc_from_tensors(key_cache, value_cache, kv_cache_dtype, heads)
+    g = abi.gather_desc(seqs, max_seq_len, heads, dim, _FLOAT_CODES[key_out.dtype], key_out.data_ptr(),
+                        value_out.data_ptr(), _INDEX_CODES[block_table.dtype], block_table.data_ptr(),
+                        block_table.shape[1], seq_lens.data_ptr())
+    code = _FLOAT_CODES[key_out.dtype]
+    g.io.num_tokens = rows
+    g.io.key = abi.tensor_desc(key_out.data_ptr(), code, key_out.shape, key_out.stride(), abi.LAYOUT_INVALID)
+    g.io.value = abi.tensor_desc(value_out.data_ptr(), code, value_out.shape, value_out.stride(), abi.LAYOUT_INVALID)
+    g.seq_lens.seq_count = seq_lens.shape[0]
+    ks, vs = _scale_desc(k_scale, heads), _scale_desc(v_scale, heads)
+    status = lib().kvx_launch_gather_kv_varlen(C.byref(cache), C.byref(g), out_indptr.data_ptr(),
+                                               _INDEX_CODES[out_indptr.dtype], C.byref(ks), C.byref(vs), _stream())
+    if status != abi.STATUS_OK:
+        raise KvxError("kvx cache gather", status)
+
+
 def scales_workspace(heads: int, device: torch.device) -> torch.Tensor:
     """Zeroed scratch for :func:`compute_kv_scales`; reusable across calls on one stream."""
     n = lib().kvx_kv_scales_workspace_bytes(heads)

@@ -273,7 +273,7 @@ kvx_status_t kvx_oracle_write_kv(const kvx_cache_desc_t *cache, const kvx_write_
  * >= num_blocks is skipped (the reference reads out of bounds there). */
 static void gather_one(const kvx_cache_desc_t *c, const kvx_tensor_desc_t *pages, int kv,
                        const kvx_tensor_desc_t *dst, const kvx_gather_desc_t *g, const float *scale,
-                       int64_t scale_stride) {
+                       int64_t scale_stride, const void *out_indptr, kvx_dtype_t out_indptr_dtype) {
   const int64_t H = c->num_kv_heads, D = c->head_dim, bs = c->block_size;
   const int64_t S = g->block_table.seq_count, Lmax = g->max_seq_len;
   const int64_t mb = g->block_table.max_blocks_per_seq;
@@ -281,8 +281,18 @@ static void gather_one(const kvx_cache_desc_t *c, const kvx_tensor_desc_t *pages
   const int dequant = (pages->dtype == KVX_DTYPE_F8_E4M3 && dst->dtype != KVX_DTYPE_F8_E4M3);
   for (int64_t s = 0; s < S; ++s) {
     const int64_t len = read_index(g->seq_lens.lengths, g->seq_lens.dtype, s);
+    /* Un-padded output: row out_indptr[s] + tok, inside the rows set aside for the sequence
+     * and inside the tensor (no reference counterpart). */
+    int64_t row0 = s * Lmax, room = Lmax;
+    if (out_indptr != NULL) {
+      row0 = read_index(out_indptr, out_indptr_dtype, s);
+      room = read_index(out_indptr, out_indptr_dtype, s + 1);
+      if (room > (int64_t)g->io.num_tokens) room = (int64_t)g->io.num_tokens;
+      room -= row0;
+      if (row0 < 0) room = 0;
+    }
     for (int64_t tok = 0; tok < Lmax; ++tok) {
-      if (tok >= len) continue;
+      if (tok >= len || tok >= room) continue;
       const int64_t lb = tok / bs;
       int64_t block;
       const char *page_base = (const char *)pages->data; /* block 0 of the tensor */
@@ -317,7 +327,7 @@ static void gather_one(const kvx_cache_desc_t *c, const kvx_tensor_desc_t *pages
       const int64_t off = tok - lb * bs;
       for (int64_t h = 0; h < H; ++h) {
         for (int64_t d = 0; d < D; ++d) {
-          const int64_t oi = ((s * Lmax + tok) * H + h) * D + d;
+          const int64_t oi = ((row0 + tok) * H + h) * D + d;
           const int64_t ci = page_offset(pages, block, off, h, d);
           if (dequant) {
             const float f = kvx_oracle_e4m3_to_f32(((const uint8_t *)page_base)[ci]);
@@ -333,6 +343,12 @@ static void gather_one(const kvx_cache_desc_t *c, const kvx_tensor_desc_t *pages
 
 kvx_status_t kvx_oracle_gather_kv(const kvx_cache_desc_t *cache, const kvx_gather_desc_t *gather,
                                   const kvx_scale_desc_t *k_scale, const kvx_scale_desc_t *v_scale) {
+  return kvx_oracle_gather_kv_varlen(cache, gather, NULL, KVX_DTYPE_INVALID, k_scale, v_scale);
+}
+
+kvx_status_t kvx_oracle_gather_kv_varlen(const kvx_cache_desc_t *cache, const kvx_gather_desc_t *gather,
+                                         const void *out_indptr, kvx_dtype_t out_indptr_dtype,
+                                         const kvx_scale_desc_t *k_scale, const kvx_scale_desc_t *v_scale) {
   const float *ks = NULL, *vs = NULL;
   int64_t kss = 0, vss = 0;
   if (cache == NULL || gather == NULL) return KVX_STATUS_INVALID_ARGUMENT;
@@ -356,8 +372,8 @@ kvx_status_t kvx_oracle_gather_kv(const kvx_cache_desc_t *cache, const kvx_gathe
   } else if (gather->io.key.dtype != cache->k.dtype || gather->io.value.dtype != cache->v.dtype) {
     return KVX_STATUS_UNSUPPORTED;
   }
-  gather_one(cache, &cache->k, 0, &gather->io.key, gather, ks, kss);
-  gather_one(cache, &cache->v, 1, &gather->io.value, gather, vs, vss);
+  gather_one(cache, &cache->k, 0, &gather->io.key, gather, ks, kss, out_indptr, out_indptr_dtype);
+  gather_one(cache, &cache->v, 1, &gather->io.value, gather, vs, vss, out_indptr, out_indptr_dtype);
   return KVX_STATUS_OK;
 }
 

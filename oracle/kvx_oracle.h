@@ -19,6 +19,13 @@ kvx_status_t kvx_oracle_write_kv(const kvx_cache_desc_t *cache, const kvx_write_
 kvx_status_t kvx_oracle_gather_kv(const kvx_cache_desc_t *cache, const kvx_gather_desc_t *gather,
                                   const kvx_scale_desc_t *k_scale, const kvx_scale_desc_t *v_scale);
 
+/* The same gather into un-padded [rows, heads, dim] outputs: token tok of sequence s goes to
+ * row out_indptr[s] + tok while below out_indptr[s + 1] and below rows = io.num_tokens.
+ * out_indptr == NULL is the padded form. */
+kvx_status_t kvx_oracle_gather_kv_varlen(const kvx_cache_desc_t *cache, const kvx_gather_desc_t *gather,
+                                         const void *out_indptr, kvx_dtype_t out_indptr_dtype,
+                                         const kvx_scale_desc_t *k_scale, const kvx_scale_desc_t *v_scale);
+
 /* scale = absmax / 448 per head or per tensor; outputs are host float arrays. */
 kvx_status_t kvx_oracle_kv_scales(const kvx_kv_io_desc_t *io, kvx_scale_granularity_t granularity,
                                   float *k_scale_out, float *v_scale_out);

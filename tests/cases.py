@@ -260,3 +260,35 @@ def expected_without_secondary(packed: Case, off: Case, packed_k: np.ndarray, pa
             if in_secondary[NB + b]:
                 ev[s, tok] = packed.out_v[s, tok]
     return ek, ev
+
+
+def to_varlen(case: Case, indptr_dtype=np.int32, gap: int = 0, short=(), rows_cut: int = 0) -> Case:
+    """The same gather into un-padded ``[rows, H, D]`` outputs: sequence s starts at row
+    ``out_indptr[s]``.  ``gap`` leaves unused rows between sequences, ``short`` lists sequences
+    given half the rows they need (the gather must stop there), ``rows_cut`` removes rows from
+    the end of the tensors (the gather must not write past them)."""
+    import dataclasses
+    H, D = case.geom.num_kv_heads, case.geom.head_dim
+    counts = []
+    for s in range(case.table.shape[0]):
+        n = int(min(max(int(case.lens[s]), 0), case.max_seq_len))
+        counts.append((n // 2 if s in short else n) + gap)
+    indptr = np.concatenate([[0], np.cumsum(counts)]).astype(indptr_dtype)
+    rows = max(0, int(indptr[-1]) - rows_cut)
+    return dataclasses.replace(case, out_indptr=indptr,
+                               out_k=sentinel_fill(rows * H * D, case.io_dtype).reshape(rows, H, D),
+                               out_v=sentinel_fill(rows * H * D, case.io_dtype).reshape(rows, H, D))
+
+
+def expected_varlen_from_padded(case: Case, padded_k: np.ndarray, padded_v: np.ndarray, gap: int = 0):
+    """Expected un-padded outputs derived from the PADDED gather result of the same case: row
+    out_indptr[s] + tok takes padded[s, tok] where the padded gather wrote it (tok below the
+    sequence length), limited to the rows of the sequence and of the tensor."""
+    ek, ev = case.out_k.copy(), case.out_v.copy()
+    rows = ek.shape[0]
+    for s in range(case.table.shape[0]):
+        first, room = int(case.out_indptr[s]), int(case.out_indptr[s + 1] - case.out_indptr[s])
+        n = min(max(int(case.lens[s]), 0), case.max_seq_len, room, max(0, rows - first))
+        ek[first:first + n] = padded_k[s, :n]
+        ev[first:first + n] = padded_v[s, :n]
+    return ek, ev

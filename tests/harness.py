@@ -85,6 +85,9 @@ class Case:
     pool_primary: Optional[np.ndarray] = None    # 1-D raw bits
     pool_secondary: Optional[np.ndarray] = None  # 1-D raw bits or None
     pool_block_bytes: int = 0
+    # un-padded output (kvx_launch_gather_kv_varlen): out_k / out_v are [rows, H, D] and
+    # sequence s starts at row out_indptr[s]
+    out_indptr: Optional[np.ndarray] = None      # [S + 1] int32 / int64
     note: str = ""
     keep: list = field(default_factory=list)
 
@@ -139,6 +142,12 @@ def descriptors(case: Case, bufs: dict, memory: int):
             b.indptr_dtype = index_code(case.indptr)
             b.indices, b.indices_count = _addr(bufs["ragged"]), int(case.ragged.shape[0])
             b.indptr, b.indptr_count = _addr(bufs["indptr"]), int(case.indptr.shape[0])
+        if case.out_indptr is not None:
+            rows = int(case.out_k.shape[0])
+            gather.io.num_tokens = rows
+            for t, buf in ((gather.io.key, "out_k"), (gather.io.value, "out_v")):
+                new = abi.tensor_desc(_addr(bufs[buf]), case.io_dtype, (rows, g.num_kv_heads, g.head_dim), memory=memory)
+                C.memmove(C.byref(t), C.byref(new), C.sizeof(new))
         if case.kv_offsets is not None:
             b = gather.block_table
             b.format, b.flags = abi.TABLE_KV_OFFSETS, abi.TABLE_FLAG_KVCACHEINDEX
@@ -148,7 +157,7 @@ def descriptors(case: Case, bufs: dict, memory: int):
 
 
 _FIELDS = ("key", "value", "slots", "cache_k", "cache_v", "k_scale", "v_scale", "table", "lens", "out_k", "out_v",
-           "ragged", "indptr", "kv_offsets", "pool_primary", "pool_secondary")
+           "ragged", "indptr", "kv_offsets", "pool_primary", "pool_secondary", "out_indptr")
 
 
 def host_buffers(case: Case) -> dict:
@@ -193,7 +202,11 @@ def oracle_gather(case: Case, cache_k=None, cache_v=None):
     if cache_k is not None:
         b["cache_k"], b["cache_v"] = cache_k.copy(), cache_v.copy()
     cache, _, gather, ks, vs = descriptors(case, b, abi.MEMORY_HOST)
-    st = oracle().kvx_oracle_gather_kv(C.byref(cache), C.byref(gather), C.byref(ks), C.byref(vs))
+    if case.out_indptr is not None:
+        st = oracle().kvx_oracle_gather_kv_varlen(C.byref(cache), C.byref(gather), _addr(b["out_indptr"]),
+                                                  index_code(case.out_indptr), C.byref(ks), C.byref(vs))
+    else:
+        st = oracle().kvx_oracle_gather_kv(C.byref(cache), C.byref(gather), C.byref(ks), C.byref(vs))
     return st, b["out_k"], b["out_v"]
 
 
@@ -236,7 +249,10 @@ def gpu_gather(case: Case, cache_k=None, cache_v=None, entry: str = "dispatch", 
         src = dataclasses.replace(case, cache_k=cache_k, cache_v=cache_v)
     b = device_buffers(src)
     cache, _, gather, ks, vs = descriptors(src, b, abi.MEMORY_DEVICE)
-    if case.cache_dtype == abi.DTYPE_F8_E4M3:
+    if case.out_indptr is not None:
+        st = L.kvx_launch_gather_kv_varlen(C.byref(cache), C.byref(gather), _addr(b["out_indptr"]),
+                                           index_code(case.out_indptr), C.byref(ks), C.byref(vs), stream)
+    elif case.cache_dtype == abi.DTYPE_F8_E4M3:
         st = L.kvx_launch_gather_kv_f8e4m3(C.byref(cache), C.byref(gather), C.byref(ks), C.byref(vs), stream)
     elif entry == "dispatch":
         st = L.kvx_launch_gather_kv(C.byref(cache), C.byref(gather), stream)

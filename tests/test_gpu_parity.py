@@ -256,6 +256,56 @@ def test_kv_offsets_block_table_gather_fp8():
     assert np.array_equal(gk, pk) and np.array_equal(gv, pv)
 
 
+@pytest.mark.parametrize("layout", [abi.LAYOUT_NHD, abi.LAYOUT_HND])
+def test_varlen_output_gather(layout):
+    """kvx_launch_gather_kv_varlen: un-padded [rows, H, D] outputs addressed through out_indptr,
+    with every table format, both index widths, gaps, short allotments and truncated tensors;
+    the vector tiers (wide and 16-byte) and the generic tier (odd head_dim)."""
+    for i, kw in enumerate([
+        dict(heads=8, dim=128, block_size=16, num_blocks=60, lens=[100, 17, 256, 1, 0, 333], bad_blocks=3),
+        dict(heads=2, dim=64, block_size=32, num_blocks=30, lens=[31, 33, 160], index_dtype=np.int64),
+        dict(heads=1, dim=7, block_size=4, num_blocks=16, lens=[9, 4, 0, 6]),
+        dict(heads=3, dim=24, block_size=8, num_blocks=40, lens=[50, 70], max_seq_len=40),
+    ]):
+        packed = cases.make_case(1000 + i, layout=layout, dtype=abi.DTYPE_BF16, **kw)
+        _, k, v = oracle_write(packed)
+        _, pk, pv = oracle_gather(packed, k, v)
+        for vkw in (dict(), dict(indptr_dtype=np.int64, gap=3), dict(short=(0, 1)), dict(rows_cut=5)):
+            var = cases.to_varlen(packed, **vkw)
+            var.note = f"varlen {i} {vkw}"
+            check_gather(var, k, v)
+            ek, ev = cases.expected_varlen_from_padded(var, pk, pv)
+            st, gk, gv = gpu_gather(var, k, v)
+            assert np.array_equal(gk, ek) and np.array_equal(gv, ev), var.note
+        check_gather(cases.to_varlen(cases.to_ragged(packed)), k, v)
+        if packed.table.dtype == np.int32:
+            check_gather(cases.to_varlen(cases.to_kv_offsets(packed, k, v, seed=i)), k, v)
+
+
+def test_varlen_output_gather_fp8_and_statuses():
+    packed = cases.make_case(1050, dtype=abi.DTYPE_BF16, cache_dtype=abi.DTYPE_F8_E4M3, real_values=True, heads=4,
+                             dim=64, block_size=16, num_blocks=24, lens=[100, 40, 7], scale_gran=abi.SCALE_PER_HEAD)
+    _, k, v = oracle_write(packed)
+    var = cases.to_varlen(packed, gap=1)
+    check_gather(var, k, v)
+    # a 4-D output, a missing or mistyped out_indptr are refused before any launch
+    import ctypes as C
+    import kvx_b200
+    from harness import descriptors, device_buffers
+    L = kvx_b200.lib()
+    b = device_buffers(var)
+    cache, _, g, ks, vs = descriptors(var, b, abi.MEMORY_DEVICE)
+    ptr = b["out_indptr"].data_ptr()
+    assert L.kvx_launch_gather_kv_varlen(C.byref(cache), C.byref(g), None, abi.DTYPE_S32, C.byref(ks), C.byref(vs), None) \
+        == abi.STATUS_INVALID_ARGUMENT
+    assert L.kvx_launch_gather_kv_varlen(C.byref(cache), C.byref(g), ptr, abi.DTYPE_F32, C.byref(ks), C.byref(vs), None) \
+        == abi.STATUS_INVALID_ARGUMENT
+    b2 = device_buffers(packed)
+    cache2, _, g2, ks2, vs2 = descriptors(packed, b2, abi.MEMORY_DEVICE)
+    assert L.kvx_launch_gather_kv_varlen(C.byref(cache2), C.byref(g2), ptr, abi.DTYPE_S32, C.byref(ks2), C.byref(vs2), None) \
+        == abi.STATUS_INVALID_ARGUMENT
+
+
 def test_empty_and_degenerate_batches():
     case = cases.make_case(3, dtype=abi.DTYPE_F16, heads=2, dim=64, lens=[0, 0], num_blocks=4)
     assert case.T == 0

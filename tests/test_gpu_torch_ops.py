@@ -149,6 +149,31 @@ def test_ops_accept_a_logical_nhd_view_of_hnd_memory(route):
     assert np.array_equal(_bits(cv, case.cache_dtype), ev.reshape(-1))
 
 
+def test_ops_varlen_gather_matches_padded_gather():
+    import torch
+
+    from kvx_b200 import ops
+
+    case = cases.make_case(15, dtype=abi.DTYPE_BF16, num_blocks=40, block_size=16, heads=8, dim=128,
+                           lens=[70, 0, 16, 129, 5], index_dtype=np.int32)
+    _, ek, ev = oracle_write(case)
+    ck = _to_dev(torch, ek, case.cache_dtype).view(case.geom.shape)
+    cv = _to_dev(torch, ev, case.cache_dtype).view(case.geom.shape)
+    table, lens = torch.from_numpy(case.table).cuda(), torch.from_numpy(case.lens).cuda()
+    pk = torch.zeros(case.out_k.shape, dtype=torch.bfloat16, device="cuda"); pv = pk.clone()
+    ops.gather_kv(ck, cv, table, lens, pk, pv)
+    indptr = torch.cat([torch.zeros(1, dtype=torch.int32, device="cuda"), torch.cumsum(lens, 0).to(torch.int32)])
+    rows = int(indptr[-1])
+    vk = torch.full((rows, 8, 128), 3.0, dtype=torch.bfloat16, device="cuda"); vv = vk.clone()
+    ops.gather_kv_varlen(ck, cv, table, lens, indptr, vk, vv, case.max_seq_len)
+    torch.cuda.synchronize()
+    for s, n in enumerate(case.lens.tolist()):
+        a = int(indptr[s])
+        i16 = torch.int16  # compare bit patterns: the random payload contains NaNs
+        assert torch.equal(vk[a:a + n].view(i16), pk[s, :n].view(i16))
+        assert torch.equal(vv[a:a + n].view(i16), pv[s, :n].view(i16))
+
+
 def test_ops_report_the_status():
     """A launcher status other than OK surfaces as KvxError carrying it, on both routes."""
     import torch

@@ -136,6 +136,27 @@ def test_kv_offsets_table_gather_equals_packed(layout):
     assert oracle_gather(beams)[0] == abi.STATUS_UNSUPPORTED
 
 
+def test_varlen_output_gather_equals_padded_rows():
+    """Un-padded outputs: row out_indptr[s] + tok holds what the padded gather puts at [s, tok];
+    rows between sequences, beyond a short allotment and beyond the tensor stay untouched."""
+    for seed, kw in enumerate([dict(lens=[9, 4, 0, 13], num_blocks=16), dict(lens=[5, 12], max_seq_len=7, bad_blocks=2),
+                               dict(lens=[20, 3], index_dtype=np.int64, block_size=5, num_blocks=8)]):
+        packed = cases.make_case(470 + seed, dtype=abi.DTYPE_F16, **kw)
+        _, k, v = oracle_write(packed)
+        _, pk, pv = oracle_gather(packed, k, v)
+        for vkw in (dict(), dict(indptr_dtype=np.int64, gap=2), dict(short=(0,)), dict(rows_cut=3)):
+            var = cases.to_varlen(packed, **vkw)
+            st, ok_, ov_ = oracle_gather(var, k, v)
+            assert st == abi.STATUS_OK
+            ek, ev = cases.expected_varlen_from_padded(var, pk, pv)
+            assert np.array_equal(ok_, ek) and np.array_equal(ov_, ev), (seed, vkw)
+        rag = cases.to_varlen(cases.to_ragged(packed))
+        st, ok_, ov_ = oracle_gather(rag, k, v)
+        ek, ev = cases.expected_varlen_from_padded(rag, pk, pv)
+        if packed.table.shape[1] * packed.geom.block_size >= packed.max_seq_len:
+            assert np.array_equal(ok_, ek) and np.array_equal(ov_, ev)
+
+
 def test_noncanonical_strides_and_untouched_bytes():
     for layout in (abi.LAYOUT_NHD, abi.LAYOUT_HND):
         case = cases.make_case(7, layout=layout, stride_pad=(16, 8, 8), pad_frac=0.2, lens=[6, 3])
