@@ -187,6 +187,15 @@ bool view_vectorisable(const PageView &v, int64_t elem, int64_t dim, int64_t vec
          v.head >= 0;
 }
 
+// HND_PACKED pages whose pack group is exactly one 16-byte vector (pack * elem == 16, the
+// packing vLLM's and TGI's non-flash paged attention use): the 16-byte vectors of one head
+// are then `dhi` bytes apart instead of adjacent, and a token's vectors 16 bytes apart.
+bool view_packed16(const PageView &v, int64_t elem, int64_t dim) {
+  return v.pack > 1 && v.pack != dim && v.pack * elem == 16 && v.dlo == elem && aligned(v.base, 16) &&
+         v.blk % 16 == 0 && v.tok % 16 == 0 && v.head % 16 == 0 && v.dhi % 16 == 0 && v.blk >= 0 && v.tok >= 0 &&
+         v.head >= 0 && v.dhi >= 0;
+}
+
 // ------------------------------------------------------------------ device helpers ----
 
 __device__ int g_device_error;  // set when a bounded wait gives up; read by the host on demand
@@ -266,18 +275,24 @@ struct WriteRowsParams {
   char *k_base, *v_base;
   int64_t k_blk, k_tok, k_head;  // bytes
   int64_t v_blk, v_tok, v_head;
+  int64_t k_vec, v_vec;  // bytes between consecutive 16-byte vectors of one head (16 unless packed)
   const void *slots;
   int64_t row_bytes;
   int32_t num_tokens, num_blocks, block_size, bs_shift;
   int32_t vpr, vpr_shift;  // 16-byte vectors per token row
   int32_t vps, vps_shift;  // 16-byte vectors per head segment
   int32_t tok_tile;        // tokens per CTA (<= kMaxTokTile)
+  int32_t tile_shift;      // log2(tok_tile), used by the token-fastest order only
 };
 
 // kSeg = false: every token row is one contiguous span in both page tensors.
 // kSeg = true : a row is num_heads spans of head_dim elements (HND pages, or NHD pages whose
-//               head stride is not head_dim).
-template <typename SlotT, bool kSeg, int kUnroll>
+//               head stride is not head_dim), or, in HND_PACKED pages with 16-byte pack
+//               groups, num_heads * head_dim / pack separate vectors (k_vec / v_vec apart).
+// kTrans      : threads run over tokens fastest, vectors slowest (tok_tile is a power of two).
+//               For packed pages the stores of neighbouring threads are then adjacent (the same
+//               vector of consecutive slots) and it is the loads that are 16-byte pieces.
+template <typename SlotT, bool kSeg, int kUnroll, bool kTrans = false>
 __global__ void __launch_bounds__(kWriteThreads) kvx_write_rows_kernel(const WriteRowsParams p) {
   pdl_prologue();
   __shared__ int64_t s_k[kMaxTokTile];
@@ -304,7 +319,7 @@ __global__ void __launch_bounds__(kWriteThreads) kvx_write_rows_kernel(const Wri
 
   const char *ksrc = p.key + tok0 * p.row_bytes;
   const char *vsrc = p.value + tok0 * p.row_bytes;
-  const int nvec = ntok * p.vpr;
+  const int nvec = (kTrans ? p.tok_tile : ntok) * p.vpr;
   for (int f0 = tid; f0 < nvec; f0 += kWriteThreads * kUnroll) {
     uint4 kr[kUnroll], vr[kUnroll];
     int64_t kd[kUnroll], vd[kUnroll];
@@ -313,21 +328,22 @@ __global__ void __launch_bounds__(kWriteThreads) kvx_write_rows_kernel(const Wri
       const int f = f0 + u * kWriteThreads;
       kd[u] = -1;
       if (f < nvec) {
-        const int tok = div_by(f, p.vpr, p.vpr_shift);
-        const int64_t ko = s_k[tok];
+        const int tok = kTrans ? (f & (p.tok_tile - 1)) : div_by(f, p.vpr, p.vpr_shift);
+        const int64_t ko = (!kTrans || tok < ntok) ? s_k[tok] : -1;
         if (ko >= 0) {
-          const int v = f - tok * p.vpr;
+          const int v = kTrans ? (f >> p.tile_shift) : f - tok * p.vpr;
           if (kSeg) {
             const int h = div_by(v, p.vps, p.vps_shift);
-            const int64_t w = static_cast<int64_t>(v - h * p.vps) * 16;
-            kd[u] = ko + h * p.k_head + w;
-            vd[u] = s_v[tok] + h * p.v_head + w;
+            const int64_t w = v - h * p.vps;
+            kd[u] = ko + h * p.k_head + w * p.k_vec;
+            vd[u] = s_v[tok] + h * p.v_head + w * p.v_vec;
           } else {
             kd[u] = ko + static_cast<int64_t>(v) * 16;
             vd[u] = s_v[tok] + static_cast<int64_t>(v) * 16;
           }
-          kr[u] = load_stream(ksrc + static_cast<int64_t>(f) * 16);
-          vr[u] = load_stream(vsrc + static_cast<int64_t>(f) * 16);
+          const int64_t from = kTrans ? static_cast<int64_t>(tok) * p.vpr + v : f;
+          kr[u] = load_stream(ksrc + from * 16);
+          vr[u] = load_stream(vsrc + from * 16);
         }
       }
     }
@@ -820,6 +836,7 @@ struct GatherPagesParams {
   const char *k_base, *v_base;
   int64_t k_blk, k_tok, k_head;  // bytes
   int64_t v_blk, v_tok, v_head;
+  int64_t k_vec, v_vec;  // bytes between consecutive 16-byte vectors of one head (16 unless packed)
   char *key_out, *value_out;
   GatherShape s;
   int64_t out_row_bytes;  // bytes of one output token row
@@ -966,6 +983,7 @@ __global__ void __launch_bounds__(kGatherThreads) kvx_gather_pages_kernel(const 
     char *dst = (kv ? p.value_out : p.key_out) + ci.out_off;
     const int64_t tok_b = kv ? p.v_tok : p.k_tok;
     const int64_t head_b = kv ? p.v_head : p.k_head;
+    const int64_t vec_b = kv ? p.v_vec : p.k_vec;
 
     for (int f0 = vbeg + lane; f0 < vend; f0 += 32 * kUnroll) {
       uint4 r[kUnroll];
@@ -978,7 +996,7 @@ __global__ void __launch_bounds__(kGatherThreads) kvx_gather_pages_kernel(const 
             const int tok = div_by(f, p.vpr, p.vpr_shift);
             const int v = f - tok * p.vpr;
             const int h = div_by(v, p.vps, p.vps_shift);
-            so = tok * tok_b + h * head_b + static_cast<int64_t>(v - h * p.vps) * 16;
+            so = tok * tok_b + h * head_b + (v - h * p.vps) * vec_b;
           } else {
             so = static_cast<int64_t>(f) * 16;
           }
@@ -996,8 +1014,10 @@ __global__ void __launch_bounds__(kGatherThreads) kvx_gather_pages_kernel(const 
 
 // Warp-granular gather of contiguous page chunks with 256-bit accesses: identical work
 // decomposition to kvx_gather_pages_kernel<IdxT, false, *>, counted in 32-byte units.
-// Needs 32-byte aligned bases, block strides and rows, and an even part_vecs.
-template <typename IdxT, int kUnroll>
+// Needs 32-byte aligned bases, block strides and rows, and an even part_vecs.  kSeg: per-head
+// segments in the pages (HND, padded pitches); token and head pitches and the segment length
+// are then multiples of 32 bytes too.
+template <typename IdxT, int kUnroll, bool kSeg = false>
 __global__ void __launch_bounds__(kGatherThreads) kvx_gather_pages_wide_kernel(const GatherPagesParams p) {
   pdl_prologue();
   extern __shared__ int32_t s_prefix[];
@@ -1033,12 +1053,26 @@ __global__ void __launch_bounds__(kGatherThreads) kvx_gather_pages_wide_kernel(c
     const int uend = min(ubeg + part_units, nunit);
     const char *src = kv ? p.v_base + ci.block * p.v_blk : p.k_base + ci.block * p.k_blk;
     char *dst = (kv ? p.value_out : p.key_out) + ci.out_off;
+    const int64_t tok_b = kv ? p.v_tok : p.k_tok;
+    const int64_t head_b = kv ? p.v_head : p.k_head;
+    const int seg_units = p.vps >> 1;
     for (int f0 = ubeg + lane; f0 < uend; f0 += 32 * kUnroll) {
       Vec32 r[kUnroll];
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u) {
         const int f = f0 + u * 32;
-        if (f < uend) r[u] = load_stream32(src + static_cast<int64_t>(f) * 32);
+        if (f < uend) {
+          int64_t so;
+          if (kSeg) {
+            const int tok = div_by(f, row_units, p.vpr_shift >= 0 ? p.vpr_shift - 1 : -1);
+            const int v = f - tok * row_units;
+            const int h = div_by(v, seg_units, p.vps_shift >= 0 ? p.vps_shift - 1 : -1);
+            so = tok * tok_b + h * head_b + static_cast<int64_t>(v - h * seg_units) * 32;
+          } else {
+            so = static_cast<int64_t>(f) * 32;
+          }
+          r[u] = load_stream32(src + so);
+        }
       }
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u) {
@@ -1707,16 +1741,18 @@ kvx_status_t write_impl(const kvx_cache_desc_t *cache, const kvx_write_desc_t *w
   // ---- vector tier: 16-byte input vectors, each inside one head -------------------------
   const int64_t row_bytes = H * D * io_elem;
   const int64_t out_vec = fp8 ? 16 / io_elem : 16;  // cache bytes produced per input vector
+  const bool k_packed = !fp8 && view_packed16(gp.k, elem, D), v_packed = !fp8 && view_packed16(gp.v, elem, D);
   const bool vec_ok = !g_opt.force_generic && (D * io_elem) % 16 == 0 &&
                       aligned(write->io.key.data, 16) && aligned(write->io.value.data, 16) &&
-                      view_vectorisable(gp.k, elem, D, out_vec) && view_vectorisable(gp.v, elem, D, out_vec) &&
-                      row_bytes / 16 <= (1 << 20);
+                      (k_packed || view_vectorisable(gp.k, elem, D, out_vec)) &&
+                      (v_packed || view_vectorisable(gp.v, elem, D, out_vec)) && row_bytes / 16 <= (1 << 20);
   if (vec_ok) {
     WriteRowsParams p;
     p.key = static_cast<const char *>(write->io.key.data);
     p.value = static_cast<const char *>(write->io.value.data);
     p.k_base = gp.k.base, p.k_blk = gp.k.blk, p.k_tok = gp.k.tok, p.k_head = gp.k.head;
     p.v_base = gp.v.base, p.v_blk = gp.v.blk, p.v_tok = gp.v.tok, p.v_head = gp.v.head;
+    p.k_vec = k_packed ? gp.k.dhi : 16, p.v_vec = v_packed ? gp.v.dhi : 16;
     p.slots = write->slots.slots;
     p.row_bytes = row_bytes;
     p.num_tokens = static_cast<int32_t>(T);
@@ -1728,6 +1764,13 @@ kvx_status_t write_impl(const kvx_cache_desc_t *cache, const kvx_write_desc_t *w
     p.vps = static_cast<int32_t>(D * io_elem / 16);
     p.vps_shift = shift_of(p.vps);
     p.tok_tile = pick_tok_tile(T, p.vpr, dev.sm_count);
+    p.tile_shift = 0;
+    if (k_packed || v_packed) {  // token-fastest order: whole runs of a page's tokens per CTA
+      int tile = 32;
+      while (tile > 1 && (T + tile - 1) / tile < static_cast<int64_t>(dev.sm_count) * 4) tile >>= 1;
+      p.tok_tile = tile;
+      p.tile_shift = shift_of(tile);
+    }
     const int grid = static_cast<int>((T + p.tok_tile - 1) / p.tok_tile);
     const int unroll = static_cast<int>(g_opt.write_unroll);
     if (fp8) {
@@ -1748,7 +1791,14 @@ kvx_status_t write_impl(const kvx_cache_desc_t *cache, const kvx_write_desc_t *w
 #undef KVX_F8_WRITE
       return finish_launch();
     }
-    const bool seg = !(gp.k.head == D * elem && gp.v.head == D * elem);
+    const bool seg = k_packed || v_packed || !(gp.k.head == D * elem && gp.v.head == D * elem);
+    if (k_packed || v_packed) {
+      if (s32)
+        launch_streaming(kvx_write_rows_kernel<int32_t, true, 4, true>, grid, kWriteThreads, 0, cs, p);
+      else
+        launch_streaming(kvx_write_rows_kernel<int64_t, true, 4, true>, grid, kWriteThreads, 0, cs, p);
+      return finish_launch();
+    }
     if (s32) {
       if (seg)
         launch_write_rows<int32_t, true>(p, grid, unroll, cs);
@@ -1916,9 +1966,12 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
   const int64_t out_row = H * D * io_elem;
   const int64_t in_vec = fp8 ? 16 / io_elem : 16;  // cache bytes consumed per output vector
   const int64_t chunk_vecs = static_cast<int64_t>(cache->block_size) * (out_row / 16);
+  const bool k_packed = !fp8 && !ragged && view_packed16(gp.k, elem, D);
+  const bool v_packed = !fp8 && !ragged && view_packed16(gp.v, elem, D);
+  const bool packed = k_packed || v_packed;
   const bool vec_ok = !g_opt.force_generic && (D * io_elem) % 16 == 0 && aligned(gather->io.key.data, 16) &&
-                      aligned(gather->io.value.data, 16) && view_vectorisable(gp.k, elem, D, in_vec) &&
-                      view_vectorisable(gp.v, elem, D, in_vec) && chunk_vecs < (int64_t{1} << 30) &&
+                      aligned(gather->io.value.data, 16) && (k_packed || view_vectorisable(gp.k, elem, D, in_vec)) &&
+                      (v_packed || view_vectorisable(gp.v, elem, D, in_vec)) && chunk_vecs < (int64_t{1} << 30) &&
                       S * static_cast<int64_t>(gs.max_blocks) < (int64_t{1} << 31) &&
                       (!offsets || (aligned(gs.pool[0], in_vec) && aligned(gs.pool[1], in_vec) &&
                                     gs.pool_block_bytes % in_vec == 0));
@@ -1926,6 +1979,7 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
     GatherPagesParams p;
     p.k_base = gp.k.base, p.k_blk = gp.k.blk, p.k_tok = gp.k.tok, p.k_head = gp.k.head;
     p.v_base = gp.v.base, p.v_blk = gp.v.blk, p.v_tok = gp.v.tok, p.v_head = gp.v.head;
+    p.k_vec = k_packed ? gp.k.dhi : 16, p.v_vec = v_packed ? gp.v.dhi : 16;
     p.key_out = static_cast<char *>(gather->io.key.data);
     p.value_out = static_cast<char *>(gather->io.value.data);
     p.s = gs;
@@ -1961,7 +2015,7 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
         return finish_launch();
       }
     }
-    const bool contiguous_pages = !fp8 && gp.k.head == D * elem && gp.v.head == D * elem &&
+    const bool contiguous_pages = !fp8 && !packed && gp.k.head == D * elem && gp.v.head == D * elem &&
                                   gp.k.tok == H * D * elem && gp.v.tok == H * D * elem;
     const size_t prefix_bytes = p.use_prefix ? static_cast<size_t>(S + 1) * sizeof(int32_t) : 0;
 
@@ -2043,15 +2097,24 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
         launch_streaming(kvx_gather_pages_kernel<int32_t, true, 8, true>, ug, kGatherThreads, prefix_bytes, cs, p);
       return finish_launch();
     }
-    if (g_opt.gather_path == 2) {  // warp-granular items
-      const bool wide_ok = g_opt.wide && contiguous_pages && (p.part_vecs % 2) == 0 && (p.vpr % 2) == 0 &&
+    if (g_opt.gather_path == 2 || packed) {  // warp-granular items
+      const bool wide_ok = g_opt.wide && !packed && (p.part_vecs % 2) == 0 && (p.vpr % 2) == 0 &&
                            aligned(p.k_base, 32) && aligned(p.v_base, 32) && aligned(p.key_out, 32) &&
-                           aligned(p.value_out, 32) && p.k_blk % 32 == 0 && p.v_blk % 32 == 0;
-      if (wide_ok) {
+                           aligned(p.value_out, 32) && p.k_blk % 32 == 0 && p.v_blk % 32 == 0 &&
+                           (contiguous_pages || ((p.vps % 2) == 0 && p.k_tok % 32 == 0 && p.v_tok % 32 == 0 &&
+                                                 p.k_head % 32 == 0 && p.v_head % 32 == 0));
+      if (wide_ok && contiguous_pages) {
         if (s32)
           launch_streaming(kvx_gather_pages_wide_kernel<int32_t, 4>, ug, kGatherThreads, prefix_bytes, cs, p);
         else
           launch_streaming(kvx_gather_pages_wide_kernel<int64_t, 4>, ug, kGatherThreads, prefix_bytes, cs, p);
+        return finish_launch();
+      }
+      if (wide_ok) {
+        if (s32)
+          launch_streaming(kvx_gather_pages_wide_kernel<int32_t, 4, true>, ug, kGatherThreads, prefix_bytes, cs, p);
+        else
+          launch_streaming(kvx_gather_pages_wide_kernel<int64_t, 4, true>, ug, kGatherThreads, prefix_bytes, cs, p);
         return finish_launch();
       }
       if (s32) {

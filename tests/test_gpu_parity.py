@@ -142,7 +142,9 @@ def test_vector_tier_shapes(layout, dtype):
 def test_noncanonical_strides(layout):
     """Padded block / token / head pitches (what views of a fused [blocks, 2, ...] allocation
     look like): still the vector tier, K and V with different strides."""
-    for pad in ((16, 8, 8), (4096, 0, 0), (0, 8, 0), (3, 1, 1)):  # the last one is misaligned -> generic
+    # (32, 16, 16): every pitch a multiple of 32 bytes -> the 256-bit segmented gather;
+    # (3, 1, 1) is misaligned -> generic
+    for pad in ((16, 8, 8), (32, 16, 16), (4096, 0, 0), (0, 8, 0), (3, 1, 1)):
         case = cases.make_case(41, layout=layout, dtype=abi.DTYPE_BF16, heads=4, dim=64, block_size=8,
                                num_blocks=12, lens=[20, 8, 31], pad_frac=0.1, stride_pad=pad)
         case.note = f"pad {pad}"
@@ -304,6 +306,33 @@ def test_varlen_output_gather_fp8_and_statuses():
     cache2, _, g2, ks2, vs2 = descriptors(packed, b2, abi.MEMORY_DEVICE)
     assert L.kvx_launch_gather_kv_varlen(C.byref(cache2), C.byref(g2), ptr, abi.DTYPE_S32, C.byref(ks2), C.byref(vs2), None) \
         == abi.STATUS_INVALID_ARGUMENT
+
+
+@pytest.mark.parametrize("dtype", [abi.DTYPE_BF16, abi.DTYPE_F16, abi.DTYPE_F32])
+def test_hnd_packed_with_16_byte_pack_groups(dtype):
+    """HND_PACKED pages [blocks, heads, dim / x, block_size, x] with x = 16 bytes / element size
+    (the packing of vLLM's and TGI's non-flash paged attention) take the vector tier: one
+    16-byte vector per pack group.  Other packings stay on the generic tier; both must equal
+    the checker."""
+    x = 16 // (4 if dtype == abi.DTYPE_F32 else 2)
+    for i, kw in enumerate([
+        dict(heads=4, dim=64, block_size=16, num_blocks=40, lens=[100, 17, 256, 1, 0, 33], pad_frac=0.1, bad_blocks=2),
+        dict(heads=8, dim=128, block_size=32, num_blocks=20, lens=[300, 5, 64], index_dtype=np.int64,
+             slot_dtype=np.int32),
+        dict(heads=1, dim=x, block_size=4, num_blocks=16, lens=[9, 4, 0, 6]),
+        dict(heads=2, dim=4 * x, block_size=8, num_blocks=12, lens=[50, 20], max_seq_len=40, oob_slots=2),
+    ]):
+        case = cases.make_case(1100 + i, layout=abi.LAYOUT_HND_PACKED, pack=x, dtype=dtype, **kw)
+        case.note = f"packed16 {i}"
+        k, v = check_write(case)
+        check_write(case, "prefill", 1)
+        check_gather(case, k, v)
+        check_gather(case, k, v, "typed")
+        check_gather(cases.to_varlen(case, gap=1), k, v)
+        wide = cases.make_case(1150 + i, layout=abi.LAYOUT_HND_PACKED, pack=2 * x, dtype=dtype,
+                               **{**kw, "dim": max(kw["dim"], 2 * x)})
+        k, v = check_write(wide)
+        check_gather(wide, k, v)
 
 
 def test_empty_and_degenerate_batches():
