@@ -23,6 +23,7 @@ EXPORTS = [
     "kvx_b200_reset_launch_count", "kvx_b200_set_option", "kvx_b200_get_option",
     "kvx_host_pipe_create", "kvx_host_pipe_destroy", "kvx_host_write_kv", "kvx_host_gather_kv",
     "kvx_host_pipe_sync", "kvx_host_pipe_traffic",
+    "kvx_paged_attention_workspace_bytes", "kvx_launch_paged_attention_decode",
 ]
 
 
@@ -61,6 +62,11 @@ def lib() -> C.CDLL:
     L.kvx_launch_gather_kv_varlen.argtypes = [P(abi.CacheDesc), P(abi.GatherDesc), C.c_void_p, C.c_int,
                                               P(abi.ScaleDesc), P(abi.ScaleDesc), C.c_void_p]
     L.kvx_launch_gather_kv_varlen.restype = st
+    L.kvx_paged_attention_workspace_bytes.argtypes = [C.c_uint32] * 5
+    L.kvx_paged_attention_workspace_bytes.restype = C.c_size_t
+    L.kvx_launch_paged_attention_decode.argtypes = [P(abi.CacheDesc), P(abi.AttentionDesc), P(abi.ScaleDesc),
+                                                    P(abi.ScaleDesc), C.c_void_p, C.c_size_t, C.c_void_p]
+    L.kvx_launch_paged_attention_decode.restype = st
     L.kvx_kv_scales_workspace_bytes.argtypes, L.kvx_kv_scales_workspace_bytes.restype = [C.c_uint32], C.c_size_t
     L.kvx_launch_kv_scales.argtypes = [P(abi.KvIoDesc), C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
                                        C.c_size_t, C.c_void_p]

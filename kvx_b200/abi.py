@@ -100,10 +100,17 @@ class GatherDesc(C.Structure):
                 ("seq_lens", SeqLens), ("max_seq_len", C.c_uint32)]
 
 
+class AttentionDesc(C.Structure):
+    """``kvx_attention_desc_t`` (include/kvx_attention.h)."""
+    _fields_ = [("size", C.c_uint32), ("num_q_heads", C.c_uint32), ("max_seq_len", C.c_uint32),
+                ("scale", C.c_float), ("query", TensorDesc), ("out", TensorDesc),
+                ("block_table", BlockTable), ("seq_lens", SeqLens)]
+
+
 # x86-64 sizes frozen by the C header's static assertions.
 ABI_SIZES = {Version: 16, TensorDesc: 112, PoolDesc: 32, CacheDesc: 280, BlockTable: 64,
              SlotMapping: 32, SeqLens: 24, KvIoDesc: 248, ScaleDesc: 104, WriteDesc: 512,
-             GatherDesc: 352}
+             GatherDesc: 352, AttentionDesc: 328}
 for _cls, _bytes in ABI_SIZES.items():
     assert C.sizeof(_cls) == _bytes, (_cls.__name__, C.sizeof(_cls), _bytes)
 
@@ -230,3 +237,24 @@ def gather_desc(seq_count: int, max_seq_len: int, heads: int, dim: int, io_dtype
     g.seq_lens.dtype, g.seq_lens.seq_count, g.seq_lens.lengths = index_dtype, seq_count, lens_addr
     g.max_seq_len = max_seq_len
     return g
+
+
+def attention_desc(seq_count: int, q_heads: int, dim: int, io_dtype: int, query_addr: int, out_addr: int,
+                   scale: float, max_seq_len: int, index_dtype: int, table_addr: int, max_blocks_per_seq: int,
+                   lens_addr: int, memory: int = MEMORY_DEVICE) -> AttentionDesc:
+    """A ``kvx_attention_desc_t`` with dense ``[seq_count, q_heads, dim]`` query / out and a
+    PACKED block table."""
+    a = AttentionDesc()
+    a.size = C.sizeof(AttentionDesc)
+    a.num_q_heads, a.max_seq_len, a.scale = q_heads, max_seq_len, scale
+    a.query = tensor_desc(query_addr, io_dtype, (seq_count, q_heads, dim), memory=memory)
+    a.out = tensor_desc(out_addr, io_dtype, (seq_count, q_heads, dim), memory=memory)
+    b = a.block_table
+    b.size = C.sizeof(BlockTable)
+    b.format, b.index_dtype, b.seq_count, b.beam_width = TABLE_PACKED, index_dtype, seq_count, 1
+    b.max_blocks_per_seq = max_blocks_per_seq
+    b.indices = table_addr
+    b.indices_count = (seq_count * max_blocks_per_seq) & 0xFFFFFFFF
+    a.seq_lens.size = C.sizeof(SeqLens)
+    a.seq_lens.dtype, a.seq_lens.seq_count, a.seq_lens.lengths = index_dtype, seq_count, lens_addr
+    return a

@@ -1,7 +1,8 @@
 """Builds the C-ABI shared library ``kvx_b200/lib/libkvx_b200.so`` in-tree with nvcc + gcc.
 
 The library holds the CUDA-free validators (``csrc/kvx_abi.c``), the launch layer and
-kernels (``csrc/kvx_paged_kv.cu``) and the host-buffer pipeline (``csrc/kvx_host.cu``),
+kernels (``csrc/kvx_paged_kv.cu``), the host-buffer pipeline (``csrc/kvx_host.cu``) and the decode
+attention over the paged cache (``csrc/kvx_attention.cu``),
 compiled for sm_100a only.  Run ``python -m kvx_b200.build`` or call :func:`build`.
 """
 from __future__ import annotations
@@ -20,7 +21,7 @@ BUILD_DIR = os.path.join(ROOT, "build")
 
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "-Xcompiler", "-fPIC", "-I" + INCLUDE]
-CU_SOURCES = ["kvx_paged_kv.cu", "kvx_host.cu"]
+CU_SOURCES = ["kvx_paged_kv.cu", "kvx_host.cu", "kvx_attention.cu"]
 
 
 def _nvcc() -> str:

@@ -280,6 +280,50 @@ def gather_kv_varlen(key_cache: torch.Tensor, value_cache: torch.Tensor, block_t
         raise KvxError("kvx cache gather", status)
 
 
+def paged_attention_decode(query: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor,
+                           block_table: torch.Tensor, seq_lens: torch.Tensor, scale: float,
+                           max_seq_len: Optional[int] = None, out: Optional[torch.Tensor] = None,
+                           workspace: Optional[torch.Tensor] = None, kv_cache_dtype: str = "auto",
+                           k_scale: Optional[torch.Tensor] = None,
+                           v_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Decode attention that reads the paged cache in place (``include/kvx_attention.h``):
+    ``query`` ``[seq_count, q_heads, dim]`` attends over each sequence's cached tokens, found
+    through ``block_table`` / ``seq_lens`` as the gather finds them; returns ``out`` (same shape
+    and dtype).  ``max_seq_len`` bounds the context (default: all the table can address).
+    ``workspace`` is reusable uint8 scratch of :func:`attention_workspace_bytes` bytes; it is
+    allocated per call when not given."""
+    if query.dim() != 3 or query.dtype not in _FLOAT_CODES or not query.is_contiguous():
+        raise ValueError("query must be a contiguous [seq_count, q_heads, dim] float tensor")
+    if block_table.dim() != 2 or not block_table.is_contiguous():
+        raise ValueError("block_table must be a contiguous [seq_count, max_blocks_per_seq] tensor")
+    if block_table.dtype not in _INDEX_CODES or seq_lens.dtype != block_table.dtype:
+        raise TypeError("block_table and seq_lens must share an int32 or int64 dtype")
+    seqs, q_heads, dim = query.shape
+    if out is None:
+        out = torch.empty_like(query)
+    cache = cache_desc_from_tensors(key_cache, value_cache, kv_cache_dtype)
+    if max_seq_len is None:
+        max_seq_len = block_table.shape[1] * cache.block_size
+    need = lib().kvx_paged_attention_workspace_bytes(seqs, q_heads, cache.num_kv_heads, dim, max_seq_len)
+    if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
+        workspace = torch.empty(need, dtype=torch.uint8, device=query.device)
+    a = abi.attention_desc(seqs, q_heads, dim, _FLOAT_CODES[query.dtype], query.data_ptr(), out.data_ptr(),
+                           float(scale), int(max_seq_len), _INDEX_CODES[block_table.dtype], block_table.data_ptr(),
+                           block_table.shape[1], seq_lens.data_ptr())
+    a.seq_lens.seq_count = seq_lens.shape[0]
+    ks, vs = _scale_desc(k_scale, cache.num_kv_heads), _scale_desc(v_scale, cache.num_kv_heads)
+    status = lib().kvx_launch_paged_attention_decode(
+        C.byref(cache), C.byref(a), C.byref(ks), C.byref(vs), workspace.data_ptr() if need else None,
+        workspace.numel() * workspace.element_size() if need else 0, _stream())
+    if status != abi.STATUS_OK:
+        raise KvxError("kvx paged attention", status)
+    return out
+
+
+def attention_workspace_bytes(seq_count: int, q_heads: int, kv_heads: int, dim: int, max_seq_len: int) -> int:
+    return lib().kvx_paged_attention_workspace_bytes(seq_count, q_heads, kv_heads, dim, max_seq_len)
+
+
 def scales_workspace(heads: int, device: torch.device) -> torch.Tensor:
     """Zeroed scratch for :func:`compute_kv_scales`; reusable across calls on one stream."""
     n = lib().kvx_kv_scales_workspace_bytes(heads)

@@ -31,6 +31,7 @@ def _stale(target: str, sources: list[str]) -> bool:
 def build_oracle(force: bool = False) -> str:
     srcs = [os.path.join(HERE, f) for f in ("kvx_oracle.c", "kvx_cpu_baseline.c", "kvx_oracle.h")]
     srcs.append(os.path.join(ROOT, "include", "kvx_abi.h"))
+    srcs.append(os.path.join(ROOT, "include", "kvx_attention.h"))
     if force or _stale(ORACLE_LIB, srcs):
         subprocess.run(["gcc", "-std=c11", "-O2", "-Wall", "-Wextra", "-fPIC", "-shared",
                         "-I" + os.path.join(ROOT, "include"), srcs[0], srcs[1], "-o", ORACLE_LIB,

@@ -24,6 +24,7 @@
 #include "kvx_oracle.h"
 
 #include <math.h>
+#include <stdlib.h>
 #include <string.h>
 
 /* ------------------------------------------------------------------ helpers ---------- */
@@ -413,5 +414,95 @@ kvx_status_t kvx_oracle_kv_scales(const kvx_kv_io_desc_t *io, kvx_scale_granular
     return KVX_STATUS_UNSUPPORTED;
   scales_one(&io->key, io->num_tokens, io->num_kv_heads, io->head_dim, granularity, k_scale_out);
   scales_one(&io->value, io->num_tokens, io->num_kv_heads, io->head_dim, granularity, v_scale_out);
+  return KVX_STATUS_OK;
+}
+
+/* ------------------------------------------------------------------ attention -------- */
+
+/* Decode attention over the paged cache, one (sequence, query head) at a time, in double
+ * precision: scores, a two-pass softmax (maximum first) and the weighted sum of V rows.  No
+ * reference counterpart (the reference stops at the gather); the token walk is the gather's
+ * (kernels/kvx_paged_kv.cu:232-266 plus the >= num_blocks skip), the arithmetic is the
+ * definition in include/kvx_attention.h.  An fp8 cache is dequantised as value * scale in f32
+ * first, exactly as the dequantising gather does. */
+static float cache_elem_f32(const kvx_tensor_desc_t *pages, int64_t at, const float *scale, int64_t scale_stride,
+                            int64_t h) {
+  if (pages->dtype == KVX_DTYPE_F8_E4M3)
+    return kvx_oracle_e4m3_to_f32(((const uint8_t *)pages->data)[at]) * scale[h * scale_stride];
+  return load_as_f32(pages->data, pages->dtype, at);
+}
+
+kvx_status_t kvx_oracle_paged_attention_decode(const kvx_cache_desc_t *cache, const kvx_attention_desc_t *attn,
+                                               const kvx_scale_desc_t *k_scale, const kvx_scale_desc_t *v_scale) {
+  const float *ks = NULL, *vs = NULL;
+  int64_t kss = 0, vss = 0;
+  int64_t S, Hq, H, D, G, bs, mb, Lmax;
+  double *score, *acc;
+  if (cache == NULL || attn == NULL) return KVX_STATUS_INVALID_ARGUMENT;
+  if (!layout_known(cache->k.layout) || !layout_known(cache->v.layout)) return KVX_STATUS_UNSUPPORTED;
+  if (attn->block_table.format != KVX_BLOCK_TABLE_PACKED) return KVX_STATUS_UNSUPPORTED;
+  if (attn->block_table.index_dtype != attn->seq_lens.dtype) return KVX_STATUS_INVALID_ARGUMENT;
+  if (cache->num_kv_heads == 0 || attn->num_q_heads == 0 || attn->num_q_heads % cache->num_kv_heads != 0)
+    return KVX_STATUS_INVALID_ARGUMENT;
+  if (!io_dtype_quantisable(attn->query.dtype) || attn->out.dtype != attn->query.dtype) return KVX_STATUS_UNSUPPORTED;
+  if (cache->k.dtype == KVX_DTYPE_F8_E4M3) {
+    if (!resolve_scale(k_scale, NULL, cache->num_kv_heads, &ks, &kss) ||
+        !resolve_scale(v_scale, NULL, cache->num_kv_heads, &vs, &vss))
+      return KVX_STATUS_UNSUPPORTED;
+  } else if (cache->k.dtype != attn->query.dtype) {
+    return KVX_STATUS_UNSUPPORTED;
+  }
+  S = attn->block_table.seq_count, Hq = attn->num_q_heads, H = cache->num_kv_heads, D = cache->head_dim;
+  G = Hq / H, bs = cache->block_size, mb = attn->block_table.max_blocks_per_seq, Lmax = attn->max_seq_len;
+  if (Lmax == 0 || bs == 0) return KVX_STATUS_INVALID_ARGUMENT;
+  score = (double *)malloc(sizeof(double) * (size_t)Lmax);
+  acc = (double *)malloc(sizeof(double) * (size_t)D);
+  if (score == NULL || acc == NULL) {
+    free(score);
+    free(acc);
+    return KVX_STATUS_INTERNAL_ERROR;
+  }
+  for (int64_t s = 0; s < S; ++s) {
+    int64_t len = read_index(attn->seq_lens.lengths, attn->seq_lens.dtype, s);
+    if (len > Lmax) len = Lmax;
+    for (int64_t q = 0; q < Hq; ++q) {
+      const int64_t h = q / G;
+      double best = -INFINITY, denom = 0.0;
+      for (int64_t d = 0; d < D; ++d) acc[d] = 0.0;
+      for (int64_t tok = 0; tok < len; ++tok) {
+        const int64_t lb = tok / bs;
+        int64_t block;
+        score[tok] = -INFINITY; /* takes no part */
+        if (lb >= mb) continue;
+        block = read_index(attn->block_table.indices, attn->block_table.index_dtype, s * mb + lb);
+        if (block < 0 || block >= (int64_t)cache->num_blocks) continue;
+        {
+          double dot = 0.0;
+          for (int64_t d = 0; d < D; ++d) {
+            const float kq = cache_elem_f32(&cache->k, page_offset(&cache->k, block, tok - lb * bs, h, d), ks, kss, h);
+            dot += (double)load_as_f32(attn->query.data, attn->query.dtype, (s * Hq + q) * D + d) * (double)kq;
+          }
+          score[tok] = dot * (double)attn->scale;
+          if (score[tok] > best) best = score[tok];
+        }
+      }
+      for (int64_t tok = 0; tok < len; ++tok) {
+        const int64_t lb = tok / bs;
+        double p;
+        int64_t block;
+        if (score[tok] == -INFINITY) continue;
+        p = exp(score[tok] - best);
+        denom += p;
+        block = read_index(attn->block_table.indices, attn->block_table.index_dtype, s * mb + lb);
+        for (int64_t d = 0; d < D; ++d)
+          acc[d] += p * (double)cache_elem_f32(&cache->v, page_offset(&cache->v, block, tok - lb * bs, h, d), vs, vss, h);
+      }
+      for (int64_t d = 0; d < D; ++d)
+        store_from_f32(attn->out.data, attn->out.dtype, (s * Hq + q) * D + d,
+                       denom > 0.0 ? (float)(acc[d] / denom) : 0.0f);
+    }
+  }
+  free(score);
+  free(acc);
   return KVX_STATUS_OK;
 }

@@ -6,6 +6,7 @@
 #define KVX_ORACLE_H
 
 #include "kvx_abi.h"
+#include "kvx_attention.h"
 
 #ifdef __cplusplus
 extern "C" {
@@ -25,6 +26,10 @@ kvx_status_t kvx_oracle_gather_kv(const kvx_cache_desc_t *cache, const kvx_gathe
 kvx_status_t kvx_oracle_gather_kv_varlen(const kvx_cache_desc_t *cache, const kvx_gather_desc_t *gather,
                                          const void *out_indptr, kvx_dtype_t out_indptr_dtype,
                                          const kvx_scale_desc_t *k_scale, const kvx_scale_desc_t *v_scale);
+
+/* Decode attention over the paged cache in double precision (include/kvx_attention.h). */
+kvx_status_t kvx_oracle_paged_attention_decode(const kvx_cache_desc_t *cache, const kvx_attention_desc_t *attn,
+                                               const kvx_scale_desc_t *k_scale, const kvx_scale_desc_t *v_scale);
 
 /* scale = absmax / 448 per head or per tensor; outputs are host float arrays. */
 kvx_status_t kvx_oracle_kv_scales(const kvx_kv_io_desc_t *io, kvx_scale_granularity_t granularity,

@@ -23,6 +23,9 @@ def oracle() -> C.CDLL:
         L.kvx_oracle_gather_kv_varlen.argtypes = [P(abi.CacheDesc), P(abi.GatherDesc), C.c_void_p, C.c_int,
                                                   P(abi.ScaleDesc), P(abi.ScaleDesc)]
         L.kvx_oracle_gather_kv_varlen.restype = C.c_int
+        L.kvx_oracle_paged_attention_decode.argtypes = [P(abi.CacheDesc), P(abi.AttentionDesc), P(abi.ScaleDesc),
+                                                        P(abi.ScaleDesc)]
+        L.kvx_oracle_paged_attention_decode.restype = C.c_int
         L.kvx_oracle_kv_scales.argtypes = [P(abi.KvIoDesc), C.c_int, C.c_void_p, C.c_void_p]
         L.kvx_oracle_e4m3_from_f32.argtypes, L.kvx_oracle_e4m3_from_f32.restype = [C.c_float], C.c_uint8
         L.kvx_oracle_e4m3_to_f32.argtypes, L.kvx_oracle_e4m3_to_f32.restype = [C.c_uint8], C.c_float

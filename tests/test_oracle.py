@@ -157,6 +157,46 @@ def test_varlen_output_gather_equals_padded_rows():
             assert np.array_equal(ok_, ek) and np.array_equal(ov_, ev)
 
 
+@pytest.mark.parametrize("layout", [abi.LAYOUT_NHD, abi.LAYOUT_HND, abi.LAYOUT_HND_PACKED])
+def test_attention_checker_matches_numpy_statement(layout):
+    """The checker's decode attention against an independent numpy formulation: gather the
+    sequence's K / V rows through the numpy statement of the gather, then a float64 softmax."""
+    import ctypes as C
+    from harness import bits_to_f32, descriptors, f32_to_bits, host_buffers
+    from oracle.kvx_oracle import oracle
+    pack = 4 if layout == abi.LAYOUT_HND_PACKED else 1
+    case = cases.make_case(480, layout=layout, pack=pack, dtype=abi.DTYPE_F32, real_values=True, heads=2, dim=8,
+                           block_size=4, num_blocks=16, lens=[9, 4, 0, 13], bad_blocks=1)
+    _, k, v = oracle_write(case)
+    G, S, H, D = 3, 4, 2, 8
+    rng = np.random.default_rng(1)
+    q = rng.standard_normal((S, H * G, D)).astype(np.float32)
+    out = np.zeros_like(q)
+    import dataclasses
+    hb = host_buffers(dataclasses.replace(case, cache_k=k, cache_v=v))
+    cache, _, _, ks, vs = descriptors(case, hb, abi.MEMORY_HOST)
+    a = abi.attention_desc(S, H * G, D, abi.DTYPE_F32, q.ctypes.data, out.ctypes.data, 0.3, case.max_seq_len,
+                           abi.DTYPE_S32, hb["table"].ctypes.data, case.table.shape[1], hb["lens"].ctypes.data,
+                           abi.MEMORY_HOST)
+    assert oracle().kvx_oracle_paged_attention_decode(C.byref(cache), C.byref(a), C.byref(ks), C.byref(vs)) == 0
+    # numpy: the gather statement leaves skipped tokens at the sentinel; find them with a marker
+    marked = dataclasses.replace(case, out_k=np.full_like(case.out_k, 0x7FC00001), out_v=np.full_like(case.out_v, 0x7FC00001))
+    gk, gv = cases.expected_gather_numpy(marked, k, v)
+    gk, gv = gk.view(np.float32), gv.view(np.float32)
+    for s in range(S):
+        n = min(int(case.lens[s]), case.max_seq_len)
+        for hq in range(H * G):
+            h = hq // G
+            live = [t for t in range(n) if not np.isnan(gk[s, t, h, 0])]
+            if not live:
+                assert not out[s, hq].any()
+                continue
+            sc = np.array([np.dot(q[s, hq].astype(np.float64), gk[s, t, h].astype(np.float64)) * np.float64(np.float32(0.3)) for t in live])
+            w = np.exp(sc - sc.max()); w /= w.sum()
+            ref = sum(w[i] * gv[s, t, h].astype(np.float64) for i, t in enumerate(live))
+            assert np.allclose(out[s, hq], ref, rtol=1e-6, atol=1e-7), (s, hq)
+
+
 def test_noncanonical_strides_and_untouched_bytes():
     for layout in (abi.LAYOUT_NHD, abi.LAYOUT_HND):
         case = cases.make_case(7, layout=layout, stride_pad=(16, 8, 8), pad_frac=0.2, lens=[6, 3])
