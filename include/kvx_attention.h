@@ -45,7 +45,9 @@ _Static_assert(sizeof(kvx_attention_desc_t) == 328, "kvx_attention_desc_t layout
 #endif
 
 /* Bytes of caller-owned DEVICE scratch kvx_launch_paged_attention_decode needs for this
- * problem size (0 when none is needed).  The library allocates nothing itself. */
+ * problem size: a work counter and, when contexts are split in chunks, the chunks' partial
+ * results.  The library allocates nothing itself; the scratch needs no initialisation and may
+ * be reused by the next call on the same stream. */
 KVX_API size_t kvx_paged_attention_workspace_bytes(uint32_t seq_count, uint32_t num_q_heads,
                                                    uint32_t num_kv_heads, uint32_t head_dim,
                                                    uint32_t max_seq_len);

@@ -35,6 +35,7 @@
 #include <stdint.h>
 
 #include <algorithm>
+#include <atomic>
 
 namespace {
 
@@ -124,11 +125,14 @@ struct AttnParams {
   char *out;
   float *part_o;   // [S, Hq, splits, D] normalised partial outputs
   float *part_ml;  // [S, Hq, splits, 2] running maximum (exp2 domain) and denominator
+  unsigned long long *counter;  // next unclaimed work item of the fast kernel (zero at launch)
   ScaleView ks, vs;
   float scale_log2;  // scale * log2(e)
   int32_t seq_count, max_blocks, max_seq_len, num_blocks, block_size;
+  int32_t bs_shift;  // log2(block_size) or -1
   int32_t heads_q, heads_kv, group, dim;
   int32_t chunk, splits;
+  int32_t use_prefix;  // 1: the fast kernel compacts its work list with a prefix sum in shared memory
 };
 
 template <typename IdxT>
@@ -137,12 +141,26 @@ __device__ __forceinline__ int64_t read_idx(const void *p, int64_t i) {
 }
 
 // Work split shared by the launcher, the workspace query and the kernels: contexts are cut in
-// chunks of `chunk` tokens (a multiple of 64); fewer, longer chunks when there are many
-// (sequence, KV head) pairs, shorter ones when the batch alone cannot fill the machine.
+// chunks of `chunk` tokens (a multiple of 64); long chunks when there are many (sequence, KV
+// head) pairs, shorter ones when the batch alone would leave the persistent CTAs with only a
+// few work items each (the bound uses max_seq_len; real contexts are shorter).
 __host__ __device__ inline int32_t choose_chunk(int64_t seq_count, int64_t heads_kv, int64_t max_seq_len) {
   int64_t chunk = 2048;
-  while (chunk > 256 && seq_count * heads_kv * ((max_seq_len + chunk - 1) / chunk) < 1024) chunk >>= 1;
+  while (chunk > 256 && seq_count * heads_kv * ((max_seq_len + chunk - 1) / chunk) < 4096) chunk >>= 1;
   return static_cast<int32_t>(chunk);
+}
+
+// Sequences whose chunk counts the fast kernel can prefix-sum in shared memory; with more,
+// it walks the padded (sequence, chunk) rectangle instead.
+constexpr int kMaxPrefixSeqs = 8192;
+
+// Chunks sequence s really has.
+template <typename IdxT>
+__device__ __forceinline__ int32_t chunks_of(const AttnParams &p, int32_t s) {
+  int64_t len = static_cast<int64_t>(static_cast<const IdxT *>(p.lens)[s]);
+  if (len <= 0) return 0;
+  if (len > p.max_seq_len) len = p.max_seq_len;
+  return static_cast<int32_t>((len + p.chunk - 1) / p.chunk);
 }
 
 // ------------------------------------------------------------------ element types ------
@@ -175,14 +193,6 @@ struct Fp16 {
   }
 };
 
-__device__ __forceinline__ uint4 load_stream(const void *p) {  // read-once data: no L1 allocation
-  uint4 r;
-  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
-               : "l"(p));
-  return r;
-}
-
 __device__ __forceinline__ uint32_t word_of(const uint4 &v, int i) {
   return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w;
 }
@@ -206,195 +216,317 @@ constexpr int kAttnThreads = kAttnWarps * 32;
 // accumulators (C of two 8-token tiles is A of one 16-token step).  For V a lane loads the
 // rows of tokens 2j, 2j+1, 2j+8, 2j+9 at dims 64*hd + 8g .. 8g+7 and zips element i of two
 // rows into one register for MMA i, whose column g is therefore head dim 64*hd + 8g + i.
+//
+// Memory pipeline.  A warp's loads for one step are 16 x 16 bytes per lane (8 KB per warp).
+// They are issued as cp.async copies into a ring of kStages steps in shared memory, each lane
+// into slots only it reads back, so no barrier is involved: the lane waits for its own copy
+// group and reloads its operands with 16-byte shared loads.  kStages - 1 steps are in flight
+// per warp while one is being multiplied (2 CTAs x 4 warps x 16 KB = 128 KB per SM), which is
+// what keeps HBM busy; with the loads going to registers directly only one step per warp could
+// be outstanding and the kernel was bound by memory latency at half the bandwidth.
+//
+// Work distribution.  Items are (sequence, chunk, KV head) triples of chunks that exist; CTAs
+// claim them one at a time from a counter in the caller's scratch (zeroed by the launcher), so
+// short and long items balance out.
+constexpr int kStages = 3;
+constexpr size_t kCounterBytes = 16;  // head of the scratch: the work counter, padded
+
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src) {
+  const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
+}
+
 template <typename T, int kD, typename IdxT, bool kUpper>
 __global__ void __launch_bounds__(kAttnThreads, 2) kvx_attention_decode_kernel(const AttnParams p) {
-  constexpr int kC = kD / 32;   // 16-byte loads per K row and lane
-  constexpr int kHd = kD / 64;  // 64-dim halves of a V row
-  constexpr int kNt = kD / 8;   // output column tiles
+  constexpr int kC = kD / 32;         // 16-byte loads per K row and lane
+  constexpr int kHd = kD / 64;        // 64-dim halves of a V row
+  constexpr int kNt = kD / 8;         // output column tiles
+  constexpr int kSlots = 2 * kC + 4 * kHd;  // 16-byte slots per lane and step (K tiles, then V rows)
+  extern __shared__ uint4 sm_dyn[];   // ring [warp][stage][slot][lane], then the chunk prefix
   __shared__ float sm_m[kAttnWarps][16];
   __shared__ float sm_l[kAttnWarps][16];
-  __shared__ float sm_o[16][kD];
+  __shared__ float sm_o[16][kD + 2];  // + 2: rows land in different banks for the atomics below
+  __shared__ int32_t sm_page[kAttnWarps][kStages];
+  __shared__ int32_t sm_scan[kAttnThreads];
+  __shared__ unsigned long long sm_item;
+  int32_t *sm_prefix = reinterpret_cast<int32_t *>(sm_dyn + kAttnWarps * kStages * kSlots * 32);
 
-  const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, j = lane & 3;
   const int G = p.group;
-  int64_t len = read_idx<IdxT>(p.lens, seq);
-  if (len > p.max_seq_len) len = p.max_seq_len;
-  const int64_t cbeg = static_cast<int64_t>(split) * p.chunk;
-  const int64_t cend = min(len, cbeg + p.chunk);
-  const int64_t q_row0 = static_cast<int64_t>(seq) * p.heads_q + static_cast<int64_t>(kvh) * G;
-  if (cbeg >= cend) {
-    if (p.splits == 1) {  // empty context: the output is defined as zero
-      for (int i = threadIdx.x; i < G * kD; i += kAttnThreads)
-        reinterpret_cast<uint16_t *>(p.out)[q_row0 * kD + i] = 0;
+  uint4 *ring = sm_dyn + (warp * kStages * kSlots) * 32 + lane;  // slot s of stage t: ring[(t*kSlots+s)*32]
+
+  int64_t chunks_total;
+  if (p.use_prefix) {
+    const int S = p.seq_count;
+    const int per = (S + kAttnThreads - 1) / kAttnThreads;
+    const int begin = min(static_cast<int>(threadIdx.x) * per, S), end = min(begin + per, S);
+    int32_t local = 0;
+    for (int s = begin; s < end; ++s) local += chunks_of<IdxT>(p, s);
+    sm_scan[threadIdx.x] = local;
+    __syncthreads();
+    int32_t run = 0;
+    for (int t = 0; t < static_cast<int>(threadIdx.x); ++t) run += sm_scan[t];
+    for (int s = begin; s < end; ++s) {
+      sm_prefix[s] = run;
+      run += chunks_of<IdxT>(p, s);
     }
-    return;
+    if (threadIdx.x == kAttnThreads - 1) sm_prefix[S] = run;
+    __syncthreads();
+    chunks_total = sm_prefix[S];
+  } else {
+    chunks_total = static_cast<int64_t>(p.seq_count) * p.splits;
+  }
+  const int64_t items = chunks_total * p.heads_kv;
+
+  // A sequence without cached tokens has no work item; its output is defined as zero.  With
+  // more than one chunk per sequence the merge kernel writes it, otherwise this loop does.
+  if (p.splits == 1) {
+    for (int s = blockIdx.x; s < p.seq_count; s += gridDim.x) {
+      if (read_idx<IdxT>(p.lens, s) > 0) continue;
+      for (int i = threadIdx.x; i < p.heads_q * kD; i += kAttnThreads)
+        reinterpret_cast<uint16_t *>(p.out)[static_cast<int64_t>(s) * p.heads_q * kD + i] = 0;
+    }
   }
 
-  // Query rows of this KV head as A operands, kept for the whole kernel.
-  uint4 qa[kC], qb[kC];
-#pragma unroll
-  for (int c = 0; c < kC; ++c) {
-    qa[c] = make_uint4(0, 0, 0, 0);
-    qb[c] = make_uint4(0, 0, 0, 0);
-    if (g < G) qa[c] = *reinterpret_cast<const uint4 *>(p.query + ((q_row0 + g) * kD + 32 * c + 8 * j) * 2);
-    if (kUpper && g + 8 < G)
-      qb[c] = *reinterpret_cast<const uint4 *>(p.query + ((q_row0 + g + 8) * kD + 32 * c + 8 * j) * 2);
-  }
+  for (;;) {
+    if (threadIdx.x == 0) sm_item = atomicAdd(p.counter, 1ull);
+    __syncthreads();
+    const int64_t item = static_cast<int64_t>(sm_item);
+    if (item >= items) break;
+    const int kvh = static_cast<int>(item % p.heads_kv);
+    const int64_t ci = item / p.heads_kv;
+    int seq, split;
+    if (p.use_prefix) {
+      int lo = 0, hi = p.seq_count;  // last s with prefix[s] <= ci
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (sm_prefix[mid] <= ci)
+          lo = mid;
+        else
+          hi = mid;
+      }
+      seq = lo;
+      split = static_cast<int>(ci - sm_prefix[lo]);
+    } else {
+      seq = static_cast<int>(ci / p.splits);
+      split = static_cast<int>(ci - static_cast<int64_t>(seq) * p.splits);
+    }
+    int64_t len = read_idx<IdxT>(p.lens, seq);
+    if (len > p.max_seq_len) len = p.max_seq_len;
+    const int64_t cbeg = static_cast<int64_t>(split) * p.chunk;
+    const int64_t cend = min(len, cbeg + p.chunk);
+    const int64_t q_row0 = static_cast<int64_t>(seq) * p.heads_q + static_cast<int64_t>(kvh) * G;
+    // (without the prefix, a chunk the sequence does not have: nsteps <= 0 below, and the
+    // epilogue writes an empty partial that the merge never reads)
 
-  float o[kNt][4];
-#pragma unroll
-  for (int nt = 0; nt < kNt; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
-  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;  // rows g and g + 8
-
-  const int nsteps = static_cast<int>((cend - cbeg + 15) >> 4);
-  const int64_t head_k = static_cast<int64_t>(kvh) * p.k.head, head_v = static_cast<int64_t>(kvh) * p.v.head;
-  for (int st = warp; st < nsteps; st += kAttnWarps) {
-    const int64_t t0 = cbeg + static_cast<int64_t>(st) * 16;
-    const int64_t lb = t0 / p.block_size;
-    if (lb >= p.max_blocks) break;  // beyond the table: these tokens take no part
-    const int64_t b = read_idx<IdxT>(p.table, static_cast<int64_t>(seq) * p.max_blocks + lb);
-    if (b < 0 || b >= p.num_blocks) continue;  // as the gather: skipped
-    const int64_t o0 = t0 - lb * p.block_size;  // a 16-token step never straddles pages
-    const char *kp = p.k.base + b * p.k.blk + head_k + o0 * p.k.tok + 16 * j;
-    const char *vp = p.v.base + b * p.v.blk + head_v + o0 * p.v.tok + 16 * g;
-
-    uint4 k0[kC], k1[kC], vv[kHd][4];
+    // Query rows of this KV head as A operands, kept for the whole item.
+    uint4 qa[kC], qb[kC];
 #pragma unroll
     for (int c = 0; c < kC; ++c) {
-      k0[c] = load_stream(kp + g * p.k.tok + 64 * c);
-      k1[c] = load_stream(kp + (g + 8) * p.k.tok + 64 * c);
-    }
-#pragma unroll
-    for (int hd = 0; hd < kHd; ++hd) {
-      vv[hd][0] = load_stream(vp + (2 * j) * p.v.tok + 128 * hd);
-      vv[hd][1] = load_stream(vp + (2 * j + 1) * p.v.tok + 128 * hd);
-      vv[hd][2] = load_stream(vp + (2 * j + 8) * p.v.tok + 128 * hd);
-      vv[hd][3] = load_stream(vp + (2 * j + 9) * p.v.tok + 128 * hd);
+      qa[c] = make_uint4(0, 0, 0, 0);
+      qb[c] = make_uint4(0, 0, 0, 0);
+      if (g < G) qa[c] = *reinterpret_cast<const uint4 *>(p.query + ((q_row0 + g) * kD + 32 * c + 8 * j) * 2);
+      if (kUpper && g + 8 < G)
+        qb[c] = *reinterpret_cast<const uint4 *>(p.query + ((q_row0 + g + 8) * kD + 32 * c + 8 * j) * 2);
     }
 
-    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+    float o[kNt][4];
 #pragma unroll
-    for (int c = 0; c < kC; ++c) {
-      T::mma(s0, qa[c].x, qb[c].x, qa[c].y, qb[c].y, k0[c].x, k0[c].y);
-      T::mma(s0, qa[c].z, qb[c].z, qa[c].w, qb[c].w, k0[c].z, k0[c].w);
-      T::mma(s1, qa[c].x, qb[c].x, qa[c].y, qb[c].y, k1[c].x, k1[c].y);
-      T::mma(s1, qa[c].z, qb[c].z, qa[c].w, qb[c].w, k1[c].z, k1[c].w);
-    }
+    for (int nt = 0; nt < kNt; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;  // rows g and g + 8
 
-    // Scale into the exp2 domain; tokens at or beyond the end of the chunk take no part, and
-    // their V rows (whatever the page holds there) are cleared so that 0 * garbage stays 0.
-    const int64_t left = cend - t0;  // valid tokens in this step, >= 1
+    const int nsteps = cend > cbeg ? static_cast<int>((cend - cbeg + 15) >> 4) : 0;
+    const int mine = nsteps > warp ? (nsteps - warp + kAttnWarps - 1) / kAttnWarps : 0;  // steps of this warp
+    const int64_t head_k = static_cast<int64_t>(kvh) * p.k.head, head_v = static_cast<int64_t>(kvh) * p.v.head;
+
+    // Page of this warp's i-th step, or -1 when its tokens take no part (beyond the table, or
+    // an id that is negative or not below num_blocks: skipped as the gather skips them).
+    // Looked up once, when the step's loads are issued, and kept in shared memory for the
+    // consumer side.  Token positions fit 32 bits (max_seq_len does).
+    auto page_of = [&](int i, uint32_t *o0) -> int64_t {
+      const uint32_t t0 = static_cast<uint32_t>(cbeg) + static_cast<uint32_t>(warp + i * kAttnWarps) * 16u;
+      const uint32_t lb = p.bs_shift >= 0 ? (t0 >> p.bs_shift) : (t0 / static_cast<uint32_t>(p.block_size));
+      *o0 = t0 - lb * static_cast<uint32_t>(p.block_size);  // a 16-token step never straddles pages
+      if (lb >= static_cast<uint32_t>(p.max_blocks)) return -1;
+      const int64_t b = read_idx<IdxT>(p.table, static_cast<int64_t>(seq) * p.max_blocks + lb);
+      return (b < 0 || b >= p.num_blocks) ? -1 : b;
+    };
+    auto issue = [&](int i) {
+      if (i < mine) {
+        uint32_t o0;
+        const int64_t b = page_of(i, &o0);
+        const int stage = i % kStages;
+        sm_page[warp][stage] = static_cast<int32_t>(b);  // every lane writes the same value
+        if (b >= 0) {
+          const char *kp = p.k.base + b * p.k.blk + head_k + static_cast<int64_t>(o0) * p.k.tok + 16 * j;
+          const char *vp = p.v.base + b * p.v.blk + head_v + static_cast<int64_t>(o0) * p.v.tok + 16 * g;
+          uint4 *dst = ring + (stage * kSlots) * 32;
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int tok0 = 2 * j + (e & 1), tok1 = tok0 + 8;
-      s0[e] = tok0 < left ? s0[e] * p.scale_log2 : -INFINITY;
-      s1[e] = tok1 < left ? s1[e] * p.scale_log2 : -INFINITY;
-    }
-    if (left < 16) {
+          for (int c = 0; c < kC; ++c) {
+            cp_async16(dst + (2 * c) * 32, kp + g * p.k.tok + 64 * c);
+            cp_async16(dst + (2 * c + 1) * 32, kp + (g + 8) * p.k.tok + 64 * c);
+          }
+#pragma unroll
+          for (int hd = 0; hd < kHd; ++hd) {
+            cp_async16(dst + (2 * kC + 4 * hd) * 32, vp + (2 * j) * p.v.tok + 128 * hd);
+            cp_async16(dst + (2 * kC + 4 * hd + 1) * 32, vp + (2 * j + 1) * p.v.tok + 128 * hd);
+            cp_async16(dst + (2 * kC + 4 * hd + 2) * 32, vp + (2 * j + 8) * p.v.tok + 128 * hd);
+            cp_async16(dst + (2 * kC + 4 * hd + 3) * 32, vp + (2 * j + 9) * p.v.tok + 128 * hd);
+          }
+        }
+      }
+      cp_async_commit();  // one group per step, empty or not, keeps the accounting uniform
+    };
+
+#pragma unroll
+    for (int i = 0; i < kStages - 1; ++i) issue(i);
+    for (int i = 0; i < mine; ++i) {
+      issue(i + kStages - 1);
+      cp_async_wait<kStages - 1>();  // this lane's copies of step i have landed
+      const int stage = i % kStages;
+      if (sm_page[warp][stage] < 0) continue;
+      const int64_t t0 = cbeg + static_cast<int64_t>(warp + i * kAttnWarps) * 16;
+      const uint4 *src = ring + (stage * kSlots) * 32;
+
+      float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int c = 0; c < kC; ++c) {
+        const uint4 k0 = src[(2 * c) * 32], k1 = src[(2 * c + 1) * 32];
+        T::mma(s0, qa[c].x, qb[c].x, qa[c].y, qb[c].y, k0.x, k0.y);
+        T::mma(s1, qa[c].x, qb[c].x, qa[c].y, qb[c].y, k1.x, k1.y);
+        T::mma(s0, qa[c].z, qb[c].z, qa[c].w, qb[c].w, k0.z, k0.w);
+        T::mma(s1, qa[c].z, qb[c].z, qa[c].w, qb[c].w, k1.z, k1.w);
+      }
+
+      // Scale into the exp2 domain; in the last step of a chunk the tokens at or beyond its end
+      // take no part.
+      const int64_t left = cend - t0;  // valid tokens in this step, >= 1
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        s0[e] *= p.scale_log2;
+        s1[e] *= p.scale_log2;
+      }
+      if (left < 16) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int tok0 = 2 * j + (e & 1), tok1 = tok0 + 8;
+          if (tok0 >= left) s0[e] = -INFINITY;
+          if (tok1 >= left) s1[e] = -INFINITY;
+        }
+      }
+
+      float mx_lo = fmaxf(fmaxf(s0[0], s0[1]), fmaxf(s1[0], s1[1]));
+      float mx_hi = fmaxf(fmaxf(s0[2], s0[3]), fmaxf(s1[2], s1[3]));
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xFFFFFFFFu, mx_lo, 1));
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xFFFFFFFFu, mx_lo, 2));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xFFFFFFFFu, mx_hi, 1));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xFFFFFFFFu, mx_hi, 2));
+      const float n_lo = fmaxf(m_lo, mx_lo), n_hi = fmaxf(m_hi, mx_hi);
+      // The running maximum rarely moves after the first steps: rescale only when some row's did.
+      if (__any_sync(0xFFFFFFFFu, n_lo != m_lo || n_hi != m_hi)) {
+        const float c_lo = exp2_diff(m_lo, n_lo), c_hi = exp2_diff(m_hi, n_hi);
+        l_lo *= c_lo, l_hi *= c_hi;
+#pragma unroll
+        for (int nt = 0; nt < kNt; ++nt) {
+          o[nt][0] *= c_lo, o[nt][1] *= c_lo;
+          o[nt][2] *= c_hi, o[nt][3] *= c_hi;
+        }
+        m_lo = n_lo, m_hi = n_hi;
+      }
+      // exp2(-inf - finite) = 0 for masked tokens.  A row whose maximum is still -inf (scores
+      // that are -inf in the data) must not compute -inf - -inf: it subtracts 0 instead.
+      const float z_lo = n_lo == -INFINITY ? 0.f : n_lo, z_hi = n_hi == -INFINITY ? 0.f : n_hi;
+      float pr[8];
+      pr[0] = exp2f(s0[0] - z_lo), pr[1] = exp2f(s0[1] - z_lo);
+      pr[2] = exp2f(s0[2] - z_hi), pr[3] = exp2f(s0[3] - z_hi);
+      pr[4] = exp2f(s1[0] - z_lo), pr[5] = exp2f(s1[1] - z_lo);
+      pr[6] = exp2f(s1[2] - z_hi), pr[7] = exp2f(s1[3] - z_hi);
+      l_lo += (pr[0] + pr[1]) + (pr[4] + pr[5]);
+      l_hi += (pr[2] + pr[3]) + (pr[6] + pr[7]);
+      const uint32_t pa0 = T::pack2(pr[0], pr[1]), pa1 = T::pack2(pr[2], pr[3]);
+      const uint32_t pa2 = T::pack2(pr[4], pr[5]), pa3 = T::pack2(pr[6], pr[7]);
 #pragma unroll
       for (int hd = 0; hd < kHd; ++hd) {
-        if (2 * j >= left) vv[hd][0] = make_uint4(0, 0, 0, 0);
-        if (2 * j + 1 >= left) vv[hd][1] = make_uint4(0, 0, 0, 0);
-        if (2 * j + 8 >= left) vv[hd][2] = make_uint4(0, 0, 0, 0);
-        if (2 * j + 9 >= left) vv[hd][3] = make_uint4(0, 0, 0, 0);
+        uint4 vv[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) vv[r] = src[(2 * kC + 4 * hd + r) * 32];
+        if (left < 16) {  // whatever the page holds beyond the chunk must not meet a zero weight
+          if (2 * j >= left) vv[0] = make_uint4(0, 0, 0, 0);
+          if (2 * j + 1 >= left) vv[1] = make_uint4(0, 0, 0, 0);
+          if (2 * j + 8 >= left) vv[2] = make_uint4(0, 0, 0, 0);
+          if (2 * j + 9 >= left) vv[3] = make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int i2 = 0; i2 < 8; ++i2) {
+          const uint32_t sel = (i2 & 1) ? 0x7632u : 0x5410u;  // high or low halves of both words
+          const uint32_t b0 = __byte_perm(word_of(vv[0], i2 >> 1), word_of(vv[1], i2 >> 1), sel);
+          const uint32_t b1 = __byte_perm(word_of(vv[2], i2 >> 1), word_of(vv[3], i2 >> 1), sel);
+          T::mma(o[hd * 8 + i2], pa0, pa1, pa2, pa3, b0, b1);
+        }
       }
     }
+    cp_async_wait<0>();  // only empty groups can be left; the ring is free for the next item
 
-    float mx_lo = fmaxf(fmaxf(s0[0], s0[1]), fmaxf(s1[0], s1[1]));
-    float mx_hi = fmaxf(fmaxf(s0[2], s0[3]), fmaxf(s1[2], s1[3]));
-    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xFFFFFFFFu, mx_lo, 1));
-    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xFFFFFFFFu, mx_lo, 2));
-    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xFFFFFFFFu, mx_hi, 1));
-    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xFFFFFFFFu, mx_hi, 2));
-    const float n_lo = fmaxf(m_lo, mx_lo), n_hi = fmaxf(m_hi, mx_hi);
-    const float c_lo = exp2_diff(m_lo, n_lo), c_hi = exp2_diff(m_hi, n_hi);
-    m_lo = n_lo, m_hi = n_hi;
-    // exp2(-inf - finite) = 0 for masked tokens; a row whose maximum is still -inf (scores
-    // that are -inf or NaN in the data) keeps p = 0 through the guard.
-    float pr[8];
-    pr[0] = n_lo == -INFINITY ? 0.f : exp2f(s0[0] - n_lo);
-    pr[1] = n_lo == -INFINITY ? 0.f : exp2f(s0[1] - n_lo);
-    pr[2] = n_hi == -INFINITY ? 0.f : exp2f(s0[2] - n_hi);
-    pr[3] = n_hi == -INFINITY ? 0.f : exp2f(s0[3] - n_hi);
-    pr[4] = n_lo == -INFINITY ? 0.f : exp2f(s1[0] - n_lo);
-    pr[5] = n_lo == -INFINITY ? 0.f : exp2f(s1[1] - n_lo);
-    pr[6] = n_hi == -INFINITY ? 0.f : exp2f(s1[2] - n_hi);
-    pr[7] = n_hi == -INFINITY ? 0.f : exp2f(s1[3] - n_hi);
-    l_lo = l_lo * c_lo + (pr[0] + pr[1] + pr[4] + pr[5]);
-    l_hi = l_hi * c_hi + (pr[2] + pr[3] + pr[6] + pr[7]);
+    // Denominators were kept per lane; complete them over the 4 lanes that share a row.
+    l_lo += __shfl_xor_sync(0xFFFFFFFFu, l_lo, 1);
+    l_lo += __shfl_xor_sync(0xFFFFFFFFu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xFFFFFFFFu, l_hi, 1);
+    l_hi += __shfl_xor_sync(0xFFFFFFFFu, l_hi, 2);
+
+    // Merge the warps' partial results: common maximum, rescaled sums.
+    if (j == 0) {
+      sm_m[warp][g] = m_lo, sm_m[warp][g + 8] = m_hi;
+      sm_l[warp][g] = l_lo, sm_l[warp][g + 8] = l_hi;
+    }
+    for (int i = threadIdx.x; i < 16 * (kD + 2); i += kAttnThreads) (&sm_o[0][0])[i] = 0.f;
+    __syncthreads();
+    float M_lo = -INFINITY, M_hi = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) {
+      M_lo = fmaxf(M_lo, sm_m[w][g]);
+      M_hi = fmaxf(M_hi, sm_m[w][g + 8]);
+    }
+    const float f_lo = exp2_diff(m_lo, M_lo), f_hi = exp2_diff(m_hi, M_hi);
 #pragma unroll
     for (int nt = 0; nt < kNt; ++nt) {
-      o[nt][0] *= c_lo, o[nt][1] *= c_lo;
-      o[nt][2] *= c_hi, o[nt][3] *= c_hi;
-    }
-    const uint32_t pa0 = T::pack2(pr[0], pr[1]), pa1 = T::pack2(pr[2], pr[3]);
-    const uint32_t pa2 = T::pack2(pr[4], pr[5]), pa3 = T::pack2(pr[6], pr[7]);
-#pragma unroll
-    for (int hd = 0; hd < kHd; ++hd) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const uint32_t sel = (i & 1) ? 0x7632u : 0x5410u;  // high or low halves of both words
-        const uint32_t b0 = __byte_perm(word_of(vv[hd][0], i >> 1), word_of(vv[hd][1], i >> 1), sel);
-        const uint32_t b1 = __byte_perm(word_of(vv[hd][2], i >> 1), word_of(vv[hd][3], i >> 1), sel);
-        T::mma(o[hd * 8 + i], pa0, pa1, pa2, pa3, b0, b1);
+      const int d0 = 64 * (nt >> 3) + 16 * j + (nt & 7);  // column 2j -> head dim 64 hd + 8 (2j) + i
+      if (g < G) {
+        atomicAdd(&sm_o[g][d0], o[nt][0] * f_lo);
+        atomicAdd(&sm_o[g][d0 + 8], o[nt][1] * f_lo);
+      }
+      if (kUpper && g + 8 < G) {
+        atomicAdd(&sm_o[g + 8][d0], o[nt][2] * f_hi);
+        atomicAdd(&sm_o[g + 8][d0 + 8], o[nt][3] * f_hi);
       }
     }
-  }
+    __syncthreads();
 
-  // Denominators were kept per lane; complete them over the 4 lanes that share a row.
-  l_lo += __shfl_xor_sync(0xFFFFFFFFu, l_lo, 1);
-  l_lo += __shfl_xor_sync(0xFFFFFFFFu, l_lo, 2);
-  l_hi += __shfl_xor_sync(0xFFFFFFFFu, l_hi, 1);
-  l_hi += __shfl_xor_sync(0xFFFFFFFFu, l_hi, 2);
-
-  // Merge the warps' partial results: common maximum, rescaled sums.
-  if (j == 0) {
-    sm_m[warp][g] = m_lo, sm_m[warp][g + 8] = m_hi;
-    sm_l[warp][g] = l_lo, sm_l[warp][g + 8] = l_hi;
-  }
-  for (int i = threadIdx.x; i < 16 * kD; i += kAttnThreads) (&sm_o[0][0])[i] = 0.f;
-  __syncthreads();
-  float M_lo = -INFINITY, M_hi = -INFINITY;
+    for (int i = threadIdx.x; i < G * kD; i += kAttnThreads) {
+      const int row = i / kD, d = i - row * kD;
+      float M = -INFINITY, L = 0.f;
 #pragma unroll
-  for (int w = 0; w < kAttnWarps; ++w) {
-    M_lo = fmaxf(M_lo, sm_m[w][g]);
-    M_hi = fmaxf(M_hi, sm_m[w][g + 8]);
-  }
-  const float f_lo = exp2_diff(m_lo, M_lo), f_hi = exp2_diff(m_hi, M_hi);
+      for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, sm_m[w][row]);
 #pragma unroll
-  for (int nt = 0; nt < kNt; ++nt) {
-    const int d0 = 64 * (nt >> 3) + 16 * j + (nt & 7);  // column 2j -> head dim 64 hd + 8 (2j) + i
-    if (g < G) {
-      atomicAdd(&sm_o[g][d0], o[nt][0] * f_lo);
-      atomicAdd(&sm_o[g][d0 + 8], o[nt][1] * f_lo);
-    }
-    if (kUpper && g + 8 < G) {
-      atomicAdd(&sm_o[g + 8][d0], o[nt][2] * f_hi);
-      atomicAdd(&sm_o[g + 8][d0 + 8], o[nt][3] * f_hi);
-    }
-  }
-  __syncthreads();
-
-  for (int i = threadIdx.x; i < G * kD; i += kAttnThreads) {
-    const int row = i / kD, d = i - row * kD;
-    float M = -INFINITY, L = 0.f;
-#pragma unroll
-    for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, sm_m[w][row]);
-#pragma unroll
-    for (int w = 0; w < kAttnWarps; ++w) L += sm_l[w][row] * exp2_diff(sm_m[w][row], M);
-    const float val = L > 0.f ? sm_o[row][d] / L : 0.f;
-    const int64_t q = q_row0 + row;
-    if (p.splits == 1) {
-      reinterpret_cast<uint16_t *>(p.out)[q * kD + d] = T::round1(val);
-    } else {
-      const int64_t at = q * p.splits + split;
-      p.part_o[at * kD + d] = val;
-      if (d == 0) {
-        p.part_ml[at * 2] = M;
-        p.part_ml[at * 2 + 1] = L;
+      for (int w = 0; w < kAttnWarps; ++w) L += sm_l[w][row] * exp2_diff(sm_m[w][row], M);
+      const float val = L > 0.f ? sm_o[row][d] / L : 0.f;
+      const int64_t q = q_row0 + row;
+      if (p.splits == 1) {
+        reinterpret_cast<uint16_t *>(p.out)[q * kD + d] = T::round1(val);
+      } else {
+        const int64_t at = q * p.splits + split;
+        p.part_o[at * kD + d] = val;
+        if (d == 0) {
+          p.part_ml[at * 2] = M;
+          p.part_ml[at * 2 + 1] = L;
+        }
       }
     }
+    __syncthreads();  // the next item reuses the merge buffers and sm_item
   }
 }
 
@@ -579,20 +711,43 @@ bool dense3(const kvx_tensor_desc_t *t, int64_t a, int64_t b, int64_t c, kvx_sta
 }
 
 template <typename T, int kD, typename IdxT>
-void launch_fast(const AttnParams &p, dim3 grid, cudaStream_t st) {
-  if (p.group > 8)
-    kvx_attention_decode_kernel<T, kD, IdxT, true><<<grid, kAttnThreads, 0, st>>>(p);
-  else
-    kvx_attention_decode_kernel<T, kD, IdxT, false><<<grid, kAttnThreads, 0, st>>>(p);
+void launch_fast(const AttnParams &p, unsigned grid, size_t smem, cudaStream_t st) {
+  // (the attribute is per device and cheap to set, so it is set on every launch)
+  if (p.group > 8) {
+    cudaFuncSetAttribute(kvx_attention_decode_kernel<T, kD, IdxT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         static_cast<int>(smem));
+    kvx_attention_decode_kernel<T, kD, IdxT, true><<<grid, kAttnThreads, smem, st>>>(p);
+  } else {
+    cudaFuncSetAttribute(kvx_attention_decode_kernel<T, kD, IdxT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         static_cast<int>(smem));
+    kvx_attention_decode_kernel<T, kD, IdxT, false><<<grid, kAttnThreads, smem, st>>>(p);
+  }
 }
 
 template <typename T, typename IdxT>
-void launch_fast_dim(const AttnParams &p, dim3 grid, cudaStream_t st) {
+void launch_fast_dim(const AttnParams &p, unsigned grid, size_t smem, cudaStream_t st) {
   if (p.dim == 128)
-    launch_fast<T, 128, IdxT>(p, grid, st);
+    launch_fast<T, 128, IdxT>(p, grid, smem, st);
   else
-    launch_fast<T, 64, IdxT>(p, grid, st);
+    launch_fast<T, 64, IdxT>(p, grid, smem, st);
 }
+
+// SM count of the current device, looked up once per device.
+int sm_count() {
+  static std::atomic<int> cached[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+    cached[dev].store(n, std::memory_order_relaxed);
+  }
+  return n;
+}
+
+int g_ctas_per_sm = 2;  // persistent CTAs per SM of the fast kernel (its launch bound)
 
 }  // namespace
 
@@ -604,8 +759,10 @@ KVX_API size_t kvx_paged_attention_workspace_bytes(uint32_t seq_count, uint32_t 
   if (seq_count == 0 || num_q_heads == 0 || num_kv_heads == 0 || head_dim == 0 || max_seq_len == 0) return 0;
   const int64_t chunk = choose_chunk(seq_count, num_kv_heads, max_seq_len);
   const int64_t splits = (static_cast<int64_t>(max_seq_len) + chunk - 1) / chunk;
-  if (splits <= 1) return 0;
-  return static_cast<size_t>(seq_count) * num_q_heads * splits * (static_cast<size_t>(head_dim) + 2) * sizeof(float);
+  size_t bytes = kCounterBytes;  // the work counter
+  if (splits > 1)
+    bytes += static_cast<size_t>(seq_count) * num_q_heads * splits * (static_cast<size_t>(head_dim) + 2) * sizeof(float);
+  return bytes;
 }
 
 KVX_API kvx_status_t kvx_launch_paged_attention_decode(const kvx_cache_desc_t *cache,
@@ -660,12 +817,16 @@ KVX_API kvx_status_t kvx_launch_paged_attention_decode(const kvx_cache_desc_t *c
   p.out = static_cast<char *>(attn->out.data);
   p.part_o = nullptr;
   p.part_ml = nullptr;
+  p.counter = nullptr;
   p.scale_log2 = attn->scale * 1.4426950408889634f;
   p.seq_count = static_cast<int32_t>(S);
   p.max_blocks = static_cast<int32_t>(attn->block_table.max_blocks_per_seq);
   p.max_seq_len = static_cast<int32_t>(attn->max_seq_len);
   p.num_blocks = static_cast<int32_t>(cache->num_blocks);
   p.block_size = static_cast<int32_t>(cache->block_size);
+  p.bs_shift = -1;
+  for (int sh = 0; sh < 31; ++sh)
+    if ((1u << sh) == cache->block_size) p.bs_shift = sh;
   p.heads_q = static_cast<int32_t>(Hq);
   p.heads_kv = static_cast<int32_t>(H);
   p.group = static_cast<int32_t>(Hq / H);
@@ -678,25 +839,31 @@ KVX_API kvx_status_t kvx_launch_paged_attention_decode(const kvx_cache_desc_t *c
                     cache->block_size % 16 == 0 && p.group <= 16 && view_rows16(p.k, elem) && view_rows16(p.v, elem) &&
                     aligned16(p.query) && H <= 65535 && S <= 65535;
   if (fast) {
+    const size_t need = kvx_paged_attention_workspace_bytes(static_cast<uint32_t>(S), static_cast<uint32_t>(Hq),
+                                                            static_cast<uint32_t>(H), static_cast<uint32_t>(D),
+                                                            attn->max_seq_len);
+    if (workspace == nullptr || workspace_bytes < need || !aligned16(workspace)) return KVX_STATUS_INVALID_ARGUMENT;
+    p.counter = static_cast<unsigned long long *>(workspace);
     if (p.splits > 1) {
-      const size_t need = kvx_paged_attention_workspace_bytes(static_cast<uint32_t>(S), static_cast<uint32_t>(Hq),
-                                                              static_cast<uint32_t>(H), static_cast<uint32_t>(D),
-                                                              attn->max_seq_len);
-      if (workspace == nullptr || workspace_bytes < need || !aligned16(workspace)) return KVX_STATUS_INVALID_ARGUMENT;
-      p.part_o = static_cast<float *>(workspace);
+      p.part_o = reinterpret_cast<float *>(static_cast<char *>(workspace) + kCounterBytes);
       p.part_ml = p.part_o + S * Hq * p.splits * D;
     }
-    const dim3 grid(static_cast<unsigned>(p.splits), static_cast<unsigned>(H), static_cast<unsigned>(S));
+    p.use_prefix = S <= kMaxPrefixSeqs ? 1 : 0;
+    const size_t ring = static_cast<size_t>(kAttnWarps) * kStages * (D / 16 + D / 16) * 32 * 16;  // 2 kC + 4 kHd slots
+    const size_t smem = ring + (p.use_prefix ? static_cast<size_t>(S + 1) * sizeof(int32_t) : 0);
+    const int64_t most = S * p.splits * H;  // work items if every context had max_seq_len tokens
+    const int64_t grid = std::max<int64_t>(1, std::min<int64_t>(most, static_cast<int64_t>(sm_count()) * g_ctas_per_sm));
+    if (cudaMemsetAsync(p.counter, 0, kCounterBytes, cs) != cudaSuccess) return KVX_STATUS_INTERNAL_ERROR;
     if (cd == KVX_DTYPE_BF16) {
       if (s32)
-        launch_fast_dim<Bf16, int32_t>(p, grid, cs);
+        launch_fast_dim<Bf16, int32_t>(p, static_cast<unsigned>(grid), smem, cs);
       else
-        launch_fast_dim<Bf16, int64_t>(p, grid, cs);
+        launch_fast_dim<Bf16, int64_t>(p, static_cast<unsigned>(grid), smem, cs);
     } else {
       if (s32)
-        launch_fast_dim<Fp16, int32_t>(p, grid, cs);
+        launch_fast_dim<Fp16, int32_t>(p, static_cast<unsigned>(grid), smem, cs);
       else
-        launch_fast_dim<Fp16, int64_t>(p, grid, cs);
+        launch_fast_dim<Fp16, int64_t>(p, static_cast<unsigned>(grid), smem, cs);
     }
     if (p.splits > 1) {
       if (s32)
