@@ -228,12 +228,28 @@ constexpr int kAttnThreads = kAttnWarps * 32;
 // Work distribution.  Items are (sequence, chunk, KV head) triples of chunks that exist; CTAs
 // claim them one at a time from a counter in the caller's scratch (zeroed by the launcher), so
 // short and long items balance out.
-constexpr int kStages = 3;
+#ifndef KVX_ATTN_STAGES
+#define KVX_ATTN_STAGES 3
+#endif
+#ifndef KVX_ATTN_CTAS
+#define KVX_ATTN_CTAS 2
+#endif
+#ifndef KVX_ATTN_PREFETCH
+#define KVX_ATTN_PREFETCH 4
+#endif
+constexpr int kStages = KVX_ATTN_STAGES;
+constexpr int kPrefetchAhead = KVX_ATTN_PREFETCH;  // steps pulled into L2 ahead of the cp.async ring (0 = off)
 constexpr size_t kCounterBytes = 16;  // head of the scratch: the work counter, padded
 
 __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src) {
   const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void prefetch_l2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+__device__ __forceinline__ float fast_exp2(float x) {  // ex2.approx: 2 ulp, -inf -> 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int kPending>
@@ -242,7 +258,7 @@ __device__ __forceinline__ void cp_async_wait() {
 }
 
 template <typename T, int kD, typename IdxT, bool kUpper>
-__global__ void __launch_bounds__(kAttnThreads, 2) kvx_attention_decode_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(kAttnThreads, KVX_ATTN_CTAS) kvx_attention_decode_kernel(const AttnParams p) {
   constexpr int kC = kD / 32;         // 16-byte loads per K row and lane
   constexpr int kHd = kD / 64;        // 64-dim halves of a V row
   constexpr int kNt = kD / 8;         // output column tiles
@@ -356,6 +372,25 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kvx_attention_decode_kernel(c
       const int64_t b = read_idx<IdxT>(p.table, static_cast<int64_t>(seq) * p.max_blocks + lb);
       return (b < 0 || b >= p.num_blocks) ? -1 : b;
     };
+    // Byte offsets of this lane's rows inside a step, fixed for the whole kernel.
+    const int64_t k_lane0 = g * p.k.tok + 16 * j, k_lane1 = (g + 8) * p.k.tok + 16 * j;
+    const int64_t v_lane0 = (2 * j) * p.v.tok + 16 * g, v_lane1 = (2 * j + 1) * p.v.tok + 16 * g;
+    const int64_t v_lane8 = (2 * j + 8) * p.v.tok + 16 * g, v_lane9 = (2 * j + 9) * p.v.tok + 16 * g;
+    // L2 prefetch: lane l pulls half of row l / 2 (D = 128) or row l (D = 64, lanes 0..15).
+    const int pf_row = kD == 128 ? (lane >> 1) : lane, pf_off = kD == 128 ? 128 * (lane & 1) : 0;
+    const bool pf_lane = kD == 128 || lane < 16;
+    const int64_t k_pf = pf_row * p.k.tok + pf_off, v_pf = pf_row * p.v.tok + pf_off;
+
+    auto prefetch = [&](int i) {  // pull step i of this warp into L2, a few steps ahead of the copies
+      if (kPrefetchAhead > 0 && i < mine && pf_lane) {
+        uint32_t o0;
+        const int64_t b = page_of(i, &o0);
+        if (b >= 0) {
+          prefetch_l2(p.k.base + b * p.k.blk + head_k + static_cast<int64_t>(o0) * p.k.tok + k_pf);
+          prefetch_l2(p.v.base + b * p.v.blk + head_v + static_cast<int64_t>(o0) * p.v.tok + v_pf);
+        }
+      }
+    };
     auto issue = [&](int i) {
       if (i < mine) {
         uint32_t o0;
@@ -363,20 +398,20 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kvx_attention_decode_kernel(c
         const int stage = i % kStages;
         sm_page[warp][stage] = static_cast<int32_t>(b);  // every lane writes the same value
         if (b >= 0) {
-          const char *kp = p.k.base + b * p.k.blk + head_k + static_cast<int64_t>(o0) * p.k.tok + 16 * j;
-          const char *vp = p.v.base + b * p.v.blk + head_v + static_cast<int64_t>(o0) * p.v.tok + 16 * g;
+          const char *kp = p.k.base + b * p.k.blk + head_k + static_cast<int64_t>(o0) * p.k.tok;
+          const char *vp = p.v.base + b * p.v.blk + head_v + static_cast<int64_t>(o0) * p.v.tok;
           uint4 *dst = ring + (stage * kSlots) * 32;
 #pragma unroll
           for (int c = 0; c < kC; ++c) {
-            cp_async16(dst + (2 * c) * 32, kp + g * p.k.tok + 64 * c);
-            cp_async16(dst + (2 * c + 1) * 32, kp + (g + 8) * p.k.tok + 64 * c);
+            cp_async16(dst + (2 * c) * 32, kp + k_lane0 + 64 * c);
+            cp_async16(dst + (2 * c + 1) * 32, kp + k_lane1 + 64 * c);
           }
 #pragma unroll
           for (int hd = 0; hd < kHd; ++hd) {
-            cp_async16(dst + (2 * kC + 4 * hd) * 32, vp + (2 * j) * p.v.tok + 128 * hd);
-            cp_async16(dst + (2 * kC + 4 * hd + 1) * 32, vp + (2 * j + 1) * p.v.tok + 128 * hd);
-            cp_async16(dst + (2 * kC + 4 * hd + 2) * 32, vp + (2 * j + 8) * p.v.tok + 128 * hd);
-            cp_async16(dst + (2 * kC + 4 * hd + 3) * 32, vp + (2 * j + 9) * p.v.tok + 128 * hd);
+            cp_async16(dst + (2 * kC + 4 * hd) * 32, vp + v_lane0 + 128 * hd);
+            cp_async16(dst + (2 * kC + 4 * hd + 1) * 32, vp + v_lane1 + 128 * hd);
+            cp_async16(dst + (2 * kC + 4 * hd + 2) * 32, vp + v_lane8 + 128 * hd);
+            cp_async16(dst + (2 * kC + 4 * hd + 3) * 32, vp + v_lane9 + 128 * hd);
           }
         }
       }
@@ -384,8 +419,11 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kvx_attention_decode_kernel(c
     };
 
 #pragma unroll
+    for (int i = 0; i < kStages - 1 + kPrefetchAhead; ++i) prefetch(i);
+#pragma unroll
     for (int i = 0; i < kStages - 1; ++i) issue(i);
     for (int i = 0; i < mine; ++i) {
+      prefetch(i + kStages - 1 + kPrefetchAhead);
       issue(i + kStages - 1);
       cp_async_wait<kStages - 1>();  // this lane's copies of step i have landed
       const int stage = i % kStages;
@@ -442,10 +480,10 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kvx_attention_decode_kernel(c
       // that are -inf in the data) must not compute -inf - -inf: it subtracts 0 instead.
       const float z_lo = n_lo == -INFINITY ? 0.f : n_lo, z_hi = n_hi == -INFINITY ? 0.f : n_hi;
       float pr[8];
-      pr[0] = exp2f(s0[0] - z_lo), pr[1] = exp2f(s0[1] - z_lo);
-      pr[2] = exp2f(s0[2] - z_hi), pr[3] = exp2f(s0[3] - z_hi);
-      pr[4] = exp2f(s1[0] - z_lo), pr[5] = exp2f(s1[1] - z_lo);
-      pr[6] = exp2f(s1[2] - z_hi), pr[7] = exp2f(s1[3] - z_hi);
+      pr[0] = fast_exp2(s0[0] - z_lo), pr[1] = fast_exp2(s0[1] - z_lo);
+      pr[2] = fast_exp2(s0[2] - z_hi), pr[3] = fast_exp2(s0[3] - z_hi);
+      pr[4] = fast_exp2(s1[0] - z_lo), pr[5] = fast_exp2(s1[1] - z_lo);
+      pr[6] = fast_exp2(s1[2] - z_hi), pr[7] = fast_exp2(s1[3] - z_hi);
       l_lo += (pr[0] + pr[1]) + (pr[4] + pr[5]);
       l_hi += (pr[2] + pr[3]) + (pr[6] + pr[7]);
       const uint32_t pa0 = T::pack2(pr[0], pr[1]), pa1 = T::pack2(pr[2], pr[3]);
@@ -506,6 +544,306 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kvx_attention_decode_kernel(c
     }
     __syncthreads();
 
+    for (int i = threadIdx.x; i < G * kD; i += kAttnThreads) {
+      const int row = i / kD, d = i - row * kD;
+      float M = -INFINITY, L = 0.f;
+#pragma unroll
+      for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, sm_m[w][row]);
+#pragma unroll
+      for (int w = 0; w < kAttnWarps; ++w) L += sm_l[w][row] * exp2_diff(sm_m[w][row], M);
+      const float val = L > 0.f ? sm_o[row][d] / L : 0.f;
+      const int64_t q = q_row0 + row;
+      if (p.splits == 1) {
+        reinterpret_cast<uint16_t *>(p.out)[q * kD + d] = T::round1(val);
+      } else {
+        const int64_t at = q * p.splits + split;
+        p.part_o[at * kD + d] = val;
+        if (d == 0) {
+          p.part_ml[at * 2] = M;
+          p.part_ml[at * 2 + 1] = L;
+        }
+      }
+    }
+    __syncthreads();  // the next item reuses the merge buffers and sm_item
+  }
+}
+
+// ------------------------------------------------------------------ fast tier, up to 8 query heads per KV head --
+//
+// The same computation with tokens, not query heads, in the 16-row dimension of the MMAs:
+//   scores^T [16 tokens x 8 heads] = K [16 tokens x dims]  x  Q^T [dims x 8 heads]
+//   out^T    [16 dims   x 8 heads] = V^T [16 dims x 16 tokens] x P^T [16 tokens x 8 heads]
+// Eight query heads fill the 8-column operand exactly, so a step costs half the MMAs of the
+// heads-in-rows form, half the output accumulators (32 registers for head_dim 128) and half the
+// exponentials, and the softmax statistics of a head sit in the thread that owns its output
+// columns.  K and V steps are staged row-major in shared memory (16-byte chunk c of row r at
+// position c ^ (r & 7), conflict-free for ldmatrix): K rows are A operands as they lie
+// (ldmatrix), V^T comes from ldmatrix.trans, and P^T from the score accumulators through
+// movmatrix.trans.  The ring is private to a warp; lanes wait for their own cp.async groups
+// and meet in __syncwarp before reading each other's chunks.
+#ifndef KVX_ATTN_T_STAGES
+#define KVX_ATTN_T_STAGES 2
+#endif
+#ifndef KVX_ATTN_T_CTAS
+#define KVX_ATTN_T_CTAS 3
+#endif
+constexpr int kTStages = KVX_ATTN_T_STAGES;
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void *smem_row) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(smem_row));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void *smem_row) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(smem_row));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(a));
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+  uint32_t y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+
+template <typename T, int kD, typename IdxT>
+__global__ void __launch_bounds__(kAttnThreads, KVX_ATTN_T_CTAS) kvx_attention_decode_t_kernel(const AttnParams p) {
+  constexpr int kKs = kD / 16;          // k-steps of the score MMAs = 16-dim row tiles of the output
+  constexpr int kRowBytes = kD * 2;     // one token row of K or V
+  constexpr int kChunks = kD / 8;       // 16-byte chunks per row
+  constexpr int kTile = 16 * kRowBytes; // one 16-token step of K (or of V)
+  constexpr int kPerLane = 16 * kChunks / 32;  // chunks of K (and of V) each lane copies per step
+  extern __shared__ uint4 sm_dyn[];     // ring [warp][stage][K tile | V tile], then the chunk prefix
+  __shared__ float sm_m[kAttnWarps][8];
+  __shared__ float sm_l[kAttnWarps][8];
+  __shared__ float sm_o[8][kD + 8];
+  __shared__ int32_t sm_page[kAttnWarps][kTStages];
+  __shared__ int32_t sm_scan[kAttnThreads];
+  __shared__ unsigned long long sm_item;
+  char *ring = reinterpret_cast<char *>(sm_dyn);
+  int32_t *sm_prefix = reinterpret_cast<int32_t *>(ring + kAttnWarps * kTStages * 2 * kTile);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, j = lane & 3;
+  const int G = p.group;
+  char *my_ring = ring + warp * (kTStages * 2 * kTile);
+
+  int64_t chunks_total;
+  if (p.use_prefix) {
+    const int S = p.seq_count;
+    const int per = (S + kAttnThreads - 1) / kAttnThreads;
+    const int begin = min(static_cast<int>(threadIdx.x) * per, S), end = min(begin + per, S);
+    int32_t local = 0;
+    for (int s = begin; s < end; ++s) local += chunks_of<IdxT>(p, s);
+    sm_scan[threadIdx.x] = local;
+    __syncthreads();
+    int32_t run = 0;
+    for (int t = 0; t < static_cast<int>(threadIdx.x); ++t) run += sm_scan[t];
+    for (int s = begin; s < end; ++s) {
+      sm_prefix[s] = run;
+      run += chunks_of<IdxT>(p, s);
+    }
+    if (threadIdx.x == kAttnThreads - 1) sm_prefix[S] = run;
+    __syncthreads();
+    chunks_total = sm_prefix[S];
+  } else {
+    chunks_total = static_cast<int64_t>(p.seq_count) * p.splits;
+  }
+  const int64_t items = chunks_total * p.heads_kv;
+
+  if (p.splits == 1) {  // sequences without cached tokens have no work item: their output is zero
+    for (int s = blockIdx.x; s < p.seq_count; s += gridDim.x) {
+      if (read_idx<IdxT>(p.lens, s) > 0) continue;
+      for (int i = threadIdx.x; i < p.heads_q * kD; i += kAttnThreads)
+        reinterpret_cast<uint16_t *>(p.out)[static_cast<int64_t>(s) * p.heads_q * kD + i] = 0;
+    }
+  }
+
+  // Fixed per lane: which chunks of a step it copies (row = it * (32 / kChunks) + lane / kChunks,
+  // chunk = lane % kChunks: a warp instruction copies whole rows, coalesced), and the
+  // shared-memory rows its ldmatrix instructions name.
+  const int cp_row0 = lane / kChunks, cp_chunk = lane % kChunks, cp_rows_per_it = 32 / kChunks;
+  // ldmatrix (K as A operand): matrix i = lane / 8 -> rows 8 (i & 1) + lane % 8, chunk 2 kk + (i >> 1)
+  const int lk_row = (lane & 7) + 8 * ((lane >> 3) & 1), lk_half = lane >> 4;
+  // ldmatrix.trans (V^T as A operand): matrix i -> tokens 8 (i >> 1) + lane % 8, chunk 2 mt + (i & 1)
+  const int lv_row = (lane & 7) + 8 * (lane >> 4), lv_half = (lane >> 3) & 1;
+
+  for (;;) {
+    if (threadIdx.x == 0) sm_item = atomicAdd(p.counter, 1ull);
+    __syncthreads();
+    const int64_t item = static_cast<int64_t>(sm_item);
+    if (item >= items) break;
+    const int kvh = static_cast<int>(item % p.heads_kv);
+    const int64_t ci = item / p.heads_kv;
+    int seq, split;
+    if (p.use_prefix) {
+      int lo = 0, hi = p.seq_count;  // last s with prefix[s] <= ci
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (sm_prefix[mid] <= ci)
+          lo = mid;
+        else
+          hi = mid;
+      }
+      seq = lo;
+      split = static_cast<int>(ci - sm_prefix[lo]);
+    } else {
+      seq = static_cast<int>(ci / p.splits);
+      split = static_cast<int>(ci - static_cast<int64_t>(seq) * p.splits);
+    }
+    int64_t len = read_idx<IdxT>(p.lens, seq);
+    if (len > p.max_seq_len) len = p.max_seq_len;
+    const int64_t cbeg = static_cast<int64_t>(split) * p.chunk;
+    const int64_t cend = min(len, cbeg + p.chunk);
+    const int64_t q_row0 = static_cast<int64_t>(seq) * p.heads_q + static_cast<int64_t>(kvh) * G;
+
+    // Q^T as B operands: column g = query head g of the group (zero beyond the group),
+    // b0 = dims 16 kk + 2j, +1; b1 = dims 16 kk + 8 + 2j, +1.
+    uint32_t qb[kKs][2];
+#pragma unroll
+    for (int kk = 0; kk < kKs; ++kk) {
+      qb[kk][0] = qb[kk][1] = 0;
+      if (g < G) {
+        const char *qrow = p.query + (q_row0 + g) * kRowBytes;
+        qb[kk][0] = *reinterpret_cast<const uint32_t *>(qrow + (16 * kk + 2 * j) * 2);
+        qb[kk][1] = *reinterpret_cast<const uint32_t *>(qrow + (16 * kk + 8 + 2 * j) * 2);
+      }
+    }
+
+    float o[kKs][4];  // out^T: tile mt = dims 16 mt ..; c0, c1 = (dim g, heads 2j, 2j+1), c2, c3 = (dim g + 8, ..)
+#pragma unroll
+    for (int mt = 0; mt < kKs; ++mt) o[mt][0] = o[mt][1] = o[mt][2] = o[mt][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;  // heads 2j and 2j + 1
+
+    const int nsteps = cend > cbeg ? static_cast<int>((cend - cbeg + 15) >> 4) : 0;
+    const int mine = nsteps > warp ? (nsteps - warp + kAttnWarps - 1) / kAttnWarps : 0;
+    const int64_t head_k = static_cast<int64_t>(kvh) * p.k.head, head_v = static_cast<int64_t>(kvh) * p.v.head;
+
+    auto issue = [&](int i) {
+      if (i < mine) {
+        const uint32_t t0 = static_cast<uint32_t>(cbeg) + static_cast<uint32_t>(warp + i * kAttnWarps) * 16u;
+        const uint32_t lb = p.bs_shift >= 0 ? (t0 >> p.bs_shift) : (t0 / static_cast<uint32_t>(p.block_size));
+        const uint32_t o0 = t0 - lb * static_cast<uint32_t>(p.block_size);  // a step never straddles pages
+        int64_t b = -1;
+        if (lb < static_cast<uint32_t>(p.max_blocks)) {
+          b = read_idx<IdxT>(p.table, static_cast<int64_t>(seq) * p.max_blocks + lb);
+          if (b < 0 || b >= p.num_blocks) b = -1;  // as the gather: skipped
+        }
+        const int stage = i % kTStages;
+        sm_page[warp][stage] = static_cast<int32_t>(b);  // every lane writes the same value
+        if (b >= 0) {
+          const int left = static_cast<int>(min(static_cast<int64_t>(16), cend - t0));  // valid rows
+          const char *kp = p.k.base + b * p.k.blk + head_k + static_cast<int64_t>(o0) * p.k.tok + 16 * cp_chunk;
+          const char *vp = p.v.base + b * p.v.blk + head_v + static_cast<int64_t>(o0) * p.v.tok + 16 * cp_chunk;
+          char *kd = my_ring + stage * (2 * kTile), *vd = kd + kTile;
+#pragma unroll
+          for (int it = 0; it < kPerLane; ++it) {
+            const int row = it * cp_rows_per_it + cp_row0;
+            const int at = row * kRowBytes + ((cp_chunk ^ (row & 7)) << 4);
+            if (row < left) {
+              cp_async16(kd + at, kp + row * p.k.tok);
+              cp_async16(vd + at, vp + row * p.v.tok);
+            } else {  // beyond the chunk: zeros, so that a zero weight never meets what the page holds there
+              *reinterpret_cast<uint4 *>(kd + at) = make_uint4(0, 0, 0, 0);
+              *reinterpret_cast<uint4 *>(vd + at) = make_uint4(0, 0, 0, 0);
+            }
+          }
+        }
+      }
+      cp_async_commit();
+    };
+
+#pragma unroll
+    for (int i = 0; i < kTStages - 1; ++i) issue(i);
+    for (int i = 0; i < mine; ++i) {
+      issue(i + kTStages - 1);
+      cp_async_wait<kTStages - 1>();
+      __syncwarp();  // every lane's chunks of step i are in place
+      const int stage = i % kTStages;
+      if (sm_page[warp][stage] < 0) continue;
+      const int64_t t0 = cbeg + static_cast<int64_t>(warp + i * kAttnWarps) * 16;
+      const char *ks = my_ring + stage * (2 * kTile), *vs = ks + kTile;
+
+      float s[4] = {0.f, 0.f, 0.f, 0.f};  // (token g, heads 2j, 2j+1), (token g + 8, heads 2j, 2j+1)
+#pragma unroll
+      for (int kk = 0; kk < kKs; ++kk) {
+        uint32_t a[4];
+        ldmatrix_x4(a, ks + lk_row * kRowBytes + (((2 * kk + lk_half) ^ (lk_row & 7)) << 4));
+        T::mma(s, a[0], a[1], a[2], a[3], qb[kk][0], qb[kk][1]);
+      }
+      const int64_t left = cend - t0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[e] *= p.scale_log2;
+      if (left < 16) {
+        if (g >= left) s[0] = s[1] = -INFINITY;
+        if (g + 8 >= left) s[2] = s[3] = -INFINITY;
+      }
+      // maxima of heads 2j and 2j + 1 over the step's 16 tokens: this lane's two, then over g
+      float x0 = fmaxf(s[0], s[2]), x1 = fmaxf(s[1], s[3]);
+#pragma unroll
+      for (int d = 4; d < 32; d <<= 1) {
+        x0 = fmaxf(x0, __shfl_xor_sync(0xFFFFFFFFu, x0, d));
+        x1 = fmaxf(x1, __shfl_xor_sync(0xFFFFFFFFu, x1, d));
+      }
+      const float n0 = fmaxf(m0, x0), n1 = fmaxf(m1, x1);
+      if (__any_sync(0xFFFFFFFFu, n0 != m0 || n1 != m1)) {
+        const float c0 = exp2_diff(m0, n0), c1 = exp2_diff(m1, n1);
+        l0 *= c0, l1 *= c1;
+#pragma unroll
+        for (int mt = 0; mt < kKs; ++mt) {
+          o[mt][0] *= c0, o[mt][2] *= c0;
+          o[mt][1] *= c1, o[mt][3] *= c1;
+        }
+        m0 = n0, m1 = n1;
+      }
+      const float z0 = n0 == -INFINITY ? 0.f : n0, z1 = n1 == -INFINITY ? 0.f : n1;
+      const float p0 = fast_exp2(s[0] - z0), p1 = fast_exp2(s[1] - z1);
+      const float p2 = fast_exp2(s[2] - z0), p3 = fast_exp2(s[3] - z1);
+      l0 += p0 + p2;
+      l1 += p1 + p3;
+      // P^T as B operand: (tokens 2j, 2j+1 | head g) and (tokens 2j+8, 2j+9 | head g)
+      const uint32_t pb0 = movmatrix_trans(T::pack2(p0, p1));
+      const uint32_t pb1 = movmatrix_trans(T::pack2(p2, p3));
+#pragma unroll
+      for (int mt = 0; mt < kKs; ++mt) {
+        uint32_t a[4];
+        ldmatrix_x4_trans(a, vs + lv_row * kRowBytes + (((2 * mt + lv_half) ^ (lv_row & 7)) << 4));
+        T::mma(o[mt], a[0], a[1], a[2], a[3], pb0, pb1);
+      }
+    }
+    cp_async_wait<0>();
+
+    // Denominators were kept per lane (its two tokens per step): complete them over g.
+#pragma unroll
+    for (int d = 4; d < 32; d <<= 1) {
+      l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, d);
+      l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, d);
+    }
+    if (g == 0) {
+      sm_m[warp][2 * j] = m0, sm_m[warp][2 * j + 1] = m1;
+      sm_l[warp][2 * j] = l0, sm_l[warp][2 * j + 1] = l1;
+    }
+    for (int i = threadIdx.x; i < 8 * (kD + 8); i += kAttnThreads) (&sm_o[0][0])[i] = 0.f;
+    __syncthreads();
+    float M0 = -INFINITY, M1 = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) {
+      M0 = fmaxf(M0, sm_m[w][2 * j]);
+      M1 = fmaxf(M1, sm_m[w][2 * j + 1]);
+    }
+    const float f0 = exp2_diff(m0, M0), f1 = exp2_diff(m1, M1);
+#pragma unroll
+    for (int mt = 0; mt < kKs; ++mt) {
+      if (2 * j < G) {
+        atomicAdd(&sm_o[2 * j][16 * mt + g], o[mt][0] * f0);
+        atomicAdd(&sm_o[2 * j][16 * mt + g + 8], o[mt][2] * f0);
+      }
+      if (2 * j + 1 < G) {
+        atomicAdd(&sm_o[2 * j + 1][16 * mt + g], o[mt][1] * f1);
+        atomicAdd(&sm_o[2 * j + 1][16 * mt + g + 8], o[mt][3] * f1);
+      }
+    }
+    __syncthreads();
     for (int i = threadIdx.x; i < G * kD; i += kAttnThreads) {
       const int row = i / kD, d = i - row * kD;
       float M = -INFINITY, L = 0.f;
@@ -732,6 +1070,23 @@ void launch_fast_dim(const AttnParams &p, unsigned grid, size_t smem, cudaStream
     launch_fast<T, 64, IdxT>(p, grid, smem, st);
 }
 
+template <typename T, int kD, typename IdxT>
+void launch_t(const AttnParams &p, unsigned grid, size_t smem, cudaStream_t st) {
+  cudaFuncSetAttribute(kvx_attention_decode_t_kernel<T, kD, IdxT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                       static_cast<int>(smem));
+  kvx_attention_decode_t_kernel<T, kD, IdxT><<<grid, kAttnThreads, smem, st>>>(p);
+}
+
+template <typename T, typename IdxT>
+void launch_t_dim(const AttnParams &p, unsigned grid, size_t smem, cudaStream_t st) {
+  if (p.dim == 128)
+    launch_t<T, 128, IdxT>(p, grid, smem, st);
+  else
+    launch_t<T, 64, IdxT>(p, grid, smem, st);
+}
+
+int g_attn_form = 0;  // 1 = always the heads-in-rows kernel (set through KVX_ATTN_FORM while tuning)
+
 // SM count of the current device, looked up once per device.
 int sm_count() {
   static std::atomic<int> cached[64];
@@ -747,7 +1102,7 @@ int sm_count() {
   return n;
 }
 
-int g_ctas_per_sm = 2;  // persistent CTAs per SM of the fast kernel (its launch bound)
+int g_ctas_per_sm = KVX_ATTN_CTAS;  // persistent CTAs per SM of the fast kernel (its launch bound)
 
 }  // namespace
 
@@ -849,12 +1204,26 @@ KVX_API kvx_status_t kvx_launch_paged_attention_decode(const kvx_cache_desc_t *c
       p.part_ml = p.part_o + S * Hq * p.splits * D;
     }
     p.use_prefix = S <= kMaxPrefixSeqs ? 1 : 0;
-    const size_t ring = static_cast<size_t>(kAttnWarps) * kStages * (D / 16 + D / 16) * 32 * 16;  // 2 kC + 4 kHd slots
+    const bool tokens_in_rows = p.group <= 8 && g_attn_form != 1;
+    const int stages = tokens_in_rows ? kTStages : kStages, per_sm = tokens_in_rows ? KVX_ATTN_T_CTAS : g_ctas_per_sm;
+    const size_t ring = static_cast<size_t>(kAttnWarps) * stages * 2 * 16 * D * 2;  // K and V steps of 16 rows
     const size_t smem = ring + (p.use_prefix ? static_cast<size_t>(S + 1) * sizeof(int32_t) : 0);
     const int64_t most = S * p.splits * H;  // work items if every context had max_seq_len tokens
-    const int64_t grid = std::max<int64_t>(1, std::min<int64_t>(most, static_cast<int64_t>(sm_count()) * g_ctas_per_sm));
+    const int64_t grid = std::max<int64_t>(1, std::min<int64_t>(most, static_cast<int64_t>(sm_count()) * per_sm));
     if (cudaMemsetAsync(p.counter, 0, kCounterBytes, cs) != cudaSuccess) return KVX_STATUS_INTERNAL_ERROR;
-    if (cd == KVX_DTYPE_BF16) {
+    if (tokens_in_rows) {
+      if (cd == KVX_DTYPE_BF16) {
+        if (s32)
+          launch_t_dim<Bf16, int32_t>(p, static_cast<unsigned>(grid), smem, cs);
+        else
+          launch_t_dim<Bf16, int64_t>(p, static_cast<unsigned>(grid), smem, cs);
+      } else {
+        if (s32)
+          launch_t_dim<Fp16, int32_t>(p, static_cast<unsigned>(grid), smem, cs);
+        else
+          launch_t_dim<Fp16, int64_t>(p, static_cast<unsigned>(grid), smem, cs);
+      }
+    } else if (cd == KVX_DTYPE_BF16) {
       if (s32)
         launch_fast_dim<Bf16, int32_t>(p, static_cast<unsigned>(grid), smem, cs);
       else
