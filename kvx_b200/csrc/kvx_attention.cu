@@ -146,7 +146,7 @@ __device__ __forceinline__ int64_t read_idx(const void *p, int64_t i) {
 // few work items each (the bound uses max_seq_len; real contexts are shorter).
 __host__ __device__ inline int32_t choose_chunk(int64_t seq_count, int64_t heads_kv, int64_t max_seq_len) {
   int64_t chunk = 2048;
-  while (chunk > 256 && seq_count * heads_kv * ((max_seq_len + chunk - 1) / chunk) < 4096) chunk >>= 1;
+  while (chunk > 256 && seq_count * heads_kv * ((max_seq_len + chunk - 1) / chunk) < 2048) chunk >>= 1;
   return static_cast<int32_t>(chunk);
 }
 
@@ -234,18 +234,13 @@ constexpr int kAttnThreads = kAttnWarps * 32;
 #ifndef KVX_ATTN_CTAS
 #define KVX_ATTN_CTAS 2
 #endif
-#ifndef KVX_ATTN_PREFETCH
-#define KVX_ATTN_PREFETCH 4
-#endif
 constexpr int kStages = KVX_ATTN_STAGES;
-constexpr int kPrefetchAhead = KVX_ATTN_PREFETCH;  // steps pulled into L2 ahead of the cp.async ring (0 = off)
 constexpr size_t kCounterBytes = 16;  // head of the scratch: the work counter, padded
 
 __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src) {
   const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gmem_src) : "memory");
 }
-__device__ __forceinline__ void prefetch_l2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 __device__ __forceinline__ float fast_exp2(float x) {  // ex2.approx: 2 ulp, -inf -> 0
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -309,8 +304,12 @@ __global__ void __launch_bounds__(kAttnThreads, KVX_ATTN_CTAS) kvx_attention_dec
     }
   }
 
-  for (;;) {
-    if (threadIdx.x == 0) sm_item = atomicAdd(p.counter, 1ull);
+  for (unsigned long long round = 0;;) {
+    // With a counter, CTAs claim items as they become free; without one (few items: one per
+    // CTA) they stride over the list.
+    if (threadIdx.x == 0)
+      sm_item = p.counter != nullptr ? atomicAdd(p.counter, 1ull) : blockIdx.x + round * static_cast<unsigned long long>(gridDim.x);
+    ++round;
     __syncthreads();
     const int64_t item = static_cast<int64_t>(sm_item);
     if (item >= items) break;
@@ -376,21 +375,6 @@ __global__ void __launch_bounds__(kAttnThreads, KVX_ATTN_CTAS) kvx_attention_dec
     const int64_t k_lane0 = g * p.k.tok + 16 * j, k_lane1 = (g + 8) * p.k.tok + 16 * j;
     const int64_t v_lane0 = (2 * j) * p.v.tok + 16 * g, v_lane1 = (2 * j + 1) * p.v.tok + 16 * g;
     const int64_t v_lane8 = (2 * j + 8) * p.v.tok + 16 * g, v_lane9 = (2 * j + 9) * p.v.tok + 16 * g;
-    // L2 prefetch: lane l pulls half of row l / 2 (D = 128) or row l (D = 64, lanes 0..15).
-    const int pf_row = kD == 128 ? (lane >> 1) : lane, pf_off = kD == 128 ? 128 * (lane & 1) : 0;
-    const bool pf_lane = kD == 128 || lane < 16;
-    const int64_t k_pf = pf_row * p.k.tok + pf_off, v_pf = pf_row * p.v.tok + pf_off;
-
-    auto prefetch = [&](int i) {  // pull step i of this warp into L2, a few steps ahead of the copies
-      if (kPrefetchAhead > 0 && i < mine && pf_lane) {
-        uint32_t o0;
-        const int64_t b = page_of(i, &o0);
-        if (b >= 0) {
-          prefetch_l2(p.k.base + b * p.k.blk + head_k + static_cast<int64_t>(o0) * p.k.tok + k_pf);
-          prefetch_l2(p.v.base + b * p.v.blk + head_v + static_cast<int64_t>(o0) * p.v.tok + v_pf);
-        }
-      }
-    };
     auto issue = [&](int i) {
       if (i < mine) {
         uint32_t o0;
@@ -419,11 +403,8 @@ __global__ void __launch_bounds__(kAttnThreads, KVX_ATTN_CTAS) kvx_attention_dec
     };
 
 #pragma unroll
-    for (int i = 0; i < kStages - 1 + kPrefetchAhead; ++i) prefetch(i);
-#pragma unroll
     for (int i = 0; i < kStages - 1; ++i) issue(i);
     for (int i = 0; i < mine; ++i) {
-      prefetch(i + kStages - 1 + kPrefetchAhead);
       issue(i + kStages - 1);
       cp_async_wait<kStages - 1>();  // this lane's copies of step i have landed
       const int stage = i % kStages;
@@ -668,8 +649,12 @@ __global__ void __launch_bounds__(kAttnThreads, KVX_ATTN_T_CTAS) kvx_attention_d
   // ldmatrix.trans (V^T as A operand): matrix i -> tokens 8 (i >> 1) + lane % 8, chunk 2 mt + (i & 1)
   const int lv_row = (lane & 7) + 8 * (lane >> 4), lv_half = (lane >> 3) & 1;
 
-  for (;;) {
-    if (threadIdx.x == 0) sm_item = atomicAdd(p.counter, 1ull);
+  for (unsigned long long round = 0;;) {
+    // With a counter, CTAs claim items as they become free; without one (few items: one per
+    // CTA) they stride over the list.
+    if (threadIdx.x == 0)
+      sm_item = p.counter != nullptr ? atomicAdd(p.counter, 1ull) : blockIdx.x + round * static_cast<unsigned long long>(gridDim.x);
+    ++round;
     __syncthreads();
     const int64_t item = static_cast<int64_t>(sm_item);
     if (item >= items) break;
@@ -1210,7 +1195,10 @@ KVX_API kvx_status_t kvx_launch_paged_attention_decode(const kvx_cache_desc_t *c
     const size_t smem = ring + (p.use_prefix ? static_cast<size_t>(S + 1) * sizeof(int32_t) : 0);
     const int64_t most = S * p.splits * H;  // work items if every context had max_seq_len tokens
     const int64_t grid = std::max<int64_t>(1, std::min<int64_t>(most, static_cast<int64_t>(sm_count()) * per_sm));
-    if (cudaMemsetAsync(p.counter, 0, kCounterBytes, cs) != cudaSuccess) return KVX_STATUS_INTERNAL_ERROR;
+    if (most <= grid)
+      p.counter = nullptr;  // every possible item has its own CTA: nothing to balance, no counter to clear
+    else if (cudaMemsetAsync(p.counter, 0, kCounterBytes, cs) != cudaSuccess)
+      return KVX_STATUS_INTERNAL_ERROR;
     if (tokens_in_rows) {
       if (cd == KVX_DTYPE_BF16) {
         if (s32)
