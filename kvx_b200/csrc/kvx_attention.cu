@@ -557,10 +557,10 @@ __global__ void __launch_bounds__(kAttnThreads, KVX_ATTN_CTAS) kvx_attention_dec
 // Eight query heads fill the 8-column operand exactly, so a step costs half the MMAs of the
 // heads-in-rows form, half the output accumulators (32 registers for head_dim 128) and half the
 // exponentials, and the softmax statistics of a head sit in the thread that owns its output
-// columns.  K and V steps are staged row-major in shared memory (16-byte chunk c of row r at
-// position c ^ (r & 7), conflict-free for ldmatrix): K rows are A operands as they lie
-// (ldmatrix), V^T comes from ldmatrix.trans, and P^T from the score accumulators through
-// movmatrix.trans.  The ring is private to a warp; lanes wait for their own cp.async groups
+// columns.  K and V steps are staged row-major in shared memory (rows padded by 16 bytes, which
+// makes ldmatrix conflict-free and every staging address a per-lane base plus a constant): K
+// rows are A operands as they lie (ldmatrix), V^T comes from ldmatrix.trans, and P^T from the
+// score accumulators through movmatrix.trans.  The ring is private to a warp; lanes wait for their own cp.async groups
 // and meet in __syncwarp before reading each other's chunks.
 #ifndef KVX_ATTN_T_STAGES
 #define KVX_ATTN_T_STAGES 2
@@ -570,17 +570,21 @@ __global__ void __launch_bounds__(kAttnThreads, KVX_ATTN_CTAS) kvx_attention_dec
 #endif
 constexpr int kTStages = KVX_ATTN_T_STAGES;
 
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void *smem_row) {
-  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(smem_row));
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t a) {  // a: shared-window address
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                : "r"(a));
 }
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void *smem_row) {
-  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(smem_row));
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t a) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                : "r"(a));
+}
+__device__ __forceinline__ void cp_async16_s(uint32_t dst, const void *gmem_src) {  // dst: shared-window address
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void st_shared_zero16(uint32_t dst) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(dst), "r"(0u) : "memory");
 }
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
   uint32_t y;
@@ -592,22 +596,27 @@ template <typename T, int kD, typename IdxT>
 __global__ void __launch_bounds__(kAttnThreads, KVX_ATTN_T_CTAS) kvx_attention_decode_t_kernel(const AttnParams p) {
   constexpr int kKs = kD / 16;          // k-steps of the score MMAs = 16-dim row tiles of the output
   constexpr int kRowBytes = kD * 2;     // one token row of K or V
+  constexpr int kPitch = kRowBytes + 16;  // staged rows are 16 bytes apart from a multiple of 128:
+                                          // 8 consecutive rows then start in 8 different bank groups
   constexpr int kChunks = kD / 8;       // 16-byte chunks per row
-  constexpr int kTile = 16 * kRowBytes; // one 16-token step of K (or of V)
+  constexpr int kTile = 16 * kPitch;    // one staged 16-token step of K (or of V)
   constexpr int kPerLane = 16 * kChunks / 32;  // chunks of K (and of V) each lane copies per step
   extern __shared__ uint4 sm_dyn[];     // ring [warp][stage][K tile | V tile], then the chunk prefix
   __shared__ float sm_m[kAttnWarps][8];
   __shared__ float sm_l[kAttnWarps][8];
-  __shared__ float sm_o[8][kD + 8];
   __shared__ int32_t sm_page[kAttnWarps][kTStages];
   __shared__ int32_t sm_scan[kAttnThreads];
   __shared__ unsigned long long sm_item;
   char *ring = reinterpret_cast<char *>(sm_dyn);
+  // merge buffer of the epilogue: lives in the ring, which is idle by then
+  float (*sm_o)[kD + 8] = reinterpret_cast<float (*)[kD + 8]>(ring);
   int32_t *sm_prefix = reinterpret_cast<int32_t *>(ring + kAttnWarps * kTStages * 2 * kTile);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, j = lane & 3;
   const int G = p.group;
-  char *my_ring = ring + warp * (kTStages * 2 * kTile);
+  // 32-bit shared-window address of this warp's ring: all staging addresses below are this
+  // plus small offsets, most of them compile-time
+  const uint32_t my_ring = static_cast<uint32_t>(__cvta_generic_to_shared(ring + warp * (kTStages * 2 * kTile)));
 
   int64_t chunks_total;
   if (p.use_prefix) {
@@ -641,13 +650,16 @@ __global__ void __launch_bounds__(kAttnThreads, KVX_ATTN_T_CTAS) kvx_attention_d
   }
 
   // Fixed per lane: which chunks of a step it copies (row = it * (32 / kChunks) + lane / kChunks,
-  // chunk = lane % kChunks: a warp instruction copies whole rows, coalesced), and the
-  // shared-memory rows its ldmatrix instructions name.
-  const int cp_row0 = lane / kChunks, cp_chunk = lane % kChunks, cp_rows_per_it = 32 / kChunks;
+  // chunk = lane % kChunks: a warp instruction copies whole rows, coalesced), and where its
+  // ldmatrix instructions start.
+  constexpr int cp_rows_per_it = 32 / kChunks;
+  const int cp_row0 = lane / kChunks, cp_chunk = lane % kChunks;
+  const uint32_t cp_at0 = cp_row0 * kPitch + cp_chunk * 16;
+  const int64_t k_step = cp_rows_per_it * p.k.tok, v_step = cp_rows_per_it * p.v.tok;
   // ldmatrix (K as A operand): matrix i = lane / 8 -> rows 8 (i & 1) + lane % 8, chunk 2 kk + (i >> 1)
-  const int lk_row = (lane & 7) + 8 * ((lane >> 3) & 1), lk_half = lane >> 4;
+  const uint32_t lk_at = ((lane & 7) + 8 * ((lane >> 3) & 1)) * kPitch + (lane >> 4) * 16;
   // ldmatrix.trans (V^T as A operand): matrix i -> tokens 8 (i >> 1) + lane % 8, chunk 2 mt + (i & 1)
-  const int lv_row = (lane & 7) + 8 * (lane >> 4), lv_half = (lane >> 3) & 1;
+  const uint32_t lv_at = kTile + ((lane & 7) + 8 * (lane >> 4)) * kPitch + ((lane >> 3) & 1) * 16;
 
   for (unsigned long long round = 0;;) {
     // With a counter, CTAs claim items as they become free; without one (few items: one per
@@ -718,19 +730,26 @@ __global__ void __launch_bounds__(kAttnThreads, KVX_ATTN_T_CTAS) kvx_attention_d
         sm_page[warp][stage] = static_cast<int32_t>(b);  // every lane writes the same value
         if (b >= 0) {
           const int left = static_cast<int>(min(static_cast<int64_t>(16), cend - t0));  // valid rows
-          const char *kp = p.k.base + b * p.k.blk + head_k + static_cast<int64_t>(o0) * p.k.tok + 16 * cp_chunk;
-          const char *vp = p.v.base + b * p.v.blk + head_v + static_cast<int64_t>(o0) * p.v.tok + 16 * cp_chunk;
-          char *kd = my_ring + stage * (2 * kTile), *vd = kd + kTile;
+          // this lane's first row of the step; later rows are cp_rows_per_it rows further on
+          const char *kp = p.k.base + b * p.k.blk + head_k + (static_cast<int64_t>(o0) + cp_row0) * p.k.tok + 16 * cp_chunk;
+          const char *vp = p.v.base + b * p.v.blk + head_v + (static_cast<int64_t>(o0) + cp_row0) * p.v.tok + 16 * cp_chunk;
+          const uint32_t kd = my_ring + stage * (2 * kTile) + cp_at0, vd = kd + kTile;
+          if (left == 16) {
 #pragma unroll
-          for (int it = 0; it < kPerLane; ++it) {
-            const int row = it * cp_rows_per_it + cp_row0;
-            const int at = row * kRowBytes + ((cp_chunk ^ (row & 7)) << 4);
-            if (row < left) {
-              cp_async16(kd + at, kp + row * p.k.tok);
-              cp_async16(vd + at, vp + row * p.v.tok);
-            } else {  // beyond the chunk: zeros, so that a zero weight never meets what the page holds there
-              *reinterpret_cast<uint4 *>(kd + at) = make_uint4(0, 0, 0, 0);
-              *reinterpret_cast<uint4 *>(vd + at) = make_uint4(0, 0, 0, 0);
+            for (int it = 0; it < kPerLane; ++it) {
+              cp_async16_s(kd + it * cp_rows_per_it * kPitch, kp + it * k_step);
+              cp_async16_s(vd + it * cp_rows_per_it * kPitch, vp + it * v_step);
+            }
+          } else {
+#pragma unroll
+            for (int it = 0; it < kPerLane; ++it) {
+              if (it * cp_rows_per_it + cp_row0 < left) {
+                cp_async16_s(kd + it * cp_rows_per_it * kPitch, kp + it * k_step);
+                cp_async16_s(vd + it * cp_rows_per_it * kPitch, vp + it * v_step);
+              } else {  // beyond the chunk: zeros, so that a zero weight never meets what the page holds there
+                st_shared_zero16(kd + it * cp_rows_per_it * kPitch);
+                st_shared_zero16(vd + it * cp_rows_per_it * kPitch);
+              }
             }
           }
         }
@@ -747,13 +766,13 @@ __global__ void __launch_bounds__(kAttnThreads, KVX_ATTN_T_CTAS) kvx_attention_d
       const int stage = i % kTStages;
       if (sm_page[warp][stage] < 0) continue;
       const int64_t t0 = cbeg + static_cast<int64_t>(warp + i * kAttnWarps) * 16;
-      const char *ks = my_ring + stage * (2 * kTile), *vs = ks + kTile;
+      const uint32_t tile = my_ring + stage * (2 * kTile);
 
       float s[4] = {0.f, 0.f, 0.f, 0.f};  // (token g, heads 2j, 2j+1), (token g + 8, heads 2j, 2j+1)
 #pragma unroll
       for (int kk = 0; kk < kKs; ++kk) {
         uint32_t a[4];
-        ldmatrix_x4(a, ks + lk_row * kRowBytes + (((2 * kk + lk_half) ^ (lk_row & 7)) << 4));
+        ldmatrix_x4(a, tile + lk_at + 32 * kk);
         T::mma(s, a[0], a[1], a[2], a[3], qb[kk][0], qb[kk][1]);
       }
       const int64_t left = cend - t0;
@@ -792,7 +811,7 @@ __global__ void __launch_bounds__(kAttnThreads, KVX_ATTN_T_CTAS) kvx_attention_d
 #pragma unroll
       for (int mt = 0; mt < kKs; ++mt) {
         uint32_t a[4];
-        ldmatrix_x4_trans(a, vs + lv_row * kRowBytes + (((2 * mt + lv_half) ^ (lv_row & 7)) << 4));
+        ldmatrix_x4_trans(a, tile + lv_at + 32 * mt);
         T::mma(o[mt], a[0], a[1], a[2], a[3], pb0, pb1);
       }
     }
@@ -808,6 +827,7 @@ __global__ void __launch_bounds__(kAttnThreads, KVX_ATTN_T_CTAS) kvx_attention_d
       sm_m[warp][2 * j] = m0, sm_m[warp][2 * j + 1] = m1;
       sm_l[warp][2 * j] = l0, sm_l[warp][2 * j + 1] = l1;
     }
+    __syncthreads();  // every warp is done with its part of the ring
     for (int i = threadIdx.x; i < 8 * (kD + 8); i += kAttnThreads) (&sm_o[0][0])[i] = 0.f;
     __syncthreads();
     float M0 = -INFINITY, M1 = -INFINITY;
@@ -1191,7 +1211,8 @@ KVX_API kvx_status_t kvx_launch_paged_attention_decode(const kvx_cache_desc_t *c
     p.use_prefix = S <= kMaxPrefixSeqs ? 1 : 0;
     const bool tokens_in_rows = p.group <= 8 && g_attn_form != 1;
     const int stages = tokens_in_rows ? kTStages : kStages, per_sm = tokens_in_rows ? KVX_ATTN_T_CTAS : g_ctas_per_sm;
-    const size_t ring = static_cast<size_t>(kAttnWarps) * stages * 2 * 16 * D * 2;  // K and V steps of 16 rows
+    // K and V steps of 16 rows; the tokens-in-rows kernel pads each row by 16 bytes
+    const size_t ring = static_cast<size_t>(kAttnWarps) * stages * 2 * 16 * (D * 2 + (tokens_in_rows ? 16 : 0));
     const size_t smem = ring + (p.use_prefix ? static_cast<size_t>(S + 1) * sizeof(int32_t) : 0);
     const int64_t most = S * p.splits * H;  // work items if every context had max_seq_len tokens
     const int64_t grid = std::max<int64_t>(1, std::min<int64_t>(most, static_cast<int64_t>(sm_count()) * per_sm));
