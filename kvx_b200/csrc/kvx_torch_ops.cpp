@@ -22,6 +22,7 @@
 #include <cstring>
 #include <string>
 
+#include "kvx_attention.h"
 #include "kvx_paged_kv.h"
 
 namespace {
@@ -219,6 +220,62 @@ void gather_kv(torch::Tensor &key_cache, torch::Tensor &value_cache, torch::Tens
   TORCH_CHECK(status == KVX_STATUS_OK, "kvx cache gather failed with status=", static_cast<int>(status));
 }
 
+// Decode attention over the paged cache (include/kvx_attention.h).  `workspace` is a uint8 CUDA
+// tensor of at least kvx_paged_attention_workspace_bytes() bytes (see attention_workspace_bytes).
+void paged_attention_decode(torch::Tensor &out, torch::Tensor &query, torch::Tensor &key_cache,
+                            torch::Tensor &value_cache, torch::Tensor &block_table, torch::Tensor &seq_lens,
+                            double scale, int64_t max_seq_len, int64_t num_kv_heads, torch::Tensor &workspace,
+                            const std::string &kv_cache_dtype, torch::Tensor &k_scale, torch::Tensor &v_scale) {
+  TORCH_CHECK(query.is_cuda() && out.is_cuda(), "query/out must be CUDA tensors");
+  TORCH_CHECK(query.dim() == 3 && query.sizes() == out.sizes() && query.scalar_type() == out.scalar_type(),
+              "query/out must be matching [seq_count, q_heads, head_dim] tensors");
+  const kvx_dtype_t io = float_code(query.scalar_type());
+  TORCH_CHECK(io != KVX_DTYPE_INVALID, "unsupported query dtype");
+  TORCH_CHECK(block_table.dim() == 2 && block_table.is_contiguous(), "block_table must be contiguous and 2-D");
+  const kvx_dtype_t idx = index_code(block_table.scalar_type());
+  TORCH_CHECK(idx != KVX_DTYPE_INVALID && seq_lens.scalar_type() == block_table.scalar_type(),
+              "block_table and seq_lens must share an int32 or int64 dtype");
+  const int64_t q_heads = query.size(1), dim = query.size(2);
+  // KV heads: given, or read off the cache with the reference's stride rule (axis 2 when it is
+  // contiguous over head_dim or the tensor is a permuted view, else axis 1)
+  TORCH_CHECK(key_cache.dim() == 4, "cache tensors must be 4-D");
+  const int64_t kv_heads = num_kv_heads > 0 ? num_kv_heads
+                           : (key_cache.stride(1) < key_cache.stride(2) || key_cache.stride(2) == dim)
+                               ? key_cache.size(2)
+                               : key_cache.size(1);
+  kvx_cache_desc_t cache;
+  describe_cache(&cache, key_cache, value_cache, kv_cache_dtype, kv_heads, dim);
+
+  kvx_attention_desc_t a;
+  std::memset(&a, 0, sizeof(a));
+  a.size = sizeof(a);
+  a.num_q_heads = static_cast<uint32_t>(q_heads);
+  a.max_seq_len = static_cast<uint32_t>(max_seq_len);
+  a.scale = static_cast<float>(scale);
+  describe(&a.query, query, io, KVX_LAYOUT_INVALID);
+  describe(&a.out, out, io, KVX_LAYOUT_INVALID);
+  a.block_table.size = sizeof(a.block_table);
+  a.block_table.format = KVX_BLOCK_TABLE_PACKED;
+  a.block_table.index_dtype = idx;
+  a.block_table.seq_count = static_cast<uint32_t>(block_table.size(0));
+  a.block_table.beam_width = 1;
+  a.block_table.max_blocks_per_seq = static_cast<uint32_t>(block_table.size(1));
+  a.block_table.indices = block_table.data_ptr();
+  a.block_table.indices_count = static_cast<uint32_t>(block_table.numel());
+  a.seq_lens.size = sizeof(a.seq_lens);
+  a.seq_lens.dtype = idx;
+  a.seq_lens.seq_count = static_cast<uint32_t>(seq_lens.size(0));
+  a.seq_lens.lengths = seq_lens.data_ptr();
+  kvx_scale_desc_t ks, vs;
+  describe_scale(&ks, k_scale, cache.num_kv_heads);
+  describe_scale(&vs, v_scale, cache.num_kv_heads);
+  TORCH_CHECK(workspace.is_cuda() && workspace.is_contiguous(), "workspace must be a contiguous CUDA tensor");
+  void *stream = reinterpret_cast<void *>(at::cuda::getCurrentCUDAStream().stream());
+  const kvx_status_t status = kvx_launch_paged_attention_decode(
+      &cache, &a, &ks, &vs, workspace.data_ptr(), static_cast<size_t>(workspace.numel() * workspace.element_size()), stream);
+  TORCH_CHECK(status == KVX_STATUS_OK, "kvx paged attention failed with status=", static_cast<int>(status));
+}
+
 }  // namespace
 
 TORCH_LIBRARY(kvx_b200, m) {
@@ -228,9 +285,15 @@ TORCH_LIBRARY(kvx_b200, m) {
   m.def(
       "gather_kv(Tensor key_cache, Tensor value_cache, Tensor block_table, Tensor seq_lens, Tensor! key_out,"
       " Tensor! value_out, str kv_cache_dtype, Tensor k_scale, Tensor v_scale) -> ()");
+  m.def(
+      "paged_attention_decode(Tensor! out, Tensor query, Tensor key_cache, Tensor value_cache, Tensor block_table,"
+      " Tensor seq_lens, float scale, int max_seq_len, int num_kv_heads, Tensor! workspace, str kv_cache_dtype,"
+      " Tensor k_scale,"
+      " Tensor v_scale) -> ()");
 }
 
 TORCH_LIBRARY_IMPL(kvx_b200, CUDA, m) {
   m.impl("reshape_and_cache_flash_kvx", &reshape_and_cache_flash_kvx);
   m.impl("gather_kv", &gather_kv);
+  m.impl("paged_attention_decode", &paged_attention_decode);
 }

@@ -44,7 +44,7 @@ def _stream() -> int:
 
 _NATIVE = None          # torch.ops.kvx_b200 once libkvx_b200_torch.so is loaded; False if it is not built
 _NO_SCALE: dict = {}    # one empty float32 tensor per device, standing for "no scale"
-_STATUS_RE = re.compile(r"(kvx cache \w+) failed with status=(\d+)")
+_STATUS_RE = re.compile(r"(kvx [\w ]+?) failed with status=(\d+)")
 
 
 def native_ops():
@@ -284,14 +284,16 @@ def paged_attention_decode(query: torch.Tensor, key_cache: torch.Tensor, value_c
                            block_table: torch.Tensor, seq_lens: torch.Tensor, scale: float,
                            max_seq_len: Optional[int] = None, out: Optional[torch.Tensor] = None,
                            workspace: Optional[torch.Tensor] = None, kv_cache_dtype: str = "auto",
-                           k_scale: Optional[torch.Tensor] = None,
-                           v_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+                           k_scale: Optional[torch.Tensor] = None, v_scale: Optional[torch.Tensor] = None,
+                           num_kv_heads: Optional[int] = None) -> torch.Tensor:
     """Decode attention that reads the paged cache in place (``include/kvx_attention.h``):
     ``query`` ``[seq_count, q_heads, dim]`` attends over each sequence's cached tokens, found
     through ``block_table`` / ``seq_lens`` as the gather finds them; returns ``out`` (same shape
     and dtype).  ``max_seq_len`` bounds the context (default: all the table can address).
     ``workspace`` is reusable uint8 scratch of :func:`attention_workspace_bytes` bytes; it is
-    allocated per call when not given."""
+    allocated per call when not given.  ``num_kv_heads`` names the cache's head axis when the
+    layout cannot be read off the strides (a contiguous ``[blocks, heads, block_size, dim]``
+    tensor)."""
     if query.dim() != 3 or query.dtype not in _FLOAT_CODES or not query.is_contiguous():
         raise ValueError("query must be a contiguous [seq_count, q_heads, dim] float tensor")
     if block_table.dim() != 2 or not block_table.is_contiguous():
@@ -301,20 +303,27 @@ def paged_attention_decode(query: torch.Tensor, key_cache: torch.Tensor, value_c
     seqs, q_heads, dim = query.shape
     if out is None:
         out = torch.empty_like(query)
-    cache = cache_desc_from_tensors(key_cache, value_cache, kv_cache_dtype)
+    cache = cache_desc_from_tensors(key_cache, value_cache, kv_cache_dtype, num_kv_heads)
     if max_seq_len is None:
         max_seq_len = block_table.shape[1] * cache.block_size
     need = lib().kvx_paged_attention_workspace_bytes(seqs, q_heads, cache.num_kv_heads, dim, max_seq_len)
-    if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
-        workspace = torch.empty(need, dtype=torch.uint8, device=query.device)
+    if workspace is None or workspace.numel() * workspace.element_size() < need:
+        workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=query.device)
+    native = native_ops() if key_cache.dim() == 4 else None
+    if native is not None:
+        dev = query.device
+        _call_native(native.paged_attention_decode, out, query, key_cache, value_cache, block_table, seq_lens,
+                     float(scale), int(max_seq_len), int(cache.num_kv_heads), workspace, kv_cache_dtype,
+                     _scale_arg(k_scale, dev), _scale_arg(v_scale, dev))
+        return out
     a = abi.attention_desc(seqs, q_heads, dim, _FLOAT_CODES[query.dtype], query.data_ptr(), out.data_ptr(),
                            float(scale), int(max_seq_len), _INDEX_CODES[block_table.dtype], block_table.data_ptr(),
                            block_table.shape[1], seq_lens.data_ptr())
     a.seq_lens.seq_count = seq_lens.shape[0]
     ks, vs = _scale_desc(k_scale, cache.num_kv_heads), _scale_desc(v_scale, cache.num_kv_heads)
     status = lib().kvx_launch_paged_attention_decode(
-        C.byref(cache), C.byref(a), C.byref(ks), C.byref(vs), workspace.data_ptr() if need else None,
-        workspace.numel() * workspace.element_size() if need else 0, _stream())
+        C.byref(cache), C.byref(a), C.byref(ks), C.byref(vs), workspace.data_ptr(),
+        workspace.numel() * workspace.element_size(), _stream())
     if status != abi.STATUS_OK:
         raise KvxError("kvx paged attention", status)
     return out

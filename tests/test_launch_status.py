@@ -182,6 +182,51 @@ def test_fp8_launcher_statuses(built_lib):
     assert L.kvx_launch_kv_scales(C.byref(w.io), abi.SCALE_PER_HEAD, FAKE, FAKE, 0x10000, 8, None) == INVALID
 
 
+def test_attention_launcher_statuses_before_any_launch(built_lib):
+    """kvx_launch_paged_attention_decode: every verdict that is reached without touching a device."""
+    L = built_lib
+
+    def attn(**kw):
+        a = abi.attention_desc(2, 4, 8, abi.DTYPE_BF16, FAKE, FAKE, 0.5, 16, abi.DTYPE_S32, FAKE, 1, FAKE)
+        for k, v in kw.items():
+            setattr(a, k, v)
+        return a
+
+    none = abi.scale_desc(None, abi.SCALE_NONE, 2)
+
+    def A(c, a):
+        return L.kvx_launch_paged_attention_decode(C.byref(c) if c is not None else None,
+                                                   C.byref(a) if a is not None else None, C.byref(none), C.byref(none),
+                                                   None, 0, None)
+
+    assert A(None, attn()) == INVALID and A(cache(), None) == INVALID
+    a = attn(); a.size -= 4
+    assert A(cache(), a) == INVALID
+    assert A(cache(), attn(num_q_heads=3)) == INVALID            # not a multiple of the 2 KV heads
+    assert A(cache(), attn(num_q_heads=0)) == INVALID
+    assert A(cache(), attn(max_seq_len=0)) == INVALID
+    a = attn(); a.block_table.format = abi.TABLE_RAGGED
+    assert A(cache(), a) == UNSUPPORTED
+    a = attn(); a.out.dtype = abi.DTYPE_F16
+    assert A(cache(), a) == UNSUPPORTED
+    assert A(cache(abi.DTYPE_F16), attn()) == UNSUPPORTED          # cache and query types differ
+    assert A(cache(abi.DTYPE_F8_E4M3), attn()) == UNSUPPORTED      # fp8 cache without scales
+    a = attn(); a.query.shape[2] = 16
+    assert A(cache(), a) == INVALID
+    a = attn(); a.out.stride[1] = 9
+    assert A(cache(), a) == UNSUPPORTED
+    a = attn(); a.seq_lens.dtype = abi.DTYPE_S64
+    assert A(cache(), a) == INVALID
+    a = attn(); a.block_table.seq_count = a.seq_lens.seq_count = 0
+    a.query.shape[0] = a.out.shape[0] = 0
+    a.query.stride[0] = a.out.stride[0] = 32
+    assert A(cache(), a) == OK                                   # no sequence: nothing to do
+    assert L.kvx_paged_attention_workspace_bytes(0, 4, 2, 8, 16) == 0
+    small = L.kvx_paged_attention_workspace_bytes(2, 4, 2, 8, 16)
+    big = L.kvx_paged_attention_workspace_bytes(2, 4, 2, 8, 100000)
+    assert 0 < small < big
+
+
 def test_options_and_counter(built_lib):
     import kvx_b200
     assert kvx_b200.get_option("gather_path") in (0, 1, 2)
