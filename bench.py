@@ -52,6 +52,7 @@ def parse_args():
     ap.add_argument("--seqs", type=int, default=None, help="override the number of sequences (small profiling cases)")
     ap.add_argument("--e2e-steps", type=int, default=None, help="steps of the host-buffer leg (default: min(steps, 3))")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-attention", action="store_true", help="skip the informational fused decode-attention leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-reference-kernels", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU baseline budget")
@@ -258,6 +259,10 @@ def main() -> None:
     if not args.no_e2e:
         e2e = run_e2e(args, dw, dist)
 
+    attention = None
+    if world == 1 and not args.no_attention and spec.cache_dtype in ("bf16", "f16"):
+        attention = run_attention(dw, min(args.steps, 3))
+
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -295,6 +300,8 @@ def main() -> None:
     }
     if e2e is not None:
         line["e2e"] = e2e
+    if attention is not None:
+        line["fused_decode_attention"] = attention
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(spec, args.cpu_seconds)
     print(json.dumps(line), flush=True)
@@ -310,6 +317,54 @@ TRAFFIC_PER_LAUNCH: dict = {
     ("c2", "gather", 1): 1_116_300_000,
     ("c2", "write", 1): 999_200_000,
 }
+
+
+def run_attention(dw, steps: int, group: int = 4) -> dict:
+    """Informational: the gather fused into its consumer.  One decode query per sequence (4 query
+    heads per KV head) attends over the workload's cached contexts through the same block table,
+    every layer on its own pages; reported as K+V bytes of the live contexts per second."""
+    import ctypes as C
+
+    import torch
+    import kvx_b200
+    from kvx_b200 import abi, bench_support as bs
+    L = kvx_b200.lib()
+    spec, m = dw.meta.spec, dw.meta
+    S, H, D = spec.seqs, dw.heads, spec.dim
+    q = torch.randn((S, H * group, D), device="cuda").to(dw.key.dtype)
+    out = torch.empty_like(q)
+    need = L.kvx_paged_attention_workspace_bytes(S, H * group, H, D, m.max_seq_len)
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
+    a = abi.attention_desc(S, H * group, D, bs.DTYPE_CODE[spec.io_dtype], q.data_ptr(), out.data_ptr(), D ** -0.5,
+                           m.max_seq_len, abi.DTYPE_S32, dw.table.data_ptr(), m.table.shape[1], dw.lens.data_ptr())
+    none = abi.scale_desc(None, abi.SCALE_NONE, H)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def step():
+        for l in range(dw.layers):
+            st = L.kvx_launch_paged_attention_decode(C.byref(dw.caches[l]), C.byref(a), C.byref(none), C.byref(none),
+                                                     ws.data_ptr(), need, stream)
+            if st != abi.STATUS_OK:
+                raise RuntimeError(f"kvx_launch_paged_attention_decode status {st}")
+
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (steps * dw.layers)
+    kv_bytes = m.gather_tokens * 2 * H * D * workloads_elem(spec.cache_dtype)
+    return {"us_per_launch": round(us, 2), "kv_read_gbs": round(kv_bytes / us / 1e3, 1), "q_heads_per_kv_head": group,
+            "note": "reads the pages in place; no gathered copy is written"}
+
+
+def workloads_elem(dtype: str) -> int:
+    from kvx_b200 import workloads
+    return workloads.ELEM[dtype]
 
 
 def run_e2e(args, dw, dist) -> dict:

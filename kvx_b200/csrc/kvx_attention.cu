@@ -10,16 +10,17 @@
  * the arithmetic hidden under it:
  *
  *   fast tier   16-bit cache, head_dim 64 / 128, pages of a multiple of 16 tokens.
- *               One CTA per (sequence, KV head, chunk of the context); its warps take
- *               16-token steps.  K and V rows go from global memory straight into
- *               mma.sync.m16n8k16 operand registers with 16-byte loads (no shared-memory
- *               staging, no ldmatrix): the reduction index of an MMA can be permuted freely
- *               as long as both operands agree, so each lane's 16 contiguous bytes of a K row
- *               feed two k-steps, and V's token pairs are zipped with one byte-permute per
- *               operand register.  All query heads of the KV head ride in the 16 rows of the
- *               A operand, so K / V are read once per group, not once per query head.
+ *               Work items are (sequence, chunk of the context, KV head) triples of chunks that
+ *               exist; persistent CTAs claim them from a counter in caller scratch, and their
+ *               warps take 16-token steps whose K and V rows are staged by cp.async into a
+ *               warp-private ring in shared memory.  All query heads of the KV head ride in
+ *               one MMA operand, so K / V are read once per group, not once per query head.
  *               Online softmax in f32 (exp2 domain); per-warp partial results are merged in
  *               shared memory, per-chunk partials in a second small kernel.
+ *               Up to 8 query heads per KV head: tokens in the 16 rows of mma.sync.m16n8k16,
+ *               heads in its 8 columns (ldmatrix / ldmatrix.trans / movmatrix operands).
+ *               9 to 16: heads in the rows, K / V operands built from per-lane 16-byte slots
+ *               with a permuted reduction index (no ldmatrix).
  *   generic     any layout (HND_PACKED included), any head_dim up to 1 024, any page size,
  *               f32 and fp8-e4m3 caches: one CTA per (sequence, query head), element loads,
  *               the same online softmax.  Correctness tier.
@@ -1090,8 +1091,6 @@ void launch_t_dim(const AttnParams &p, unsigned grid, size_t smem, cudaStream_t 
     launch_t<T, 64, IdxT>(p, grid, smem, st);
 }
 
-int g_attn_form = 0;  // 1 = always the heads-in-rows kernel (set through KVX_ATTN_FORM while tuning)
-
 // SM count of the current device, looked up once per device.
 int sm_count() {
   static std::atomic<int> cached[64];
@@ -1209,7 +1208,7 @@ KVX_API kvx_status_t kvx_launch_paged_attention_decode(const kvx_cache_desc_t *c
       p.part_ml = p.part_o + S * Hq * p.splits * D;
     }
     p.use_prefix = S <= kMaxPrefixSeqs ? 1 : 0;
-    const bool tokens_in_rows = p.group <= 8 && g_attn_form != 1;
+    const bool tokens_in_rows = p.group <= 8;
     const int stages = tokens_in_rows ? kTStages : kStages, per_sm = tokens_in_rows ? KVX_ATTN_T_CTAS : g_ctas_per_sm;
     // K and V steps of 16 rows; the tokens-in-rows kernel pads each row by 16 bytes
     const size_t ring = static_cast<size_t>(kAttnWarps) * stages * 2 * 16 * (D * 2 + (tokens_in_rows ? 16 : 0));
