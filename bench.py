@@ -53,6 +53,9 @@ def parse_args():
     ap.add_argument("--e2e-steps", type=int, default=None, help="steps of the host-buffer leg (default: min(steps, 3))")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-attention", action="store_true", help="skip the informational fused decode-attention leg")
+    ap.add_argument("--only-attention", action="store_true",
+                    help="fill the pages with one write per layer, time only the fused decode attention and print its "
+                         "numbers (the small command the attention kernel is profiled with)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-reference-kernels", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU baseline budget")
@@ -214,6 +217,14 @@ def main() -> None:
     dw = bs.setup_device_workload(spec, rank, world, layers=args.layers, pool_gb=args.pool_gb)
     layers, meta = dw.layers, dw.meta
     stream = torch.cuda.current_stream().cuda_stream
+
+    if args.only_attention:
+        for l in range(layers):
+            bs.launch_write(dw, l, stream)
+        res = run_attention(dw, args.steps)
+        res.update({"workload": spec.name, "layers": layers, "steps": args.steps, "gather_tokens": meta.gather_tokens})
+        print(json.dumps({"fused_decode_attention": res}), flush=True)
+        return
 
     def step(events=None):
         if events:
