@@ -110,6 +110,19 @@ def test_split_contexts_and_merge():
     check(case, k, v, 4, max_seq_len=100)
 
 
+def test_more_sequences_than_the_shared_memory_prefix_holds():
+    """Beyond 8 192 sequences the tensor-core kernels enumerate the padded (sequence, chunk)
+    rectangle instead of a compacted list; both forms (heads in columns / in rows)."""
+    rng = np.random.default_rng(78)
+    lens = [int(x) for x in rng.integers(0, 40, size=8300)]
+    for i, group in enumerate((2, 12)):
+        case = cases.make_case(2150 + i, dtype=abi.DTYPE_F16, real_values=True, heads=1, dim=64, block_size=16,
+                               num_blocks=25000, lens=lens)
+        case.note = f"many sequences, group {group}"
+        _, k, v = oracle_write(case)
+        check(case, k, v, group)
+
+
 def test_generic_tier_shapes():
     """Everything the tensor-core tier does not take: f32 data, odd head_dim, small pages,
     HND_PACKED pages, an fp8-e4m3 cache with per-head scales."""

@@ -335,6 +335,20 @@ def test_hnd_packed_with_16_byte_pack_groups(dtype):
         check_gather(wide, k, v)
 
 
+def test_more_sequences_than_the_shared_memory_prefix_holds():
+    """Beyond 10 240 sequences the gather kernels cannot keep the page-count prefix in shared
+    memory and walk the padded (sequence, page) rectangle instead; same result."""
+    rng = np.random.default_rng(77)
+    lens = [int(x) for x in rng.integers(0, 10, size=10500)]
+    for dim in (16, 8):  # 256-bit and 128-bit vector kernels
+        case = cases.make_case(1200 + dim, dtype=abi.DTYPE_BF16, heads=1, dim=dim, block_size=4, num_blocks=27000,
+                               lens=lens, bad_blocks=5)
+        case.note = f"many sequences, dim {dim}"
+        _, k, v = oracle_write(case)
+        check_gather(case, k, v)
+        check_gather(cases.to_varlen(case), k, v)
+
+
 def test_empty_and_degenerate_batches():
     case = cases.make_case(3, dtype=abi.DTYPE_F16, heads=2, dim=64, lens=[0, 0], num_blocks=4)
     assert case.T == 0

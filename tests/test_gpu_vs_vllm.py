@@ -97,6 +97,36 @@ def _compare_with_vllm():
     # the Llama-3-8B prefill shape, one layer, 10 % padding, pages spread over 2.3 GB
     both(torch.bfloat16, 8, 128, 16, 142060, 71525, 0.10, 99, "c2_one_layer", True)
 
+    # vLLM's other cache-write operator (non-flash paged attention): K [blocks, heads, dim / x,
+    # block_size, x] with x = 16 bytes / element, V [blocks, heads, dim, block_size].  Here that
+    # is HND_PACKED (V with pack 1), reached through the TGI adapter's "paged" layout
+    # (reference: KV_CACHE_LAYOUTS.md:14-17).  Skipped when this vLLM build lacks the operator.
+    legacy = getattr(torch.ops._C_cache_ops, "reshape_and_cache", None)
+    if legacy is not None:
+        from kvx_b200 import adapters
+        from kvx_b200.adapters import tgi_adapter
+        nb, bs, H, D, x, T = 64, 16, 4, 128, 8, 500
+        g = torch.Generator(device="cuda"); g.manual_seed(7)
+        key = torch.randn((T, H, D), generator=g, device="cuda").to(torch.bfloat16)
+        value = torch.randn((T, H, D), generator=g, device="cuda").to(torch.bfloat16)
+        slots = torch.randperm(nb * bs, generator=g, device="cuda")[:T].to(torch.int64)
+        ka = torch.zeros((nb, H, D // x, bs, x), dtype=torch.bfloat16, device="cuda"); kb = ka.clone()
+        va = torch.zeros((nb, H, D, bs), dtype=torch.bfloat16, device="cuda"); vb = va.clone()
+        try:
+            legacy(key, value, kb, vb, slots, "auto", one, one)
+            ran = True
+        except Exception as exc:  # another signature in this vLLM version
+            print(f"reshape_and_cache not comparable here: {exc!r}"[:200])
+            ran = False
+        if ran:
+            view = tgi_adapter.TgiCacheView(ka, va, torch.zeros((1, 1), dtype=torch.int32, device="cuda"), None, slots,
+                                            bs, H, D, "auto", "paged")
+            adapters.write(tgi_adapter.build_kvx_descriptors(view), key, value)
+            torch.cuda.synchronize()
+            assert torch.equal(ka.view(torch.int16), kb.view(torch.int16)), "packed K differs from vLLM"
+            assert torch.equal(va.view(torch.int16), vb.view(torch.int16)), "packed V differs from vLLM"
+            rows.append({"case": "reshape_and_cache_packed", "dtype": "bfloat16", "tokens": T, "bit_identical": True})
+
     out_dir = os.path.join(ROOT, "gpurun_out")
     if os.path.isdir(out_dir):
         with open(os.path.join(out_dir, "vs_vllm.json"), "w") as f:
