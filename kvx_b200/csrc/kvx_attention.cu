@@ -9,18 +9,15 @@
  * byte with 4 query heads per KV head), so the design goal is the gather's read stream with
  * the arithmetic hidden under it:
  *
- *   fast tier   16-bit cache, head_dim 64 / 128, pages of a multiple of 16 tokens.
- *               Work items are (sequence, chunk of the context, KV head) triples of chunks that
- *               exist; persistent CTAs claim them from a counter in caller scratch, and their
- *               warps take 16-token steps whose K and V rows are staged by cp.async into a
- *               warp-private ring in shared memory.  All query heads of the KV head ride in
- *               one MMA operand, so K / V are read once per group, not once per query head.
- *               Online softmax in f32 (exp2 domain); per-warp partial results are merged in
- *               shared memory, per-chunk partials in a second small kernel.
- *               Up to 8 query heads per KV head: tokens in the 16 rows of mma.sync.m16n8k16,
- *               heads in its 8 columns (ldmatrix / ldmatrix.trans / movmatrix operands).
- *               9 to 16: heads in the rows, K / V operands built from per-lane 16-byte slots
- *               with a permuted reduction index (no ldmatrix).
+ *   fast tier   16-bit cache, head_dim 64 / 128, pages of a multiple of 16 tokens, up to 16 query
+ *               heads per KV head.  Work items are (sequence, chunk of the context, KV head)
+ *               triples of chunks that exist; persistent CTAs claim them from a counter in
+ *               caller scratch, and their warps take 16-token steps whose K and V rows are staged
+ *               by cp.async into a warp-private ring in shared memory.  All query heads of the
+ *               KV head ride in the 8-column operand of mma.sync.m16n8k16 (tokens in its 16
+ *               rows), so K / V are read once per group, not once per query head.  Online
+ *               softmax in f32 (exp2 domain); per-warp partial results are merged in shared
+ *               memory, per-chunk partials in a second small kernel.
  *   generic     any layout (HND_PACKED included), any head_dim up to 1 024, any page size,
  *               f32 and fp8-e4m3 caches: one CTA per (sequence, query head), element loads,
  *               the same online softmax.  Correctness tier.
@@ -194,54 +191,122 @@ struct Fp16 {
   }
 };
 
-__device__ __forceinline__ uint32_t word_of(const uint4 &v, int i) {
-  return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w;
-}
-
 // exp2(a - b) for running maxima, 0 when `a` is -inf (nothing accumulated yet).
 __device__ __forceinline__ float exp2_diff(float a, float b) { return a == -INFINITY ? 0.f : exp2f(a - b); }
 
-// ------------------------------------------------------------------ fast tier ----------
+// ------------------------------------------------------------------ work list of the fast tier --
 
 constexpr int kAttnWarps = 4;
 constexpr int kAttnThreads = kAttnWarps * 32;
 
-// MMA operand layouts used below (m16n8k16, g = lane / 4, j = lane % 4):
+// Work items are (sequence, chunk, KV head) triples of chunks that exist.  The lengths live on
+// the device, so every CTA builds the same exclusive prefix sum of chunks per sequence in shared
+// memory (sm_prefix[0..S]); with too many sequences for that it enumerates the padded
+// (sequence, chunk) rectangle and meets chunks that do not exist.  Returns the item count.
+template <typename IdxT>
+__device__ int64_t build_work_list(const AttnParams &p, int32_t *sm_prefix, int32_t *sm_scan) {
+  if (!p.use_prefix) return static_cast<int64_t>(p.seq_count) * p.splits * p.heads_kv;
+  const int S = p.seq_count;
+  const int per = (S + kAttnThreads - 1) / kAttnThreads;
+  const int begin = min(static_cast<int>(threadIdx.x) * per, S), end = min(begin + per, S);
+  int32_t local = 0;
+  for (int s = begin; s < end; ++s) local += chunks_of<IdxT>(p, s);
+  sm_scan[threadIdx.x] = local;
+  __syncthreads();
+  int32_t run = 0;
+  for (int t = 0; t < static_cast<int>(threadIdx.x); ++t) run += sm_scan[t];
+  for (int s = begin; s < end; ++s) {
+    sm_prefix[s] = run;
+    run += chunks_of<IdxT>(p, s);
+  }
+  if (threadIdx.x == kAttnThreads - 1) sm_prefix[S] = run;
+  __syncthreads();
+  return static_cast<int64_t>(sm_prefix[S]) * p.heads_kv;
+}
+
+struct WorkItem {
+  int seq, split, kvh;
+  int64_t begin, end;  // token range of the chunk; empty for a chunk the sequence does not have
+};
+
+// The CTA's next item.  With a counter, CTAs claim items as they become free; without one (few
+// items: one per CTA) they stride over the list.  Contains a barrier, which also separates the
+// previous item's use of shared buffers from the next one's.
+template <typename IdxT>
+__device__ bool next_item(const AttnParams &p, int64_t items, unsigned long long *round,
+                          unsigned long long *sm_item, const int32_t *sm_prefix, WorkItem *w) {
+  if (threadIdx.x == 0)
+    *sm_item = p.counter != nullptr ? atomicAdd(p.counter, 1ull)
+                                    : blockIdx.x + *round * static_cast<unsigned long long>(gridDim.x);
+  ++*round;
+  __syncthreads();
+  const int64_t item = static_cast<int64_t>(*sm_item);
+  if (item >= items) return false;
+  w->kvh = static_cast<int>(item % p.heads_kv);
+  const int64_t ci = item / p.heads_kv;
+  if (p.use_prefix) {
+    int lo = 0, hi = p.seq_count;  // last s with prefix[s] <= ci
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (sm_prefix[mid] <= ci)
+        lo = mid;
+      else
+        hi = mid;
+    }
+    w->seq = lo;
+    w->split = static_cast<int>(ci - sm_prefix[lo]);
+  } else {
+    w->seq = static_cast<int>(ci / p.splits);
+    w->split = static_cast<int>(ci - static_cast<int64_t>(w->seq) * p.splits);
+  }
+  int64_t len = read_idx<IdxT>(p.lens, w->seq);
+  if (len > p.max_seq_len) len = p.max_seq_len;
+  w->begin = static_cast<int64_t>(w->split) * p.chunk;
+  w->end = min(len, w->begin + p.chunk);
+  return true;
+}
+
+// A sequence without cached tokens has no work item; its output is defined as zero.  With more
+// than one chunk per sequence the merge kernel writes it, otherwise the fast kernels call this.
+template <typename IdxT>
+__device__ void zero_empty_sequences(const AttnParams &p) {
+  if (p.splits != 1) return;
+  for (int s = blockIdx.x; s < p.seq_count; s += gridDim.x) {
+    if (read_idx<IdxT>(p.lens, s) > 0) continue;
+    for (int i = threadIdx.x; i < p.heads_q * p.dim; i += kAttnThreads)
+      reinterpret_cast<uint16_t *>(p.out)[static_cast<int64_t>(s) * p.heads_q * p.dim + i] = 0;
+  }
+}
+
+// ------------------------------------------------------------------ fast tier ----------
+
+// ------------------------------------------------------------------ fast tier ----------
+//
+// Tokens, not query heads, sit in the 16-row dimension of mma.sync.m16n8k16, and 8 query heads in
+// its 8 columns:
+//   scores^T [16 tokens x 8 heads] = K [16 tokens x dims]  x  Q^T [dims x 8 heads]
+//   out^T    [16 dims   x 8 heads] = V^T [16 dims x 16 tokens] x P^T [16 tokens x 8 heads]
+// so no MMA row is padding (with heads in the rows 4 of 16 would be used), a step of head_dim 128
+// costs 16 MMAs and 32 accumulator registers per 8 heads, and the softmax statistics of a head
+// sit in the thread that owns its output columns.  Operand layouts (g = lane / 4, j = lane % 4):
 //   A (16 x 16, row): a0 = (row g, k 2j..2j+1)  a1 = (row g+8, same k)  a2 = (row g, k 2j+8..2j+9)  a3 = (row g+8, ..)
 //   B (16 x 8, col) : b0 = (k 2j..2j+1, col g)  b1 = (k 2j+8..2j+9, col g)
 //   C (16 x 8)      : c0, c1 = (row g, cols 2j, 2j+1)   c2, c3 = (row g+8, cols 2j, 2j+1)
-// Scores: rows = query heads of the group, k = head dims, cols = tokens.  A lane's 16 bytes at
-// dims 32c + 8j .. 8j+7 of a Q row and of a K row are used as (k 2j..2j+1 | k 2j+8..2j+9) of
-// k-step 2c and of k-step 2c+1: a permutation of the dims, the same on both operands.
-// Output: rows = query heads, k = tokens, cols = head dims.  P comes straight from the score
-// accumulators (C of two 8-token tiles is A of one 16-token step).  For V a lane loads the
-// rows of tokens 2j, 2j+1, 2j+8, 2j+9 at dims 64*hd + 8g .. 8g+7 and zips element i of two
-// rows into one register for MMA i, whose column g is therefore head dim 64*hd + 8g + i.
 //
-// Memory pipeline.  A warp's loads for one step are 16 x 16 bytes per lane (8 KB per warp).
-// They are issued as cp.async copies into a ring of kStages steps in shared memory, each lane
-// into slots only it reads back, so no barrier is involved: the lane waits for its own copy
-// group and reloads its operands with 16-byte shared loads.  kStages - 1 steps are in flight
-// per warp while one is being multiplied (2 CTAs x 4 warps x 16 KB = 128 KB per SM), which is
-// what keeps HBM busy; with the loads going to registers directly only one step per warp could
-// be outstanding and the kernel was bound by memory latency at half the bandwidth.
+// Memory pipeline.  A warp's K and V rows for one 16-token step (8 KB at head_dim 128) are staged
+// by cp.async (16 bytes per lane, whole rows per warp instruction, coalesced) into a ring of
+// kTStages steps in shared memory that is private to the warp: lanes wait for their own copy
+// groups and meet in __syncwarp before reading each other's chunks, no CTA barrier involved.
+// Rows are padded by 16 bytes, which makes ldmatrix conflict-free and every staging address a
+// per-lane base plus a compile-time constant.  K rows are A operands as they lie (ldmatrix),
+// V^T comes from ldmatrix.trans, P^T from the score accumulators through movmatrix.trans.
+// 3 CTAs x 4 warps per SM keep 12 steps in flight while 12 are being multiplied.
 //
 // Work distribution.  Items are (sequence, chunk, KV head) triples of chunks that exist; CTAs
 // claim them one at a time from a counter in the caller's scratch (zeroed by the launcher), so
 // short and long items balance out.
-#ifndef KVX_ATTN_STAGES
-#define KVX_ATTN_STAGES 3
-#endif
-#ifndef KVX_ATTN_CTAS
-#define KVX_ATTN_CTAS 2
-#endif
-constexpr int kStages = KVX_ATTN_STAGES;
 constexpr size_t kCounterBytes = 16;  // head of the scratch: the work counter, padded
 
-__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src) {
-  const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gmem_src) : "memory");
-}
 __device__ __forceinline__ float fast_exp2(float x) {  // ex2.approx: 2 ulp, -inf -> 0
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -253,316 +318,6 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
 }
 
-template <typename T, int kD, typename IdxT, bool kUpper>
-__global__ void __launch_bounds__(kAttnThreads, KVX_ATTN_CTAS) kvx_attention_decode_kernel(const AttnParams p) {
-  constexpr int kC = kD / 32;         // 16-byte loads per K row and lane
-  constexpr int kHd = kD / 64;        // 64-dim halves of a V row
-  constexpr int kNt = kD / 8;         // output column tiles
-  constexpr int kSlots = 2 * kC + 4 * kHd;  // 16-byte slots per lane and step (K tiles, then V rows)
-  extern __shared__ uint4 sm_dyn[];   // ring [warp][stage][slot][lane], then the chunk prefix
-  __shared__ float sm_m[kAttnWarps][16];
-  __shared__ float sm_l[kAttnWarps][16];
-  __shared__ float sm_o[16][kD + 2];  // + 2: rows land in different banks for the atomics below
-  __shared__ int32_t sm_page[kAttnWarps][kStages];
-  __shared__ int32_t sm_scan[kAttnThreads];
-  __shared__ unsigned long long sm_item;
-  int32_t *sm_prefix = reinterpret_cast<int32_t *>(sm_dyn + kAttnWarps * kStages * kSlots * 32);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, j = lane & 3;
-  const int G = p.group;
-  uint4 *ring = sm_dyn + (warp * kStages * kSlots) * 32 + lane;  // slot s of stage t: ring[(t*kSlots+s)*32]
-
-  int64_t chunks_total;
-  if (p.use_prefix) {
-    const int S = p.seq_count;
-    const int per = (S + kAttnThreads - 1) / kAttnThreads;
-    const int begin = min(static_cast<int>(threadIdx.x) * per, S), end = min(begin + per, S);
-    int32_t local = 0;
-    for (int s = begin; s < end; ++s) local += chunks_of<IdxT>(p, s);
-    sm_scan[threadIdx.x] = local;
-    __syncthreads();
-    int32_t run = 0;
-    for (int t = 0; t < static_cast<int>(threadIdx.x); ++t) run += sm_scan[t];
-    for (int s = begin; s < end; ++s) {
-      sm_prefix[s] = run;
-      run += chunks_of<IdxT>(p, s);
-    }
-    if (threadIdx.x == kAttnThreads - 1) sm_prefix[S] = run;
-    __syncthreads();
-    chunks_total = sm_prefix[S];
-  } else {
-    chunks_total = static_cast<int64_t>(p.seq_count) * p.splits;
-  }
-  const int64_t items = chunks_total * p.heads_kv;
-
-  // A sequence without cached tokens has no work item; its output is defined as zero.  With
-  // more than one chunk per sequence the merge kernel writes it, otherwise this loop does.
-  if (p.splits == 1) {
-    for (int s = blockIdx.x; s < p.seq_count; s += gridDim.x) {
-      if (read_idx<IdxT>(p.lens, s) > 0) continue;
-      for (int i = threadIdx.x; i < p.heads_q * kD; i += kAttnThreads)
-        reinterpret_cast<uint16_t *>(p.out)[static_cast<int64_t>(s) * p.heads_q * kD + i] = 0;
-    }
-  }
-
-  for (unsigned long long round = 0;;) {
-    // With a counter, CTAs claim items as they become free; without one (few items: one per
-    // CTA) they stride over the list.
-    if (threadIdx.x == 0)
-      sm_item = p.counter != nullptr ? atomicAdd(p.counter, 1ull) : blockIdx.x + round * static_cast<unsigned long long>(gridDim.x);
-    ++round;
-    __syncthreads();
-    const int64_t item = static_cast<int64_t>(sm_item);
-    if (item >= items) break;
-    const int kvh = static_cast<int>(item % p.heads_kv);
-    const int64_t ci = item / p.heads_kv;
-    int seq, split;
-    if (p.use_prefix) {
-      int lo = 0, hi = p.seq_count;  // last s with prefix[s] <= ci
-      while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        if (sm_prefix[mid] <= ci)
-          lo = mid;
-        else
-          hi = mid;
-      }
-      seq = lo;
-      split = static_cast<int>(ci - sm_prefix[lo]);
-    } else {
-      seq = static_cast<int>(ci / p.splits);
-      split = static_cast<int>(ci - static_cast<int64_t>(seq) * p.splits);
-    }
-    int64_t len = read_idx<IdxT>(p.lens, seq);
-    if (len > p.max_seq_len) len = p.max_seq_len;
-    const int64_t cbeg = static_cast<int64_t>(split) * p.chunk;
-    const int64_t cend = min(len, cbeg + p.chunk);
-    const int64_t q_row0 = static_cast<int64_t>(seq) * p.heads_q + static_cast<int64_t>(kvh) * G;
-    // (without the prefix, a chunk the sequence does not have: nsteps <= 0 below, and the
-    // epilogue writes an empty partial that the merge never reads)
-
-    // Query rows of this KV head as A operands, kept for the whole item.
-    uint4 qa[kC], qb[kC];
-#pragma unroll
-    for (int c = 0; c < kC; ++c) {
-      qa[c] = make_uint4(0, 0, 0, 0);
-      qb[c] = make_uint4(0, 0, 0, 0);
-      if (g < G) qa[c] = *reinterpret_cast<const uint4 *>(p.query + ((q_row0 + g) * kD + 32 * c + 8 * j) * 2);
-      if (kUpper && g + 8 < G)
-        qb[c] = *reinterpret_cast<const uint4 *>(p.query + ((q_row0 + g + 8) * kD + 32 * c + 8 * j) * 2);
-    }
-
-    float o[kNt][4];
-#pragma unroll
-    for (int nt = 0; nt < kNt; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
-    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;  // rows g and g + 8
-
-    const int nsteps = cend > cbeg ? static_cast<int>((cend - cbeg + 15) >> 4) : 0;
-    const int mine = nsteps > warp ? (nsteps - warp + kAttnWarps - 1) / kAttnWarps : 0;  // steps of this warp
-    const int64_t head_k = static_cast<int64_t>(kvh) * p.k.head, head_v = static_cast<int64_t>(kvh) * p.v.head;
-
-    // Page of this warp's i-th step, or -1 when its tokens take no part (beyond the table, or
-    // an id that is negative or not below num_blocks: skipped as the gather skips them).
-    // Looked up once, when the step's loads are issued, and kept in shared memory for the
-    // consumer side.  Token positions fit 32 bits (max_seq_len does).
-    auto page_of = [&](int i, uint32_t *o0) -> int64_t {
-      const uint32_t t0 = static_cast<uint32_t>(cbeg) + static_cast<uint32_t>(warp + i * kAttnWarps) * 16u;
-      const uint32_t lb = p.bs_shift >= 0 ? (t0 >> p.bs_shift) : (t0 / static_cast<uint32_t>(p.block_size));
-      *o0 = t0 - lb * static_cast<uint32_t>(p.block_size);  // a 16-token step never straddles pages
-      if (lb >= static_cast<uint32_t>(p.max_blocks)) return -1;
-      const int64_t b = read_idx<IdxT>(p.table, static_cast<int64_t>(seq) * p.max_blocks + lb);
-      return (b < 0 || b >= p.num_blocks) ? -1 : b;
-    };
-    // Byte offsets of this lane's rows inside a step, fixed for the whole kernel.
-    const int64_t k_lane0 = g * p.k.tok + 16 * j, k_lane1 = (g + 8) * p.k.tok + 16 * j;
-    const int64_t v_lane0 = (2 * j) * p.v.tok + 16 * g, v_lane1 = (2 * j + 1) * p.v.tok + 16 * g;
-    const int64_t v_lane8 = (2 * j + 8) * p.v.tok + 16 * g, v_lane9 = (2 * j + 9) * p.v.tok + 16 * g;
-    auto issue = [&](int i) {
-      if (i < mine) {
-        uint32_t o0;
-        const int64_t b = page_of(i, &o0);
-        const int stage = i % kStages;
-        sm_page[warp][stage] = static_cast<int32_t>(b);  // every lane writes the same value
-        if (b >= 0) {
-          const char *kp = p.k.base + b * p.k.blk + head_k + static_cast<int64_t>(o0) * p.k.tok;
-          const char *vp = p.v.base + b * p.v.blk + head_v + static_cast<int64_t>(o0) * p.v.tok;
-          uint4 *dst = ring + (stage * kSlots) * 32;
-#pragma unroll
-          for (int c = 0; c < kC; ++c) {
-            cp_async16(dst + (2 * c) * 32, kp + k_lane0 + 64 * c);
-            cp_async16(dst + (2 * c + 1) * 32, kp + k_lane1 + 64 * c);
-          }
-#pragma unroll
-          for (int hd = 0; hd < kHd; ++hd) {
-            cp_async16(dst + (2 * kC + 4 * hd) * 32, vp + v_lane0 + 128 * hd);
-            cp_async16(dst + (2 * kC + 4 * hd + 1) * 32, vp + v_lane1 + 128 * hd);
-            cp_async16(dst + (2 * kC + 4 * hd + 2) * 32, vp + v_lane8 + 128 * hd);
-            cp_async16(dst + (2 * kC + 4 * hd + 3) * 32, vp + v_lane9 + 128 * hd);
-          }
-        }
-      }
-      cp_async_commit();  // one group per step, empty or not, keeps the accounting uniform
-    };
-
-#pragma unroll
-    for (int i = 0; i < kStages - 1; ++i) issue(i);
-    for (int i = 0; i < mine; ++i) {
-      issue(i + kStages - 1);
-      cp_async_wait<kStages - 1>();  // this lane's copies of step i have landed
-      const int stage = i % kStages;
-      if (sm_page[warp][stage] < 0) continue;
-      const int64_t t0 = cbeg + static_cast<int64_t>(warp + i * kAttnWarps) * 16;
-      const uint4 *src = ring + (stage * kSlots) * 32;
-
-      float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int c = 0; c < kC; ++c) {
-        const uint4 k0 = src[(2 * c) * 32], k1 = src[(2 * c + 1) * 32];
-        T::mma(s0, qa[c].x, qb[c].x, qa[c].y, qb[c].y, k0.x, k0.y);
-        T::mma(s1, qa[c].x, qb[c].x, qa[c].y, qb[c].y, k1.x, k1.y);
-        T::mma(s0, qa[c].z, qb[c].z, qa[c].w, qb[c].w, k0.z, k0.w);
-        T::mma(s1, qa[c].z, qb[c].z, qa[c].w, qb[c].w, k1.z, k1.w);
-      }
-
-      // Scale into the exp2 domain; in the last step of a chunk the tokens at or beyond its end
-      // take no part.
-      const int64_t left = cend - t0;  // valid tokens in this step, >= 1
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        s0[e] *= p.scale_log2;
-        s1[e] *= p.scale_log2;
-      }
-      if (left < 16) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int tok0 = 2 * j + (e & 1), tok1 = tok0 + 8;
-          if (tok0 >= left) s0[e] = -INFINITY;
-          if (tok1 >= left) s1[e] = -INFINITY;
-        }
-      }
-
-      float mx_lo = fmaxf(fmaxf(s0[0], s0[1]), fmaxf(s1[0], s1[1]));
-      float mx_hi = fmaxf(fmaxf(s0[2], s0[3]), fmaxf(s1[2], s1[3]));
-      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xFFFFFFFFu, mx_lo, 1));
-      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xFFFFFFFFu, mx_lo, 2));
-      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xFFFFFFFFu, mx_hi, 1));
-      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xFFFFFFFFu, mx_hi, 2));
-      const float n_lo = fmaxf(m_lo, mx_lo), n_hi = fmaxf(m_hi, mx_hi);
-      // The running maximum rarely moves after the first steps: rescale only when some row's did.
-      if (__any_sync(0xFFFFFFFFu, n_lo != m_lo || n_hi != m_hi)) {
-        const float c_lo = exp2_diff(m_lo, n_lo), c_hi = exp2_diff(m_hi, n_hi);
-        l_lo *= c_lo, l_hi *= c_hi;
-#pragma unroll
-        for (int nt = 0; nt < kNt; ++nt) {
-          o[nt][0] *= c_lo, o[nt][1] *= c_lo;
-          o[nt][2] *= c_hi, o[nt][3] *= c_hi;
-        }
-        m_lo = n_lo, m_hi = n_hi;
-      }
-      // exp2(-inf - finite) = 0 for masked tokens.  A row whose maximum is still -inf (scores
-      // that are -inf in the data) must not compute -inf - -inf: it subtracts 0 instead.
-      const float z_lo = n_lo == -INFINITY ? 0.f : n_lo, z_hi = n_hi == -INFINITY ? 0.f : n_hi;
-      float pr[8];
-      pr[0] = fast_exp2(s0[0] - z_lo), pr[1] = fast_exp2(s0[1] - z_lo);
-      pr[2] = fast_exp2(s0[2] - z_hi), pr[3] = fast_exp2(s0[3] - z_hi);
-      pr[4] = fast_exp2(s1[0] - z_lo), pr[5] = fast_exp2(s1[1] - z_lo);
-      pr[6] = fast_exp2(s1[2] - z_hi), pr[7] = fast_exp2(s1[3] - z_hi);
-      l_lo += (pr[0] + pr[1]) + (pr[4] + pr[5]);
-      l_hi += (pr[2] + pr[3]) + (pr[6] + pr[7]);
-      const uint32_t pa0 = T::pack2(pr[0], pr[1]), pa1 = T::pack2(pr[2], pr[3]);
-      const uint32_t pa2 = T::pack2(pr[4], pr[5]), pa3 = T::pack2(pr[6], pr[7]);
-#pragma unroll
-      for (int hd = 0; hd < kHd; ++hd) {
-        uint4 vv[4];
-#pragma unroll
-        for (int r = 0; r < 4; ++r) vv[r] = src[(2 * kC + 4 * hd + r) * 32];
-        if (left < 16) {  // whatever the page holds beyond the chunk must not meet a zero weight
-          if (2 * j >= left) vv[0] = make_uint4(0, 0, 0, 0);
-          if (2 * j + 1 >= left) vv[1] = make_uint4(0, 0, 0, 0);
-          if (2 * j + 8 >= left) vv[2] = make_uint4(0, 0, 0, 0);
-          if (2 * j + 9 >= left) vv[3] = make_uint4(0, 0, 0, 0);
-        }
-#pragma unroll
-        for (int i2 = 0; i2 < 8; ++i2) {
-          const uint32_t sel = (i2 & 1) ? 0x7632u : 0x5410u;  // high or low halves of both words
-          const uint32_t b0 = __byte_perm(word_of(vv[0], i2 >> 1), word_of(vv[1], i2 >> 1), sel);
-          const uint32_t b1 = __byte_perm(word_of(vv[2], i2 >> 1), word_of(vv[3], i2 >> 1), sel);
-          T::mma(o[hd * 8 + i2], pa0, pa1, pa2, pa3, b0, b1);
-        }
-      }
-    }
-    cp_async_wait<0>();  // only empty groups can be left; the ring is free for the next item
-
-    // Denominators were kept per lane; complete them over the 4 lanes that share a row.
-    l_lo += __shfl_xor_sync(0xFFFFFFFFu, l_lo, 1);
-    l_lo += __shfl_xor_sync(0xFFFFFFFFu, l_lo, 2);
-    l_hi += __shfl_xor_sync(0xFFFFFFFFu, l_hi, 1);
-    l_hi += __shfl_xor_sync(0xFFFFFFFFu, l_hi, 2);
-
-    // Merge the warps' partial results: common maximum, rescaled sums.
-    if (j == 0) {
-      sm_m[warp][g] = m_lo, sm_m[warp][g + 8] = m_hi;
-      sm_l[warp][g] = l_lo, sm_l[warp][g + 8] = l_hi;
-    }
-    for (int i = threadIdx.x; i < 16 * (kD + 2); i += kAttnThreads) (&sm_o[0][0])[i] = 0.f;
-    __syncthreads();
-    float M_lo = -INFINITY, M_hi = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < kAttnWarps; ++w) {
-      M_lo = fmaxf(M_lo, sm_m[w][g]);
-      M_hi = fmaxf(M_hi, sm_m[w][g + 8]);
-    }
-    const float f_lo = exp2_diff(m_lo, M_lo), f_hi = exp2_diff(m_hi, M_hi);
-#pragma unroll
-    for (int nt = 0; nt < kNt; ++nt) {
-      const int d0 = 64 * (nt >> 3) + 16 * j + (nt & 7);  // column 2j -> head dim 64 hd + 8 (2j) + i
-      if (g < G) {
-        atomicAdd(&sm_o[g][d0], o[nt][0] * f_lo);
-        atomicAdd(&sm_o[g][d0 + 8], o[nt][1] * f_lo);
-      }
-      if (kUpper && g + 8 < G) {
-        atomicAdd(&sm_o[g + 8][d0], o[nt][2] * f_hi);
-        atomicAdd(&sm_o[g + 8][d0 + 8], o[nt][3] * f_hi);
-      }
-    }
-    __syncthreads();
-
-    for (int i = threadIdx.x; i < G * kD; i += kAttnThreads) {
-      const int row = i / kD, d = i - row * kD;
-      float M = -INFINITY, L = 0.f;
-#pragma unroll
-      for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, sm_m[w][row]);
-#pragma unroll
-      for (int w = 0; w < kAttnWarps; ++w) L += sm_l[w][row] * exp2_diff(sm_m[w][row], M);
-      const float val = L > 0.f ? sm_o[row][d] / L : 0.f;
-      const int64_t q = q_row0 + row;
-      if (p.splits == 1) {
-        reinterpret_cast<uint16_t *>(p.out)[q * kD + d] = T::round1(val);
-      } else {
-        const int64_t at = q * p.splits + split;
-        p.part_o[at * kD + d] = val;
-        if (d == 0) {
-          p.part_ml[at * 2] = M;
-          p.part_ml[at * 2 + 1] = L;
-        }
-      }
-    }
-    __syncthreads();  // the next item reuses the merge buffers and sm_item
-  }
-}
-
-// ------------------------------------------------------------------ fast tier, up to 8 query heads per KV head --
-//
-// The same computation with tokens, not query heads, in the 16-row dimension of the MMAs:
-//   scores^T [16 tokens x 8 heads] = K [16 tokens x dims]  x  Q^T [dims x 8 heads]
-//   out^T    [16 dims   x 8 heads] = V^T [16 dims x 16 tokens] x P^T [16 tokens x 8 heads]
-// Eight query heads fill the 8-column operand exactly, so a step costs half the MMAs of the
-// heads-in-rows form, half the output accumulators (32 registers for head_dim 128) and half the
-// exponentials, and the softmax statistics of a head sit in the thread that owns its output
-// columns.  K and V steps are staged row-major in shared memory (rows padded by 16 bytes, which
-// makes ldmatrix conflict-free and every staging address a per-lane base plus a constant): K
-// rows are A operands as they lie (ldmatrix), V^T comes from ldmatrix.trans, and P^T from the
-// score accumulators through movmatrix.trans.  The ring is private to a warp; lanes wait for their own cp.async groups
-// and meet in __syncwarp before reading each other's chunks.
 #ifndef KVX_ATTN_T_STAGES
 #define KVX_ATTN_T_STAGES 2
 #endif
@@ -593,8 +348,11 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
   return y;
 }
 
-template <typename T, int kD, typename IdxT>
-__global__ void __launch_bounds__(kAttnThreads, KVX_ATTN_T_CTAS) kvx_attention_decode_t_kernel(const AttnParams p) {
+// kNt = 8-head column tiles: 1 for up to 8 query heads per KV head, 2 for 9..16 (twice the MMAs and
+// accumulators on the same K / V operands).
+template <typename T, int kD, typename IdxT, int kNt>
+__global__ void __launch_bounds__(kAttnThreads, kNt == 1 ? KVX_ATTN_T_CTAS : 2)
+    kvx_attention_decode_t_kernel(const AttnParams p) {
   constexpr int kKs = kD / 16;          // k-steps of the score MMAs = 16-dim row tiles of the output
   constexpr int kRowBytes = kD * 2;     // one token row of K or V
   constexpr int kPitch = kRowBytes + 16;  // staged rows are 16 bytes apart from a multiple of 128:
@@ -603,14 +361,14 @@ __global__ void __launch_bounds__(kAttnThreads, KVX_ATTN_T_CTAS) kvx_attention_d
   constexpr int kTile = 16 * kPitch;    // one staged 16-token step of K (or of V)
   constexpr int kPerLane = 16 * kChunks / 32;  // chunks of K (and of V) each lane copies per step
   extern __shared__ uint4 sm_dyn[];     // ring [warp][stage][K tile | V tile], then the chunk prefix
-  __shared__ float sm_m[kAttnWarps][8];
-  __shared__ float sm_l[kAttnWarps][8];
+  __shared__ float sm_m[kAttnWarps][8 * kNt];
+  __shared__ float sm_l[kAttnWarps][8 * kNt];
   __shared__ int32_t sm_page[kAttnWarps][kTStages];
   __shared__ int32_t sm_scan[kAttnThreads];
   __shared__ unsigned long long sm_item;
   char *ring = reinterpret_cast<char *>(sm_dyn);
   // merge buffer of the epilogue: lives in the ring, which is idle by then
-  float (*sm_o)[kD + 8] = reinterpret_cast<float (*)[kD + 8]>(ring);
+  float (*sm_o)[kD + 8] = reinterpret_cast<float (*)[kD + 8]>(ring);  // [8 * kNt][kD + 8]
   int32_t *sm_prefix = reinterpret_cast<int32_t *>(ring + kAttnWarps * kTStages * 2 * kTile);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, j = lane & 3;
@@ -619,36 +377,9 @@ __global__ void __launch_bounds__(kAttnThreads, KVX_ATTN_T_CTAS) kvx_attention_d
   // plus small offsets, most of them compile-time
   const uint32_t my_ring = static_cast<uint32_t>(__cvta_generic_to_shared(ring + warp * (kTStages * 2 * kTile)));
 
-  int64_t chunks_total;
-  if (p.use_prefix) {
-    const int S = p.seq_count;
-    const int per = (S + kAttnThreads - 1) / kAttnThreads;
-    const int begin = min(static_cast<int>(threadIdx.x) * per, S), end = min(begin + per, S);
-    int32_t local = 0;
-    for (int s = begin; s < end; ++s) local += chunks_of<IdxT>(p, s);
-    sm_scan[threadIdx.x] = local;
-    __syncthreads();
-    int32_t run = 0;
-    for (int t = 0; t < static_cast<int>(threadIdx.x); ++t) run += sm_scan[t];
-    for (int s = begin; s < end; ++s) {
-      sm_prefix[s] = run;
-      run += chunks_of<IdxT>(p, s);
-    }
-    if (threadIdx.x == kAttnThreads - 1) sm_prefix[S] = run;
-    __syncthreads();
-    chunks_total = sm_prefix[S];
-  } else {
-    chunks_total = static_cast<int64_t>(p.seq_count) * p.splits;
-  }
-  const int64_t items = chunks_total * p.heads_kv;
+  const int64_t items = build_work_list<IdxT>(p, sm_prefix, sm_scan);
 
-  if (p.splits == 1) {  // sequences without cached tokens have no work item: their output is zero
-    for (int s = blockIdx.x; s < p.seq_count; s += gridDim.x) {
-      if (read_idx<IdxT>(p.lens, s) > 0) continue;
-      for (int i = threadIdx.x; i < p.heads_q * kD; i += kAttnThreads)
-        reinterpret_cast<uint16_t *>(p.out)[static_cast<int64_t>(s) * p.heads_q * kD + i] = 0;
-    }
-  }
+  zero_empty_sequences<IdxT>(p);
 
   // Fixed per lane: which chunks of a step it copies (row = it * (32 / kChunks) + lane / kChunks,
   // chunk = lane % kChunks: a warp instruction copies whole rows, coalesced), and where its
@@ -663,55 +394,38 @@ __global__ void __launch_bounds__(kAttnThreads, KVX_ATTN_T_CTAS) kvx_attention_d
   const uint32_t lv_at = kTile + ((lane & 7) + 8 * (lane >> 4)) * kPitch + ((lane >> 3) & 1) * 16;
 
   for (unsigned long long round = 0;;) {
-    // With a counter, CTAs claim items as they become free; without one (few items: one per
-    // CTA) they stride over the list.
-    if (threadIdx.x == 0)
-      sm_item = p.counter != nullptr ? atomicAdd(p.counter, 1ull) : blockIdx.x + round * static_cast<unsigned long long>(gridDim.x);
-    ++round;
-    __syncthreads();
-    const int64_t item = static_cast<int64_t>(sm_item);
-    if (item >= items) break;
-    const int kvh = static_cast<int>(item % p.heads_kv);
-    const int64_t ci = item / p.heads_kv;
-    int seq, split;
-    if (p.use_prefix) {
-      int lo = 0, hi = p.seq_count;  // last s with prefix[s] <= ci
-      while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        if (sm_prefix[mid] <= ci)
-          lo = mid;
-        else
-          hi = mid;
-      }
-      seq = lo;
-      split = static_cast<int>(ci - sm_prefix[lo]);
-    } else {
-      seq = static_cast<int>(ci / p.splits);
-      split = static_cast<int>(ci - static_cast<int64_t>(seq) * p.splits);
-    }
-    int64_t len = read_idx<IdxT>(p.lens, seq);
-    if (len > p.max_seq_len) len = p.max_seq_len;
-    const int64_t cbeg = static_cast<int64_t>(split) * p.chunk;
-    const int64_t cend = min(len, cbeg + p.chunk);
+    WorkItem w;
+    if (!next_item<IdxT>(p, items, &round, &sm_item, sm_prefix, &w)) break;
+    const int seq = w.seq, split = w.split, kvh = w.kvh;
+    const int64_t cbeg = w.begin, cend = w.end;
     const int64_t q_row0 = static_cast<int64_t>(seq) * p.heads_q + static_cast<int64_t>(kvh) * G;
 
-    // Q^T as B operands: column g = query head g of the group (zero beyond the group),
-    // b0 = dims 16 kk + 2j, +1; b1 = dims 16 kk + 8 + 2j, +1.
-    uint32_t qb[kKs][2];
+    // Q^T as B operands: column g of tile nt = query head 8 nt + g of the group (zero beyond the
+    // group), b0 = dims 16 kk + 2j, +1; b1 = dims 16 kk + 8 + 2j, +1.
+    uint32_t qb[kNt][kKs][2];
 #pragma unroll
-    for (int kk = 0; kk < kKs; ++kk) {
-      qb[kk][0] = qb[kk][1] = 0;
-      if (g < G) {
-        const char *qrow = p.query + (q_row0 + g) * kRowBytes;
-        qb[kk][0] = *reinterpret_cast<const uint32_t *>(qrow + (16 * kk + 2 * j) * 2);
-        qb[kk][1] = *reinterpret_cast<const uint32_t *>(qrow + (16 * kk + 8 + 2 * j) * 2);
+    for (int nt = 0; nt < kNt; ++nt) {
+#pragma unroll
+      for (int kk = 0; kk < kKs; ++kk) {
+        qb[nt][kk][0] = qb[nt][kk][1] = 0;
+        if (8 * nt + g < G) {
+          const char *qrow = p.query + (q_row0 + 8 * nt + g) * kRowBytes;
+          qb[nt][kk][0] = *reinterpret_cast<const uint32_t *>(qrow + (16 * kk + 2 * j) * 2);
+          qb[nt][kk][1] = *reinterpret_cast<const uint32_t *>(qrow + (16 * kk + 8 + 2 * j) * 2);
+        }
       }
     }
 
-    float o[kKs][4];  // out^T: tile mt = dims 16 mt ..; c0, c1 = (dim g, heads 2j, 2j+1), c2, c3 = (dim g + 8, ..)
+    // out^T: tile mt = dims 16 mt ..; c0, c1 = (dim g, heads 8 nt + 2j, + 1), c2, c3 = (dim g + 8, ..)
+    float o[kNt][kKs][4];
+    float m0[kNt], m1[kNt], l0[kNt], l1[kNt];  // running maxima / denominators of heads 8 nt + 2j and + 1
 #pragma unroll
-    for (int mt = 0; mt < kKs; ++mt) o[mt][0] = o[mt][1] = o[mt][2] = o[mt][3] = 0.f;
-    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;  // heads 2j and 2j + 1
+    for (int nt = 0; nt < kNt; ++nt) {
+#pragma unroll
+      for (int mt = 0; mt < kKs; ++mt) o[nt][mt][0] = o[nt][mt][1] = o[nt][mt][2] = o[nt][mt][3] = 0.f;
+      m0[nt] = m1[nt] = -INFINITY;
+      l0[nt] = l1[nt] = 0.f;
+    }
 
     const int nsteps = cend > cbeg ? static_cast<int>((cend - cbeg + 15) >> 4) : 0;
     const int mine = nsteps > warp ? (nsteps - warp + kAttnWarps - 1) / kAttnWarps : 0;
@@ -769,84 +483,101 @@ __global__ void __launch_bounds__(kAttnThreads, KVX_ATTN_T_CTAS) kvx_attention_d
       const int64_t t0 = cbeg + static_cast<int64_t>(warp + i * kAttnWarps) * 16;
       const uint32_t tile = my_ring + stage * (2 * kTile);
 
-      float s[4] = {0.f, 0.f, 0.f, 0.f};  // (token g, heads 2j, 2j+1), (token g + 8, heads 2j, 2j+1)
+      float s[kNt][4];  // (token g, heads 8 nt + 2j, + 1), (token g + 8, same heads)
+#pragma unroll
+      for (int nt = 0; nt < kNt; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
 #pragma unroll
       for (int kk = 0; kk < kKs; ++kk) {
         uint32_t a[4];
         ldmatrix_x4(a, tile + lk_at + 32 * kk);
-        T::mma(s, a[0], a[1], a[2], a[3], qb[kk][0], qb[kk][1]);
+#pragma unroll
+        for (int nt = 0; nt < kNt; ++nt) T::mma(s[nt], a[0], a[1], a[2], a[3], qb[nt][kk][0], qb[nt][kk][1]);
       }
       const int64_t left = cend - t0;
+      uint32_t pb[kNt][2];  // P^T as B operand: (tokens 2j, 2j+1 | head g of the tile), (tokens 2j+8, 2j+9 | ..)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) s[e] *= p.scale_log2;
-      if (left < 16) {
-        if (g >= left) s[0] = s[1] = -INFINITY;
-        if (g + 8 >= left) s[2] = s[3] = -INFINITY;
-      }
-      // maxima of heads 2j and 2j + 1 over the step's 16 tokens: this lane's two, then over g
-      float x0 = fmaxf(s[0], s[2]), x1 = fmaxf(s[1], s[3]);
+      for (int nt = 0; nt < kNt; ++nt) {
 #pragma unroll
-      for (int d = 4; d < 32; d <<= 1) {
-        x0 = fmaxf(x0, __shfl_xor_sync(0xFFFFFFFFu, x0, d));
-        x1 = fmaxf(x1, __shfl_xor_sync(0xFFFFFFFFu, x1, d));
-      }
-      const float n0 = fmaxf(m0, x0), n1 = fmaxf(m1, x1);
-      if (__any_sync(0xFFFFFFFFu, n0 != m0 || n1 != m1)) {
-        const float c0 = exp2_diff(m0, n0), c1 = exp2_diff(m1, n1);
-        l0 *= c0, l1 *= c1;
-#pragma unroll
-        for (int mt = 0; mt < kKs; ++mt) {
-          o[mt][0] *= c0, o[mt][2] *= c0;
-          o[mt][1] *= c1, o[mt][3] *= c1;
+        for (int e = 0; e < 4; ++e) s[nt][e] *= p.scale_log2;
+        if (left < 16) {
+          if (g >= left) s[nt][0] = s[nt][1] = -INFINITY;
+          if (g + 8 >= left) s[nt][2] = s[nt][3] = -INFINITY;
         }
-        m0 = n0, m1 = n1;
+        // maxima of the two heads over the step's 16 tokens: this lane's two, then over g
+        float x0 = fmaxf(s[nt][0], s[nt][2]), x1 = fmaxf(s[nt][1], s[nt][3]);
+#pragma unroll
+        for (int d = 4; d < 32; d <<= 1) {
+          x0 = fmaxf(x0, __shfl_xor_sync(0xFFFFFFFFu, x0, d));
+          x1 = fmaxf(x1, __shfl_xor_sync(0xFFFFFFFFu, x1, d));
+        }
+        const float n0 = fmaxf(m0[nt], x0), n1 = fmaxf(m1[nt], x1);
+        // The running maximum rarely moves after the first steps: rescale only when some head's did.
+        if (__any_sync(0xFFFFFFFFu, n0 != m0[nt] || n1 != m1[nt])) {
+          const float c0 = exp2_diff(m0[nt], n0), c1 = exp2_diff(m1[nt], n1);
+          l0[nt] *= c0, l1[nt] *= c1;
+#pragma unroll
+          for (int mt = 0; mt < kKs; ++mt) {
+            o[nt][mt][0] *= c0, o[nt][mt][2] *= c0;
+            o[nt][mt][1] *= c1, o[nt][mt][3] *= c1;
+          }
+          m0[nt] = n0, m1[nt] = n1;
+        }
+        // exp2(-inf - finite) = 0 for masked tokens; a head whose maximum is still -inf (scores
+        // that are -inf in the data) must not compute -inf - -inf: it subtracts 0 instead.
+        const float z0 = n0 == -INFINITY ? 0.f : n0, z1 = n1 == -INFINITY ? 0.f : n1;
+        const float p0 = fast_exp2(s[nt][0] - z0), p1 = fast_exp2(s[nt][1] - z1);
+        const float p2 = fast_exp2(s[nt][2] - z0), p3 = fast_exp2(s[nt][3] - z1);
+        l0[nt] += p0 + p2;
+        l1[nt] += p1 + p3;
+        pb[nt][0] = movmatrix_trans(T::pack2(p0, p1));
+        pb[nt][1] = movmatrix_trans(T::pack2(p2, p3));
       }
-      const float z0 = n0 == -INFINITY ? 0.f : n0, z1 = n1 == -INFINITY ? 0.f : n1;
-      const float p0 = fast_exp2(s[0] - z0), p1 = fast_exp2(s[1] - z1);
-      const float p2 = fast_exp2(s[2] - z0), p3 = fast_exp2(s[3] - z1);
-      l0 += p0 + p2;
-      l1 += p1 + p3;
-      // P^T as B operand: (tokens 2j, 2j+1 | head g) and (tokens 2j+8, 2j+9 | head g)
-      const uint32_t pb0 = movmatrix_trans(T::pack2(p0, p1));
-      const uint32_t pb1 = movmatrix_trans(T::pack2(p2, p3));
 #pragma unroll
       for (int mt = 0; mt < kKs; ++mt) {
         uint32_t a[4];
         ldmatrix_x4_trans(a, tile + lv_at + 32 * mt);
-        T::mma(o[mt], a[0], a[1], a[2], a[3], pb0, pb1);
+#pragma unroll
+        for (int nt = 0; nt < kNt; ++nt) T::mma(o[nt][mt], a[0], a[1], a[2], a[3], pb[nt][0], pb[nt][1]);
       }
     }
     cp_async_wait<0>();
 
     // Denominators were kept per lane (its two tokens per step): complete them over g.
 #pragma unroll
-    for (int d = 4; d < 32; d <<= 1) {
-      l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, d);
-      l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, d);
-    }
-    if (g == 0) {
-      sm_m[warp][2 * j] = m0, sm_m[warp][2 * j + 1] = m1;
-      sm_l[warp][2 * j] = l0, sm_l[warp][2 * j + 1] = l1;
+    for (int nt = 0; nt < kNt; ++nt) {
+#pragma unroll
+      for (int d = 4; d < 32; d <<= 1) {
+        l0[nt] += __shfl_xor_sync(0xFFFFFFFFu, l0[nt], d);
+        l1[nt] += __shfl_xor_sync(0xFFFFFFFFu, l1[nt], d);
+      }
+      if (g == 0) {
+        sm_m[warp][8 * nt + 2 * j] = m0[nt], sm_m[warp][8 * nt + 2 * j + 1] = m1[nt];
+        sm_l[warp][8 * nt + 2 * j] = l0[nt], sm_l[warp][8 * nt + 2 * j + 1] = l1[nt];
+      }
     }
     __syncthreads();  // every warp is done with its part of the ring
-    for (int i = threadIdx.x; i < 8 * (kD + 8); i += kAttnThreads) (&sm_o[0][0])[i] = 0.f;
+    for (int i = threadIdx.x; i < 8 * kNt * (kD + 8); i += kAttnThreads) (&sm_o[0][0])[i] = 0.f;
     __syncthreads();
-    float M0 = -INFINITY, M1 = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < kAttnWarps; ++w) {
-      M0 = fmaxf(M0, sm_m[w][2 * j]);
-      M1 = fmaxf(M1, sm_m[w][2 * j + 1]);
-    }
-    const float f0 = exp2_diff(m0, M0), f1 = exp2_diff(m1, M1);
+    for (int nt = 0; nt < kNt; ++nt) {
+      const int h0 = 8 * nt + 2 * j;
+      float M0 = -INFINITY, M1 = -INFINITY;
 #pragma unroll
-    for (int mt = 0; mt < kKs; ++mt) {
-      if (2 * j < G) {
-        atomicAdd(&sm_o[2 * j][16 * mt + g], o[mt][0] * f0);
-        atomicAdd(&sm_o[2 * j][16 * mt + g + 8], o[mt][2] * f0);
+      for (int w = 0; w < kAttnWarps; ++w) {
+        M0 = fmaxf(M0, sm_m[w][h0]);
+        M1 = fmaxf(M1, sm_m[w][h0 + 1]);
       }
-      if (2 * j + 1 < G) {
-        atomicAdd(&sm_o[2 * j + 1][16 * mt + g], o[mt][1] * f1);
-        atomicAdd(&sm_o[2 * j + 1][16 * mt + g + 8], o[mt][3] * f1);
+      const float f0 = exp2_diff(m0[nt], M0), f1 = exp2_diff(m1[nt], M1);
+#pragma unroll
+      for (int mt = 0; mt < kKs; ++mt) {
+        if (h0 < G) {
+          atomicAdd(&sm_o[h0][16 * mt + g], o[nt][mt][0] * f0);
+          atomicAdd(&sm_o[h0][16 * mt + g + 8], o[nt][mt][2] * f0);
+        }
+        if (h0 + 1 < G) {
+          atomicAdd(&sm_o[h0 + 1][16 * mt + g], o[nt][mt][1] * f1);
+          atomicAdd(&sm_o[h0 + 1][16 * mt + g + 8], o[nt][mt][3] * f1);
+        }
       }
     }
     __syncthreads();
@@ -870,7 +601,7 @@ __global__ void __launch_bounds__(kAttnThreads, KVX_ATTN_T_CTAS) kvx_attention_d
         }
       }
     }
-    __syncthreads();  // the next item reuses the merge buffers and sm_item
+    // (next_item's barrier comes before the merge buffers and sm_item are reused)
   }
 }
 
@@ -1055,32 +786,16 @@ bool dense3(const kvx_tensor_desc_t *t, int64_t a, int64_t b, int64_t c, kvx_sta
 }
 
 template <typename T, int kD, typename IdxT>
-void launch_fast(const AttnParams &p, unsigned grid, size_t smem, cudaStream_t st) {
-  // (the attribute is per device and cheap to set, so it is set on every launch)
-  if (p.group > 8) {
-    cudaFuncSetAttribute(kvx_attention_decode_kernel<T, kD, IdxT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         static_cast<int>(smem));
-    kvx_attention_decode_kernel<T, kD, IdxT, true><<<grid, kAttnThreads, smem, st>>>(p);
-  } else {
-    cudaFuncSetAttribute(kvx_attention_decode_kernel<T, kD, IdxT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         static_cast<int>(smem));
-    kvx_attention_decode_kernel<T, kD, IdxT, false><<<grid, kAttnThreads, smem, st>>>(p);
-  }
-}
-
-template <typename T, typename IdxT>
-void launch_fast_dim(const AttnParams &p, unsigned grid, size_t smem, cudaStream_t st) {
-  if (p.dim == 128)
-    launch_fast<T, 128, IdxT>(p, grid, smem, st);
-  else
-    launch_fast<T, 64, IdxT>(p, grid, smem, st);
-}
-
-template <typename T, int kD, typename IdxT>
 void launch_t(const AttnParams &p, unsigned grid, size_t smem, cudaStream_t st) {
-  cudaFuncSetAttribute(kvx_attention_decode_t_kernel<T, kD, IdxT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                       static_cast<int>(smem));
-  kvx_attention_decode_t_kernel<T, kD, IdxT><<<grid, kAttnThreads, smem, st>>>(p);
+  if (p.group <= 8) {
+    cudaFuncSetAttribute(kvx_attention_decode_t_kernel<T, kD, IdxT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         static_cast<int>(smem));
+    kvx_attention_decode_t_kernel<T, kD, IdxT, 1><<<grid, kAttnThreads, smem, st>>>(p);
+  } else {
+    cudaFuncSetAttribute(kvx_attention_decode_t_kernel<T, kD, IdxT, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         static_cast<int>(smem));
+    kvx_attention_decode_t_kernel<T, kD, IdxT, 2><<<grid, kAttnThreads, smem, st>>>(p);
+  }
 }
 
 template <typename T, typename IdxT>
@@ -1105,8 +820,6 @@ int sm_count() {
   }
   return n;
 }
-
-int g_ctas_per_sm = KVX_ATTN_CTAS;  // persistent CTAs per SM of the fast kernel (its launch bound)
 
 }  // namespace
 
@@ -1208,10 +921,9 @@ KVX_API kvx_status_t kvx_launch_paged_attention_decode(const kvx_cache_desc_t *c
       p.part_ml = p.part_o + S * Hq * p.splits * D;
     }
     p.use_prefix = S <= kMaxPrefixSeqs ? 1 : 0;
-    const bool tokens_in_rows = p.group <= 8;
-    const int stages = tokens_in_rows ? kTStages : kStages, per_sm = tokens_in_rows ? KVX_ATTN_T_CTAS : g_ctas_per_sm;
-    // K and V steps of 16 rows; the tokens-in-rows kernel pads each row by 16 bytes
-    const size_t ring = static_cast<size_t>(kAttnWarps) * stages * 2 * 16 * (D * 2 + (tokens_in_rows ? 16 : 0));
+    const int per_sm = p.group <= 8 ? KVX_ATTN_T_CTAS : 2;  // the kernels' launch bounds
+    // K and V steps of 16 rows, each row padded by 16 bytes
+    const size_t ring = static_cast<size_t>(kAttnWarps) * kTStages * 2 * 16 * (D * 2 + 16);
     const size_t smem = ring + (p.use_prefix ? static_cast<size_t>(S + 1) * sizeof(int32_t) : 0);
     const int64_t most = S * p.splits * H;  // work items if every context had max_seq_len tokens
     const int64_t grid = std::max<int64_t>(1, std::min<int64_t>(most, static_cast<int64_t>(sm_count()) * per_sm));
@@ -1219,28 +931,16 @@ KVX_API kvx_status_t kvx_launch_paged_attention_decode(const kvx_cache_desc_t *c
       p.counter = nullptr;  // every possible item has its own CTA: nothing to balance, no counter to clear
     else if (cudaMemsetAsync(p.counter, 0, kCounterBytes, cs) != cudaSuccess)
       return KVX_STATUS_INTERNAL_ERROR;
-    if (tokens_in_rows) {
-      if (cd == KVX_DTYPE_BF16) {
-        if (s32)
-          launch_t_dim<Bf16, int32_t>(p, static_cast<unsigned>(grid), smem, cs);
-        else
-          launch_t_dim<Bf16, int64_t>(p, static_cast<unsigned>(grid), smem, cs);
-      } else {
-        if (s32)
-          launch_t_dim<Fp16, int32_t>(p, static_cast<unsigned>(grid), smem, cs);
-        else
-          launch_t_dim<Fp16, int64_t>(p, static_cast<unsigned>(grid), smem, cs);
-      }
-    } else if (cd == KVX_DTYPE_BF16) {
+    if (cd == KVX_DTYPE_BF16) {
       if (s32)
-        launch_fast_dim<Bf16, int32_t>(p, static_cast<unsigned>(grid), smem, cs);
+        launch_t_dim<Bf16, int32_t>(p, static_cast<unsigned>(grid), smem, cs);
       else
-        launch_fast_dim<Bf16, int64_t>(p, static_cast<unsigned>(grid), smem, cs);
+        launch_t_dim<Bf16, int64_t>(p, static_cast<unsigned>(grid), smem, cs);
     } else {
       if (s32)
-        launch_fast_dim<Fp16, int32_t>(p, static_cast<unsigned>(grid), smem, cs);
+        launch_t_dim<Fp16, int32_t>(p, static_cast<unsigned>(grid), smem, cs);
       else
-        launch_fast_dim<Fp16, int64_t>(p, static_cast<unsigned>(grid), smem, cs);
+        launch_t_dim<Fp16, int64_t>(p, static_cast<unsigned>(grid), smem, cs);
     }
     if (p.splits > 1) {
       if (s32)
