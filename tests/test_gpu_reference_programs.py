@@ -5,7 +5,7 @@ against THIS library instead of the reference kernels:
 * its micro-benchmark (benchmarks/kvx_bench.cu) must run the eight cases of its comparison
   script (benchmarks/fair_bench.py:176-185) and keep the CSV contract its tools parse
   (benchmarks/tests/kvx_bench_cli_test.py: a `write,` line of >= 13 fields reflecting the
-  arguments).  Timings of both builds are written to gpurun_out/ for the record.
+  arguments).  Timings of both builds are written to the folder named by KVX_RESULTS_DIR, when set.
 
 Skipped where the binaries were not built (no reference checkout at build time)."""
 import json
@@ -67,8 +67,8 @@ def test_reference_bench_program_runs_on_this_library_and_keeps_its_csv_contract
             rows.append({"dtype": dtype, **case,
                          "write_us": {"this": float(a["write"][9]) * 1e3, "reference": float(b["write"][9]) * 1e3},
                          "gather_us": {"this": float(a["gather"][9]) * 1e3, "reference": float(b["gather"][9]) * 1e3}})
-    out_dir = os.path.join(ROOT, "gpurun_out")
-    if os.path.isdir(out_dir):
+    out_dir = os.environ.get("KVX_RESULTS_DIR", "")
+    if out_dir and os.path.isdir(out_dir):
         with open(os.path.join(out_dir, "fair_bench_programs.json"), "w") as f:
             json.dump(rows, f, indent=1)
     # bad arguments still make the program fail (benchmarks/tests/kvx_bench_cli_test.py:44-53)

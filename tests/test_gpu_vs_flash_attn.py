@@ -1,7 +1,8 @@
 """Cross-implementation check of the paged decode attention against the flash_attn package's
 paged kv-cache kernel (library code in this image; `flash_attn_with_kvcache` with a block
 table, pages of 256 tokens as that kernel requires): same inputs, outputs within bf16
-rounding of each other, CUDA-event timings of both written to gpurun_out/ for the record.
+rounding of each other, CUDA-event timings of both written to the folder named by
+KVX_RESULTS_DIR, when set, for the record.
 Runs in a child process and is skipped when flash_attn cannot be imported or run here."""
 import json
 import os
@@ -84,8 +85,8 @@ def _compare():
         a, b = _time(ours), _time(theirs)
         rows.append({"case": label, "kv_gb": round(kv_bytes / 1e9, 3), "this_us": round(a, 1), "flash_attn_us": round(b, 1),
                      "this_kv_gbs": round(kv_bytes / a / 1e3, 1), "flash_attn_kv_gbs": round(kv_bytes / b / 1e3, 1)})
-    out_dir = os.path.join(ROOT, "gpurun_out")
-    if os.path.isdir(out_dir):
+    out_dir = os.environ.get("KVX_RESULTS_DIR", "")
+    if out_dir and os.path.isdir(out_dir):
         with open(os.path.join(out_dir, "vs_flash_attn.json"), "w") as f:
             json.dump(rows, f, indent=1)
     print(json.dumps(rows))

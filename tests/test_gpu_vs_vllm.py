@@ -4,8 +4,8 @@ reference project publishes (benchmarks/fair_bench.py:84-94) and tests inside it
 
 The vLLM wheel in this image is not the version the reference pinned, so this is an extra
 column, not the parity pin: outputs must be bit-identical (for kv_cache_dtype "auto" both are
-plain copies), and CUDA-event timings of both operators are written to gpurun_out/ for the
-record.  Skipped when vLLM's compiled ops cannot be loaded."""
+plain copies), and CUDA-event timings of both operators are written to the folder named by
+KVX_RESULTS_DIR, when set, for the record.  Skipped when vLLM's compiled ops cannot be loaded."""
 import json
 import os
 
@@ -127,8 +127,8 @@ def _compare_with_vllm():
             assert torch.equal(va.view(torch.int16), vb.view(torch.int16)), "packed V differs from vLLM"
             rows.append({"case": "reshape_and_cache_packed", "dtype": "bfloat16", "tokens": T, "bit_identical": True})
 
-    out_dir = os.path.join(ROOT, "gpurun_out")
-    if os.path.isdir(out_dir):
+    out_dir = os.environ.get("KVX_RESULTS_DIR", "")
+    if out_dir and os.path.isdir(out_dir):
         with open(os.path.join(out_dir, "vs_vllm.json"), "w") as f:
             json.dump(rows, f, indent=1)
 
