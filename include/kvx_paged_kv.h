@@ -35,6 +35,12 @@ extern "C" {
  *
  * kvx_launch_write_kv dispatches on cache->k.dtype: F16 / BF16 / F32 need IO tensors of
  * the same type; F8_E4M3 (ABI 1.2) quantises 16/32-bit IO on the fly, see below.
+ *
+ * key / value are [num_tokens, heads, dim] with dense heads and dims (stride[2] = 1,
+ * stride[1] = dim).  Their token stride may exceed heads * dim -- slices of a fused projection
+ * output are written as they are; the reference's launchers answer UNSUPPORTED for anything
+ * but stride[0] = heads * dim (kernels/kvx_paged_kv.cu:269-313), which still applies to the
+ * validate-only kvx_write_kv and to a token stride below heads * dim.
  * reference: kernels/kvx_paged_kv.h:11-13, kernels/kvx_paged_kv.cu:472-491 */
 KVX_API kvx_status_t kvx_launch_write_kv(const kvx_cache_desc_t *cache,
                                          const kvx_write_desc_t *write, void *stream);

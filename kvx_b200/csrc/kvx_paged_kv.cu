@@ -276,6 +276,7 @@ struct WriteRowsParams {
   int64_t k_blk, k_tok, k_head;  // bytes
   int64_t v_blk, v_tok, v_head;
   int64_t k_vec, v_vec;  // bytes between consecutive 16-byte vectors of one head (16 unless packed)
+  int64_t k_pitch, v_pitch;  // bytes between consecutive token rows of key / value (row_bytes when dense)
   const void *slots;
   int64_t row_bytes;
   int32_t num_tokens, num_blocks, block_size, bs_shift;
@@ -292,7 +293,9 @@ struct WriteRowsParams {
 // kTrans      : threads run over tokens fastest, vectors slowest (tok_tile is a power of two).
 //               For packed pages the stores of neighbouring threads are then adjacent (the same
 //               vector of consecutive slots) and it is the loads that are 16-byte pieces.
-template <typename SlotT, bool kSeg, int kUnroll, bool kTrans = false>
+// kPitched    : token rows of key / value are k_pitch / v_pitch bytes apart (slices of a fused
+//               projection output) instead of dense.
+template <typename SlotT, bool kSeg, int kUnroll, bool kTrans = false, bool kPitched = false>
 __global__ void __launch_bounds__(kWriteThreads) kvx_write_rows_kernel(const WriteRowsParams p) {
   pdl_prologue();
   __shared__ int64_t s_k[kMaxTokTile];
@@ -317,8 +320,8 @@ __global__ void __launch_bounds__(kWriteThreads) kvx_write_rows_kernel(const Wri
   }
   __syncthreads();
 
-  const char *ksrc = p.key + tok0 * p.row_bytes;
-  const char *vsrc = p.value + tok0 * p.row_bytes;
+  const char *ksrc = p.key + tok0 * (kPitched ? p.k_pitch : p.row_bytes);
+  const char *vsrc = p.value + tok0 * (kPitched ? p.v_pitch : p.row_bytes);
   const int nvec = (kTrans ? p.tok_tile : ntok) * p.vpr;
   for (int f0 = tid; f0 < nvec; f0 += kWriteThreads * kUnroll) {
     uint4 kr[kUnroll], vr[kUnroll];
@@ -341,9 +344,14 @@ __global__ void __launch_bounds__(kWriteThreads) kvx_write_rows_kernel(const Wri
             kd[u] = ko + static_cast<int64_t>(v) * 16;
             vd[u] = s_v[tok] + static_cast<int64_t>(v) * 16;
           }
-          const int64_t from = kTrans ? static_cast<int64_t>(tok) * p.vpr + v : f;
-          kr[u] = load_stream(ksrc + from * 16);
-          vr[u] = load_stream(vsrc + from * 16);
+          if (kPitched) {
+            kr[u] = load_stream(ksrc + tok * p.k_pitch + static_cast<int64_t>(v) * 16);
+            vr[u] = load_stream(vsrc + tok * p.v_pitch + static_cast<int64_t>(v) * 16);
+          } else {
+            const int64_t from = kTrans ? static_cast<int64_t>(tok) * p.vpr + v : f;
+            kr[u] = load_stream(ksrc + from * 16);
+            vr[u] = load_stream(vsrc + from * 16);
+          }
         }
       }
     }
@@ -596,8 +604,8 @@ __global__ void __launch_bounds__(kWriteThreads) kvx_write_f8_kernel(const Write
   }
   __syncthreads();
 
-  const char *ksrc = p.key + tok0 * p.row_bytes;
-  const char *vsrc = p.value + tok0 * p.row_bytes;
+  const char *ksrc = p.key + tok0 * p.k_pitch;
+  const char *vsrc = p.value + tok0 * p.v_pitch;
   const int nvec = ntok * p.vpr;
   for (int f0 = tid; f0 < nvec; f0 += kWriteThreads * kUnroll) {
     uint4 kr[kUnroll], vr[kUnroll];
@@ -617,8 +625,8 @@ __global__ void __launch_bounds__(kWriteThreads) kvx_write_f8_kernel(const Write
           hh[u] = h;
           kd[u] = ko + h * p.k_head + w;
           vd[u] = s_v[tok] + h * p.v_head + w;
-          kr[u] = load_stream(ksrc + static_cast<int64_t>(f) * 16);
-          vr[u] = load_stream(vsrc + static_cast<int64_t>(f) * 16);
+          kr[u] = load_stream(ksrc + tok * p.k_pitch + static_cast<int64_t>(v) * 16);  // pitch = row when dense
+          vr[u] = load_stream(vsrc + tok * p.v_pitch + static_cast<int64_t>(v) * 16);
         }
       }
     }
@@ -680,8 +688,8 @@ struct Convert<SrcT, F8> {  // quantise
 // One (token, head, dim) element per thread, any layout / stride / alignment.
 template <typename IoT, typename CacheT, typename SlotT>
 __global__ void __launch_bounds__(256)
-    kvx_write_generic_kernel(const IoT *key, const IoT *value, const void *slots, int64_t num_tokens,
-                             const GenericParams p) {
+    kvx_write_generic_kernel(const IoT *key, const IoT *value, int64_t k_pitch, int64_t v_pitch, const void *slots,
+                             int64_t num_tokens, const GenericParams p) {  // pitches in elements
   const int64_t hd = static_cast<int64_t>(p.g.heads) * p.g.dim;
   const int64_t total = num_tokens * hd;
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -698,9 +706,9 @@ __global__ void __launch_bounds__(256)
   const float sk = p.ks.base ? __ldg(p.ks.base + h * p.ks.stride) : 1.f;
   const float sv = p.vs.base ? __ldg(p.vs.base + h * p.vs.stride) : 1.f;
   *reinterpret_cast<CacheT *>(p.k.base + page_byte_offset(p.k, b, o, h, d)) =
-      Convert<IoT, CacheT>::apply(key[idx], sk);
+      Convert<IoT, CacheT>::apply(key[t * k_pitch + rem], sk);
   *reinterpret_cast<CacheT *>(p.v.base + page_byte_offset(p.v, b, o, h, d)) =
-      Convert<IoT, CacheT>::apply(value[idx], sv);
+      Convert<IoT, CacheT>::apply(value[t * v_pitch + rem], sv);
 }
 
 struct GatherShape {
@@ -1589,6 +1597,18 @@ kvx_status_t check_io_tensor(const kvx_tensor_desc_t *t, uint32_t ndim, const in
   return KVX_STATUS_OK;
 }
 
+// The write's key / value: as check_io_tensor, except that token rows may lie further apart
+// than heads * dim elements (a slice of a fused projection output, which is what vLLM hands its
+// own cache-write operator).  The reference asks for dense rows (kernels/kvx_paged_kv.cu:269-313)
+// and answers UNSUPPORTED; everything else about the tensor is checked as it does.
+kvx_status_t check_write_rows(const kvx_tensor_desc_t *t, const int64_t *dims) {
+  if (t->ndim != 3) return KVX_STATUS_INVALID_ARGUMENT;
+  for (uint32_t i = 0; i < 3; ++i)
+    if (t->shape[i] != dims[i]) return KVX_STATUS_INVALID_ARGUMENT;
+  if (t->stride[2] != 1 || t->stride[1] != dims[2] || t->stride[0] < dims[1] * dims[2]) return KVX_STATUS_UNSUPPORTED;
+  return KVX_STATUS_OK;
+}
+
 bool resolve_scale(const kvx_scale_desc_t *d, const void *scalar, uint32_t heads, ScaleView *out) {
   if (d != nullptr && d->size >= sizeof(kvx_scale_desc_t) && d->data != nullptr) {
     if (d->dtype != KVX_DTYPE_F32) return false;
@@ -1658,10 +1678,12 @@ kvx_status_t launch_write_generic(const kvx_write_desc_t *w, const GenericParams
   const IoT *v = static_cast<const IoT *>(w->io.value.data);
   if (w->slots.dtype == KVX_DTYPE_S32)
     kvx_write_generic_kernel<IoT, CacheT, int32_t>
-        <<<static_cast<unsigned>(grid), 256, 0, st>>>(k, v, w->slots.slots, w->io.num_tokens, gp);
+        <<<static_cast<unsigned>(grid), 256, 0, st>>>(k, v, w->io.key.stride[0], w->io.value.stride[0], w->slots.slots,
+                                                      w->io.num_tokens, gp);
   else
     kvx_write_generic_kernel<IoT, CacheT, int64_t>
-        <<<static_cast<unsigned>(grid), 256, 0, st>>>(k, v, w->slots.slots, w->io.num_tokens, gp);
+        <<<static_cast<unsigned>(grid), 256, 0, st>>>(k, v, w->io.key.stride[0], w->io.value.stride[0], w->slots.slots,
+                                                      w->io.num_tokens, gp);
   return finish_launch();
 }
 
@@ -1705,9 +1727,9 @@ kvx_status_t write_impl(const kvx_cache_desc_t *cache, const kvx_write_desc_t *w
   if (write->io.num_kv_heads != cache->num_kv_heads || write->io.head_dim != cache->head_dim)
     return KVX_STATUS_INVALID_ARGUMENT;
   const int64_t dims[3] = {write->io.num_tokens, write->io.num_kv_heads, write->io.head_dim};
-  kvx_status_t st = check_io_tensor(&write->io.key, 3, dims);
+  kvx_status_t st = check_write_rows(&write->io.key, dims);
   if (st != KVX_STATUS_OK) return st;
-  st = check_io_tensor(&write->io.value, 3, dims);
+  st = check_write_rows(&write->io.value, dims);
   if (st != KVX_STATUS_OK) return st;
   if (write->slots.token_count != write->io.num_tokens) return KVX_STATUS_INVALID_ARGUMENT;
 
@@ -1742,7 +1764,10 @@ kvx_status_t write_impl(const kvx_cache_desc_t *cache, const kvx_write_desc_t *w
   const int64_t row_bytes = H * D * io_elem;
   const int64_t out_vec = fp8 ? 16 / io_elem : 16;  // cache bytes produced per input vector
   const bool k_packed = !fp8 && view_packed16(gp.k, elem, D), v_packed = !fp8 && view_packed16(gp.v, elem, D);
-  const bool vec_ok = !g_opt.force_generic && (D * io_elem) % 16 == 0 &&
+  const int64_t k_pitch = write->io.key.stride[0] * io_elem, v_pitch = write->io.value.stride[0] * io_elem;
+  const bool pitched = k_pitch != row_bytes || v_pitch != row_bytes;  // token rows further apart than dense
+  const bool vec_ok = !g_opt.force_generic && (D * io_elem) % 16 == 0 && k_pitch % 16 == 0 && v_pitch % 16 == 0 &&
+                      !(pitched && (k_packed || v_packed)) &&
                       aligned(write->io.key.data, 16) && aligned(write->io.value.data, 16) &&
                       (k_packed || view_vectorisable(gp.k, elem, D, out_vec)) &&
                       (v_packed || view_vectorisable(gp.v, elem, D, out_vec)) && row_bytes / 16 <= (1 << 20);
@@ -1755,6 +1780,7 @@ kvx_status_t write_impl(const kvx_cache_desc_t *cache, const kvx_write_desc_t *w
     p.k_vec = k_packed ? gp.k.dhi : 16, p.v_vec = v_packed ? gp.v.dhi : 16;
     p.slots = write->slots.slots;
     p.row_bytes = row_bytes;
+    p.k_pitch = k_pitch, p.v_pitch = v_pitch;
     p.num_tokens = static_cast<int32_t>(T);
     p.num_blocks = gp.g.num_blocks;
     p.block_size = gp.g.block_size;
@@ -1802,6 +1828,13 @@ kvx_status_t write_impl(const kvx_cache_desc_t *cache, const kvx_write_desc_t *w
         launch_streaming(kvx_write_rows_kernel<int32_t, true, 4, true>, grid, kWriteThreads, 0, cs, p);
       else
         launch_streaming(kvx_write_rows_kernel<int64_t, true, 4, true>, grid, kWriteThreads, 0, cs, p);
+      return finish_launch();
+    }
+    if (pitched) {
+      if (s32)
+        launch_streaming(kvx_write_rows_kernel<int32_t, true, 4, false, true>, grid, kWriteThreads, 0, cs, p);
+      else
+        launch_streaming(kvx_write_rows_kernel<int64_t, true, 4, false, true>, grid, kWriteThreads, 0, cs, p);
       return finish_launch();
     }
     if (s32) {

@@ -232,7 +232,7 @@ static void write_one(const kvx_cache_desc_t *c, const kvx_tensor_desc_t *pages,
     if (block >= (int64_t)c->num_blocks) continue; /* silently skipped */
     for (int64_t h = 0; h < H; ++h) {
       for (int64_t d = 0; d < D; ++d) {
-        const int64_t si = (t * H + h) * D + d;
+        const int64_t si = t * src->stride[0] + h * D + d; /* token rows may be pitched; dense: stride[0] = H * D */
         const int64_t di = page_offset(pages, block, off, h, d);
         if (quant) {
           const float x = load_as_f32(src->data, src->dtype, si);

@@ -292,3 +292,20 @@ def expected_varlen_from_padded(case: Case, padded_k: np.ndarray, padded_v: np.n
         ek[first:first + n] = padded_k[s, :n]
         ev[first:first + n] = padded_v[s, :n]
     return ek, ev
+
+
+def to_pitched(case: Case, key_extra: int, value_extra: int, seed: int = 0) -> Case:
+    """The same write with key / value token rows ``heads * dim + extra`` elements apart, as
+    slices of a fused projection output are; the gaps hold random bits that must not be read
+    into the cache."""
+    import dataclasses
+    rng = np.random.default_rng(seed)
+    hd = case.geom.num_kv_heads * case.geom.head_dim
+    out = {}
+    for name, extra in (("key", key_extra), ("value", value_extra)):
+        src = getattr(case, name).reshape(case.T, hd)
+        wide = random_bits(rng, (case.T, hd + extra), case.io_dtype)
+        wide[:, :hd] = src
+        out[name] = wide
+        out[name + "_pitch"] = hd + extra
+    return dataclasses.replace(case, **out)

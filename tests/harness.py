@@ -88,6 +88,10 @@ class Case:
     # un-padded output (kvx_launch_gather_kv_varlen): out_k / out_v are [rows, H, D] and
     # sequence s starts at row out_indptr[s]
     out_indptr: Optional[np.ndarray] = None      # [S + 1] int32 / int64
+    # token rows of key / value further apart than heads * dim: key / value are then [T, pitch]
+    # arrays whose first heads * dim columns are the row (elements; 0 = dense [T, H, D])
+    key_pitch: int = 0
+    value_pitch: int = 0
     note: str = ""
     keep: list = field(default_factory=list)
 
@@ -130,6 +134,10 @@ def descriptors(case: Case, bufs: dict, memory: int):
     ks, vs = _scale(case, bufs.get("k_scale"), "k"), _scale(case, bufs.get("v_scale"), "v")
     write = abi.write_desc(case.T, g.num_kv_heads, g.head_dim, case.io_dtype, _addr(bufs["key"]),
                            _addr(bufs["value"]), index_code(case.slots), _addr(bufs["slots"]), memory, ks, vs)
+    if case.key_pitch:
+        write.io.key.stride[0] = case.key_pitch
+    if case.value_pitch:
+        write.io.value.stride[0] = case.value_pitch
     gather = None
     if case.table is not None:
         S, mb = case.table.shape

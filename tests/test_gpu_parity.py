@@ -349,6 +349,29 @@ def test_more_sequences_than_the_shared_memory_prefix_holds():
         check_gather(cases.to_varlen(case), k, v)
 
 
+@pytest.mark.parametrize("layout", [abi.LAYOUT_NHD, abi.LAYOUT_HND])
+def test_key_value_rows_with_a_token_pitch(layout):
+    """key / value whose token rows are further apart than heads * dim (slices of a fused
+    projection output, which vLLM passes to its own operator): accepted by the write launchers
+    here (the reference answers UNSUPPORTED), vector tier for 16-byte pitches, generic tier
+    otherwise, fp8 cache included; what lies between the rows must not reach the cache."""
+    for i, (kw, extras) in enumerate([
+        (dict(heads=8, dim=128, block_size=16, num_blocks=40, lens=[100, 17, 256, 1, 0, 33], pad_frac=0.1), (2048, 1024)),
+        (dict(heads=2, dim=64, block_size=32, num_blocks=20, lens=[31, 33, 160], slot_dtype=np.int32), (8, 0)),
+        (dict(heads=2, dim=64, block_size=16, num_blocks=20, lens=[50, 70]), (3, 5)),           # misaligned pitch
+        (dict(heads=3, dim=40, block_size=6, num_blocks=50, lens=[7, 100, 13], oob_slots=2), (40, 40)),
+    ]):
+        case = cases.to_pitched(cases.make_case(1300 + i, layout=layout, dtype=abi.DTYPE_BF16, **kw), *extras, seed=i)
+        case.note = f"pitched {i}"
+        check_write(case)
+        check_write(case, "typed")
+        check_write(case, "prefill", 1)
+    f8 = cases.make_case(1350, layout=layout, dtype=abi.DTYPE_BF16, cache_dtype=abi.DTYPE_F8_E4M3, real_values=True,
+                         heads=4, dim=64, block_size=16, num_blocks=24, lens=[100, 40, 7], scale_gran=abi.SCALE_PER_HEAD)
+    check_write(cases.to_pitched(f8, 256, 64))
+    check_write(cases.to_pitched(f8, 1, 0))
+
+
 def test_empty_and_degenerate_batches():
     case = cases.make_case(3, dtype=abi.DTYPE_F16, heads=2, dim=64, lens=[0, 0], num_blocks=4)
     assert case.T == 0

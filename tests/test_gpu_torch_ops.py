@@ -95,8 +95,9 @@ def test_ops_fp8_equal_checker(route, gran):
 
 def test_ops_slice_of_a_larger_batch_and_int32_slots():
     """The batch is sized by slot_mapping, so key/value may hold more rows than are written
-    (reference: kvx.patch:208).  Rows must be dense, as in the reference (kvx.patch:213-218):
-    a strided view is answered with UNSUPPORTED, not copied."""
+    (reference: kvx.patch:208).  Views of a fused projection output, whose token rows are not
+    dense, are written as they are (the reference's operator refuses them, kvx.patch:213-218;
+    vLLM's own operator takes them); a view with strided heads is still UNSUPPORTED."""
     import torch
 
     from kvx_b200 import ops
@@ -104,49 +105,32 @@ def test_ops_slice_of_a_larger_batch_and_int32_slots():
     case = cases.make_case(5, dtype=abi.DTYPE_F16, num_blocks=16, block_size=16, heads=4, dim=64, lens=[48, 20],
                            slot_dtype=np.int32)
     T = case.key.shape[0]
+    st, ek, ev = oracle_write(case)
+    slots = torch.from_numpy(case.slots).cuda()
     kv = torch.zeros((2, T + 3, 4, 64), dtype=torch.float16, device="cuda")
     kv[0, :T] = _to_dev(torch, case.key, case.io_dtype).view(case.key.shape)
     kv[1, :T] = _to_dev(torch, case.value, case.io_dtype).view(case.value.shape)
-    ck = _to_dev(torch, case.cache_k, case.cache_dtype).view(case.geom.shape)
-    cv = _to_dev(torch, case.cache_v, case.cache_dtype).view(case.geom.shape)
-    slots = torch.from_numpy(case.slots).cuda()
-    ops.reshape_and_cache_flash_kvx(kv[0], kv[1], ck, cv, slots)
-    torch.cuda.synchronize()
-    qkv = torch.zeros((T, 3, 4, 64), dtype=torch.float16, device="cuda")
+    qkv = torch.randn((T, 3, 4, 64), device="cuda").to(torch.float16)       # [token, q|k|v, head, dim]
+    qkv[:, 1] = kv[0, :T]
+    qkv[:, 2] = kv[1, :T]
+    for key, value in ((kv[0], kv[1]), (qkv[:, 1], qkv[:, 2])):
+        for native in (True, False):
+            ck = _to_dev(torch, case.cache_k, case.cache_dtype).view(case.geom.shape)
+            cv = _to_dev(torch, case.cache_v, case.cache_dtype).view(case.geom.shape)
+            saved = ops._NATIVE
+            if not native:
+                ops._NATIVE = False
+            try:
+                ops.reshape_and_cache_flash_kvx(key, value, ck, cv, slots)
+            finally:
+                ops._NATIVE = saved
+            torch.cuda.synchronize()
+            assert np.array_equal(_bits(ck, case.cache_dtype), ek.reshape(-1))
+            assert np.array_equal(_bits(cv, case.cache_dtype), ev.reshape(-1))
+    hqkv = torch.zeros((T, 4, 3, 64), dtype=torch.float16, device="cuda")   # heads not dense in the view
     with pytest.raises(ops.KvxError) as e:
-        ops.reshape_and_cache_flash_kvx(qkv[:, 1], qkv[:, 2], ck.clone(), cv.clone(), slots)
+        ops.reshape_and_cache_flash_kvx(hqkv[:, :, 1], hqkv[:, :, 2], ck.clone(), cv.clone(), slots)
     assert e.value.status == abi.STATUS_UNSUPPORTED
-    st, ek, ev = oracle_write(case)
-    assert np.array_equal(_bits(ck, case.cache_dtype), ek.reshape(-1))
-    assert np.array_equal(_bits(cv, case.cache_dtype), ev.reshape(-1))
-
-
-@pytest.mark.parametrize("route", ["native", "ctypes"])
-def test_ops_accept_a_logical_nhd_view_of_hnd_memory(route):
-    """vLLM hands an HND cache over as a [blocks, block_size, heads, dim] view with permuted
-    strides; both routes must describe the memory underneath."""
-    import torch
-
-    from kvx_b200 import ops
-
-    case = cases.make_case(9, layout=abi.LAYOUT_HND, dtype=abi.DTYPE_BF16, num_blocks=12, block_size=16, heads=4,
-                           dim=64, lens=[40, 100])
-    ck = _to_dev(torch, case.cache_k, case.cache_dtype).view(case.geom.shape)
-    cv = _to_dev(torch, case.cache_v, case.cache_dtype).view(case.geom.shape)
-    key = _to_dev(torch, case.key, case.io_dtype).view(case.key.shape)
-    value = _to_dev(torch, case.value, case.io_dtype).view(case.value.shape)
-    saved = ops._NATIVE
-    if route == "ctypes":
-        ops._NATIVE = False
-    try:
-        ops.reshape_and_cache_flash_kvx(key, value, ck.permute(0, 2, 1, 3), cv.permute(0, 2, 1, 3),
-                                        torch.from_numpy(case.slots).cuda())
-    finally:
-        ops._NATIVE = saved
-    torch.cuda.synchronize()
-    st, ek, ev = oracle_write(case)
-    assert np.array_equal(_bits(ck, case.cache_dtype), ek.reshape(-1))
-    assert np.array_equal(_bits(cv, case.cache_dtype), ev.reshape(-1))
 
 
 def test_ops_varlen_gather_matches_padded_gather():

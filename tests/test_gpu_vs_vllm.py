@@ -97,6 +97,24 @@ def _compare_with_vllm():
     # the Llama-3-8B prefill shape, one layer, 10 % padding, pages spread over 2.3 GB
     both(torch.bfloat16, 8, 128, 16, 142060, 71525, 0.10, 99, "c2_one_layer", True)
 
+    # key / value as views of a fused [token, q | k | v, head, dim] projection output (32 query heads
+    # and 8 + 8 KV heads): token rows 6 144 elements apart.  Both operators take them as they are.
+    T, H, D, nb = 142060, 8, 128, 71525
+    g = torch.Generator(device="cuda"); g.manual_seed(11)
+    fused = torch.randn((T, 48, D), generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    key, value = fused[:, 32:40], fused[:, 40:48]
+    slots = torch.randperm(nb * 16, generator=g, device="cuda")[:T].to(torch.int64)
+    ck_a = torch.zeros((nb, 16, H, D), dtype=torch.bfloat16, device="cuda"); cv_a = ck_a.clone()
+    ck_b = ck_a.clone(); cv_b = ck_a.clone()
+    ops.reshape_and_cache_flash_kvx(key, value, ck_a, cv_a, slots, "auto", one, one)
+    op(key, value, ck_b, cv_b, slots, "auto", one, one)
+    torch.cuda.synchronize()
+    assert torch.equal(ck_a.view(torch.int16), ck_b.view(torch.int16)) and torch.equal(cv_a.view(torch.int16), cv_b.view(torch.int16))
+    rows.append({"case": "c2_one_layer_fused_qkv_views", "dtype": "bfloat16", "tokens": T,
+                 "this_us": round(_time(lambda: ops.reshape_and_cache_flash_kvx(key, value, ck_a, cv_a, slots, "auto", one, one)), 2),
+                 "vllm_us": round(_time(lambda: op(key, value, ck_b, cv_b, slots, "auto", one, one)), 2)})
+    del fused, ck_a, cv_a, ck_b, cv_b
+
     # vLLM's other cache-write operator (non-flash paged attention): K [blocks, heads, dim / x,
     # block_size, x] with x = 16 bytes / element, V [blocks, heads, dim, block_size].  Here that
     # is HND_PACKED (V with pack 1), reached through the TGI adapter's "paged" layout
