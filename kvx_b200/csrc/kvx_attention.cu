@@ -9,7 +9,7 @@
  * byte with 4 query heads per KV head), so the design goal is the gather's read stream with
  * the arithmetic hidden under it:
  *
- *   fast tier   16-bit cache, head_dim 64 / 128, pages of a multiple of 16 tokens, up to 16 query
+ *   fast tier   16-bit or e4m3 cache, head_dim 64 / 128 / 256, pages of a multiple of 16 tokens, up to 16 query
  *               heads per KV head.  Work items are (sequence, chunk of the context, KV head)
  *               triples of chunks that exist; persistent CTAs claim them from a counter in
  *               caller scratch, and their warps take 16-token steps whose K and V rows are staged
@@ -169,6 +169,10 @@ struct Bf16 {
     return *reinterpret_cast<const uint32_t *>(&r);
   }
   static __device__ __forceinline__ uint16_t round1(float z) { return __bfloat16_as_ushort(__float2bfloat16_rn(z)); }
+  static __device__ __forceinline__ uint32_t to_f16x2(uint32_t x) {  // two bf16 -> two f16 (nearest)
+    const __half2 r = __floats2half2_rn(__uint_as_float(x << 16), __uint_as_float(x & 0xFFFF0000u));
+    return *reinterpret_cast<const uint32_t *>(&r);
+  }
   static __device__ __forceinline__ void mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                              uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -183,6 +187,7 @@ struct Fp16 {
     return *reinterpret_cast<const uint32_t *>(&r);
   }
   static __device__ __forceinline__ uint16_t round1(float z) { return __half_as_ushort(__float2half_rn(z)); }
+  static __device__ __forceinline__ uint32_t to_f16x2(uint32_t x) { return x; }
   static __device__ __forceinline__ void mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                              uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -348,16 +353,37 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
   return y;
 }
 
+// Two e4m3 pairs (the halves of x) -> two f16x2 registers, exact.
+__device__ __forceinline__ void e4m3x4_to_f16x4(uint32_t x, uint32_t *lo, uint32_t *hi) {
+  asm("{ .reg .b16 a, b;\n\t"
+      "mov.b32 {a, b}, %2;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %0, a;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %1, b; }"
+      : "=r"(*lo), "=r"(*hi)
+      : "r"(x));
+}
+
 // kNt = 8-head column tiles: 1 for up to 8 query heads per KV head, 2 for 9..16 (twice the MMAs and
 // accumulators on the same K / V operands).
-template <typename T, int kD, typename IdxT, int kNt>
-__global__ void __launch_bounds__(kAttnThreads, kNt == 1 ? KVX_ATTN_T_CTAS : 2)
+// kFp8: the pages hold e4m3 bytes.  They are staged as they are (half the bytes per step) and
+// converted to f16 between ldmatrix and the MMA, which is exact; QT is the query / output type
+// (the query is converted to f16 for the MMA), T is then Fp16.  ldmatrix moves 16-bit units, so
+// a lane receives e4m3 pairs: for K four consecutive dims, used as (k 2j..2j+1 | k 2j+8..2j+9)
+// of one k-step -- a permutation of the reduction index that Q^T follows; for V^T two tokens x
+// two dims, unzipped by one byte permute into the rows of dims 16 c + 2g (rows g) and 16 c + 2g + 1
+// (rows g + 8) of the MMA for chunk c.  The K scale multiplies the scores, the V scale the output.
+constexpr int attn_ctas_per_sm(int dim, int column_tiles) {  // what registers and the ring allow
+  return dim > 128 ? (column_tiles == 1 ? 2 : 1) : (column_tiles == 1 ? KVX_ATTN_T_CTAS : 2);
+}
+
+template <typename T, int kD, typename IdxT, int kNt, bool kFp8 = false, typename QT = T>
+__global__ void __launch_bounds__(kAttnThreads, attn_ctas_per_sm(kD, kNt))
     kvx_attention_decode_t_kernel(const AttnParams p) {
   constexpr int kKs = kD / 16;          // k-steps of the score MMAs = 16-dim row tiles of the output
-  constexpr int kRowBytes = kD * 2;     // one token row of K or V
-  constexpr int kPitch = kRowBytes + 16;  // staged rows are 16 bytes apart from a multiple of 128:
+  constexpr int kRowBytes = kFp8 ? kD : kD * 2;  // one token row of K or V
+  constexpr int kPitch = kRowBytes + 16;  // staged rows are 16 bytes apart from a multiple of 64:
                                           // 8 consecutive rows then start in 8 different bank groups
-  constexpr int kChunks = kD / 8;       // 16-byte chunks per row
+  constexpr int kChunks = kRowBytes / 16;  // 16-byte chunks per row
   constexpr int kTile = 16 * kPitch;    // one staged 16-token step of K (or of V)
   constexpr int kPerLane = 16 * kChunks / 32;  // chunks of K (and of V) each lane copies per step
   extern __shared__ uint4 sm_dyn[];     // ring [warp][stage][K tile | V tile], then the chunk prefix
@@ -409,12 +435,19 @@ __global__ void __launch_bounds__(kAttnThreads, kNt == 1 ? KVX_ATTN_T_CTAS : 2)
       for (int kk = 0; kk < kKs; ++kk) {
         qb[nt][kk][0] = qb[nt][kk][1] = 0;
         if (8 * nt + g < G) {
-          const char *qrow = p.query + (q_row0 + 8 * nt + g) * kRowBytes;
-          qb[nt][kk][0] = *reinterpret_cast<const uint32_t *>(qrow + (16 * kk + 2 * j) * 2);
-          qb[nt][kk][1] = *reinterpret_cast<const uint32_t *>(qrow + (16 * kk + 8 + 2 * j) * 2);
+          const char *qrow = p.query + (q_row0 + 8 * nt + g) * (kD * 2);
+          if (kFp8) {  // dims 16 kk + 4j .. 4j+3, as f16 (see the note on the K operand above)
+            const uint2 q4 = *reinterpret_cast<const uint2 *>(qrow + (16 * kk + 4 * j) * 2);
+            qb[nt][kk][0] = QT::to_f16x2(q4.x);
+            qb[nt][kk][1] = QT::to_f16x2(q4.y);
+          } else {
+            qb[nt][kk][0] = *reinterpret_cast<const uint32_t *>(qrow + (16 * kk + 2 * j) * 2);
+            qb[nt][kk][1] = *reinterpret_cast<const uint32_t *>(qrow + (16 * kk + 8 + 2 * j) * 2);
+          }
         }
       }
     }
+    const float score_mul = kFp8 ? p.scale_log2 * p.ks.base[kvh * p.ks.stride] : p.scale_log2;
 
     // out^T: tile mt = dims 16 mt ..; c0, c1 = (dim g, heads 8 nt + 2j, + 1), c2, c3 = (dim g + 8, ..)
     float o[kNt][kKs][4];
@@ -486,19 +519,36 @@ __global__ void __launch_bounds__(kAttnThreads, kNt == 1 ? KVX_ATTN_T_CTAS : 2)
       float s[kNt][4];  // (token g, heads 8 nt + 2j, + 1), (token g + 8, same heads)
 #pragma unroll
       for (int nt = 0; nt < kNt; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+      if (kFp8) {
 #pragma unroll
-      for (int kk = 0; kk < kKs; ++kk) {
-        uint32_t a[4];
-        ldmatrix_x4(a, tile + lk_at + 32 * kk);
+        for (int cc = 0; cc < kKs / 2; ++cc) {  // one ldmatrix = chunks 2 cc and 2 cc + 1 = two k-steps
+          uint32_t r[4], a[4];
+          ldmatrix_x4(r, tile + lk_at + 32 * cc);
+          e4m3x4_to_f16x4(r[0], &a[0], &a[2]);
+          e4m3x4_to_f16x4(r[1], &a[1], &a[3]);
 #pragma unroll
-        for (int nt = 0; nt < kNt; ++nt) T::mma(s[nt], a[0], a[1], a[2], a[3], qb[nt][kk][0], qb[nt][kk][1]);
+          for (int nt = 0; nt < kNt; ++nt) T::mma(s[nt], a[0], a[1], a[2], a[3], qb[nt][2 * cc][0], qb[nt][2 * cc][1]);
+          e4m3x4_to_f16x4(r[2], &a[0], &a[2]);
+          e4m3x4_to_f16x4(r[3], &a[1], &a[3]);
+#pragma unroll
+          for (int nt = 0; nt < kNt; ++nt)
+            T::mma(s[nt], a[0], a[1], a[2], a[3], qb[nt][2 * cc + 1][0], qb[nt][2 * cc + 1][1]);
+        }
+      } else {
+#pragma unroll
+        for (int kk = 0; kk < kKs; ++kk) {
+          uint32_t a[4];
+          ldmatrix_x4(a, tile + lk_at + 32 * kk);
+#pragma unroll
+          for (int nt = 0; nt < kNt; ++nt) T::mma(s[nt], a[0], a[1], a[2], a[3], qb[nt][kk][0], qb[nt][kk][1]);
+        }
       }
       const int64_t left = cend - t0;
       uint32_t pb[kNt][2];  // P^T as B operand: (tokens 2j, 2j+1 | head g of the tile), (tokens 2j+8, 2j+9 | ..)
 #pragma unroll
       for (int nt = 0; nt < kNt; ++nt) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) s[nt][e] *= p.scale_log2;
+        for (int e = 0; e < 4; ++e) s[nt][e] *= score_mul;
         if (left < 16) {
           if (g >= left) s[nt][0] = s[nt][1] = -INFINITY;
           if (g + 8 >= left) s[nt][2] = s[nt][3] = -INFINITY;
@@ -532,12 +582,29 @@ __global__ void __launch_bounds__(kAttnThreads, kNt == 1 ? KVX_ATTN_T_CTAS : 2)
         pb[nt][0] = movmatrix_trans(T::pack2(p0, p1));
         pb[nt][1] = movmatrix_trans(T::pack2(p2, p3));
       }
+      if (kFp8) {
 #pragma unroll
-      for (int mt = 0; mt < kKs; ++mt) {
-        uint32_t a[4];
-        ldmatrix_x4_trans(a, tile + lv_at + 32 * mt);
+        for (int cc = 0; cc < kKs / 2; ++cc) {
+          // x[0], x[1] = tokens 0-7 of chunks 2 cc, 2 cc + 1; x[2], x[3] = tokens 8-15: each holds
+          // bytes (token 2j | dims d, d+1), (token 2j+1 | dims d, d+1) with d = 16 c + 2g
+          uint32_t x[4], a[4];
+          ldmatrix_x4_trans(x, tile + lv_at + 32 * cc);
 #pragma unroll
-        for (int nt = 0; nt < kNt; ++nt) T::mma(o[nt][mt], a[0], a[1], a[2], a[3], pb[nt][0], pb[nt][1]);
+          for (int half = 0; half < 2; ++half) {
+            e4m3x4_to_f16x4(__byte_perm(x[half], 0, 0x3120), &a[0], &a[1]);      // (d | tokens), (d + 1 | tokens)
+            e4m3x4_to_f16x4(__byte_perm(x[2 + half], 0, 0x3120), &a[2], &a[3]);  // the same for tokens 8-15
+#pragma unroll
+            for (int nt = 0; nt < kNt; ++nt) T::mma(o[nt][2 * cc + half], a[0], a[1], a[2], a[3], pb[nt][0], pb[nt][1]);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int mt = 0; mt < kKs; ++mt) {
+          uint32_t a[4];
+          ldmatrix_x4_trans(a, tile + lv_at + 32 * mt);
+#pragma unroll
+          for (int nt = 0; nt < kNt; ++nt) T::mma(o[nt][mt], a[0], a[1], a[2], a[3], pb[nt][0], pb[nt][1]);
+        }
       }
     }
     cp_async_wait<0>();
@@ -570,13 +637,15 @@ __global__ void __launch_bounds__(kAttnThreads, kNt == 1 ? KVX_ATTN_T_CTAS : 2)
       const float f0 = exp2_diff(m0[nt], M0), f1 = exp2_diff(m1[nt], M1);
 #pragma unroll
       for (int mt = 0; mt < kKs; ++mt) {
+        // rows g and g + 8 of output tile mt: dims 16 mt + g, + 8, or (fp8) 16 mt + 2g, + 1
+        const int d_lo = kFp8 ? 16 * mt + 2 * g : 16 * mt + g, d_hi = kFp8 ? d_lo + 1 : d_lo + 8;
         if (h0 < G) {
-          atomicAdd(&sm_o[h0][16 * mt + g], o[nt][mt][0] * f0);
-          atomicAdd(&sm_o[h0][16 * mt + g + 8], o[nt][mt][2] * f0);
+          atomicAdd(&sm_o[h0][d_lo], o[nt][mt][0] * f0);
+          atomicAdd(&sm_o[h0][d_hi], o[nt][mt][2] * f0);
         }
         if (h0 + 1 < G) {
-          atomicAdd(&sm_o[h0 + 1][16 * mt + g], o[nt][mt][1] * f1);
-          atomicAdd(&sm_o[h0 + 1][16 * mt + g + 8], o[nt][mt][3] * f1);
+          atomicAdd(&sm_o[h0 + 1][d_lo], o[nt][mt][1] * f1);
+          atomicAdd(&sm_o[h0 + 1][d_hi], o[nt][mt][3] * f1);
         }
       }
     }
@@ -588,10 +657,11 @@ __global__ void __launch_bounds__(kAttnThreads, kNt == 1 ? KVX_ATTN_T_CTAS : 2)
       for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, sm_m[w][row]);
 #pragma unroll
       for (int w = 0; w < kAttnWarps; ++w) L += sm_l[w][row] * exp2_diff(sm_m[w][row], M);
-      const float val = L > 0.f ? sm_o[row][d] / L : 0.f;
+      float val = L > 0.f ? sm_o[row][d] / L : 0.f;
+      if (kFp8) val *= p.vs.base[kvh * p.vs.stride];
       const int64_t q = q_row0 + row;
       if (p.splits == 1) {
-        reinterpret_cast<uint16_t *>(p.out)[q * kD + d] = T::round1(val);
+        reinterpret_cast<uint16_t *>(p.out)[q * kD + d] = QT::round1(val);
       } else {
         const int64_t at = q * p.splits + split;
         p.part_o[at * kD + d] = val;
@@ -785,25 +855,44 @@ bool dense3(const kvx_tensor_desc_t *t, int64_t a, int64_t b, int64_t c, kvx_sta
   return true;
 }
 
-template <typename T, int kD, typename IdxT>
+template <typename T, int kD, typename IdxT, bool kFp8, typename QT>
 void launch_t(const AttnParams &p, unsigned grid, size_t smem, cudaStream_t st) {
+  // (the attribute is per device and cheap to set, so it is set on every launch)
   if (p.group <= 8) {
-    cudaFuncSetAttribute(kvx_attention_decode_t_kernel<T, kD, IdxT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         static_cast<int>(smem));
-    kvx_attention_decode_t_kernel<T, kD, IdxT, 1><<<grid, kAttnThreads, smem, st>>>(p);
+    cudaFuncSetAttribute(kvx_attention_decode_t_kernel<T, kD, IdxT, 1, kFp8, QT>,
+                         cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    kvx_attention_decode_t_kernel<T, kD, IdxT, 1, kFp8, QT><<<grid, kAttnThreads, smem, st>>>(p);
   } else {
-    cudaFuncSetAttribute(kvx_attention_decode_t_kernel<T, kD, IdxT, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         static_cast<int>(smem));
-    kvx_attention_decode_t_kernel<T, kD, IdxT, 2><<<grid, kAttnThreads, smem, st>>>(p);
+    cudaFuncSetAttribute(kvx_attention_decode_t_kernel<T, kD, IdxT, 2, kFp8, QT>,
+                         cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    kvx_attention_decode_t_kernel<T, kD, IdxT, 2, kFp8, QT><<<grid, kAttnThreads, smem, st>>>(p);
   }
 }
 
-template <typename T, typename IdxT>
+// T = MMA operand type, QT = query / output type (they differ only for an fp8 cache).
+template <typename T, typename IdxT, bool kFp8, typename QT>
 void launch_t_dim(const AttnParams &p, unsigned grid, size_t smem, cudaStream_t st) {
-  if (p.dim == 128)
-    launch_t<T, 128, IdxT>(p, grid, smem, st);
+  if (p.dim == 256)
+    launch_t<T, 256, IdxT, kFp8, QT>(p, grid, smem, st);
+  else if (p.dim == 128)
+    launch_t<T, 128, IdxT, kFp8, QT>(p, grid, smem, st);
   else
-    launch_t<T, 64, IdxT>(p, grid, smem, st);
+    launch_t<T, 64, IdxT, kFp8, QT>(p, grid, smem, st);
+}
+
+template <typename IdxT>
+void launch_t_types(const AttnParams &p, kvx_dtype_t cache, kvx_dtype_t io, unsigned grid, size_t smem,
+                    cudaStream_t st) {
+  if (cache == KVX_DTYPE_F8_E4M3) {
+    if (io == KVX_DTYPE_BF16)
+      launch_t_dim<Fp16, IdxT, true, Bf16>(p, grid, smem, st);
+    else
+      launch_t_dim<Fp16, IdxT, true, Fp16>(p, grid, smem, st);
+  } else if (cache == KVX_DTYPE_BF16) {
+    launch_t_dim<Bf16, IdxT, false, Bf16>(p, grid, smem, st);
+  } else {
+    launch_t_dim<Fp16, IdxT, false, Fp16>(p, grid, smem, st);
+  }
 }
 
 // SM count of the current device, looked up once per device.
@@ -907,9 +996,10 @@ KVX_API kvx_status_t kvx_launch_paged_attention_decode(const kvx_cache_desc_t *c
   p.splits = static_cast<int32_t>((static_cast<int64_t>(attn->max_seq_len) + p.chunk - 1) / p.chunk);
   const cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
 
-  const bool fast = (cd == KVX_DTYPE_BF16 || cd == KVX_DTYPE_F16) && (D == 64 || D == 128) &&
-                    cache->block_size % 16 == 0 && p.group <= 16 && view_rows16(p.k, elem) && view_rows16(p.v, elem) &&
-                    aligned16(p.query) && H <= 65535 && S <= 65535;
+  const bool fp8 = cd == KVX_DTYPE_F8_E4M3;
+  const bool fast = (cd == KVX_DTYPE_BF16 || cd == KVX_DTYPE_F16 || (fp8 && io != KVX_DTYPE_F32)) &&
+                    (D == 64 || D == 128 || D == 256) && cache->block_size % 16 == 0 && p.group <= 16 && view_rows16(p.k, elem) &&
+                    view_rows16(p.v, elem) && aligned16(p.query) && H <= 65535 && S <= 65535;
   if (fast) {
     const size_t need = kvx_paged_attention_workspace_bytes(static_cast<uint32_t>(S), static_cast<uint32_t>(Hq),
                                                             static_cast<uint32_t>(H), static_cast<uint32_t>(D),
@@ -921,9 +1011,9 @@ KVX_API kvx_status_t kvx_launch_paged_attention_decode(const kvx_cache_desc_t *c
       p.part_ml = p.part_o + S * Hq * p.splits * D;
     }
     p.use_prefix = S <= kMaxPrefixSeqs ? 1 : 0;
-    const int per_sm = p.group <= 8 ? KVX_ATTN_T_CTAS : 2;  // the kernels' launch bounds
+    const int per_sm = attn_ctas_per_sm(static_cast<int>(D), p.group <= 8 ? 1 : 2);  // the kernels' launch bounds
     // K and V steps of 16 rows, each row padded by 16 bytes
-    const size_t ring = static_cast<size_t>(kAttnWarps) * kTStages * 2 * 16 * (D * 2 + 16);
+    const size_t ring = static_cast<size_t>(kAttnWarps) * kTStages * 2 * 16 * (D * elem + 16);
     const size_t smem = ring + (p.use_prefix ? static_cast<size_t>(S + 1) * sizeof(int32_t) : 0);
     const int64_t most = S * p.splits * H;  // work items if every context had max_seq_len tokens
     const int64_t grid = std::max<int64_t>(1, std::min<int64_t>(most, static_cast<int64_t>(sm_count()) * per_sm));
@@ -931,17 +1021,10 @@ KVX_API kvx_status_t kvx_launch_paged_attention_decode(const kvx_cache_desc_t *c
       p.counter = nullptr;  // every possible item has its own CTA: nothing to balance, no counter to clear
     else if (cudaMemsetAsync(p.counter, 0, kCounterBytes, cs) != cudaSuccess)
       return KVX_STATUS_INTERNAL_ERROR;
-    if (cd == KVX_DTYPE_BF16) {
-      if (s32)
-        launch_t_dim<Bf16, int32_t>(p, static_cast<unsigned>(grid), smem, cs);
-      else
-        launch_t_dim<Bf16, int64_t>(p, static_cast<unsigned>(grid), smem, cs);
-    } else {
-      if (s32)
-        launch_t_dim<Fp16, int32_t>(p, static_cast<unsigned>(grid), smem, cs);
-      else
-        launch_t_dim<Fp16, int64_t>(p, static_cast<unsigned>(grid), smem, cs);
-    }
+    if (s32)
+      launch_t_types<int32_t>(p, cd, io, static_cast<unsigned>(grid), smem, cs);
+    else
+      launch_t_types<int64_t>(p, cd, io, static_cast<unsigned>(grid), smem, cs);
     if (p.splits > 1) {
       if (s32)
         kvx_attention_merge_kernel<int32_t><<<static_cast<unsigned>(S * Hq), 128, 0, cs>>>(p, io);

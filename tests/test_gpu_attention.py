@@ -82,7 +82,7 @@ def check(case, k, v, group, **kw):
 @pytest.mark.parametrize("dtype", [abi.DTYPE_BF16, abi.DTYPE_F16])
 @pytest.mark.parametrize("layout", [abi.LAYOUT_NHD, abi.LAYOUT_HND])
 def test_fast_tier_shapes(layout, dtype):
-    """Tensor-core tier: head_dim 64 / 128, pages of 16 / 32 tokens, 1..16 query heads per KV
+    """Tensor-core tier: head_dim 64 / 128 / 256, pages of 16 / 32 / 64 tokens, 1..16 query heads per KV
     head, empty / one-token / page-edge / long contexts, invalid page ids, both index widths."""
     for i, kw in enumerate([
         dict(heads=2, dim=128, block_size=16, num_blocks=80, lens=[100, 17, 256, 1, 0, 333, 16, 15], group=4),
@@ -90,6 +90,8 @@ def test_fast_tier_shapes(layout, dtype):
         dict(heads=1, dim=128, block_size=16, num_blocks=64, lens=[500, 3], group=8, bad_blocks=3),
         dict(heads=2, dim=64, block_size=16, num_blocks=32, lens=[47, 200], group=16),
         dict(heads=1, dim=128, block_size=64, num_blocks=12, lens=[130, 400], group=12),
+        dict(heads=2, dim=256, block_size=16, num_blocks=60, lens=[130, 400, 1], group=4),
+        dict(heads=1, dim=256, block_size=32, num_blocks=20, lens=[99, 300], group=9),
     ]):
         group = kw.pop("group")
         case = cases.make_case(2000 + i, layout=layout, dtype=dtype, real_values=True, **kw)
@@ -123,6 +125,28 @@ def test_more_sequences_than_the_shared_memory_prefix_holds():
         check(case, k, v, group)
 
 
+@pytest.mark.parametrize("dtype", [abi.DTYPE_BF16, abi.DTYPE_F16])
+@pytest.mark.parametrize("layout", [abi.LAYOUT_NHD, abi.LAYOUT_HND])
+def test_fp8_cache_fast_tier(layout, dtype):
+    """e4m3 pages under the tensor-core tier: bytes are staged as they are and converted to f16
+    between ldmatrix and the MMA; K scale on the scores, V scale on the output; per-head and
+    per-tensor scales, one and two column tiles of query heads, split contexts."""
+    for i, (kw, group, gran) in enumerate([
+        (dict(heads=2, dim=128, block_size=16, num_blocks=80, lens=[100, 17, 256, 1, 0, 333, 16, 15]), 4, abi.SCALE_PER_HEAD),
+        (dict(heads=4, dim=64, block_size=32, num_blocks=40, lens=[31, 33, 160, 64], index_dtype=np.int64), 1,
+         abi.SCALE_PER_TENSOR),
+        (dict(heads=1, dim=128, block_size=64, num_blocks=12, lens=[130, 400], bad_blocks=1), 12, abi.SCALE_PER_HEAD),
+        (dict(heads=2, dim=128, block_size=16, num_blocks=400, lens=[3000, 700, 2049]), 8, abi.SCALE_PER_HEAD),
+        (dict(heads=2, dim=256, block_size=64, num_blocks=24, lens=[300, 5, 640]), 4, abi.SCALE_PER_HEAD),
+        (dict(heads=1, dim=256, block_size=16, num_blocks=40, lens=[200, 77]), 16, abi.SCALE_PER_TENSOR),
+    ]):
+        case = cases.make_case(2500 + i, layout=layout, dtype=dtype, cache_dtype=abi.DTYPE_F8_E4M3, scale_gran=gran,
+                               real_values=True, **kw)
+        case.note = f"fp8 fast {i}"
+        _, k, v = oracle_write(case)
+        check(case, k, v, group, seed=i)
+
+
 def test_generic_tier_shapes():
     """Everything the tensor-core tier does not take: f32 data, odd head_dim, small pages,
     HND_PACKED pages, an fp8-e4m3 cache with per-head scales."""
@@ -132,7 +156,7 @@ def test_generic_tier_shapes():
         (abi.DTYPE_F16, dict(heads=2, dim=64, block_size=8, num_blocks=200, lens=[50, 70, 1200]), 4),
         (abi.DTYPE_BF16, dict(heads=2, dim=64, block_size=16, num_blocks=24, lens=[50, 70], layout=abi.LAYOUT_HND_PACKED,
                               pack=8), 1),
-        (abi.DTYPE_BF16, dict(heads=4, dim=128, block_size=16, num_blocks=24, lens=[100, 40, 7],
+        (abi.DTYPE_BF16, dict(heads=4, dim=80, block_size=16, num_blocks=24, lens=[100, 40, 7],
                               cache_dtype=abi.DTYPE_F8_E4M3, scale_gran=abi.SCALE_PER_HEAD), 2),
     ]):
         case = cases.make_case(2200 + i, dtype=dtype, real_values=True, **kw)
