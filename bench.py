@@ -271,7 +271,7 @@ def main() -> None:
         e2e = run_e2e(args, dw, dist)
 
     attention = None
-    if world == 1 and not args.no_attention and spec.cache_dtype in ("bf16", "f16"):
+    if world == 1 and not args.no_attention:
         attention = run_attention(dw, min(args.steps, 3))
 
     if rank != 0:
@@ -349,11 +349,12 @@ def run_attention(dw, steps: int, group: int = 4) -> dict:
     a = abi.attention_desc(S, H * group, D, bs.DTYPE_CODE[spec.io_dtype], q.data_ptr(), out.data_ptr(), D ** -0.5,
                            m.max_seq_len, abi.DTYPE_S32, dw.table.data_ptr(), m.table.shape[1], dw.lens.data_ptr())
     none = abi.scale_desc(None, abi.SCALE_NONE, H)
+    ks, vs = (dw.ks_desc, dw.vs_desc) if dw.ks_desc is not None else (none, none)  # fp8 cache: per-head scales
     stream = torch.cuda.current_stream().cuda_stream
 
     def step():
         for l in range(dw.layers):
-            st = L.kvx_launch_paged_attention_decode(C.byref(dw.caches[l]), C.byref(a), C.byref(none), C.byref(none),
+            st = L.kvx_launch_paged_attention_decode(C.byref(dw.caches[l]), C.byref(a), C.byref(ks), C.byref(vs),
                                                      ws.data_ptr(), need, stream)
             if st != abi.STATUS_OK:
                 raise RuntimeError(f"kvx_launch_paged_attention_decode status {st}")
