@@ -26,6 +26,8 @@
  */
 #include "kvx_attention.h"
 
+#include "kvx_pages.h"
+
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -39,53 +41,10 @@ namespace {
 
 // ------------------------------------------------------------------ page addressing ----
 
-// A page tensor with its axes renamed (block, token-in-block, head, dim), strides in BYTES:
-// element (b, o, h, d) sits at b*blk + o*tok + h*head + (d / pack)*dhi + (d % pack)*dlo.
-struct PageView {
-  const char *base;
-  int64_t blk, tok, head, dhi, dlo;
-  int32_t pack;
-};
-
-int64_t dtype_bytes(kvx_dtype_t t) {
-  switch (t) {
-    case KVX_DTYPE_F16:
-    case KVX_DTYPE_BF16:
-      return 2;
-    case KVX_DTYPE_F32:
-      return 4;
-    case KVX_DTYPE_F8_E4M3:
-      return 1;
-    default:
-      return 0;
-  }
-}
-
-kvx_status_t make_page_view(const kvx_cache_desc_t *c, const kvx_tensor_desc_t *t, int64_t elem, PageView *out) {
-  const int64_t *s = t->stride;
-  out->base = static_cast<const char *>(t->data);
-  out->pack = 1;
-  out->dlo = 0;
-  switch (t->layout) {
-    case KVX_LAYOUT_BLOCK_NHD:
-      out->blk = s[0] * elem, out->tok = s[1] * elem, out->head = s[2] * elem, out->dhi = s[3] * elem;
-      return KVX_STATUS_OK;
-    case KVX_LAYOUT_BLOCK_HND:
-      out->blk = s[0] * elem, out->head = s[1] * elem, out->tok = s[2] * elem, out->dhi = s[3] * elem;
-      return KVX_STATUS_OK;
-    case KVX_LAYOUT_BLOCK_HND_PACKED: {
-      const int64_t pack = t->shape[4];
-      if (pack <= 0 || (static_cast<int64_t>(c->head_dim) % pack) != 0 || pack > INT32_MAX)
-        return KVX_STATUS_INVALID_ARGUMENT;
-      out->blk = s[0] * elem, out->head = s[1] * elem, out->dhi = s[2] * elem, out->tok = s[3] * elem;
-      out->dlo = s[4] * elem;
-      out->pack = static_cast<int32_t>(pack);
-      return KVX_STATUS_OK;
-    }
-    default:
-      return KVX_STATUS_UNSUPPORTED;
-  }
-}
+using kvx_detail::PageView;
+using kvx_detail::ScaleView;
+using kvx_detail::dtype_bytes;
+using kvx_detail::make_page_view;
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
@@ -93,25 +52,6 @@ bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 bool view_rows16(const PageView &v, int64_t elem) {
   return v.pack == 1 && v.dhi == elem && aligned16(v.base) && v.blk % 16 == 0 && v.tok % 16 == 0 &&
          v.head % 16 == 0 && v.blk >= 0 && v.tok >= 0 && v.head >= 0;
-}
-
-struct ScaleView {
-  const float *base;  // NULL = no scale (not an fp8 cache)
-  int64_t stride;     // elements between heads (0 = one scale for all)
-};
-
-bool resolve_scale(const kvx_scale_desc_t *d, uint32_t heads, ScaleView *out) {
-  if (d == nullptr || d->size < sizeof(kvx_scale_desc_t) || d->data == nullptr || d->dtype != KVX_DTYPE_F32)
-    return false;
-  if (d->granularity == KVX_SCALE_PER_TENSOR) {
-    *out = ScaleView{static_cast<const float *>(d->data), 0};
-    return true;
-  }
-  if (d->granularity == KVX_SCALE_PER_HEAD && d->ndim == 1 && d->shape[0] == static_cast<int64_t>(heads)) {
-    *out = ScaleView{static_cast<const float *>(d->data), d->stride[0]};
-    return true;
-  }
-  return false;
 }
 
 // ------------------------------------------------------------------ parameters ---------
@@ -947,7 +887,8 @@ KVX_API kvx_status_t kvx_launch_paged_attention_decode(const kvx_cache_desc_t *c
   p.ks = ScaleView{nullptr, 0};
   p.vs = ScaleView{nullptr, 0};
   if (cd == KVX_DTYPE_F8_E4M3) {
-    if (!resolve_scale(k_scale, cache->num_kv_heads, &p.ks) || !resolve_scale(v_scale, cache->num_kv_heads, &p.vs))
+    if (!kvx_detail::resolve_scale(k_scale, nullptr, cache->num_kv_heads, &p.ks) ||
+        !kvx_detail::resolve_scale(v_scale, nullptr, cache->num_kv_heads, &p.vs))
       return KVX_STATUS_UNSUPPORTED;
   } else if (cd != io) {
     return KVX_STATUS_UNSUPPORTED;

@@ -28,6 +28,8 @@
  */
 #include "kvx_paged_kv.h"
 
+#include "kvx_pages.h"
+
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -106,64 +108,16 @@ const DeviceInfo &device_info() {
 
 // ------------------------------------------------------------------ geometry ----------
 
-// A page tensor with its axes renamed (block, token-in-block, head, dim) whatever the
-// layout, strides in BYTES.  The offset of element (b, o, h, d) is
-//   b*blk + o*tok + h*head + (d / pack)*dhi + (d % pack)*dlo
-// which restates the reference's per-layout switch (kernels/kvx_paged_kv.cu:54-75):
-//   NHD        strides (s0,s1,s2,s3)     -> blk=s0 tok=s1 head=s2 dhi=s3 pack=1
-//   HND        strides (s0,s1,s2,s3)     -> blk=s0 head=s1 tok=s2 dhi=s3 pack=1
-//   HND_PACKED strides (s0,s1,s2,s3,s4)  -> blk=s0 head=s1 dhi=s2 tok=s3 dlo=s4 pack=shape[4]
-struct PageView {
-  char *base;
-  int64_t blk, tok, head, dhi, dlo;
-  int32_t pack;
-};
+using kvx_detail::PageView;
+using kvx_detail::ScaleView;
+using kvx_detail::dtype_bytes;
+using kvx_detail::make_page_view;
+using kvx_detail::resolve_scale;
 
 struct Geometry {
   int32_t num_blocks, block_size, heads, dim;
   int32_t elem;  // bytes per cache element
 };
-
-kvx_status_t make_page_view(const kvx_cache_desc_t *c, const kvx_tensor_desc_t *t, int64_t elem,
-                            PageView *out) {
-  const int64_t *s = t->stride;
-  out->base = static_cast<char *>(t->data);
-  out->pack = 1;
-  out->dlo = 0;
-  switch (t->layout) {
-    case KVX_LAYOUT_BLOCK_NHD:
-      out->blk = s[0] * elem, out->tok = s[1] * elem, out->head = s[2] * elem, out->dhi = s[3] * elem;
-      return KVX_STATUS_OK;
-    case KVX_LAYOUT_BLOCK_HND:
-      out->blk = s[0] * elem, out->head = s[1] * elem, out->tok = s[2] * elem, out->dhi = s[3] * elem;
-      return KVX_STATUS_OK;
-    case KVX_LAYOUT_BLOCK_HND_PACKED: {
-      const int64_t pack = t->shape[4];
-      if (pack <= 0 || (static_cast<int64_t>(c->head_dim) % pack) != 0 || pack > INT32_MAX)
-        return KVX_STATUS_INVALID_ARGUMENT;
-      out->blk = s[0] * elem, out->head = s[1] * elem, out->dhi = s[2] * elem, out->tok = s[3] * elem;
-      out->dlo = s[4] * elem;
-      out->pack = static_cast<int32_t>(pack);
-      return KVX_STATUS_OK;
-    }
-    default:
-      return KVX_STATUS_UNSUPPORTED;
-  }
-}
-
-int64_t dtype_bytes(kvx_dtype_t t) {
-  switch (t) {
-    case KVX_DTYPE_F16:
-    case KVX_DTYPE_BF16:
-      return 2;
-    case KVX_DTYPE_F32:
-      return 4;
-    case KVX_DTYPE_F8_E4M3:
-      return 1;
-    default:
-      return 0;
-  }
-}
 
 bool aligned(const void *p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 bool is_pow2(int64_t v) { return v > 0 && (v & (v - 1)) == 0; }
@@ -549,11 +503,6 @@ __device__ __forceinline__ uint4 dequant_vec(uint2 q, float scale, IoT) {
     return make_uint4(o[0], o[1], o[2], o[3]);
   }
 }
-
-struct ScaleView {
-  const float *base;  // device
-  int64_t stride;     // elements between heads; 0 = one scale per tensor
-};
 
 // ------------------------------------------------------------------ write: fp8 vector --
 
@@ -1607,26 +1556,6 @@ kvx_status_t check_write_rows(const kvx_tensor_desc_t *t, const int64_t *dims) {
     if (t->shape[i] != dims[i]) return KVX_STATUS_INVALID_ARGUMENT;
   if (t->stride[2] != 1 || t->stride[1] != dims[2] || t->stride[0] < dims[1] * dims[2]) return KVX_STATUS_UNSUPPORTED;
   return KVX_STATUS_OK;
-}
-
-bool resolve_scale(const kvx_scale_desc_t *d, const void *scalar, uint32_t heads, ScaleView *out) {
-  if (d != nullptr && d->size >= sizeof(kvx_scale_desc_t) && d->data != nullptr) {
-    if (d->dtype != KVX_DTYPE_F32) return false;
-    if (d->granularity == KVX_SCALE_PER_TENSOR) {
-      *out = ScaleView{static_cast<const float *>(d->data), 0};
-      return true;
-    }
-    if (d->granularity == KVX_SCALE_PER_HEAD && d->ndim == 1 && d->shape[0] == static_cast<int64_t>(heads)) {
-      *out = ScaleView{static_cast<const float *>(d->data), d->stride[0]};
-      return true;
-    }
-    return false;
-  }
-  if (scalar != nullptr) {
-    *out = ScaleView{static_cast<const float *>(scalar), 0};
-    return true;
-  }
-  return false;
 }
 
 bool io_dtype_quantisable(kvx_dtype_t t) {

@@ -247,3 +247,20 @@ def test_torch_operator_library_registers_its_operators(built_lib):
     gather = native.gather_kv.default._schema
     assert [a.name for a in gather.arguments][:6] == ["key_cache", "value_cache", "block_table", "seq_lens",
                                                        "key_out", "value_out"]
+
+
+def test_single_source_build_as_in_the_vllm_patch(tmp_path):
+    """The reference's vLLM patch compiles <root>/kernels/kvx_paged_kv.cu as ONE source file with
+    <root> and <root>/kernels on the include path and nothing else from this project
+    (patches/vllm/kvx.patch:25-32, :43, :53).  The forwarding files must keep that working."""
+    import shutil
+    import subprocess
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        pytest.skip("nvcc not available")
+    out = tmp_path / "kvx_paged_kv.o"
+    cmd = [nvcc, "-std=c++17", "-O1", "-gencode", "arch=compute_100a,code=sm_100a", "-I" + ROOT,
+           "-I" + os.path.join(ROOT, "kernels"), "-c", os.path.join(ROOT, "kernels", "kvx_paged_kv.cu"), "-o", str(out)]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert out.stat().st_size > 0
