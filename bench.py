@@ -52,6 +52,7 @@ def parse_args():
     ap.add_argument("--seqs", type=int, default=None, help="override the number of sequences (small profiling cases)")
     ap.add_argument("--e2e-steps", type=int, default=None, help="steps of the host-buffer leg (default: min(steps, 3))")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--e2e-chunk-mb", type=int, default=64, help="staging chunk of the host-buffer pipeline")
     ap.add_argument("--no-attention", action="store_true", help="skip the informational fused decode-attention leg")
     ap.add_argument("--only-attention", action="store_true",
                     help="fill the pages with one write per layer, time only the fused decode attention and print its "
@@ -397,7 +398,7 @@ def run_e2e(args, dw, dist) -> dict:
     hok = torch.empty(dw.out_k.shape, dtype=dw.out_k.dtype).pin_memory()
     hov = torch.empty(dw.out_v.shape, dtype=dw.out_v.dtype).pin_memory()
     seq_bytes = dw.out_k[0].numel() * dw.out_k.element_size()
-    chunk = max(64 << 20, seq_bytes)
+    chunk = max(args.e2e_chunk_mb << 20, seq_bytes)
     pipe = C.c_void_p()
     st = L.kvx_host_pipe_create(chunk, spec.seqs, meta.table.shape[1], C.byref(pipe))
     if st != abi.STATUS_OK:
