@@ -174,20 +174,18 @@ struct WorkItem {
   int64_t begin, end;  // token range of the chunk; empty for a chunk the sequence does not have
 };
 
-// The CTA's next item.  With a counter, CTAs claim items as they become free; without one (few
-// items: one per CTA) they stride over the list.  Contains a barrier, which also separates the
-// previous item's use of shared buffers from the next one's.
+// Claiming the CTA's next item (one thread does it).  With a counter, CTAs claim items as they
+// become free; without one (few items: one per CTA) they stride over the list.
+__device__ __forceinline__ unsigned long long claim_item(const AttnParams &p, unsigned long long *round) {
+  const unsigned long long r = (*round)++;
+  return p.counter != nullptr ? atomicAdd(p.counter, 1ull) : blockIdx.x + r * static_cast<unsigned long long>(gridDim.x);
+}
+
+// (sequence, chunk, KV head) and token range of item `item` of the work list.
 template <typename IdxT>
-__device__ bool next_item(const AttnParams &p, int64_t items, unsigned long long *round,
-                          unsigned long long *sm_item, const int32_t *sm_prefix, WorkItem *w) {
-  if (threadIdx.x == 0)
-    *sm_item = p.counter != nullptr ? atomicAdd(p.counter, 1ull)
-                                    : blockIdx.x + *round * static_cast<unsigned long long>(gridDim.x);
-  ++*round;
-  __syncthreads();
-  const int64_t item = static_cast<int64_t>(*sm_item);
-  if (item >= items) return false;
-  w->kvh = static_cast<int>(item % p.heads_kv);
+__device__ __forceinline__ WorkItem locate_item(const AttnParams &p, int64_t item, const int32_t *sm_prefix) {
+  WorkItem w;
+  w.kvh = static_cast<int>(item % p.heads_kv);
   const int64_t ci = item / p.heads_kv;
   if (p.use_prefix) {
     int lo = 0, hi = p.seq_count;  // last s with prefix[s] <= ci
@@ -198,17 +196,17 @@ __device__ bool next_item(const AttnParams &p, int64_t items, unsigned long long
       else
         hi = mid;
     }
-    w->seq = lo;
-    w->split = static_cast<int>(ci - sm_prefix[lo]);
+    w.seq = lo;
+    w.split = static_cast<int>(ci - sm_prefix[lo]);
   } else {
-    w->seq = static_cast<int>(ci / p.splits);
-    w->split = static_cast<int>(ci - static_cast<int64_t>(w->seq) * p.splits);
+    w.seq = static_cast<int>(ci / p.splits);
+    w.split = static_cast<int>(ci - static_cast<int64_t>(w.seq) * p.splits);
   }
-  int64_t len = read_idx<IdxT>(p.lens, w->seq);
+  int64_t len = read_idx<IdxT>(p.lens, w.seq);
   if (len > p.max_seq_len) len = p.max_seq_len;
-  w->begin = static_cast<int64_t>(w->split) * p.chunk;
-  w->end = min(len, w->begin + p.chunk);
-  return true;
+  w.begin = static_cast<int64_t>(w.split) * p.chunk;
+  w.end = min(len, w.begin + p.chunk);
+  return w;
 }
 
 // A sequence without cached tokens has no work item; its output is defined as zero.  With more
@@ -331,7 +329,7 @@ __global__ void __launch_bounds__(kAttnThreads, attn_ctas_per_sm(kD, kNt))
   __shared__ float sm_l[kAttnWarps][8 * kNt];
   __shared__ int32_t sm_page[kAttnWarps][kTStages];
   __shared__ int32_t sm_scan[kAttnThreads];
-  __shared__ unsigned long long sm_item;
+  __shared__ unsigned long long sm_item[2];  // this item and the next, claimed one item ahead
   char *ring = reinterpret_cast<char *>(sm_dyn);
   // merge buffer of the epilogue: lives in the ring, which is idle by then
   float (*sm_o)[kD + 8] = reinterpret_cast<float (*)[kD + 8]>(ring);  // [8 * kNt][kD + 8]
@@ -359,9 +357,13 @@ __global__ void __launch_bounds__(kAttnThreads, attn_ctas_per_sm(kD, kNt))
   // ldmatrix.trans (V^T as A operand): matrix i -> tokens 8 (i >> 1) + lane % 8, chunk 2 mt + (i & 1)
   const uint32_t lv_at = kTile + ((lane & 7) + 8 * (lane >> 4)) * kPitch + ((lane >> 3) & 1) * 16;
 
-  for (unsigned long long round = 0;;) {
-    WorkItem w;
-    if (!next_item<IdxT>(p, items, &round, &sm_item, sm_prefix, &w)) break;
+  unsigned long long round = 0;
+  if (threadIdx.x == 0) sm_item[0] = claim_item(p, &round);
+  __syncthreads();
+  for (int parity = 0;; parity ^= 1) {
+    const int64_t item = static_cast<int64_t>(sm_item[parity]);
+    if (item >= items) break;
+    const WorkItem w = locate_item<IdxT>(p, item, sm_prefix);
     const int seq = w.seq, split = w.split, kvh = w.kvh;
     const int64_t cbeg = w.begin, cend = w.end;
     const int64_t q_row0 = static_cast<int64_t>(seq) * p.heads_q + static_cast<int64_t>(kvh) * G;
@@ -447,6 +449,9 @@ __global__ void __launch_bounds__(kAttnThreads, attn_ctas_per_sm(kD, kNt))
 
 #pragma unroll
     for (int i = 0; i < kTStages - 1; ++i) issue(i);
+    // The next item is claimed now, behind this item's first loads, so that the round trip of
+    // the atomic is off the path between two items.
+    if (threadIdx.x == 0) sm_item[parity ^ 1] = claim_item(p, &round);
     for (int i = 0; i < mine; ++i) {
       issue(i + kTStages - 1);
       cp_async_wait<kTStages - 1>();
@@ -611,7 +616,7 @@ __global__ void __launch_bounds__(kAttnThreads, attn_ctas_per_sm(kD, kNt))
         }
       }
     }
-    // (next_item's barrier comes before the merge buffers and sm_item are reused)
+    __syncthreads();  // the next item's id is visible; merge buffers and the ring are free again
   }
 }
 
