@@ -51,11 +51,17 @@ def build(force: bool = False, verbose: bool = False) -> str:
     run = lambda cmd: subprocess.run(cmd, check=True, stdout=None if verbose else subprocess.PIPE,
                                      stderr=subprocess.STDOUT)
     run(["gcc", "-std=c11", "-O2", "-fPIC", "-Wall", "-I" + INCLUDE, "-c", c_src, "-o", c_obj])
-    objs = []
+    # the translation units are independent: compile them side by side
+    objs, jobs = [], []
     for src in cu:
         obj = os.path.join(BUILD_DIR, os.path.basename(src) + ".o")
-        run([_nvcc(), *NVCC_FLAGS, "-c", src, "-o", obj])
+        jobs.append((src, subprocess.Popen([_nvcc(), *NVCC_FLAGS, "-c", src, "-o", obj],
+                                           stdout=None if verbose else subprocess.PIPE, stderr=subprocess.STDOUT)))
         objs.append(obj)
+    for src, job in jobs:
+        out, _ = job.communicate()
+        if job.returncode != 0:
+            raise RuntimeError(f"nvcc failed on {src}:\n" + (out.decode(errors="replace") if out else ""))
     run([_nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", *objs, c_obj, "-o", LIB_PATH])
     return LIB_PATH
 
