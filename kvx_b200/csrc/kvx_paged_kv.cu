@@ -506,6 +506,9 @@ __device__ __forceinline__ uint4 dequant_vec(uint2 q, float scale, IoT) {
 
 // ------------------------------------------------------------------ write: fp8 vector --
 
+#ifndef KVX_F8_WRITE_UNROLL
+#define KVX_F8_WRITE_UNROLL 2  // input vectors of K and of V in flight per thread
+#endif
 constexpr int kF8CachedHeads = 128;
 
 struct WriteF8Params {
@@ -517,7 +520,7 @@ struct WriteF8Params {
 
 // Same token tiling as kvx_write_rows_kernel; each 16-byte input vector (8 or 4 elements,
 // all of one head) becomes 8 or 4 cache bytes.
-template <typename IoT, typename SlotT, int kUnroll>
+template <typename IoT, typename SlotT, int kUnroll, bool kPitched = false>
 __global__ void __launch_bounds__(kWriteThreads) kvx_write_f8_kernel(const WriteF8Params q) {
   pdl_prologue();
   constexpr int kPer = ElemTraits<IoT>::per_vec;
@@ -553,8 +556,8 @@ __global__ void __launch_bounds__(kWriteThreads) kvx_write_f8_kernel(const Write
   }
   __syncthreads();
 
-  const char *ksrc = p.key + tok0 * p.k_pitch;
-  const char *vsrc = p.value + tok0 * p.v_pitch;
+  const char *ksrc = p.key + tok0 * (kPitched ? p.k_pitch : p.row_bytes);
+  const char *vsrc = p.value + tok0 * (kPitched ? p.v_pitch : p.row_bytes);
   const int nvec = ntok * p.vpr;
   for (int f0 = tid; f0 < nvec; f0 += kWriteThreads * kUnroll) {
     uint4 kr[kUnroll], vr[kUnroll];
@@ -574,8 +577,13 @@ __global__ void __launch_bounds__(kWriteThreads) kvx_write_f8_kernel(const Write
           hh[u] = h;
           kd[u] = ko + h * p.k_head + w;
           vd[u] = s_v[tok] + h * p.v_head + w;
-          kr[u] = load_stream(ksrc + tok * p.k_pitch + static_cast<int64_t>(v) * 16);  // pitch = row when dense
-          vr[u] = load_stream(vsrc + tok * p.v_pitch + static_cast<int64_t>(v) * 16);
+          if (kPitched) {
+            kr[u] = load_stream(ksrc + tok * p.k_pitch + static_cast<int64_t>(v) * 16);
+            vr[u] = load_stream(vsrc + tok * p.v_pitch + static_cast<int64_t>(v) * 16);
+          } else {
+            kr[u] = load_stream(ksrc + static_cast<int64_t>(f) * 16);
+            vr[u] = load_stream(vsrc + static_cast<int64_t>(f) * 16);
+          }
         }
       }
     }
@@ -1735,12 +1743,18 @@ kvx_status_t write_impl(const kvx_cache_desc_t *cache, const kvx_write_desc_t *w
     const int unroll = static_cast<int>(g_opt.write_unroll);
     if (fp8) {
       WriteF8Params q{p, ks, vs, static_cast<int32_t>(D), static_cast<int32_t>(H)};
-#define KVX_F8_WRITE(IoT)                                                                  \
-  do {                                                                                     \
-    if (s32)                                                                               \
-      launch_streaming(kvx_write_f8_kernel<IoT, int32_t, 2>, grid, kWriteThreads, 0, cs, q);             \
-    else                                                                                   \
-      launch_streaming(kvx_write_f8_kernel<IoT, int64_t, 2>, grid, kWriteThreads, 0, cs, q);             \
+#define KVX_F8_WRITE(IoT)                                                                                     \
+  do {                                                                                                        \
+    if (pitched) {                                                                                            \
+      if (s32)                                                                                                \
+        launch_streaming(kvx_write_f8_kernel<IoT, int32_t, KVX_F8_WRITE_UNROLL, true>, grid, kWriteThreads, 0, cs, q); \
+      else                                                                                                    \
+        launch_streaming(kvx_write_f8_kernel<IoT, int64_t, KVX_F8_WRITE_UNROLL, true>, grid, kWriteThreads, 0, cs, q); \
+    } else if (s32) {                                                                                         \
+      launch_streaming(kvx_write_f8_kernel<IoT, int32_t, KVX_F8_WRITE_UNROLL>, grid, kWriteThreads, 0, cs, q); \
+    } else {                                                                                                  \
+      launch_streaming(kvx_write_f8_kernel<IoT, int64_t, KVX_F8_WRITE_UNROLL>, grid, kWriteThreads, 0, cs, q); \
+    }                                                                                                         \
   } while (0)
       if (io_dtype == KVX_DTYPE_BF16)
         KVX_F8_WRITE(BF16);
