@@ -385,6 +385,19 @@ __device__ __forceinline__ uint32_t quant2_fast(float lo, float hi, float s, flo
   asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(c) : "f"(qhi), "f"(qlo));
   return c;
 }
+// The same without the sign copy: only x = -0 comes out with the wrong sign (+0); the caller
+// repairs the signs of four results at once from the inputs' sign bytes.
+__device__ __forceinline__ float quotient_rn_unsigned_zero(float x, float s, float r) {
+  const float q0 = __fmul_rn(x, r);
+  const float q1 = __fmaf_rn(__fmaf_rn(-s, q0, x), r, q0);
+  return __fmaf_rn(__fmaf_rn(-s, q1, x), r, q1);
+}
+__device__ __forceinline__ uint32_t quant2_fast_unsigned_zero(float lo, float hi, float s, float r) {
+  const float qlo = quotient_rn_unsigned_zero(lo, s, r), qhi = quotient_rn_unsigned_zero(hi, s, r);
+  uint16_t c;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(c) : "f"(qhi), "f"(qlo));
+  return c;
+}
 
 // Two E4M3 bytes (bits 0-15) -> two f32, exact.
 __device__ __forceinline__ float2 e4m3x2_to_f32(uint32_t q) {
@@ -464,9 +477,21 @@ __device__ __forceinline__ uint2 quant_vec(const uint4 &x, float scale, float r,
   float f[8];
   unpack_vec(x, f, IoT{});
   uint32_t q[4] = {0u, 0u, 0u, 0u};
+  uint2 out;
+  if constexpr (ElemTraits<IoT>::per_vec == 8) {
+    // 16-bit inputs: the sign of element i is the top bit of byte 2 i + 1 of the vector, so one
+    // byte permute gathers four sign bytes and one logic operation puts them on four results
+    // (instead of one sign copy per element inside the quotient).
 #pragma unroll
-  for (int i = 0; i < kPairs; ++i) q[i] = quant2_fast(f[2 * i], f[2 * i + 1], scale, r);
-  const uint2 out = make_uint2(q[0] | (q[1] << 16), q[2] | (q[3] << 16));
+    for (int i = 0; i < kPairs; ++i) q[i] = quant2_fast_unsigned_zero(f[2 * i], f[2 * i + 1], scale, r);
+    const uint32_t lo = q[0] | (q[1] << 16), hi = q[2] | (q[3] << 16);
+    out.x = (lo & 0x7F7F7F7Fu) | (__byte_perm(x.x, x.y, 0x7531) & 0x80808080u);
+    out.y = (hi & 0x7F7F7F7Fu) | (__byte_perm(x.z, x.w, 0x7531) & 0x80808080u);
+  } else {
+#pragma unroll
+    for (int i = 0; i < kPairs; ++i) q[i] = quant2_fast(f[2 * i], f[2 * i + 1], scale, r);
+    out = make_uint2(q[0] | (q[1] << 16), q[2] | (q[3] << 16));
+  }
   // bytes equal to 0x7F after dropping the sign = NaN codes
   const uint32_t nan_bytes = __vcmpeq4(out.x & 0x7F7F7F7Fu, 0x7F7F7F7Fu) | __vcmpeq4(out.y & 0x7F7F7F7Fu, 0x7F7F7F7Fu);
   if (nan_bytes != 0u || r == 0.f)  // inf / NaN / out-of-range quotient somewhere, or an extreme scale
@@ -527,8 +552,7 @@ __global__ void __launch_bounds__(kWriteThreads) kvx_write_f8_kernel(const Write
   const WriteRowsParams &p = q.w;
   __shared__ int64_t s_k[kMaxTokTile];
   __shared__ int64_t s_v[kMaxTokTile];
-  __shared__ float s_sk[kF8CachedHeads], s_sv[kF8CachedHeads];  // scale per head
-  __shared__ float s_rk[kF8CachedHeads], s_rv[kF8CachedHeads];  // fast_reciprocal per head
+  __shared__ float4 s_scale[kF8CachedHeads];  // per head: K scale, its fast_reciprocal, V scale, its fast_reciprocal
   const int tid = threadIdx.x;
   const int64_t tok0 = static_cast<int64_t>(blockIdx.x) * p.tok_tile;
   const int ntok = static_cast<int>(min(static_cast<int64_t>(p.tok_tile), p.num_tokens - tok0));
@@ -536,8 +560,7 @@ __global__ void __launch_bounds__(kWriteThreads) kvx_write_f8_kernel(const Write
   if (cached) {
     for (int h = tid; h < q.heads; h += kWriteThreads) {
       const float a = __ldg(q.ks.base + h * q.ks.stride), b = __ldg(q.vs.base + h * q.vs.stride);
-      s_sk[h] = a, s_sv[h] = b;
-      s_rk[h] = fast_reciprocal(a), s_rv[h] = fast_reciprocal(b);
+      s_scale[h] = make_float4(a, fast_reciprocal(a), b, fast_reciprocal(b));
     }
   }
   if (tid < ntok) {
@@ -590,10 +613,14 @@ __global__ void __launch_bounds__(kWriteThreads) kvx_write_f8_kernel(const Write
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       if (kd[u] >= 0) {
-        const float sk = cached ? s_sk[hh[u]] : __ldg(q.ks.base + hh[u] * q.ks.stride);
-        const float sv = cached ? s_sv[hh[u]] : __ldg(q.vs.base + hh[u] * q.vs.stride);
-        const float rk = cached ? s_rk[hh[u]] : fast_reciprocal(sk);
-        const float rv = cached ? s_rv[hh[u]] : fast_reciprocal(sv);
+        float sk, rk, sv, rv;
+        if (cached) {
+          const float4 sc = s_scale[hh[u]];
+          sk = sc.x, rk = sc.y, sv = sc.z, rv = sc.w;
+        } else {
+          sk = __ldg(q.ks.base + hh[u] * q.ks.stride), sv = __ldg(q.vs.base + hh[u] * q.vs.stride);
+          rk = fast_reciprocal(sk), rv = fast_reciprocal(sv);
+        }
         const uint2 a = quant_vec(kr[u], sk, rk, IoT{});
         const uint2 b = quant_vec(vr[u], sv, rv, IoT{});
         if (kPer == 8) {
