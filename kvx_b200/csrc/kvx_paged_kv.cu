@@ -545,7 +545,8 @@ struct WriteF8Params {
 
 // Same token tiling as kvx_write_rows_kernel; each 16-byte input vector (8 or 4 elements,
 // all of one head) becomes 8 or 4 cache bytes.
-template <typename IoT, typename SlotT, int kUnroll, bool kPitched = false>
+// kPow2: vectors per row and per head are powers of two (shifts instead of divisions).
+template <typename IoT, typename SlotT, int kUnroll, bool kPitched = false, bool kPow2 = false>
 __global__ void __launch_bounds__(kWriteThreads) kvx_write_f8_kernel(const WriteF8Params q) {
   pdl_prologue();
   constexpr int kPer = ElemTraits<IoT>::per_vec;
@@ -557,6 +558,7 @@ __global__ void __launch_bounds__(kWriteThreads) kvx_write_f8_kernel(const Write
   const int64_t tok0 = static_cast<int64_t>(blockIdx.x) * p.tok_tile;
   const int ntok = static_cast<int>(min(static_cast<int64_t>(p.tok_tile), p.num_tokens - tok0));
   const bool cached = q.heads <= kF8CachedHeads;
+  const int k_head32 = static_cast<int>(p.k_head), v_head32 = static_cast<int>(p.v_head);
   if (cached) {
     for (int h = tid; h < q.heads; h += kWriteThreads) {
       const float a = __ldg(q.ks.base + h * q.ks.stride), b = __ldg(q.vs.base + h * q.vs.stride);
@@ -591,15 +593,16 @@ __global__ void __launch_bounds__(kWriteThreads) kvx_write_f8_kernel(const Write
       const int f = f0 + u * kWriteThreads;
       kd[u] = -1;
       if (f < nvec) {
-        const int tok = div_by(f, p.vpr, p.vpr_shift);
+        const int tok = kPow2 ? (f >> p.vpr_shift) : div_by(f, p.vpr, p.vpr_shift);
         const int64_t ko = s_k[tok];
         if (ko >= 0) {
           const int v = f - tok * p.vpr;
-          const int h = div_by(v, p.vps, p.vps_shift);
-          const int64_t w = static_cast<int64_t>(v - h * p.vps) * kPer;  // cache bytes into the head
+          const int h = kPow2 ? (v >> p.vps_shift) : div_by(v, p.vps, p.vps_shift);
+          const int w = (v - h * p.vps) * kPer;  // cache bytes into the head
           hh[u] = h;
-          kd[u] = ko + h * p.k_head + w;
-          vd[u] = s_v[tok] + h * p.v_head + w;
+          // offsets inside a page fit 32 bits (the launcher checks the head pitch)
+          kd[u] = ko + (h * k_head32 + w);
+          vd[u] = s_v[tok] + (h * v_head32 + w);
           if (kPitched) {
             kr[u] = load_stream(ksrc + tok * p.k_pitch + static_cast<int64_t>(v) * 16);
             vr[u] = load_stream(vsrc + tok * p.v_pitch + static_cast<int64_t>(v) * 16);
@@ -1732,6 +1735,7 @@ kvx_status_t write_impl(const kvx_cache_desc_t *cache, const kvx_write_desc_t *w
   const bool pitched = k_pitch != row_bytes || v_pitch != row_bytes;  // token rows further apart than dense
   const bool vec_ok = !g_opt.force_generic && (D * io_elem) % 16 == 0 && k_pitch % 16 == 0 && v_pitch % 16 == 0 &&
                       !(pitched && (k_packed || v_packed)) &&
+                      (!fp8 || (gp.k.head * H < INT32_MAX && gp.v.head * H < INT32_MAX)) &&  // 32-bit in-page offsets
                       aligned(write->io.key.data, 16) && aligned(write->io.value.data, 16) &&
                       (k_packed || view_vectorisable(gp.k, elem, D, out_vec)) &&
                       (v_packed || view_vectorisable(gp.v, elem, D, out_vec)) && row_bytes / 16 <= (1 << 20);
@@ -1777,6 +1781,11 @@ kvx_status_t write_impl(const kvx_cache_desc_t *cache, const kvx_write_desc_t *w
         launch_streaming(kvx_write_f8_kernel<IoT, int32_t, KVX_F8_WRITE_UNROLL, true>, grid, kWriteThreads, 0, cs, q); \
       else                                                                                                    \
         launch_streaming(kvx_write_f8_kernel<IoT, int64_t, KVX_F8_WRITE_UNROLL, true>, grid, kWriteThreads, 0, cs, q); \
+    } else if (p.vpr_shift >= 0 && p.vps_shift >= 0) {                                                        \
+      if (s32)                                                                                                \
+        launch_streaming(kvx_write_f8_kernel<IoT, int32_t, KVX_F8_WRITE_UNROLL, false, true>, grid, kWriteThreads, 0, cs, q); \
+      else                                                                                                    \
+        launch_streaming(kvx_write_f8_kernel<IoT, int64_t, KVX_F8_WRITE_UNROLL, false, true>, grid, kWriteThreads, 0, cs, q); \
     } else if (s32) {                                                                                         \
       launch_streaming(kvx_write_f8_kernel<IoT, int32_t, KVX_F8_WRITE_UNROLL>, grid, kWriteThreads, 0, cs, q); \
     } else {                                                                                                  \
