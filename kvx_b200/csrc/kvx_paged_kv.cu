@@ -638,6 +638,64 @@ __global__ void __launch_bounds__(kWriteThreads) kvx_write_f8_kernel(const Write
   }
 }
 
+// The common case of kvx_write_f8_kernel with 256-bit loads: 16-bit inputs, dense rows, vectors
+// per row and per head powers of two, per-head constants in shared memory.  One thread turns 32
+// bytes of K and 32 bytes of V (16 + 16 elements of one head) into two 16-byte stores, which
+// halves the index arithmetic per element -- the kernel is bound by instruction issue.
+// p.vpr / p.vps count 32-byte input vectors here.
+template <typename IoT, typename SlotT>
+__global__ void __launch_bounds__(kWriteThreads) kvx_write_f8_wide_kernel(const WriteF8Params q) {
+  pdl_prologue();
+  const WriteRowsParams &p = q.w;
+  __shared__ int64_t s_k[kMaxTokTile];
+  __shared__ int64_t s_v[kMaxTokTile];
+  __shared__ float4 s_scale[kF8CachedHeads];
+  const int tid = threadIdx.x;
+  const int64_t tok0 = static_cast<int64_t>(blockIdx.x) * p.tok_tile;
+  const int ntok = static_cast<int>(min(static_cast<int64_t>(p.tok_tile), p.num_tokens - tok0));
+  const int k_head32 = static_cast<int>(p.k_head), v_head32 = static_cast<int>(p.v_head);
+  for (int h = tid; h < q.heads; h += kWriteThreads) {
+    const float a = __ldg(q.ks.base + h * q.ks.stride), b = __ldg(q.vs.base + h * q.vs.stride);
+    s_scale[h] = make_float4(a, fast_reciprocal(a), b, fast_reciprocal(b));
+  }
+  if (tid < ntok) {
+    const int64_t slot = static_cast<int64_t>(static_cast<const SlotT *>(p.slots)[tok0 + tid]);
+    int64_t ko = -1, vo = -1;
+    if (slot >= 0) {
+      int64_t b, o;
+      split_slot(slot, p.block_size, p.bs_shift, &b, &o);
+      if (b < p.num_blocks) {
+        ko = b * p.k_blk + o * p.k_tok;
+        vo = b * p.v_blk + o * p.v_tok;
+      }
+    }
+    s_k[tid] = ko;
+    s_v[tid] = vo;
+  }
+  __syncthreads();
+
+  const char *ksrc = p.key + tok0 * p.row_bytes;
+  const char *vsrc = p.value + tok0 * p.row_bytes;
+  const int nvec = ntok * p.vpr;
+  for (int f = tid; f < nvec; f += kWriteThreads) {
+    const int tok = f >> p.vpr_shift;
+    const int64_t ko = s_k[tok];
+    if (ko < 0) continue;
+    const int v = f - (tok << p.vpr_shift);
+    const int h = v >> p.vps_shift;
+    const int w = (v - (h << p.vps_shift)) * 16;  // cache bytes into the head
+    const Vec32 kr = load_stream32(ksrc + static_cast<int64_t>(f) * 32);
+    const Vec32 vr = load_stream32(vsrc + static_cast<int64_t>(f) * 32);
+    const float4 sc = s_scale[h];
+    const uint2 a0 = quant_vec(make_uint4(kr.w[0], kr.w[1], kr.w[2], kr.w[3]), sc.x, sc.y, IoT{});
+    const uint2 a1 = quant_vec(make_uint4(kr.w[4], kr.w[5], kr.w[6], kr.w[7]), sc.x, sc.y, IoT{});
+    const uint2 b0 = quant_vec(make_uint4(vr.w[0], vr.w[1], vr.w[2], vr.w[3]), sc.z, sc.w, IoT{});
+    const uint2 b1 = quant_vec(make_uint4(vr.w[4], vr.w[5], vr.w[6], vr.w[7]), sc.z, sc.w, IoT{});
+    *reinterpret_cast<uint4 *>(p.k_base + ko + (h * k_head32 + w)) = make_uint4(a0.x, a0.y, a1.x, a1.y);
+    *reinterpret_cast<uint4 *>(p.v_base + s_v[tok] + (h * v_head32 + w)) = make_uint4(b0.x, b0.y, b1.x, b1.y);
+  }
+}
+
 // ------------------------------------------------------------------ generic tier ------
 
 struct GenericParams {
@@ -1774,6 +1832,30 @@ kvx_status_t write_impl(const kvx_cache_desc_t *cache, const kvx_write_desc_t *w
     const int unroll = static_cast<int>(g_opt.write_unroll);
     if (fp8) {
       WriteF8Params q{p, ks, vs, static_cast<int32_t>(D), static_cast<int32_t>(H)};
+      // 256-bit variant: 16-bit inputs whose head rows are whole 32-byte vectors, dense and 32-byte
+      // aligned, destinations 16-byte aligned, shapes powers of two
+      const int64_t row32 = row_bytes / 32, head32 = D * io_elem / 32;
+      if (g_opt.wide && io_elem == 2 && !pitched && (D * io_elem) % 32 == 0 && H <= kF8CachedHeads &&
+          is_pow2(row32) && is_pow2(head32) && aligned(write->io.key.data, 32) && aligned(write->io.value.data, 32) &&
+          aligned(gp.k.base, 16) && aligned(gp.v.base, 16) && gp.k.blk % 16 == 0 && gp.v.blk % 16 == 0 &&
+          gp.k.tok % 16 == 0 && gp.v.tok % 16 == 0 && gp.k.head % 16 == 0 && gp.v.head % 16 == 0) {
+        q.w.vpr = static_cast<int32_t>(row32), q.w.vpr_shift = shift_of(row32);
+        q.w.vps = static_cast<int32_t>(head32), q.w.vps_shift = shift_of(head32);
+        q.w.tok_tile = pick_tok_tile(T, 2 * q.w.vpr, dev.sm_count);  // same bytes per CTA as the 128-bit form
+        const int wgrid = static_cast<int>((T + q.w.tok_tile - 1) / q.w.tok_tile);
+        if (io_dtype == KVX_DTYPE_BF16) {
+          if (s32)
+            launch_streaming(kvx_write_f8_wide_kernel<BF16, int32_t>, wgrid, kWriteThreads, 0, cs, q);
+          else
+            launch_streaming(kvx_write_f8_wide_kernel<BF16, int64_t>, wgrid, kWriteThreads, 0, cs, q);
+        } else {
+          if (s32)
+            launch_streaming(kvx_write_f8_wide_kernel<F16, int32_t>, wgrid, kWriteThreads, 0, cs, q);
+          else
+            launch_streaming(kvx_write_f8_wide_kernel<F16, int64_t>, wgrid, kWriteThreads, 0, cs, q);
+        }
+        return finish_launch();
+      }
 #define KVX_F8_WRITE(IoT)                                                                                     \
   do {                                                                                                        \
     if (pitched) {                                                                                            \
