@@ -58,6 +58,8 @@ struct Options {
   int64_t force_generic = 0;          // 1 = always take the one-element-per-thread tier
   int64_t pdl = 1;                    // 1 = launch with programmatic stream serialization
   int64_t wide = 1;                   // 1 = 256-bit accesses where alignment allows
+  int64_t gather_rect_items = 40000;  // padded (sequence, page, part, K|V) rectangles up to this size are walked as they are
+  int64_t write_prefetch_waves = 2;   // leading write CTAs (in units of 8 per SM) that prefetch their rows into the L2
 };
 Options g_opt;
 std::atomic<uint64_t> g_launches{0};
@@ -72,6 +74,8 @@ const OptionName kOptionNames[] = {
     {"gather_path", &Options::gather_path},
     {"gather_tile_bytes", &Options::gather_tile_bytes},
     {"gather_ctas_per_sm", &Options::gather_ctas_per_sm},
+    {"write_prefetch_waves", &Options::write_prefetch_waves},
+    {"gather_rect_items", &Options::gather_rect_items},
     {"gather_part_bytes", &Options::gather_part_bytes},
     {"bulk_stage_bytes", &Options::bulk_stage_bytes},
     {"bulk_stages", &Options::bulk_stages},
@@ -198,6 +202,13 @@ __device__ __forceinline__ void pdl_prologue() {
   asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
+// The two halves of pdl_prologue() for kernels that warm the L2 in between.  A prefetch
+// consumes no value: the L2 is the point of coherence, so a line fetched early still shows
+// what the previous kernel writes to it later, and stream order is kept as above.
+__device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void prefetch_l2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 // n / d and n % d for a runtime d with a known power-of-two shift (or -1).
 __device__ __forceinline__ int div_by(int n, int d, int shift) {
   return shift >= 0 ? (n >> shift) : (n / d);
@@ -238,7 +249,30 @@ struct WriteRowsParams {
   int32_t vps, vps_shift;  // 16-byte vectors per head segment
   int32_t tok_tile;        // tokens per CTA (<= kMaxTokTile)
   int32_t tile_shift;      // log2(tok_tile), used by the token-fastest order only
+  int32_t early_ctas;      // CTAs that can be resident before the previous kernel has ended
 };
+
+// pdl_prologue() of the write kernels.  Between letting the next kernel in and waiting for the
+// previous one, the leading CTAs of the grid ask for their slots and their dense key / value
+// rows: CTAs that sit at the wait while the previous kernel drains then start from the L2, and
+// in a launch no larger than that (a shard of the batch) the rows are on their way while the
+// slots are still being turned into page offsets.  Further CTAs skip it: once the kernel runs
+// at the memory's rate the extra requests only cost (padded rows are asked for too).
+template <typename SlotT>
+__device__ __forceinline__ void write_prologue(const WriteRowsParams &p, int64_t tok0, int ntok, bool pitched) {
+  pdl_release();
+  if (!pitched && static_cast<int>(blockIdx.x) < p.early_ctas) {
+    const int tid = threadIdx.x;
+    if (tid * 128 < ntok * static_cast<int>(sizeof(SlotT)))
+      prefetch_l2(static_cast<const char *>(p.slots) + tok0 * sizeof(SlotT) + tid * 128);
+    const int64_t bytes = ntok * p.row_bytes;
+    for (int64_t off = static_cast<int64_t>(tid) * 128; off < bytes; off += kWriteThreads * 128) {
+      prefetch_l2(p.key + tok0 * p.row_bytes + off);
+      prefetch_l2(p.value + tok0 * p.row_bytes + off);
+    }
+  }
+  pdl_wait();
+}
 
 // kSeg = false: every token row is one contiguous span in both page tensors.
 // kSeg = true : a row is num_heads spans of head_dim elements (HND pages, or NHD pages whose
@@ -251,12 +285,12 @@ struct WriteRowsParams {
 //               projection output) instead of dense.
 template <typename SlotT, bool kSeg, int kUnroll, bool kTrans = false, bool kPitched = false>
 __global__ void __launch_bounds__(kWriteThreads) kvx_write_rows_kernel(const WriteRowsParams p) {
-  pdl_prologue();
   __shared__ int64_t s_k[kMaxTokTile];
   __shared__ int64_t s_v[kMaxTokTile];
   const int tid = threadIdx.x;
   const int64_t tok0 = static_cast<int64_t>(blockIdx.x) * p.tok_tile;
   const int ntok = static_cast<int>(min(static_cast<int64_t>(p.tok_tile), p.num_tokens - tok0));
+  write_prologue<SlotT>(p, tok0, ntok, kPitched);
 
   if (tid < ntok) {
     const int64_t slot = static_cast<int64_t>(static_cast<const SlotT *>(p.slots)[tok0 + tid]);
@@ -548,7 +582,6 @@ struct WriteF8Params {
 // kPow2: vectors per row and per head are powers of two (shifts instead of divisions).
 template <typename IoT, typename SlotT, int kUnroll, bool kPitched = false, bool kPow2 = false>
 __global__ void __launch_bounds__(kWriteThreads) kvx_write_f8_kernel(const WriteF8Params q) {
-  pdl_prologue();
   constexpr int kPer = ElemTraits<IoT>::per_vec;
   const WriteRowsParams &p = q.w;
   __shared__ int64_t s_k[kMaxTokTile];
@@ -557,6 +590,7 @@ __global__ void __launch_bounds__(kWriteThreads) kvx_write_f8_kernel(const Write
   const int tid = threadIdx.x;
   const int64_t tok0 = static_cast<int64_t>(blockIdx.x) * p.tok_tile;
   const int ntok = static_cast<int>(min(static_cast<int64_t>(p.tok_tile), p.num_tokens - tok0));
+  write_prologue<SlotT>(p, tok0, ntok, kPitched);
   const bool cached = q.heads <= kF8CachedHeads;
   const int k_head32 = static_cast<int>(p.k_head), v_head32 = static_cast<int>(p.v_head);
   if (cached) {
@@ -645,7 +679,6 @@ __global__ void __launch_bounds__(kWriteThreads) kvx_write_f8_kernel(const Write
 // p.vpr / p.vps count 32-byte input vectors here.
 template <typename IoT, typename SlotT>
 __global__ void __launch_bounds__(kWriteThreads) kvx_write_f8_wide_kernel(const WriteF8Params q) {
-  pdl_prologue();
   const WriteRowsParams &p = q.w;
   __shared__ int64_t s_k[kMaxTokTile];
   __shared__ int64_t s_v[kMaxTokTile];
@@ -653,6 +686,7 @@ __global__ void __launch_bounds__(kWriteThreads) kvx_write_f8_wide_kernel(const 
   const int tid = threadIdx.x;
   const int64_t tok0 = static_cast<int64_t>(blockIdx.x) * p.tok_tile;
   const int ntok = static_cast<int>(min(static_cast<int64_t>(p.tok_tile), p.num_tokens - tok0));
+  write_prologue<SlotT>(p, tok0, ntok, false);
   const int k_head32 = static_cast<int>(p.k_head), v_head32 = static_cast<int>(p.v_head);
   for (int h = tid; h < q.heads; h += kWriteThreads) {
     const float a = __ldg(q.ks.base + h * q.ks.stride), b = __ldg(q.vs.base + h * q.vs.stride);
@@ -758,6 +792,7 @@ __global__ void __launch_bounds__(256)
 
 struct GatherShape {
   const void *table, *lens;
+  int64_t table_bytes;  // bytes of `table` the leading CTAs prefetch into the L2 (0 = none)
   int32_t seq_count, max_blocks, max_seq_len;
   // RAGGED tables: table[indptr[s] + tok] is the page of token `tok` of sequence s, for
   // tok < indptr[s + 1] - indptr[s] (one entry per cached token).
@@ -973,20 +1008,35 @@ __device__ __forceinline__ ChunkInfo resolve_chunk(const GatherPagesParams &p, i
   c.block = -1;
   c.tokens = 0;
   c.out_off = 0;
+  if (lb >= p.s.max_blocks) return c;
+  // The table entry exists whatever the sequence's length: it is asked for together with the
+  // length, not after it.
+  int64_t b = 0;
+  if (!kOffsets) b = read_idx<IdxT>(p.s.table, static_cast<int64_t>(seq) * p.s.max_blocks + lb);
   const OutSpan span = out_span<IdxT>(p.s, seq);
   const int64_t len = span.tokens;
   const int64_t first = static_cast<int64_t>(lb) * p.block_size;
-  if (first >= len || lb >= p.s.max_blocks) return c;  // (reference: kernels/kvx_paged_kv.cu:247-253)
-  if (kOffsets) {
-    c.block = 0;  // the K and the V page are looked up by the caller
-  } else {
-    const int64_t b = read_idx<IdxT>(p.s.table, static_cast<int64_t>(seq) * p.s.max_blocks + lb);
-    if (b < 0 || b >= p.num_blocks) return c;  // negative id: skipped (:256-258); too large: skipped too
-    c.block = b;
-  }
+  if (first >= len) return c;  // (reference: kernels/kvx_paged_kv.cu:247-253)
+  if (b < 0 || b >= p.num_blocks) return c;  // negative id: skipped (:256-258); too large: skipped too
+  c.block = b;  // with kOffsets 0: the K and the V page are looked up by the caller
   c.tokens = static_cast<int32_t>(min(len - first, static_cast<int64_t>(p.block_size)));
   c.out_off = (span.first_row + first) * p.out_row_bytes;
   return c;
+}
+
+// pdl_prologue() of the gather kernels: between letting the next kernel in and waiting for the
+// previous one, the leading CTAs ask for the lengths and the block table, so that the lookups
+// in front of the first data loads are answered by the L2.
+template <typename IdxT>
+__device__ __forceinline__ void gather_prologue(const GatherPagesParams &p) {
+  pdl_release();
+  if (p.s.table_bytes > 0) {
+    const int64_t at = (static_cast<int64_t>(blockIdx.x) * kGatherThreads + threadIdx.x) * 128;
+    if (at < p.s.table_bytes) prefetch_l2(static_cast<const char *>(p.s.table) + at);
+    if (at < static_cast<int64_t>(p.s.seq_count) * static_cast<int64_t>(sizeof(IdxT)))
+      prefetch_l2(static_cast<const char *>(p.s.lens) + at);
+  }
+  pdl_wait();
 }
 
 // Persistent CTAs; warp-granular work items (chunk, part, K|V).
@@ -995,7 +1045,7 @@ __device__ __forceinline__ ChunkInfo resolve_chunk(const GatherPagesParams &p, i
 //   kOffsets     : KV_OFFSETS table; K and V pages are resolved separately (offsets_page).
 template <typename IdxT, bool kSeg, int kUnroll, bool kOffsets = false>
 __global__ void __launch_bounds__(kGatherThreads) kvx_gather_pages_kernel(const GatherPagesParams p) {
-  pdl_prologue();
+  gather_prologue<IdxT>(p);
   extern __shared__ int32_t s_prefix[];
   __shared__ int32_t s_warp_tot[kGatherWarps];
   int64_t chunks;
@@ -1072,7 +1122,7 @@ __global__ void __launch_bounds__(kGatherThreads) kvx_gather_pages_kernel(const 
 // are then multiples of 32 bytes too.
 template <typename IdxT, int kUnroll, bool kSeg = false>
 __global__ void __launch_bounds__(kGatherThreads) kvx_gather_pages_wide_kernel(const GatherPagesParams p) {
-  pdl_prologue();
+  gather_prologue<IdxT>(p);
   extern __shared__ int32_t s_prefix[];
   __shared__ int32_t s_warp_tot[kGatherWarps];
   int64_t chunks;
@@ -1143,7 +1193,7 @@ __global__ void __launch_bounds__(kGatherThreads) kvx_gather_pages_wide_kernel(c
 // never sits in front of the data loads.
 template <typename IdxT, bool kSeg, int kUnroll>
 __global__ void __launch_bounds__(kGatherThreads, 4) kvx_gather_tiles_kernel(const GatherPagesParams p) {
-  pdl_prologue();
+  gather_prologue<IdxT>(p);
   extern __shared__ int32_t s_prefix[];
   __shared__ int32_t s_warp_tot[kGatherWarps];
   int64_t chunks;
@@ -1292,7 +1342,7 @@ __global__ void __launch_bounds__(kGatherThreads) kvx_gather_ragged_kernel(const
 // one head) is produced from 8 or 4 cache bytes.
 template <typename IoT, typename IdxT, int kUnroll, bool kOffsets = false>
 __global__ void __launch_bounds__(kGatherThreads) kvx_gather_f8_kernel(const GatherPagesParams p) {
-  pdl_prologue();
+  gather_prologue<IdxT>(p);
   constexpr int kPer = ElemTraits<IoT>::per_vec;
   extern __shared__ int32_t s_prefix[];
   __shared__ int32_t s_warp_tot[kGatherWarps];
@@ -1817,6 +1867,7 @@ kvx_status_t write_impl(const kvx_cache_desc_t *cache, const kvx_write_desc_t *w
     p.vps_shift = shift_of(p.vps);
     p.tok_tile = pick_tok_tile(T, p.vpr, dev.sm_count);
     p.tile_shift = 0;
+    p.early_ctas = static_cast<int32_t>(std::min<int64_t>(dev.sm_count * 8 * g_opt.write_prefetch_waves, INT32_MAX));
     if (k_packed || v_packed) {
       // Token-fastest order over tiles of 16 tokens: a warp then covers 16 consecutive slots x
       // 2 pack groups, i.e. two 256-byte runs of a page on the store side and whole 32-byte
@@ -2023,6 +2074,9 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
   GatherShape gs;
   gs.table = gather->block_table.indices;
   gs.lens = gather->seq_lens.lengths;
+  gs.table_bytes = ragged ? 0
+                          : static_cast<int64_t>(S) * gather->block_table.max_blocks_per_seq *
+                                (offsets ? 8 : (gather->block_table.index_dtype == KVX_DTYPE_S64 ? 8 : 4));
   gs.seq_count = static_cast<int32_t>(S);
   gs.max_blocks = static_cast<int32_t>(gather->block_table.max_blocks_per_seq);
   gs.max_seq_len = static_cast<int32_t>(L);
@@ -2165,6 +2219,12 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
     // (sequence, page) rectangle: beyond that most CTAs would only run their prefix scan.
     const int64_t max_items = S * gs.max_blocks * p.parts * 2;
     const int64_t need = (max_items + kGatherWarps - 1) / kGatherWarps;
+    // A small rectangle is walked as it is: without the scan a warp asks for its length and its
+    // table entry at once, which takes about 1 us off a launch that lasts 25 us (an eighth of
+    // the Llama-3-8B batch: 24.4 us instead of 25.5 us), while the items of pages that do not
+    // exist cost a resident warp a few cached loads each.  Large rectangles can be mostly
+    // padding (decode batches with contexts of 1 to 1 024 pages: 1.8x slower uncompacted).
+    if (!fp8 && max_items <= g_opt.gather_rect_items) p.use_prefix = 0;
     int64_t per_sm = g_opt.gather_ctas_per_sm < 1 ? 1 : g_opt.gather_ctas_per_sm;
     if (fp8) per_sm = std::min<int64_t>(per_sm, 8);
     int64_t grid = static_cast<int64_t>(dev.sm_count) * per_sm;
