@@ -139,6 +139,14 @@ struct Fp16 {
 // exp2(a - b) for running maxima, 0 when `a` is -inf (nothing accumulated yet).
 __device__ __forceinline__ float exp2_diff(float a, float b) { return a == -INFINITY ? 0.f : exp2f(a - b); }
 
+// Programmatic dependent launch: the kernels are launched with the stream-serialization
+// attribute, let the next kernel of the stream schedule its CTAs at once, and read or write
+// nothing before everything enqueued ahead of them has completed.
+__device__ __forceinline__ void pdl_prologue() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // ------------------------------------------------------------------ work list of the fast tier --
 
 constexpr int kAttnWarps = 4;
@@ -341,6 +349,7 @@ __global__ void __launch_bounds__(kAttnThreads, attn_ctas_per_sm(kD, kNt))
   // plus small offsets, most of them compile-time
   const uint32_t my_ring = static_cast<uint32_t>(__cvta_generic_to_shared(ring + warp * (kTStages * 2 * kTile)));
 
+  pdl_prologue();
   const int64_t items = build_work_list<IdxT>(p, sm_prefix, sm_scan);
 
   zero_empty_sequences<IdxT>(p);
@@ -626,6 +635,7 @@ __global__ void __launch_bounds__(kAttnThreads, attn_ctas_per_sm(kD, kNt))
 // sequence really has, w_s = L_s * exp2(M_s - max M).
 template <typename IdxT>
 __global__ void __launch_bounds__(128) kvx_attention_merge_kernel(const AttnParams p, int out_code) {
+  pdl_prologue();
   const int64_t q = blockIdx.x;
   const int seq = static_cast<int>(q / p.heads_q);
   int64_t len = read_idx<IdxT>(p.lens, seq);
@@ -702,6 +712,7 @@ __global__ void __launch_bounds__(kGenThreads)
   __shared__ int64_t sm_page[kGenChunk];  // byte offset of the token's page + token, -1 = no part
   __shared__ float scratch[kGenThreads / 32];
   float *sm_p = sm_q + p.dim;
+  pdl_prologue();
   const int64_t q = blockIdx.x;
   const int seq = static_cast<int>(q / p.heads_q);
   const int head_q = static_cast<int>(q - static_cast<int64_t>(seq) * p.heads_q);
@@ -800,17 +811,33 @@ bool dense3(const kvx_tensor_desc_t *t, int64_t a, int64_t b, int64_t c, kvx_sta
   return true;
 }
 
+// Launch with the programmatic-stream-serialization attribute (see pdl_prologue).
+template <typename... Args>
+void launch_pdl(void (*kernel)(Args...), unsigned grid, unsigned block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 template <typename T, int kD, typename IdxT, bool kFp8, typename QT>
 void launch_t(const AttnParams &p, unsigned grid, size_t smem, cudaStream_t st) {
   // (the attribute is per device and cheap to set, so it is set on every launch)
   if (p.group <= 8) {
     cudaFuncSetAttribute(kvx_attention_decode_t_kernel<T, kD, IdxT, 1, kFp8, QT>,
                          cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    kvx_attention_decode_t_kernel<T, kD, IdxT, 1, kFp8, QT><<<grid, kAttnThreads, smem, st>>>(p);
+    launch_pdl(kvx_attention_decode_t_kernel<T, kD, IdxT, 1, kFp8, QT>, grid, kAttnThreads, smem, st, p);
   } else {
     cudaFuncSetAttribute(kvx_attention_decode_t_kernel<T, kD, IdxT, 2, kFp8, QT>,
                          cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    kvx_attention_decode_t_kernel<T, kD, IdxT, 2, kFp8, QT><<<grid, kAttnThreads, smem, st>>>(p);
+    launch_pdl(kvx_attention_decode_t_kernel<T, kD, IdxT, 2, kFp8, QT>, grid, kAttnThreads, smem, st, p);
   }
 }
 
@@ -973,9 +1000,9 @@ KVX_API kvx_status_t kvx_launch_paged_attention_decode(const kvx_cache_desc_t *c
       launch_t_types<int64_t>(p, cd, io, static_cast<unsigned>(grid), smem, cs);
     if (p.splits > 1) {
       if (s32)
-        kvx_attention_merge_kernel<int32_t><<<static_cast<unsigned>(S * Hq), 128, 0, cs>>>(p, io);
+        launch_pdl(kvx_attention_merge_kernel<int32_t>, static_cast<unsigned>(S * Hq), 128u, size_t{0}, cs, p, static_cast<int>(io));
       else
-        kvx_attention_merge_kernel<int64_t><<<static_cast<unsigned>(S * Hq), 128, 0, cs>>>(p, io);
+        launch_pdl(kvx_attention_merge_kernel<int64_t>, static_cast<unsigned>(S * Hq), 128u, size_t{0}, cs, p, static_cast<int>(io));
     }
     return cudaGetLastError() == cudaSuccess ? KVX_STATUS_OK : KVX_STATUS_INTERNAL_ERROR;
   }
@@ -984,9 +1011,11 @@ KVX_API kvx_status_t kvx_launch_paged_attention_decode(const kvx_cache_desc_t *c
   p.splits = 1;
   const size_t smem = (static_cast<size_t>(D) + kGenChunk) * sizeof(float);
   if (s32)
-    kvx_attention_generic_kernel<int32_t><<<static_cast<unsigned>(S * Hq), kGenThreads, smem, cs>>>(p, cd, io);
+    launch_pdl(kvx_attention_generic_kernel<int32_t>, static_cast<unsigned>(S * Hq), static_cast<unsigned>(kGenThreads), smem, cs, p,
+               static_cast<int>(cd), static_cast<int>(io));
   else
-    kvx_attention_generic_kernel<int64_t><<<static_cast<unsigned>(S * Hq), kGenThreads, smem, cs>>>(p, cd, io);
+    launch_pdl(kvx_attention_generic_kernel<int64_t>, static_cast<unsigned>(S * Hq), static_cast<unsigned>(kGenThreads), smem, cs, p,
+               static_cast<int>(cd), static_cast<int>(io));
   return cudaGetLastError() == cudaSuccess ? KVX_STATUS_OK : KVX_STATUS_INTERNAL_ERROR;
 }
 
