@@ -82,9 +82,12 @@ __device__ __forceinline__ int64_t read_idx(const void *p, int64_t i) {
 // chunks of `chunk` tokens (a multiple of 64); long chunks when there are many (sequence, KV
 // head) pairs, shorter ones when the batch alone would leave the persistent CTAs with only a
 // few work items each (the bound uses max_seq_len; real contexts are shorter).
+#ifndef KVX_ATTN_MIN_ITEMS
+#define KVX_ATTN_MIN_ITEMS 2048
+#endif
 __host__ __device__ inline int32_t choose_chunk(int64_t seq_count, int64_t heads_kv, int64_t max_seq_len) {
   int64_t chunk = 2048;
-  while (chunk > 256 && seq_count * heads_kv * ((max_seq_len + chunk - 1) / chunk) < 2048) chunk >>= 1;
+  while (chunk > 256 && seq_count * heads_kv * ((max_seq_len + chunk - 1) / chunk) < KVX_ATTN_MIN_ITEMS) chunk >>= 1;
   return static_cast<int32_t>(chunk);
 }
 

@@ -24,7 +24,8 @@ LAYOUTS = [(abi.LAYOUT_NHD, 1), (abi.LAYOUT_HND, 1), (abi.LAYOUT_HND_PACKED, 4)]
 def _defaults():
     """Every test starts from the library's default tuning."""
     saved = {n: kvx_b200.get_option(n) for n in ("gather_path", "force_generic", "write_unroll",
-                                                  "write_vecs_per_cta", "gather_part_bytes", "gather_tile_bytes", "wide", "pdl")}
+                                                  "write_vecs_per_cta", "gather_part_bytes", "gather_tile_bytes", "wide", "pdl",
+                                                  "write_prefetch_waves", "gather_rect_items")}
     yield
     for n, v in saved.items():
         kvx_b200.set_option(n, v)
@@ -41,12 +42,20 @@ def check_write(case: Case, entry="dispatch", tps=1):
 
 
 def check_gather(case: Case, k, v, entry="dispatch"):
+    """Every case runs twice: with the (sequence, page) rectangle compacted in the kernel, and
+    walked as it is (what the library picks for small rectangles like the ones tested here)."""
     st, ek, ev = oracle_gather(case, k, v)
     assert st == OK
-    st, gk, gv = gpu_gather(case, k, v, entry)
-    assert st == OK, (entry, st)
-    assert np.array_equal(gk, ek), f"K out differs ({case.note}, {entry})"
-    assert np.array_equal(gv, ev), f"V out differs ({case.note}, {entry})"
+    saved = kvx_b200.get_option("gather_rect_items")
+    try:
+        for rect in (0, 1 << 40):
+            kvx_b200.set_option("gather_rect_items", rect)
+            st, gk, gv = gpu_gather(case, k, v, entry)
+            assert st == OK, (entry, st)
+            assert np.array_equal(gk, ek), f"K out differs ({case.note}, {entry}, rect {rect})"
+            assert np.array_equal(gv, ev), f"V out differs ({case.note}, {entry}, rect {rect})"
+    finally:
+        kvx_b200.set_option("gather_rect_items", saved)
 
 
 # ------------------------------------------------------------------ reference's own cases -
@@ -172,7 +181,9 @@ def test_tuning_knobs_do_not_change_results():
             for part in (512, 4096, 65536):
                 kvx_b200.set_option("gather_part_bytes", part)
                 check_gather(case, ek, ev)
-            check_write(case)
+            for waves in (0, 1, 2):        # leading write CTAs that prefetch their rows
+                kvx_b200.set_option("write_prefetch_waves", waves)
+                check_write(case)
 
 
 def test_bulk_gather_path_matches():
