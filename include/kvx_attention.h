@@ -52,7 +52,7 @@ KVX_API size_t kvx_paged_attention_workspace_bytes(uint32_t seq_count, uint32_t 
                                                    uint32_t num_kv_heads, uint32_t head_dim,
                                                    uint32_t max_seq_len);
 
-/* Enqueues the attention on `stream` (1 or 2 kernels) and returns without synchronising.
+/* Enqueues the attention on `stream` (1 to 3 kernels) and returns without synchronising.
  *
  * Cache: F16 / BF16 / F32 (query and out of the same type), or F8_E4M3 with 16/32-bit query
  * and F32 scales in k_scale / v_scale (PER_TENSOR or PER_HEAD, as for the fp8 gather; NULL

@@ -257,7 +257,7 @@ __device__ void zero_empty_sequences(const AttnParams &p) {
 // 3 CTAs x 4 warps per SM keep 12 steps in flight while 12 are being multiplied.
 //
 // Work distribution.  Items are (sequence, chunk, KV head) triples of chunks that exist; CTAs
-// claim them one at a time from a counter in the caller's scratch (zeroed by the launcher), so
+// claim them one at a time from a counter in the caller's scratch (cleared by a one-warp kernel ahead of it), so
 // short and long items balance out.
 constexpr size_t kCounterBytes = 16;  // head of the scratch: the work counter, padded
 
@@ -632,6 +632,12 @@ __global__ void __launch_bounds__(kAttnThreads, attn_ctas_per_sm(kD, kNt))
   }
 }
 
+// Clears the work counter ahead of the fast kernel.
+__global__ void kvx_attention_reset_kernel(unsigned long long *counter) {
+  pdl_prologue();
+  if (threadIdx.x == 0) *counter = 0ull;
+}
+
 // ------------------------------------------------------------------ merge of chunks ----
 
 // One CTA per (sequence, query head): out = sum_s w_s O_s / sum_s w_s over the chunks the
@@ -995,8 +1001,8 @@ KVX_API kvx_status_t kvx_launch_paged_attention_decode(const kvx_cache_desc_t *c
     const int64_t grid = std::max<int64_t>(1, std::min<int64_t>(most, static_cast<int64_t>(sm_count()) * per_sm));
     if (most <= grid)
       p.counter = nullptr;  // every possible item has its own CTA: nothing to balance, no counter to clear
-    else if (cudaMemsetAsync(p.counter, 0, kCounterBytes, cs) != cudaSuccess)
-      return KVX_STATUS_INTERNAL_ERROR;
+    else  // a kernel, not a memset: it keeps the chain of programmatic launches unbroken
+      launch_pdl(kvx_attention_reset_kernel, 1u, 32u, size_t{0}, cs, p.counter);
     if (s32)
       launch_t_types<int32_t>(p, cd, io, static_cast<unsigned>(grid), smem, cs);
     else
