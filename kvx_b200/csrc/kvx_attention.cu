@@ -352,7 +352,18 @@ __global__ void __launch_bounds__(kAttnThreads, attn_ctas_per_sm(kD, kNt))
   // plus small offsets, most of them compile-time
   const uint32_t my_ring = static_cast<uint32_t>(__cvta_generic_to_shared(ring + warp * (kTStages * 2 * kTile)));
 
-  pdl_prologue();
+  // Programmatic launch: while the kernel ahead (the counter reset, or the caller's previous
+  // kernel) drains, the lengths and the block table are asked into the L2; no value is used
+  // before the wait.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  {
+    const int64_t at = (static_cast<int64_t>(blockIdx.x) * kAttnThreads + threadIdx.x) * 128;
+    if (at < static_cast<int64_t>(p.seq_count) * p.max_blocks * static_cast<int64_t>(sizeof(IdxT)))
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const char *>(p.table) + at));
+    if (at < static_cast<int64_t>(p.seq_count) * static_cast<int64_t>(sizeof(IdxT)))
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const char *>(p.lens) + at));
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int64_t items = build_work_list<IdxT>(p, sm_prefix, sm_scan);
 
   zero_empty_sequences<IdxT>(p);
