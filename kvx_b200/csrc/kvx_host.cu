@@ -52,6 +52,9 @@ struct kvx_host_pipe {
   char *table_dev = nullptr;
   char *lens_dev = nullptr;
   cudaStream_t h2d = nullptr, exec = nullptr, d2h = nullptr;
+  cudaStream_t d2h_v = nullptr;  // V runs come back on a stream of their own: the gaps between the many
+                                 // per-sequence copies of one stream are filled by the other
+  cudaEvent_t v_back = nullptr;  // the V copies of a staging set are done
   cudaEvent_t ready[kRings * kSets] = {};  // staging set filled (h2d) / gathered (exec)
   cudaEvent_t freed[kRings * kSets] = {};  // staging set consumed (exec) / copied back (d2h)
   cudaEvent_t meta_done = nullptr;   // kernels of the last gather are done with table_dev / lens_dev
@@ -104,6 +107,8 @@ KVX_API kvx_status_t kvx_host_pipe_create(size_t chunk_bytes, uint32_t max_seqs,
          cudaStreamCreateWithFlags(&p->h2d, cudaStreamNonBlocking) == cudaSuccess &&
          cudaStreamCreateWithFlags(&p->exec, cudaStreamNonBlocking) == cudaSuccess &&
          cudaStreamCreateWithFlags(&p->d2h, cudaStreamNonBlocking) == cudaSuccess &&
+         cudaStreamCreateWithFlags(&p->d2h_v, cudaStreamNonBlocking) == cudaSuccess &&
+         cudaEventCreateWithFlags(&p->v_back, cudaEventDisableTiming) == cudaSuccess &&
          cudaEventCreateWithFlags(&p->meta_done, cudaEventDisableTiming) == cudaSuccess &&
          cudaEventCreateWithFlags(&p->meta_ready, cudaEventDisableTiming) == cudaSuccess;
   if (!good) {
@@ -120,6 +125,7 @@ KVX_API void kvx_host_pipe_destroy(kvx_host_pipe_t *p) {
   if (p->h2d) cudaStreamSynchronize(p->h2d);
   if (p->exec) cudaStreamSynchronize(p->exec);
   if (p->d2h) cudaStreamSynchronize(p->d2h);
+  if (p->d2h_v) cudaStreamSynchronize(p->d2h_v);
   for (int i = 0; i < kRings * kSets; ++i) {
     cudaFree(p->k_stage[i]);
     cudaFree(p->v_stage[i]);
@@ -134,6 +140,8 @@ KVX_API void kvx_host_pipe_destroy(kvx_host_pipe_t *p) {
   if (p->h2d) cudaStreamDestroy(p->h2d);
   if (p->exec) cudaStreamDestroy(p->exec);
   if (p->d2h) cudaStreamDestroy(p->d2h);
+  if (p->d2h_v) cudaStreamDestroy(p->d2h_v);
+  if (p->v_back) cudaEventDestroy(p->v_back);
   delete p;
 }
 
@@ -235,6 +243,7 @@ KVX_API kvx_status_t kvx_host_gather_kv(kvx_host_pipe_t *p, const kvx_cache_desc
     status = launch(&g, p->exec);
     ok(p, cudaEventRecord(p->ready[set], p->exec));
     ok(p, cudaStreamWaitEvent(p->d2h, p->ready[set], 0));
+    ok(p, cudaStreamWaitEvent(p->d2h_v, p->ready[set], 0));
 
     // Copy back runs of consecutive defined pages, never a byte more.
     for (int64_t i = 0; i < n && status == KVX_STATUS_OK; ++i) {
@@ -256,12 +265,14 @@ KVX_API kvx_status_t kvx_host_gather_kv(kvx_host_pipe_t *p, const kvx_cache_desc
           char *hk = static_cast<char *>(gather->io.key.data) + s * seq_bytes + off;
           char *hv = static_cast<char *>(gather->io.value.data) + s * seq_bytes + off;
           ok(p, cudaMemcpyAsync(hk, p->k_stage[set] + i * seq_bytes + off, bytes, cudaMemcpyDeviceToHost, p->d2h));
-          ok(p, cudaMemcpyAsync(hv, p->v_stage[set] + i * seq_bytes + off, bytes, cudaMemcpyDeviceToHost, p->d2h));
+          ok(p, cudaMemcpyAsync(hv, p->v_stage[set] + i * seq_bytes + off, bytes, cudaMemcpyDeviceToHost, p->d2h_v));
           p->d2h_bytes += static_cast<uint64_t>(2 * bytes);
           run_begin = -1;
         }
       }
     }
+    ok(p, cudaEventRecord(p->v_back, p->d2h_v));
+    ok(p, cudaStreamWaitEvent(p->d2h, p->v_back, 0));
     ok(p, cudaEventRecord(p->freed[set], p->d2h));
   }
   ok(p, cudaEventRecord(p->meta_done, p->exec));
@@ -274,6 +285,7 @@ KVX_API kvx_status_t kvx_host_pipe_sync(kvx_host_pipe_t *p) {
   bool good = cudaStreamSynchronize(p->h2d) == cudaSuccess;
   good = (cudaStreamSynchronize(p->exec) == cudaSuccess) && good;
   good = (cudaStreamSynchronize(p->d2h) == cudaSuccess) && good;
+  good = (cudaStreamSynchronize(p->d2h_v) == cudaSuccess) && good;
   if (!good || p->failed) {
     p->failed = false;
     return KVX_STATUS_INTERNAL_ERROR;
