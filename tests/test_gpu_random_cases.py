@@ -96,3 +96,39 @@ def test_random_fp8_cases(group):
         st, gk, gv = gpu_gather(case, ek, ev, "dispatch")
         assert st == OK, case.note
         assert np.array_equal(gk, eok) and np.array_equal(gv, eov), f"fp8 gather differs, {case.note}"
+
+
+@pytest.mark.parametrize("group_id", range(2))
+def test_random_attention_cases(group_id):
+    """Decode attention over random shapes against the checker's double-precision statement
+    (tolerances of tests/test_gpu_attention.py): tensor-core and generic tier, 16-bit, f32 and
+    fp8 caches, 1..16 query heads per KV head, contexts from empty to several chunks, truncated
+    by max_seq_len, damaged tables."""
+    from test_gpu_attention import check
+
+    for i in range(20):
+        seed = 900 + group_id * 20 + i
+        rng = np.random.default_rng(seed)
+        dtype = int(rng.choice([abi.DTYPE_BF16, abi.DTYPE_F16, abi.DTYPE_F32]))
+        fp8 = dtype != abi.DTYPE_F32 and rng.random() < 0.3
+        block_size = int(rng.choice([4, 16, 32, 64]))
+        heads = int(rng.choice([1, 2, 4]))
+        dim = int(rng.choice([32, 64, 128, 256]))
+        seqs = int(rng.integers(1, 6))
+        top = int(rng.choice([40, 300, 2500]))
+        lens = [int(x) for x in rng.integers(0, top + 1, seqs)]
+        need = sum(-(-n // block_size) for n in lens)
+        kw = dict(layout=int(rng.choice([abi.LAYOUT_NHD, abi.LAYOUT_HND])), dtype=dtype, heads=heads, dim=dim,
+                  block_size=block_size, lens=lens, num_blocks=need + 3, bad_blocks=int(rng.integers(0, 3)),
+                  index_dtype=rng.choice([np.int32, np.int64]), real_values=True)
+        if fp8:
+            kw.update(cache_dtype=abi.DTYPE_F8_E4M3,
+                      scale_gran=int(rng.choice([abi.SCALE_PER_TENSOR, abi.SCALE_PER_HEAD])))
+        case = cases.make_case(seed, **kw)
+        q_per_kv = int(rng.choice([1, 2, 4, 7, 8, 12, 16]))
+        case.note = f"seed {seed}: group {q_per_kv}, {kw}"
+        _, k, v = oracle_write(case)
+        extra = {}
+        if max(lens) > 2 and rng.random() < 0.3:
+            extra["max_seq_len"] = int(rng.integers(1, max(lens)))
+        check(case, k, v, q_per_kv, seed=seed, **extra)
