@@ -1867,7 +1867,6 @@ kvx_status_t write_impl(const kvx_cache_desc_t *cache, const kvx_write_desc_t *w
     p.vps_shift = shift_of(p.vps);
     p.tok_tile = pick_tok_tile(T, p.vpr, dev.sm_count);
     p.tile_shift = 0;
-    p.early_ctas = static_cast<int32_t>(std::min<int64_t>(dev.sm_count * 8 * g_opt.write_prefetch_waves, INT32_MAX));
     if (k_packed || v_packed) {
       // Token-fastest order over tiles of 16 tokens: a warp then covers 16 consecutive slots x
       // 2 pack groups, i.e. two 256-byte runs of a page on the store side and whole 32-byte
@@ -1881,6 +1880,12 @@ kvx_status_t write_impl(const kvx_cache_desc_t *cache, const kvx_write_desc_t *w
     }
     const int grid = static_cast<int>((T + p.tok_tile - 1) / p.tok_tile);
     const int unroll = static_cast<int>(g_opt.write_unroll);
+    // Leading CTAs that prefetch (see write_prologue): worth 1 us on a launch of a few tens of
+    // microseconds, nothing on a long one, where back-to-back writes even lose 1 % to the early
+    // requests competing with the previous launch's last stores -- so only grids of up to twice
+    // that many CTAs use it.
+    const int64_t lead = static_cast<int64_t>(dev.sm_count) * 8 * g_opt.write_prefetch_waves;
+    p.early_ctas = grid <= 2 * lead ? static_cast<int32_t>(std::min<int64_t>(lead, INT32_MAX)) : 0;
     if (fp8) {
       WriteF8Params q{p, ks, vs, static_cast<int32_t>(D), static_cast<int32_t>(H)};
       // 256-bit variant: 16-bit inputs whose head rows are whole 32-byte vectors, dense and 32-byte
