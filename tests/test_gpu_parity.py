@@ -170,6 +170,7 @@ def test_tuning_knobs_do_not_change_results():
             kvx_b200.set_option("write_unroll", unroll)
             kvx_b200.set_option("write_vecs_per_cta", vecs)
             check_write(case)
+    kvx_b200.set_option("gather_path", 0)  # CTA-granular items
     for tile in (4096, 16384, 65536):
         kvx_b200.set_option("gather_tile_bytes", tile)
         check_gather(case, ek, ev)
