@@ -63,14 +63,19 @@ def test_random_copy_cases(group):
         assert np.array_equal(k, ek) and np.array_equal(v, ev), f"cache differs, {case.note}"
         st, eok, eov = oracle_gather(case, ek, ev)
         assert st == OK, case.note
-        for rect in (0, 1 << 40):   # compacted and uncompacted (sequence, page) rectangle
-            kvx_b200.set_option("gather_rect_items", rect)
-            try:
+        saved = {n: kvx_b200.get_option(n) for n in ("gather_rect_items", "gather_path", "wide")}
+        kvx_b200.set_option("gather_path", seed % 3)       # CTA-granular, bulk-staged, warp-granular items
+        kvx_b200.set_option("wide", (seed // 3) % 2)       # 128-bit / 256-bit accesses
+        try:
+            for rect in (0, 1 << 40):   # compacted and uncompacted (sequence, page) rectangle
+                kvx_b200.set_option("gather_rect_items", rect)
                 st, gk, gv = gpu_gather(case, ek, ev, "dispatch")
-            finally:
-                kvx_b200.set_option("gather_rect_items", 40000)
-            assert st == OK, case.note
-            assert np.array_equal(gk, eok) and np.array_equal(gv, eov), f"gather differs (rect {rect}), {case.note}"
+                assert st == OK, case.note
+                assert np.array_equal(gk, eok) and np.array_equal(gv, eov), \
+                    f"gather differs (rect {rect}, path {seed % 3}, wide {(seed // 3) % 2}), {case.note}"
+        finally:
+            for n, v in saved.items():
+                kvx_b200.set_option(n, v)
 
 
 @pytest.mark.parametrize("group", range(2))
