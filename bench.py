@@ -58,6 +58,13 @@ def parse_args():
                     help="fill the pages with one write per layer, time only the fused decode attention and print its "
                          "numbers (the small command the attention kernel is profiled with)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-verify", action="store_true", help="skip the byte check of the timed buffers")
+    ap.add_argument("--layout", default="nhd", choices=["nhd", "hnd", "packed", "paged"],
+                    help="page layout of the headline workload: NHD (default), HND, HND_PACKED with 16-byte pack "
+                         "groups for K and V, or 'paged' = packed K + [blocks, heads, dim, block_size] V")
+    ap.add_argument("--configs", default="c4,c5,c3,c4:packed,c2:packed",
+                    help="other configurations (name or name:layout) timed on a few layers each and verified after "
+                         "the headline workload; '' = none")
     ap.add_argument("--no-reference-kernels", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU baseline budget")
     ap.add_argument("--option", action="append", default=[], help="tuning knob name=value")
@@ -215,7 +222,7 @@ def main() -> None:
         spec = dataclasses.replace(spec, seqs=args.seqs, name=f"{spec.name}_seqs{args.seqs}")
     peak, peak_kind = measured_peak()
 
-    dw = bs.setup_device_workload(spec, rank, world, layers=args.layers, pool_gb=args.pool_gb)
+    dw = bs.setup_device_workload(spec, rank, world, layers=args.layers, pool_gb=args.pool_gb, layout=args.layout)
     layers, meta = dw.layers, dw.meta
     stream = torch.cuda.current_stream().cuda_stream
 
@@ -245,6 +252,8 @@ def main() -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
+    if not args.no_verify:
+        bs.fill_sentinel(dw)  # before the warm-up: the check below looks at the buffers the timed steps used
     sampler = bs.ClockSampler(local, period_ms=20)
     sampler.start()  # sampled from the warm-up on: the timed region alone can be shorter than one period
     for _ in range(max(args.warmup, 3)):
@@ -266,6 +275,12 @@ def main() -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     total_ms, write_ms, gather_ms = [float(x) for x in t.tolist()]
 
+    # ---- byte check of the buffers the timed steps wrote and gathered, on every rank -------
+    verified, verify_detail = None, None
+    if not args.no_verify:
+        verify_detail = bs.verify_layer(dw, layers - 1)
+        verified = all_ranks_true(verify_detail["ok"], dist)
+
     # ---- host-buffer leg (the call a user of the C ABI with host buffers makes) -------------
     e2e = None
     if not args.no_e2e:
@@ -275,6 +290,22 @@ def main() -> None:
     if world == 1 and not args.no_attention:
         attention = run_attention(dw, min(args.steps, 3))
 
+    # ---- the other configurations, a few layers each, sharded over the same ranks -----------
+    pool_gb_used = round(dw.pool.numel() / 1e9, 2)
+    write_bytes_rank, gather_bytes_rank, heads_rank = dw.write_bytes, dw.gather_bytes, dw.heads
+    configs = None
+    wanted = [c for c in args.configs.split(",") if c and c != args.workload]
+    if args.layers is not None or args.seqs is not None or args.pool_gb is not None:
+        wanted = []  # a cut-down run (profiling, experiments) times its own workload only
+    if wanted and not args.only_attention:
+        del dw, step
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        configs = {}
+        for name in wanted:
+            configs[name] = run_config_leg(name, rank, world, dist, peak, verify=not args.no_verify)
+
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -283,19 +314,22 @@ def main() -> None:
     wb_all, gb_all = meta.write_bytes(spec.heads), meta.gather_bytes(spec.heads)  # all heads = all ranks
     steps = args.steps
     value = (wb_all + gb_all) * layers * steps / (total_ms * 1e-3) / 1e9
-    write_gbs_rank = dw.write_bytes * layers * steps / (write_ms * 1e-3) / 1e9
-    gather_gbs_rank = dw.gather_bytes * layers * steps / (gather_ms * 1e-3) / 1e9
-    dom, dom_gbs, dom_bytes, dom_ms = ("gather", gather_gbs_rank, dw.gather_bytes, gather_ms) \
-        if dw.gather_bytes >= dw.write_bytes else ("write", write_gbs_rank, dw.write_bytes, write_ms)
+    write_gbs_rank = write_bytes_rank * layers * steps / (write_ms * 1e-3) / 1e9
+    gather_gbs_rank = gather_bytes_rank * layers * steps / (gather_ms * 1e-3) / 1e9
+    dom, dom_gbs, dom_bytes, dom_ms = ("gather", gather_gbs_rank, gather_bytes_rank, gather_ms) \
+        if gather_bytes_rank >= write_bytes_rank else ("write", write_gbs_rank, write_bytes_rank, write_ms)
+    traffic = TRAFFIC_PER_LAUNCH.get((args.workload, dom)) if args.layout == "nhd" else None
+    if traffic is not None and args.seqs is not None:
+        traffic = None  # the capture was taken on the configuration's own token counts
     line = {
         "metric": "kv_write_gather_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
         "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": round(total_ms / steps, 4),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-        "config": {"workload": spec.name, "layers": layers, "heads_global": spec.heads, "heads_per_gpu": dw.heads,
+        "config": {"workload": spec.name, "layout": args.layout, "layers": layers, "heads_global": spec.heads, "heads_per_gpu": heads_rank,
                    "head_dim": spec.dim, "block_size": spec.block_size, "seqs": spec.seqs,
                    "write_tokens": meta.write_tokens, "valid_tokens": meta.valid_tokens,
                    "gather_tokens": meta.gather_tokens, "pool_blocks_per_tensor": meta.num_blocks,
-                   "pool_gb_per_gpu": round(dw.pool.numel() / 1e9, 2), "parallelism": f"kv_head_shard{world}",
+                   "pool_gb_per_gpu": pool_gb_used, "parallelism": f"kv_head_shard{world}",
                    "l2": "inputs (K+V batch, page pool) larger than L2; every layer has its own pages"},
         "pct_of_nominal_8tbs": round(100 * value / world / NOMINAL_HBM_GBS, 1),
         "write": {"gbs_per_gpu": round(write_gbs_rank, 1), "us_per_launch": round(write_ms * 1e3 / (layers * steps), 2),
@@ -307,9 +341,18 @@ def main() -> None:
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": round(dom_gbs, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(dom_gbs / peak, 4), "peak_kind": peak_kind,
                      "bytes_per_launch": dom_bytes, "us_per_launch": round(dom_ms * 1e3 / (layers * steps), 2),
-                     "traffic": TRAFFIC_PER_LAUNCH.get((args.workload, dom, world))},
+                     # DRAM bytes of one launch; the capture is of all heads on one GPU and the traffic is
+                     # proportional to the heads a rank owns
+                     "traffic": None if traffic is None else traffic // world},
         "gpu_launches": int(launches), "clocks": clocks,
     }
+    if verified is not None:
+        line["verified"] = verified
+        line["verify"] = {"what": "last layer of the timed buffers, every rank: pool rows at valid slots == input rows, "
+                                  "all other pool rows == fill pattern, gathered rows below len == pages[table], rows "
+                                  "past len == sentinel", "rank0": verify_detail}
+    if configs is not None:
+        line["configs"] = configs
     if e2e is not None:
         line["e2e"] = e2e
     if attention is not None:
@@ -321,14 +364,101 @@ def main() -> None:
         dist.destroy_process_group()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
-# captures summarised under profiles/ (bytes); filled in as captures are taken.
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch on one GPU holding all KV heads, from
+# an ncu capture of the kernel that the launcher picks for the workload (2 layers, 4 GB pool, the
+# workload's own token counts per launch, so nothing is scaled).
 TRAFFIC_PER_LAUNCH: dict = {
-    # profiles/gather_write_c2_ncu_full.md: kvx_gather_pages_kernel, c2 token counts (2-layer case,
-    # same tokens per launch): 582.1 MB read + 534.2 MB written (the rest still dirty in L2)
-    ("c2", "gather", 1): 1_116_300_000,
-    ("c2", "write", 1): 999_200_000,
+    ("c2", "gather"): 1_115_400_000,  # kvx_gather_pages_wide_kernel: 581.9 MB read + 533.5 MB written
+    ("c2", "write"): 999_200_000,     # kvx_write_rows_kernel
 }
+
+
+def all_ranks_true(flag: bool, dist) -> bool:
+    """Logical AND of a per-rank flag over the job."""
+    import torch
+    t = torch.tensor([1 if flag else 0], dtype=torch.int32, device="cuda")
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    return bool(int(t.item()))
+
+
+CONFIG_LEG_LAYERS = {"c1": 22, "c2": 2, "c3": 2, "c4": 4, "c5": 4}
+
+
+def run_config_leg(name: str, rank: int, world: int, dist, peak: float, verify: bool = True, reps: int = 5) -> dict:
+    """One of the other configurations on a few layers (each on its own pages), sharded by KV head
+    over the job's ranks like the headline workload: writes and gathers timed separately with CUDA
+    events (max over ranks), then the last layer byte-checked on every rank.  The fp8 configuration
+    also times the absmax -> scale reduction that precedes its writes."""
+    import torch
+    import kvx_b200
+    from kvx_b200 import abi, bench_support as bs, workloads
+    L = kvx_b200.lib()
+    name, _, layout = name.partition(":")
+    layout = layout or "nhd"
+    spec = workloads.SPECS[name]
+    out = {"workload": spec.name, "layout": layout}
+    if spec.heads % world:
+        return {"workload": spec.name, "skipped": f"{world} GPUs do not divide {spec.heads} KV heads"}
+    try:
+        dw = bs.setup_device_workload(spec, rank, world, layers=CONFIG_LEG_LAYERS[name], layout=layout)
+    except Exception as exc:  # e.g. out of memory on a smaller device
+        return {"workload": spec.name, "error": repr(exc)[:160]}
+    stream = torch.cuda.current_stream().cuda_stream
+    if verify:
+        bs.fill_sentinel(dw)
+    legs = [("write", lambda l: bs.launch_write(dw, l, stream), dw.write_bytes),
+            ("gather", lambda l: bs.launch_gather(dw, l, stream), dw.gather_bytes)]
+    if spec.cache_dtype == "f8e4m3":
+        io = abi.kv_io_desc(dw.meta.write_tokens, dw.heads, spec.dim, bs.DTYPE_CODE[spec.io_dtype],
+                            dw.key.data_ptr(), dw.value.data_ptr())
+        need = L.kvx_kv_scales_workspace_bytes(dw.heads)
+        ws = torch.zeros(need, dtype=torch.uint8, device="cuda")
+        ks, vs = torch.empty_like(dw.k_scale), torch.empty_like(dw.v_scale)
+
+        def scales(_l):
+            st = L.kvx_launch_kv_scales(C.byref(io), abi.SCALE_PER_HEAD, ks.data_ptr(), vs.data_ptr(), ws.data_ptr(),
+                                        need, stream)
+            if st != abi.STATUS_OK:
+                raise RuntimeError(f"kvx_launch_kv_scales status {st}")
+        legs.insert(0, ("scales", scales, 2 * dw.key.numel() * dw.key.element_size()))
+    for _ in range(2):  # warm-up
+        for _n, fn, _b in legs:
+            for l in range(dw.layers):
+                fn(l)
+    for leg, fn, nbytes in legs:
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            for l in range(dw.layers):
+                fn(l)
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device="cuda")
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us = float(t.item()) * 1e3 / (reps * dw.layers)
+        gbs = nbytes / us / 1e3
+        out[leg] = {"us_per_launch": round(us, 2), "gbs_per_gpu": round(gbs, 1), "frac_of_peak": round(gbs / peak, 4),
+                    "bytes_per_launch": int(nbytes)}
+    out["layers"] = dw.layers
+    out["heads_per_gpu"] = dw.heads
+    out["tokens"] = {"write": dw.meta.write_tokens, "valid": dw.meta.valid_tokens, "gathered": dw.meta.gather_tokens}
+    if spec.cache_dtype == "f8e4m3":
+        out["scales_match"] = all_ranks_true(bool(torch.equal(ks, dw.k_scale) and torch.equal(vs, dw.v_scale)), dist)
+    if verify:
+        res = bs.verify_layer(dw, dw.layers - 1)
+        out["verified"] = all_ranks_true(res["ok"], dist)
+        if not res["ok"]:
+            out["verify_rank%d" % rank] = res
+    del dw
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out
 
 
 def run_attention(dw, steps: int, group: int = 4) -> dict:

@@ -34,7 +34,10 @@ KVX_API void kvx_host_pipe_destroy(kvx_host_pipe_t *pipe);
  * DEVICE pointers.  Tokens are staged chunk by chunk (host->device copy of chunk i+1
  * overlaps the kernel of chunk i).  Asynchronous: returns once everything is enqueued; the
  * host buffers must stay valid until kvx_host_pipe_sync.  Semantics and status codes are
- * those of kvx_launch_write_kv. */
+ * those of kvx_launch_write_kv, including key / value whose token rows are further apart than
+ * num_kv_heads * head_dim elements (stride[0] larger than dense; the rows are then copied with a
+ * pitched copy and staged densely); elements inside a token row must be dense (UNSUPPORTED
+ * otherwise), and K and V must have one dtype. */
 KVX_API kvx_status_t kvx_host_write_kv(kvx_host_pipe_t *pipe, const kvx_cache_desc_t *cache,
                                        const kvx_write_desc_t *write);
 
@@ -50,7 +53,8 @@ KVX_API kvx_status_t kvx_host_gather_kv(kvx_host_pipe_t *pipe, const kvx_cache_d
                                         const kvx_scale_desc_t *v_scale);
 
 /* Blocks until every copy and kernel enqueued through the pipe has finished.
- * INTERNAL_ERROR if any of them failed. */
+ * INTERNAL_ERROR if any of them failed, or if a gather kernel abandoned a bounded wait
+ * (kvx_b200_device_error in kvx_paged_kv.h; the word is cleared). */
 KVX_API kvx_status_t kvx_host_pipe_sync(kvx_host_pipe_t *pipe);
 
 /* Bytes moved host->device and device->host through the pipe since creation. */

@@ -192,10 +192,22 @@ KVX_API kvx_status_t kvx_launch_kv_scales_static(const kvx_kv_io_desc_t *io,
 KVX_API uint64_t kvx_b200_launch_count(void);
 KVX_API void kvx_b200_reset_launch_count(void);
 
+/* Device-side give-up word.  The only kernels of this library that wait on anything are those
+ * of the bulk-async gather path ("gather_path" = 1, off by default): a wait on a staged copy is
+ * abandoned after one second ("bulk_wait_us"), the waiting thread sets a word in device memory,
+ * lets its copies in flight finish and returns; rows it had not reached stay unwritten, and the
+ * launcher has long since returned KVX_STATUS_OK.  This call returns that word for the current
+ * device (0 = no wait ever gave up, 1 = one did, -1 = the word could not be read) and, when
+ * `reset` is non-zero, clears it.  It copies from the device synchronously: call it after the
+ * streams in question have been synchronised.  kvx_host_pipe_sync consults it for its own
+ * launches.  No counterpart in the reference. */
+KVX_API int kvx_b200_device_error(int reset);
+
 /* Tuning knobs for experiments: name = "write_vecs_per_cta", "gather_path" (0 = registers,
  * 1 = bulk-async staging), ...; returns 0 when the name is known.  Defaults are the
- * measured-best values; production callers never need this.  No counterpart in the
- * reference. */
+ * measured-best values; production callers never need this.  Each knob is an atomic word: it
+ * may be set from any host thread at any time, and a launch that is being prepared meanwhile
+ * uses the old or the new value.  No counterpart in the reference. */
 KVX_API int kvx_b200_set_option(const char *name, int64_t value);
 KVX_API int64_t kvx_b200_get_option(const char *name);
 

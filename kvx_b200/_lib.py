@@ -19,7 +19,7 @@ EXPORTS = [
     "kvx_launch_write_kv_prefill_bf16", "kvx_launch_gather_kv_f32", "kvx_launch_gather_kv_f16",
     "kvx_launch_gather_kv_bf16", "kvx_launch_write_kv_f8e4m3", "kvx_launch_gather_kv_f8e4m3",
     "kvx_launch_gather_kv_varlen", "kvx_kv_scales_workspace_bytes", "kvx_launch_kv_scales", "kvx_launch_kv_scales_static",
-    "kvx_b200_launch_count",
+    "kvx_b200_launch_count", "kvx_b200_device_error",
     "kvx_b200_reset_launch_count", "kvx_b200_set_option", "kvx_b200_get_option",
     "kvx_host_pipe_create", "kvx_host_pipe_destroy", "kvx_host_write_kv", "kvx_host_gather_kv",
     "kvx_host_pipe_sync", "kvx_host_pipe_traffic",
@@ -74,6 +74,7 @@ def lib() -> C.CDLL:
     L.kvx_launch_kv_scales_static.argtypes = [P(abi.KvIoDesc), C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
     L.kvx_launch_kv_scales_static.restype = st
     L.kvx_b200_launch_count.argtypes, L.kvx_b200_launch_count.restype = [], C.c_uint64
+    L.kvx_b200_device_error.argtypes, L.kvx_b200_device_error.restype = [C.c_int], C.c_int
     L.kvx_b200_reset_launch_count.argtypes, L.kvx_b200_reset_launch_count.restype = [], None
     L.kvx_b200_set_option.argtypes, L.kvx_b200_set_option.restype = [C.c_char_p, C.c_int64], C.c_int
     L.kvx_b200_get_option.argtypes, L.kvx_b200_get_option.restype = [C.c_char_p], C.c_int64

@@ -196,6 +196,17 @@ def scale_desc(addr: Optional[int], granularity: int, heads: int, stride: int = 
     return s
 
 
+def kv_io_desc(num_tokens: int, heads: int, dim: int, io_dtype: int, key_addr: int, value_addr: int,
+               memory: int = MEMORY_DEVICE) -> KvIoDesc:
+    """A ``kvx_kv_io_desc_t`` for dense ``[num_tokens, heads, dim]`` K and V."""
+    io = KvIoDesc()
+    io.size = C.sizeof(KvIoDesc)
+    io.num_tokens, io.num_kv_heads, io.head_dim = num_tokens, heads, dim
+    io.key = tensor_desc(key_addr, io_dtype, (num_tokens, heads, dim), memory=memory)
+    io.value = tensor_desc(value_addr, io_dtype, (num_tokens, heads, dim), memory=memory)
+    return io
+
+
 def write_desc(num_tokens: int, heads: int, dim: int, io_dtype: int, key_addr: int, value_addr: int,
                slot_dtype: int, slots_addr: int, memory: int = MEMORY_DEVICE,
                k_scale: Optional[ScaleDesc] = None, v_scale: Optional[ScaleDesc] = None) -> WriteDesc:

@@ -38,6 +38,8 @@ class DeviceWorkload:
     gather: Optional[abi.GatherDesc] = None
     ks_desc: Optional[abi.ScaleDesc] = None
     vs_desc: Optional[abi.ScaleDesc] = None
+    layout: str = "nhd"             # "nhd" | "hnd" | "packed" (K and V in 16-byte pack groups) | "paged"
+                                    # (K in 16-byte pack groups, V [blocks, heads, dim, block_size])
 
     @property
     def write_bytes(self) -> int:
@@ -47,23 +49,44 @@ class DeviceWorkload:
     def gather_bytes(self) -> int:
         return self.meta.gather_bytes(self.heads)
 
+    def tensor_bytes(self) -> int:
+        s = self.meta.spec
+        return self.meta.num_blocks * s.block_size * self.heads * s.dim * workloads.ELEM[s.cache_dtype]
+
+    def packs(self) -> tuple[int, int]:
+        """Pack factor (elements per pack group) of the K and of the V tensor; 0 = not packed."""
+        x = 16 // workloads.ELEM[self.meta.spec.cache_dtype]
+        return {"nhd": (0, 0), "hnd": (0, 0), "packed": (x, x), "paged": (x, 1)}[self.layout]
+
     def layer_pages(self, layer: int):
-        """(K pages, V pages) of one layer as [num_blocks, block_size, heads, dim] views."""
+        """(K pages, V pages) of one layer, each a view of the pool with the axes in the order
+        (block, token in block, head, ...dim): [num_blocks, block_size, heads, dim] for NHD (as it
+        lies in memory) and HND (permuted), [num_blocks, block_size, heads, dim / pack, pack] for the
+        packed layouts.  Indexing the first two axes gives one token's row whatever the layout."""
         import torch
         s = self.meta.spec
-        n = self.meta.num_blocks * s.block_size * self.heads * s.dim * workloads.ELEM[s.cache_dtype]
-        shape = (self.meta.num_blocks, s.block_size, self.heads, s.dim)
+        n = self.tensor_bytes()
+        nb, bs, H, D = self.meta.num_blocks, s.block_size, self.heads, s.dim
         dt = workloads.torch_dtype(s.cache_dtype)
-        k = self.pool[(2 * layer) * n:(2 * layer + 1) * n].view(dt).view(shape)
-        v = self.pool[(2 * layer + 1) * n:(2 * layer + 2) * n].view(dt).view(shape)
-        return k, v
+        out = []
+        for which, pack in zip((0, 1), self.packs()):
+            flat = self.pool[(2 * layer + which) * n:(2 * layer + which + 1) * n].view(dt)
+            if self.layout == "nhd":
+                out.append(flat.view(nb, bs, H, D))
+            elif self.layout == "hnd":
+                out.append(flat.view(nb, H, bs, D).permute(0, 2, 1, 3))
+            else:
+                out.append(flat.view(nb, H, D // pack, bs, pack).permute(0, 3, 1, 2, 4))
+        return out[0], out[1]
 
 
 def setup_device_workload(spec: workloads.Spec, rank: int = 0, world: int = 1, layers: Optional[int] = None,
                           pool_gb: Optional[float] = None, num_blocks: Optional[int] = None,
-                          reserve_bytes: float = 6e9, seed: Optional[int] = None) -> DeviceWorkload:
+                          reserve_bytes: float = 6e9, seed: Optional[int] = None,
+                          layout: str = "nhd") -> DeviceWorkload:
     """Allocate and fill one rank's share.  The pool takes ``spec.pool_bytes / world`` or what
-    the device can spare (free memory minus inputs, outputs and ``reserve_bytes``)."""
+    the device can spare (free memory minus inputs, outputs and ``reserve_bytes``).  ``layout``
+    is the page layout the descriptors announce (see :class:`DeviceWorkload`)."""
     import torch
     dev = torch.device("cuda", torch.cuda.current_device())
     layers = spec.layers if layers is None else layers
@@ -102,7 +125,7 @@ def setup_device_workload(spec: workloads.Spec, rank: int = 0, world: int = 1, l
                         slots=torch.from_numpy(meta.slots).to(dev), table=torch.from_numpy(meta.table).to(dev),
                         lens=torch.from_numpy(meta.lens).to(dev),
                         out_k=torch.empty((S, Lmax, heads, spec.dim), dtype=key.dtype, device=dev),
-                        out_v=torch.empty((S, Lmax, heads, spec.dim), dtype=key.dtype, device=dev))
+                        out_v=torch.empty((S, Lmax, heads, spec.dim), dtype=key.dtype, device=dev), layout=layout)
     build_descriptors(dw)
     return dw
 
@@ -110,12 +133,20 @@ def setup_device_workload(spec: workloads.Spec, rank: int = 0, world: int = 1, l
 def build_descriptors(dw: DeviceWorkload) -> None:
     """Per-layer cache descriptors plus one write and one gather descriptor."""
     s, m = dw.meta.spec, dw.meta
-    geom = abi.CacheGeometry(m.num_blocks, s.block_size, dw.heads, s.dim)
+    code = {"nhd": abi.LAYOUT_NHD, "hnd": abi.LAYOUT_HND, "packed": abi.LAYOUT_HND_PACKED,
+            "paged": abi.LAYOUT_HND_PACKED}[dw.layout]
+    pack_k, pack_v = dw.packs()
+    geom = abi.CacheGeometry(m.num_blocks, s.block_size, dw.heads, s.dim, code, max(pack_k, 1))
+    geom_v = abi.CacheGeometry(m.num_blocks, s.block_size, dw.heads, s.dim, code, max(pack_v, 1))
     tensor_bytes = geom.elems * workloads.ELEM[s.cache_dtype]
     base = dw.pool.data_ptr()
     code_c, code_io = DTYPE_CODE[s.cache_dtype], DTYPE_CODE[s.io_dtype]
-    dw.caches = [abi.cache_desc(geom, code_c, base + (2 * l) * tensor_bytes, base + (2 * l + 1) * tensor_bytes)
-                 for l in range(dw.layers)]
+    dw.caches = []
+    for l in range(dw.layers):
+        c = abi.cache_desc(geom, code_c, base + (2 * l) * tensor_bytes, base + (2 * l + 1) * tensor_bytes)
+        if pack_v != pack_k:
+            c.v = abi.tensor_desc(base + (2 * l + 1) * tensor_bytes, code_c, geom_v.shape, None, code)
+        dw.caches.append(c)
     if s.cache_dtype == "f8e4m3":
         from . import ops
         dw.k_scale, dw.v_scale = ops.compute_kv_scales(dw.key, dw.value, per_head=True)
@@ -142,6 +173,147 @@ def launch_gather(dw: DeviceWorkload, layer: int, stream: int) -> None:
         st = lib().kvx_launch_gather_kv(C.byref(dw.caches[layer]), C.byref(dw.gather), stream)
     if st != abi.STATUS_OK:
         raise RuntimeError(f"kvx_launch_gather_kv status {st}")
+
+
+SENTINEL = 0x5A  # byte pattern the gather outputs are filled with before a verified run
+
+
+def fill_sentinel(dw: DeviceWorkload) -> None:
+    """Prepares a workload for :func:`verify_layer`: the page pool becomes a position-dependent
+    pattern (64-bit word i holds i, so no two rows of the pool look alike and a page taken from
+    the wrong place shows) and every byte of the gather outputs becomes ``SENTINEL``."""
+    import torch
+    words = dw.pool.view(torch.int64)
+    step = 1 << 28
+    for w0 in range(0, words.shape[0], step):
+        w1 = min(w0 + step, words.shape[0])
+        torch.arange(w0, w1, dtype=torch.int64, device=words.device, out=words[w0:w1])
+    dw.out_k.view(torch.uint8).fill_(SENTINEL)
+    dw.out_v.view(torch.uint8).fill_(SENTINEL)
+
+
+def _all_sentinel(rows) -> bool:
+    return bool((rows == SENTINEL).all())
+
+
+def _bits(t):
+    """The tensor's elements as integers of the same width: comparisons must see bit patterns
+    (the fill pattern and the sentinel contain NaN encodings, which never compare equal as floats)."""
+    import torch
+    return t.contiguous().view({1: torch.uint8, 2: torch.int16, 4: torch.int32}[t.element_size()])
+
+
+def verify_layer(dw: DeviceWorkload, layer: int) -> dict:
+    """Byte check of one layer of a workload that was prepared with :func:`fill_sentinel`,
+    then written, then gathered into ``dw.out_k`` / ``dw.out_v``.  Torch index operations on the
+    device only: an independent statement of the write and of the gather, for every page layout
+    :func:`build_descriptors` knows, that needs no CPU copy of the data.
+
+    * write_rows: rows of the pool addressed by valid slots hold the input rows (an fp8 cache:
+      within half an e4m3 step of ``input / scale``),
+    * untouched_pages: every other row of the layer's K and V tensors still holds the fill pattern,
+    * gather_live: output rows below a sequence's length hold what the pages hold at
+      ``table[s, p // block_size] * block_size + p % block_size`` (an fp8 cache: those bytes
+      dequantised with the head's scale and rounded to the output type),
+    * gather_dead: output rows at or past the length still hold the sentinel.
+    """
+    import torch
+    s, m = dw.meta.spec, dw.meta
+    dev = dw.pool.device
+    fp8 = s.cache_dtype == "f8e4m3"
+    bs_, nb = s.block_size, m.num_blocks
+    row_io = dw.heads * s.dim * workloads.ELEM[s.io_dtype]
+    kp, vp = dw.layer_pages(layer)
+    slots = dw.slots
+    valid = slots >= 0
+    idx = slots[valid]
+    inside = idx < nb * bs_                       # a slot beyond the pool is skipped by the write
+    blk, off = (idx // bs_)[inside], (idx % bs_)[inside]
+    vi = valid.nonzero().flatten()[inside]         # token numbers of the rows that must have landed
+
+    def rows_of(pages, b, o):                      # [n, heads * dim] elements of the given (block, offset) rows
+        return pages[b, o].reshape(b.shape[0], -1)
+
+    res = {}
+    ok = True
+    for pages, src, scale in ((kp, dw.key, dw.k_scale), (vp, dw.value, dw.v_scale)):
+        if fp8:
+            n = min(int(vi.shape[0]), 1 << 15)
+            got = rows_of(pages, blk[:n], off[:n]).view(torch.float8_e4m3fn).float().view(n, dw.heads, s.dim)
+            want = (src[vi[:n]].float() / scale[None, :, None]).clamp(-448.0, 448.0)
+            ulp = torch.clamp(want.abs(), min=2.0 ** -6) * 2.0 ** -3   # at least the e4m3 step at |want|
+            ok = ok and bool(((got - want).abs() <= 0.5 * ulp * 1.0001 + 2.0 ** -10).all())
+        else:
+            for t0 in range(0, vi.shape[0], 1 << 17):
+                sl = slice(t0, t0 + (1 << 17))
+                ok = ok and bool(torch.equal(_bits(rows_of(pages, blk[sl], off[sl])),
+                                             _bits(src[vi[sl]].reshape(-1, dw.heads * s.dim))))
+    res["write_rows"] = ok
+
+    # untouched rows, a slab of blocks at a time: the fill pattern is rebuilt for the slab and seen
+    # through the same permutation of axes as the pages
+    touched = torch.zeros(nb * bs_, dtype=torch.bool, device=dev)
+    touched[idx[inside]] = True
+    touched = touched.view(nb, bs_)
+    page_words = kp[0].numel() * kp.element_size() // 8
+    slab = max(1, int(2.5e8 // (page_words * 8)))
+    ok = True
+    for which, pages in ((0, kp), (1, vp)):
+        first_word = ((2 * layer + which) * dw.tensor_bytes()) // 8
+        for b0 in range(0, nb, slab):
+            b1 = min(nb, b0 + slab)
+            free = ~touched[b0:b1]
+            if not bool(free.any()):
+                continue
+            want = torch.arange(first_word + b0 * page_words, first_word + b1 * page_words, dtype=torch.int64,
+                                device=dev)
+            # same shape games as layer_pages, on 8-byte words viewed as cache elements
+            want_pages = _like_pages(dw, want.view(kp.dtype), b1 - b0, which)
+            ok = ok and bool(torch.equal(_bits(pages[b0:b1][free]), _bits(want_pages[free])))
+            del want, want_pages
+    res["untouched_pages"] = ok
+    del touched
+
+    S, Lmax = s.seqs, m.max_seq_len
+    lens = dw.lens.to(torch.int64)
+    ok_b = dw.out_k.view(torch.uint8).view(S, Lmax, row_io)
+    ov_b = dw.out_v.view(torch.uint8).view(S, Lmax, row_io)
+    step = max(1, int(2.5e8 // (Lmax * row_io)))
+    pos = torch.arange(Lmax, device=dev)
+    dead_ok, live_ok = True, True
+    block = dw.table.to(torch.int64)
+    for s0 in range(0, S, step):
+        live = pos[None, :] < lens[s0:s0 + step, None]
+        dead_ok = dead_ok and _all_sentinel(ok_b[s0:s0 + step][~live]) and _all_sentinel(ov_b[s0:s0 + step][~live])
+        sq, pp = live.nonzero(as_tuple=True)
+        b_of = block[s0 + sq, pp // bs_]
+        for out_b, pages, scale in ((ok_b, kp, dw.k_scale), (ov_b, vp, dw.v_scale)):
+            got = out_b[s0:s0 + step][live]
+            held = rows_of(pages, b_of, pp % bs_)
+            if fp8:
+                want = held.view(torch.float8_e4m3fn).float().view(-1, dw.heads, s.dim) * scale[None, :, None]
+                want = want.to(workloads.torch_dtype(s.io_dtype))
+            else:
+                want = held
+            live_ok = live_ok and bool(torch.equal(got, want.reshape(got.shape[0], -1).contiguous().view(torch.uint8)))
+            del got, want, held
+    res["gather_live"] = live_ok
+    res["gather_dead"] = dead_ok
+    res["ok"] = all(res.values())
+    return res
+
+
+def _like_pages(dw: DeviceWorkload, flat, blocks: int, which: int):
+    """``flat`` (the elements of ``blocks`` whole pages of the K (which = 0) or V (1) tensor, as
+    they lie in memory) with the axes in the order :meth:`DeviceWorkload.layer_pages` uses."""
+    s = dw.meta.spec
+    bs_, H, D = s.block_size, dw.heads, s.dim
+    pack = dw.packs()[which]
+    if dw.layout == "nhd":
+        return flat.view(blocks, bs_, H, D)
+    if dw.layout == "hnd":
+        return flat.view(blocks, H, bs_, D).permute(0, 2, 1, 3)
+    return flat.view(blocks, H, D // pack, bs_, pack).permute(0, 3, 1, 2, 4)
 
 
 class ClockSampler:

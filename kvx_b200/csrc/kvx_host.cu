@@ -157,16 +157,35 @@ KVX_API kvx_status_t kvx_host_write_kv(kvx_host_pipe_t *p, const kvx_cache_desc_
   if (write->io.key.data == nullptr || write->io.value.data == nullptr || write->slots.slots == nullptr)
     return KVX_STATUS_INVALID_ARGUMENT;
   if (row < 16 || static_cast<size_t>(row) > p->chunk_bytes) return KVX_STATUS_UNSUPPORTED;
+  // Host token rows may lie further apart than heads * dim elements (a view of a fused
+  // projection output), as kvx_launch_write_kv allows for device rows; inside a row the
+  // elements must be dense.  Rows are staged densely, so the kernels always see dense rows.
+  const int64_t e = elem_bytes(write->io.key.dtype);
+  const int64_t hd = static_cast<int64_t>(write->io.num_kv_heads) * write->io.head_dim;
+  for (const kvx_tensor_desc_t *t : {&write->io.key, &write->io.value}) {
+    if (t->ndim != 3) return KVX_STATUS_INVALID_ARGUMENT;
+    if (t->shape[0] != T || t->shape[1] != write->io.num_kv_heads || t->shape[2] != write->io.head_dim)
+      return KVX_STATUS_INVALID_ARGUMENT;
+    if (t->stride[2] != 1 || t->stride[1] != write->io.head_dim || t->stride[0] < hd) return KVX_STATUS_UNSUPPORTED;
+  }
+  if (write->io.value.dtype != write->io.key.dtype) return KVX_STATUS_UNSUPPORTED;
+  const int64_t k_pitch = write->io.key.stride[0] * e, v_pitch = write->io.value.stride[0] * e;
   const int64_t per_chunk = static_cast<int64_t>(p->chunk_bytes) / row;
 
   for (int64_t t0 = 0; t0 < T; t0 += per_chunk) {
     const int64_t n = std::min(per_chunk, T - t0);
     const int s = acquire_set(p, 0, p->h2d);
-    const char *hk = static_cast<const char *>(write->io.key.data) + t0 * row;
-    const char *hv = static_cast<const char *>(write->io.value.data) + t0 * row;
+    const char *hk = static_cast<const char *>(write->io.key.data) + t0 * k_pitch;
+    const char *hv = static_cast<const char *>(write->io.value.data) + t0 * v_pitch;
     const char *hs = static_cast<const char *>(write->slots.slots) + t0 * slot_b;
-    ok(p, cudaMemcpyAsync(p->k_stage[s], hk, n * row, cudaMemcpyHostToDevice, p->h2d));
-    ok(p, cudaMemcpyAsync(p->v_stage[s], hv, n * row, cudaMemcpyHostToDevice, p->h2d));
+    if (k_pitch == row)
+      ok(p, cudaMemcpyAsync(p->k_stage[s], hk, n * row, cudaMemcpyHostToDevice, p->h2d));
+    else
+      ok(p, cudaMemcpy2DAsync(p->k_stage[s], row, hk, k_pitch, row, n, cudaMemcpyHostToDevice, p->h2d));
+    if (v_pitch == row)
+      ok(p, cudaMemcpyAsync(p->v_stage[s], hv, n * row, cudaMemcpyHostToDevice, p->h2d));
+    else
+      ok(p, cudaMemcpy2DAsync(p->v_stage[s], row, hv, v_pitch, row, n, cudaMemcpyHostToDevice, p->h2d));
     ok(p, cudaMemcpyAsync(p->slot_stage[s], hs, n * slot_b, cudaMemcpyHostToDevice, p->h2d));
     ok(p, cudaEventRecord(p->ready[s], p->h2d));
     ok(p, cudaStreamWaitEvent(p->exec, p->ready[s], 0));
@@ -175,6 +194,7 @@ KVX_API kvx_status_t kvx_host_write_kv(kvx_host_pipe_t *p, const kvx_cache_desc_
     kvx_write_desc_t w = *write;
     w.io.num_tokens = static_cast<uint32_t>(n);
     w.io.key.shape[0] = w.io.value.shape[0] = n;
+    w.io.key.stride[0] = w.io.value.stride[0] = hd;  // staged rows are dense
     w.io.key.data = p->k_stage[s];
     w.io.value.data = p->v_stage[s];
     w.io.key.memory = w.io.value.memory = KVX_MEMORY_DEVICE;
@@ -286,6 +306,8 @@ KVX_API kvx_status_t kvx_host_pipe_sync(kvx_host_pipe_t *p) {
   good = (cudaStreamSynchronize(p->exec) == cudaSuccess) && good;
   good = (cudaStreamSynchronize(p->d2h) == cudaSuccess) && good;
   good = (cudaStreamSynchronize(p->d2h_v) == cudaSuccess) && good;
+  // a gather kernel that abandoned a bounded wait has left rows unwritten
+  if (good && kvx_b200_device_error(1) != 0) good = false;
   if (!good || p->failed) {
     p->failed = false;
     return KVX_STATUS_INTERNAL_ERROR;

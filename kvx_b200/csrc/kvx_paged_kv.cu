@@ -43,30 +43,36 @@ namespace {
 
 // ------------------------------------------------------------------ tunables ----------
 
+// Written by kvx_b200_set_option, read by the launchers, possibly from different host threads:
+// every field is an atomic, read and written with relaxed ordering (a launch sees the old or the
+// new value of a knob, never a torn one).
 struct Options {
-  int64_t write_vecs_per_cta = 1024;  // 16-byte vectors of K (and of V) one write CTA moves
-  int64_t write_unroll = 4;           // vectors of K and of V in flight per thread (1,2,4)
-  int64_t gather_path = 2;            // 0 = CTA-granular register copy, 1 = cp.async.bulk staging, 2 = warp-granular
-  int64_t gather_tile_bytes = 16384;  // bytes of K (and of V) one CTA moves per work item (path 0)
-  int64_t gather_ctas_per_sm = 256;   // most CTAs launched per SM (register paths; 4 are resident at a time)
-  int64_t gather_part_bytes = 4096;   // span one warp copies per work item (one unrolled iteration)
-  int64_t bulk_stage_bytes = 16384;   // bytes per shared-memory stage (bulk path)
-  int64_t bulk_stages = 4;            // stages per pipe (bulk path)
-  int64_t bulk_pipes = 3;             // pipes (elected threads) per CTA (bulk path)
-  int64_t bulk_lag = 2;               // loads a pipe keeps in flight ahead of its stores
-  int64_t bulk_ctas_per_sm = 1;
-  int64_t force_generic = 0;          // 1 = always take the one-element-per-thread tier
-  int64_t pdl = 1;                    // 1 = launch with programmatic stream serialization
-  int64_t wide = 1;                   // 1 = 256-bit accesses where alignment allows
-  int64_t gather_rect_items = 40000;  // padded (sequence, page, part, K|V) rectangles up to this size are walked as they are
-  int64_t write_prefetch_waves = 2;   // leading write CTAs (in units of 8 per SM) that prefetch their rows into the L2
+  std::atomic<int64_t> write_vecs_per_cta{1024};  // 16-byte vectors of K (and of V) one write CTA moves
+  std::atomic<int64_t> write_unroll{4};           // vectors of K and of V in flight per thread (1,2,4)
+  std::atomic<int64_t> gather_path{2};            // 0 = CTA-granular register copy, 1 = cp.async.bulk staging, 2 = warp-granular
+  std::atomic<int64_t> gather_tile_bytes{16384};  // bytes of K (and of V) one CTA moves per work item (path 0)
+  std::atomic<int64_t> gather_ctas_per_sm{256};   // most CTAs launched per SM (register paths; 4 are resident at a time)
+  std::atomic<int64_t> gather_part_bytes{4096};   // span one warp copies per work item (one unrolled iteration)
+  std::atomic<int64_t> bulk_stage_bytes{16384};   // bytes per shared-memory stage (bulk path)
+  std::atomic<int64_t> bulk_stages{4};            // stages per pipe (bulk path)
+  std::atomic<int64_t> bulk_pipes{3};             // pipes (elected threads) per CTA (bulk path)
+  std::atomic<int64_t> bulk_lag{2};               // loads a pipe keeps in flight ahead of its stores
+  std::atomic<int64_t> bulk_ctas_per_sm{1};
+  std::atomic<int64_t> force_generic{0};          // 1 = always take the one-element-per-thread tier
+  std::atomic<int64_t> pdl{1};                    // 1 = launch with programmatic stream serialization
+  std::atomic<int64_t> wide{1};                   // 1 = 256-bit accesses where alignment allows
+  std::atomic<int64_t> gather_rect_items{40000};  // padded (sequence, page, part, K|V) rectangles up to this size are walked as they are
+  std::atomic<int64_t> write_prefetch_waves{2};   // leading write CTAs (in units of 8 per SM) that prefetch their rows into the L2
+  std::atomic<int64_t> bulk_wait_us{1000000};     // a bulk-path wait on a copy is abandoned after this long
+  std::atomic<int64_t> bulk_test_stall{0};        // test hook: pipe 0 of CTA 0 first waits on a barrier nothing completes
 };
 Options g_opt;
+inline int64_t opt(const std::atomic<int64_t> &knob) { return knob.load(std::memory_order_relaxed); }
 std::atomic<uint64_t> g_launches{0};
 
 struct OptionName {
   const char *name;
-  int64_t Options::*field;
+  std::atomic<int64_t> Options::*field;
 };
 const OptionName kOptionNames[] = {
     {"write_vecs_per_cta", &Options::write_vecs_per_cta},
@@ -85,6 +91,8 @@ const OptionName kOptionNames[] = {
     {"force_generic", &Options::force_generic},
     {"pdl", &Options::pdl},
     {"wide", &Options::wide},
+    {"bulk_wait_us", &Options::bulk_wait_us},
+    {"bulk_test_stall", &Options::bulk_test_stall},
 };
 
 // Per-device facts, looked up once (never per launch).
@@ -156,7 +164,9 @@ bool view_packed16(const PageView &v, int64_t elem, int64_t dim) {
 
 // ------------------------------------------------------------------ device helpers ----
 
-__device__ int g_device_error;  // set when a bounded wait gives up; read by the host on demand
+// Set to 1 when a bounded wait gives up (the bulk gather path is the only place that waits);
+// the host reads and clears it with kvx_b200_device_error().
+__device__ int g_device_error;
 
 __device__ __forceinline__ uint4 load_stream(const void *p) {
   // Read-once data: bypass L1 allocation.
@@ -798,6 +808,7 @@ struct GatherShape {
   // tok < indptr[s + 1] - indptr[s] (one entry per cached token).
   const void *indptr;  // NULL = PACKED
   int32_t indptr64;    // indptr entries are 64-bit
+  int64_t indices_count;  // entries of `table` (RAGGED): tokens whose entry would lie outside are skipped
   // KV_OFFSETS tables (KVX_SPEC.md:116-122, KV_CACHE_LAYOUTS.md:89-96): int32
   // [S, beam_width, 2, max_blocks]; entry [s][0][0][lb] names the K page and [s][0][1][lb] the V
   // page of logical block lb.  Bit 31 of an entry selects the secondary pool, the low 31 bits
@@ -884,6 +895,7 @@ __global__ void __launch_bounds__(256)
     if (s.indptr != nullptr) {
       const int64_t first = read_indptr(s, seq);
       if (tok >= read_indptr(s, seq + 1) - first) return;
+      if (first < 0 || first + tok >= s.indices_count) return;  // damaged indptr: skipped, like a bad page id
       b = read_idx<IdxT>(s.table, first + tok);
     } else {
       if (lb >= s.max_blocks) return;
@@ -1292,7 +1304,9 @@ __global__ void __launch_bounds__(kGatherThreads) kvx_gather_ragged_kernel(const
   const int ntok = static_cast<int>(min(static_cast<int64_t>(p.part_vecs), len - t0));
   if (tid < ntok) {
     const int tok = t0 + tid;
-    const int64_t b = read_idx<IdxT>(p.s.table, first + tok);
+    // an entry outside the index array (damaged indptr) is skipped, like a bad page id
+    const bool inside = first >= 0 && first + tok < p.s.indices_count;
+    const int64_t b = inside ? read_idx<IdxT>(p.s.table, first + tok) : -1;
     int64_t ko = -1, vo = -1;
     if (b >= 0 && b < p.num_blocks) {
       const int64_t o = tok % p.block_size;
@@ -1423,7 +1437,6 @@ __global__ void __launch_bounds__(kGatherThreads) kvx_gather_f8_kernel(const Gat
 
 constexpr int kBulkMaxPipes = 8;
 constexpr int kBulkMaxStages = 8;
-constexpr uint64_t kBulkWaitNs = 1000000000ull;  // a wait on a copy is abandoned after one second
 
 __device__ __forceinline__ uint32_t smem_addr(const void *p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -1440,9 +1453,9 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// Wait for the phase with the given parity, for at most kBulkWaitNs of wall time (a copy that
-// has not landed after that long never will); false = gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+// Wait for the phase with the given parity, for at most limit_ns of wall time (one second unless
+// the knob says otherwise: a copy that has not landed after that long never will); false = gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint64_t limit_ns) {
   const uint32_t a = smem_addr(bar);
   uint64_t deadline = 0;
   for (uint32_t i = 0;; ++i) {
@@ -1459,7 +1472,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
       __nanosleep(64);
       const uint64_t now = global_timer_ns();
       if (deadline == 0)
-        deadline = now + kBulkWaitNs;
+        deadline = now + limit_ns;
       else if (now > deadline)
         return false;
     }
@@ -1489,6 +1502,8 @@ __device__ __forceinline__ void bulk_wait_all() {
 struct BulkParams {
   GatherPagesParams g;  // kSeg = false geometry; part_vecs * 16 <= stage_bytes
   int32_t stage_bytes, stages, pipes, lag;
+  int64_t wait_ns;     // limit of every wait on a copy
+  int32_t test_stall;  // test hook, see kvx_gather_bulk_kernel
 };
 
 template <typename IdxT>
@@ -1496,13 +1511,13 @@ __global__ void __launch_bounds__(kGatherThreads) kvx_gather_bulk_kernel(const B
   const GatherPagesParams &p = bp.g;
   extern __shared__ __align__(128) unsigned char s_raw[];
   __shared__ int32_t s_warp_tot[kGatherWarps];
-  __shared__ __align__(8) uint64_t s_bar[kBulkMaxPipes * kBulkMaxStages];
+  __shared__ __align__(8) uint64_t s_bar[kBulkMaxPipes * kBulkMaxStages + 1];
   // layout of dynamic shared memory: [stages of all pipes][prefix]
   unsigned char *stage_mem = s_raw;
   int32_t *s_prefix =
       reinterpret_cast<int32_t *>(s_raw + static_cast<size_t>(bp.pipes) * bp.stages * bp.stage_bytes);
 
-  if (threadIdx.x < kBulkMaxPipes * kBulkMaxStages) mbar_init(&s_bar[threadIdx.x], 1);
+  if (threadIdx.x <= kBulkMaxPipes * kBulkMaxStages) mbar_init(&s_bar[threadIdx.x], 1);
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   int64_t chunks;
   if (p.use_prefix)
@@ -1528,11 +1543,16 @@ __global__ void __launch_bounds__(kGatherThreads) kvx_gather_bulk_kernel(const B
   uint32_t bytes_q[kBulkMaxStages] = {};
   int64_t issued = 0, retired = 0;
   bool failed = false;
+  // Test hook for the give-up path: the first pipe of the grid waits on the spare barrier, for
+  // which no copy was ever issued, before it has issued anything itself.  The wait runs out,
+  // the pipe reports and leaves with nothing in flight; its work items stay undone.
+  if (bp.test_stall && pipe == 0)
+    failed = !mbar_wait(&s_bar[kBulkMaxPipes * kBulkMaxStages], 0, static_cast<uint64_t>(bp.wait_ns));
 
   auto retire_one = [&]() {
     const int st = static_cast<int>(retired % bp.stages);
     const uint32_t parity = static_cast<uint32_t>((retired / bp.stages) & 1);
-    if (!mbar_wait(&my_bar[st], parity)) {
+    if (!mbar_wait(&my_bar[st], parity, static_cast<uint64_t>(bp.wait_ns))) {
       failed = true;
       return;
     }
@@ -1728,7 +1748,7 @@ void launch_streaming(void (*kernel)(Params), unsigned grid, unsigned block, siz
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = g_opt.pdl ? 1 : 0;
+  cfg.numAttrs = opt(g_opt.pdl) ? 1 : 0;
   cudaLaunchKernelEx(&cfg, kernel, p);
 }
 
@@ -1765,7 +1785,7 @@ kvx_status_t launch_write_generic(const kvx_write_desc_t *w, const GenericParams
 // Tokens per CTA: aim at `write_vecs_per_cta` vectors of K per CTA, but never fewer CTAs
 // than fill the machine twice when the batch is small.
 int pick_tok_tile(int64_t tokens, int64_t vpr, int sm_count) {
-  int64_t tile = g_opt.write_vecs_per_cta / vpr;
+  int64_t tile = opt(g_opt.write_vecs_per_cta) / vpr;
   if (tile < 1) tile = 1;
   if (tile > kMaxTokTile) tile = kMaxTokTile;
   const int64_t want_ctas = static_cast<int64_t>(sm_count) * 4;
@@ -1841,7 +1861,7 @@ kvx_status_t write_impl(const kvx_cache_desc_t *cache, const kvx_write_desc_t *w
   const bool k_packed = !fp8 && view_packed16(gp.k, elem, D), v_packed = !fp8 && view_packed16(gp.v, elem, D);
   const int64_t k_pitch = write->io.key.stride[0] * io_elem, v_pitch = write->io.value.stride[0] * io_elem;
   const bool pitched = k_pitch != row_bytes || v_pitch != row_bytes;  // token rows further apart than dense
-  const bool vec_ok = !g_opt.force_generic && (D * io_elem) % 16 == 0 && k_pitch % 16 == 0 && v_pitch % 16 == 0 &&
+  const bool vec_ok = !opt(g_opt.force_generic) && (D * io_elem) % 16 == 0 && k_pitch % 16 == 0 && v_pitch % 16 == 0 &&
                       !(pitched && (k_packed || v_packed)) &&
                       (!fp8 || (gp.k.head * H < INT32_MAX && gp.v.head * H < INT32_MAX)) &&  // 32-bit in-page offsets
                       aligned(write->io.key.data, 16) && aligned(write->io.value.data, 16) &&
@@ -1879,19 +1899,19 @@ kvx_status_t write_impl(const kvx_cache_desc_t *cache, const kvx_write_desc_t *w
       p.tile_shift = shift_of(tile);
     }
     const int grid = static_cast<int>((T + p.tok_tile - 1) / p.tok_tile);
-    const int unroll = static_cast<int>(g_opt.write_unroll);
+    const int unroll = static_cast<int>(opt(g_opt.write_unroll));
     // Leading CTAs that prefetch (see write_prologue): worth 1 us on a launch of a few tens of
     // microseconds, nothing on a long one, where back-to-back writes even lose 1 % to the early
     // requests competing with the previous launch's last stores -- so only grids of up to twice
     // that many CTAs use it.
-    const int64_t lead = static_cast<int64_t>(dev.sm_count) * 8 * g_opt.write_prefetch_waves;
+    const int64_t lead = static_cast<int64_t>(dev.sm_count) * 8 * opt(g_opt.write_prefetch_waves);
     p.early_ctas = grid <= 2 * lead ? static_cast<int32_t>(std::min<int64_t>(lead, INT32_MAX)) : 0;
     if (fp8) {
       WriteF8Params q{p, ks, vs, static_cast<int32_t>(D), static_cast<int32_t>(H)};
       // 256-bit variant: 16-bit inputs whose head rows are whole 32-byte vectors, dense and 32-byte
       // aligned, destinations 16-byte aligned, shapes powers of two
       const int64_t row32 = row_bytes / 32, head32 = D * io_elem / 32;
-      if (g_opt.wide && io_elem == 2 && !pitched && (D * io_elem) % 32 == 0 && H <= kF8CachedHeads &&
+      if (opt(g_opt.wide) && io_elem == 2 && !pitched && (D * io_elem) % 32 == 0 && H <= kF8CachedHeads &&
           is_pow2(row32) && is_pow2(head32) && aligned(write->io.key.data, 32) && aligned(write->io.value.data, 32) &&
           aligned(gp.k.base, 16) && aligned(gp.v.base, 16) && gp.k.blk % 16 == 0 && gp.v.blk % 16 == 0 &&
           gp.k.tok % 16 == 0 && gp.v.tok % 16 == 0 && gp.k.head % 16 == 0 && gp.v.head % 16 == 0) {
@@ -2087,6 +2107,7 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
   gs.max_seq_len = static_cast<int32_t>(L);
   gs.indptr = nullptr;
   gs.indptr64 = 0;
+  gs.indices_count = gather->block_table.indices_count;
   gs.pool[0] = gs.pool[1] = nullptr;
   gs.pool_block_bytes = 0;
   gs.beam_width = 1;
@@ -2127,7 +2148,7 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
   const bool k_packed = !fp8 && !ragged && view_packed16(gp.k, elem, D);
   const bool v_packed = !fp8 && !ragged && view_packed16(gp.v, elem, D);
   const bool packed = k_packed || v_packed;
-  const bool vec_ok = !g_opt.force_generic && (D * io_elem) % 16 == 0 && aligned(gather->io.key.data, 16) &&
+  const bool vec_ok = !opt(g_opt.force_generic) && (D * io_elem) % 16 == 0 && aligned(gather->io.key.data, 16) &&
                       aligned(gather->io.value.data, 16) && (k_packed || view_vectorisable(gp.k, elem, D, in_vec)) &&
                       (v_packed || view_vectorisable(gp.v, elem, D, in_vec)) && chunk_vecs < (int64_t{1} << 30) &&
                       S * static_cast<int64_t>(gs.max_blocks) < (int64_t{1} << 31) &&
@@ -2165,7 +2186,7 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
-        cfg.numAttrs = g_opt.pdl ? 1 : 0;
+        cfg.numAttrs = opt(g_opt.pdl) ? 1 : 0;
         if (s32)
           cudaLaunchKernelEx(&cfg, kvx_gather_ragged_kernel<int32_t, 4>, p);
         else
@@ -2177,15 +2198,17 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
                                   gp.k.tok == H * D * elem && gp.v.tok == H * D * elem;
     const size_t prefix_bytes = p.use_prefix ? static_cast<size_t>(S + 1) * sizeof(int32_t) : 0;
 
-    if (contiguous_pages && g_opt.gather_path == 1 && !offsets) {
+    if (contiguous_pages && opt(g_opt.gather_path) == 1 && !offsets) {
       // ---- bulk tier ----
       BulkParams bp;
       bp.g = p;
-      int64_t stage = g_opt.bulk_stage_bytes / 16 * 16;
+      int64_t stage = opt(g_opt.bulk_stage_bytes) / 16 * 16;
       if (stage < 1024) stage = 1024;
-      bp.stages = static_cast<int32_t>(g_opt.bulk_stages < 2 ? 2 : (g_opt.bulk_stages > kBulkMaxStages ? kBulkMaxStages : g_opt.bulk_stages));
-      bp.pipes = static_cast<int32_t>(g_opt.bulk_pipes < 1 ? 1 : (g_opt.bulk_pipes > kBulkMaxPipes ? kBulkMaxPipes : g_opt.bulk_pipes));
-      bp.lag = static_cast<int32_t>(g_opt.bulk_lag < 1 ? 1 : (g_opt.bulk_lag > bp.stages - 1 ? bp.stages - 1 : g_opt.bulk_lag));
+      bp.stages = static_cast<int32_t>(opt(g_opt.bulk_stages) < 2 ? 2 : (opt(g_opt.bulk_stages) > kBulkMaxStages ? kBulkMaxStages : opt(g_opt.bulk_stages)));
+      bp.pipes = static_cast<int32_t>(opt(g_opt.bulk_pipes) < 1 ? 1 : (opt(g_opt.bulk_pipes) > kBulkMaxPipes ? kBulkMaxPipes : opt(g_opt.bulk_pipes)));
+      bp.wait_ns = std::max<int64_t>(1, opt(g_opt.bulk_wait_us)) * 1000;
+      bp.test_stall = opt(g_opt.bulk_test_stall) != 0;
+      bp.lag = static_cast<int32_t>(opt(g_opt.bulk_lag) < 1 ? 1 : (opt(g_opt.bulk_lag) > bp.stages - 1 ? bp.stages - 1 : opt(g_opt.bulk_lag)));
       const int64_t chunk_bytes = chunk_vecs * 16;
       if (stage > chunk_bytes) stage = chunk_bytes;
       bp.stage_bytes = static_cast<int32_t>(stage);
@@ -2194,7 +2217,7 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
       const size_t smem = static_cast<size_t>(bp.pipes) * bp.stages * bp.stage_bytes + prefix_bytes;
       if (smem <= static_cast<size_t>(dev.max_smem_optin) - 1024) {
         const int64_t max_items = S * gs.max_blocks * bp.g.parts * 2;
-        int64_t grid = static_cast<int64_t>(dev.sm_count) * (g_opt.bulk_ctas_per_sm < 1 ? 1 : g_opt.bulk_ctas_per_sm);
+        int64_t grid = static_cast<int64_t>(dev.sm_count) * (opt(g_opt.bulk_ctas_per_sm) < 1 ? 1 : opt(g_opt.bulk_ctas_per_sm));
         const int64_t need = (max_items + bp.pipes - 1) / bp.pipes;
         if (grid > need) grid = need;
         if (s32) {
@@ -2213,7 +2236,7 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
     // ---- register tier ----
     // The dequantising gather does more work per byte read and measured best with whole pages per
     // warp and a small grid (5 724 GB/s vs 4 886 GB/s with the copy gather's settings).
-    int64_t part_vecs = (fp8 ? std::max<int64_t>(g_opt.gather_part_bytes, 32768) : g_opt.gather_part_bytes) / 16;
+    int64_t part_vecs = (fp8 ? std::max<int64_t>(opt(g_opt.gather_part_bytes), 32768) : opt(g_opt.gather_part_bytes)) / 16;
     if (part_vecs < 32) part_vecs = 32;
     if (part_vecs > chunk_vecs) part_vecs = chunk_vecs;
     p.part_vecs = static_cast<int32_t>(part_vecs);
@@ -2229,8 +2252,8 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
     // the Llama-3-8B batch: 24.4 us instead of 25.5 us), while the items of pages that do not
     // exist cost a resident warp a few cached loads each.  Large rectangles can be mostly
     // padding (decode batches with contexts of 1 to 1 024 pages: 1.8x slower uncompacted).
-    if (!fp8 && max_items <= g_opt.gather_rect_items) p.use_prefix = 0;
-    int64_t per_sm = g_opt.gather_ctas_per_sm < 1 ? 1 : g_opt.gather_ctas_per_sm;
+    if (!fp8 && max_items <= opt(g_opt.gather_rect_items)) p.use_prefix = 0;
+    int64_t per_sm = opt(g_opt.gather_ctas_per_sm) < 1 ? 1 : opt(g_opt.gather_ctas_per_sm);
     if (fp8) per_sm = std::min<int64_t>(per_sm, 8);
     int64_t grid = static_cast<int64_t>(dev.sm_count) * per_sm;
     grid = std::max<int64_t>(1, std::min(grid, fp8 ? need : (need + 1) / 2));
@@ -2261,8 +2284,8 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
         launch_streaming(kvx_gather_pages_kernel<int32_t, true, 8, true>, ug, kGatherThreads, prefix_bytes, cs, p);
       return finish_launch();
     }
-    if (g_opt.gather_path == 2 || packed) {  // warp-granular items
-      const bool wide_ok = g_opt.wide && !packed && (p.part_vecs % 2) == 0 && (p.vpr % 2) == 0 &&
+    if (opt(g_opt.gather_path) == 2 || packed) {  // warp-granular items
+      const bool wide_ok = opt(g_opt.wide) && !packed && (p.part_vecs % 2) == 0 && (p.vpr % 2) == 0 &&
                            aligned(p.k_base, 32) && aligned(p.v_base, 32) && aligned(p.key_out, 32) &&
                            aligned(p.value_out, 32) && p.k_blk % 32 == 0 && p.v_blk % 32 == 0 &&
                            (contiguous_pages || ((p.vps % 2) == 0 && p.k_tok % 32 == 0 && p.v_tok % 32 == 0 &&
@@ -2296,13 +2319,13 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
     }
     // CTA-granular items (default): one item = K and V of one part.
     {
-      int64_t tile_vecs = g_opt.gather_tile_bytes / 16;
+      int64_t tile_vecs = opt(g_opt.gather_tile_bytes) / 16;
       if (tile_vecs < kGatherThreads) tile_vecs = kGatherThreads;
       if (tile_vecs > chunk_vecs) tile_vecs = chunk_vecs;
       p.part_vecs = static_cast<int32_t>(tile_vecs);
       p.parts = static_cast<int32_t>((chunk_vecs + tile_vecs - 1) / tile_vecs);
       const int64_t tile_items = S * gs.max_blocks * p.parts;
-      int64_t tgrid = static_cast<int64_t>(dev.sm_count) * (g_opt.gather_ctas_per_sm < 1 ? 1 : g_opt.gather_ctas_per_sm);
+      int64_t tgrid = static_cast<int64_t>(dev.sm_count) * (opt(g_opt.gather_ctas_per_sm) < 1 ? 1 : opt(g_opt.gather_ctas_per_sm));
       if (tgrid > tile_items) tgrid = tile_items;
       const unsigned tg = static_cast<unsigned>(tgrid);
       if (s32) {
@@ -2456,9 +2479,12 @@ KVX_API size_t kvx_kv_scales_workspace_bytes(uint32_t num_kv_heads) {
   return (raw + 255) / 256 * 256;
 }
 
-KVX_API kvx_status_t kvx_launch_kv_scales(const kvx_kv_io_desc_t *io, kvx_scale_granularity_t granularity,
-                                          float *k_scale_out, float *v_scale_out, void *workspace,
-                                          size_t workspace_bytes, void *stream) {
+// Body of both scale entry points.  `clear_first`: the workspace may hold anything (the shared
+// in-library array): the part this call uses is zeroed on the stream once every argument check
+// has passed, so a rejected call enqueues nothing at all.
+static kvx_status_t kv_scales_impl(const kvx_kv_io_desc_t *io, kvx_scale_granularity_t granularity,
+                                   float *k_scale_out, float *v_scale_out, void *workspace,
+                                   size_t workspace_bytes, void *stream, bool clear_first) {
   if (io == nullptr || k_scale_out == nullptr || v_scale_out == nullptr || workspace == nullptr)
     return KVX_STATUS_INVALID_ARGUMENT;
   if (io->size < sizeof(kvx_kv_io_desc_t)) return KVX_STATUS_INVALID_ARGUMENT;
@@ -2479,6 +2505,12 @@ KVX_API kvx_status_t kvx_launch_kv_scales(const kvx_kv_io_desc_t *io, kvx_scale_
   if ((D * elem) % 16 != 0 || !aligned(io->key.data, 16) || !aligned(io->value.data, 16) ||
       2 * H * sizeof(uint32_t) > 40960)
     return KVX_STATUS_UNSUPPORTED;
+
+  if (clear_first &&
+      cudaMemsetAsync(workspace, 0, kvx_kv_scales_workspace_bytes(io->num_kv_heads), as_stream(stream)) != cudaSuccess) {
+    cudaGetLastError();
+    return KVX_STATUS_INTERNAL_ERROR;
+  }
 
   ScalesParams p;
   p.key = static_cast<const char *>(io->key.data);
@@ -2513,6 +2545,12 @@ KVX_API kvx_status_t kvx_launch_kv_scales(const kvx_kv_io_desc_t *io, kvx_scale_
   return finish_launch();
 }
 
+KVX_API kvx_status_t kvx_launch_kv_scales(const kvx_kv_io_desc_t *io, kvx_scale_granularity_t granularity,
+                                          float *k_scale_out, float *v_scale_out, void *workspace,
+                                          size_t workspace_bytes, void *stream) {
+  return kv_scales_impl(io, granularity, k_scale_out, v_scale_out, workspace, workspace_bytes, stream, false);
+}
+
 // ---------------------------------------------------------------- scales, no allocation --
 // Scratch for kvx_launch_kv_scales_static: the running maxima and the CTA ticket of the scale
 // reduction, sized for KVX_KV_SCALES_STATIC_MAX_HEADS heads.  It is part of the loaded module,
@@ -2521,11 +2559,11 @@ constexpr size_t kScalesStaticWords = (2 * KVX_KV_SCALES_STATIC_MAX_HEADS + 1 + 
 static __device__ __align__(256) uint32_t g_scales_static_scratch[kScalesStaticWords];
 
 namespace {
-// Device address of g_scales_static_scratch per device.  In host code the array's name is only
-// a handle for the runtime, never an address a kernel may use, so the address is asked for
-// once per device (with that device current) and cached.
-uint32_t *g_scales_static_ptr[64];
-std::atomic<int> g_scales_static_ready[64];
+// Device address of g_scales_static_scratch per device (NULL = not asked for yet).  In host code
+// the array's name is only a handle for the runtime, never an address a kernel may use, so the
+// address is asked for once per device, with that device current, and cached.  Two host threads
+// that make the first call together both ask and both store the same address.
+std::atomic<uint32_t *> g_scales_static_ptr[64];
 }  // namespace
 
 KVX_API kvx_status_t kvx_launch_kv_scales_static(const kvx_kv_io_desc_t *io,
@@ -2536,26 +2574,34 @@ KVX_API kvx_status_t kvx_launch_kv_scales_static(const kvx_kv_io_desc_t *io,
   if (io->num_kv_heads > KVX_KV_SCALES_STATIC_MAX_HEADS) return KVX_STATUS_OUT_OF_RANGE;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return KVX_STATUS_INTERNAL_ERROR;
-  if (g_scales_static_ready[dev].load(std::memory_order_acquire) == 0) {
+  uint32_t *scratch = g_scales_static_ptr[dev].load(std::memory_order_acquire);
+  if (scratch == nullptr) {
     void *addr = nullptr;
     if (cudaGetSymbolAddress(&addr, g_scales_static_scratch) != cudaSuccess || addr == nullptr) {
       cudaGetLastError();
       return KVX_STATUS_INTERNAL_ERROR;
     }
-    g_scales_static_ptr[dev] = static_cast<uint32_t *>(addr);
-    g_scales_static_ready[dev].store(1, std::memory_order_release);
+    scratch = static_cast<uint32_t *>(addr);
+    g_scales_static_ptr[dev].store(scratch, std::memory_order_release);
   }
-  uint32_t *scratch = g_scales_static_ptr[dev];
-  const size_t bytes = sizeof(uint32_t) * kScalesStaticWords;
-  // The array is shared by every call and keeps whatever the last one left; the reduction
-  // needs zeros, so clear the part it uses on the caller's stream first.
-  const size_t used = kvx_kv_scales_workspace_bytes(io->num_kv_heads);
-  if (cudaMemsetAsync(scratch, 0, used < bytes ? used : bytes, reinterpret_cast<cudaStream_t>(stream)) !=
-      cudaSuccess) {
+  // The array is shared by every call and keeps whatever the last one left; the reduction needs
+  // zeros, so the part it uses is cleared on the caller's stream -- after the argument checks,
+  // so that a rejected call leaves the array (which an earlier call may still be using) alone.
+  return kv_scales_impl(io, granularity, k_scale_out, v_scale_out, scratch, sizeof(uint32_t) * kScalesStaticWords,
+                        stream, true);
+}
+
+KVX_API int kvx_b200_device_error(int reset) {
+  int word = 0;
+  if (cudaMemcpyFromSymbol(&word, g_device_error, sizeof(word)) != cudaSuccess) {
     cudaGetLastError();
-    return KVX_STATUS_INTERNAL_ERROR;
+    return -1;
   }
-  return kvx_launch_kv_scales(io, granularity, k_scale_out, v_scale_out, scratch, bytes, stream);
+  if (word != 0 && reset) {
+    const int zero = 0;
+    if (cudaMemcpyToSymbol(g_device_error, &zero, sizeof(zero)) != cudaSuccess) cudaGetLastError();
+  }
+  return word;
 }
 
 KVX_API uint64_t kvx_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
@@ -2565,7 +2611,7 @@ KVX_API int kvx_b200_set_option(const char *name, int64_t value) {
   if (name == nullptr) return -1;
   for (const OptionName &o : kOptionNames)
     if (strcmp(o.name, name) == 0) {
-      g_opt.*(o.field) = value;
+      (g_opt.*(o.field)).store(value, std::memory_order_relaxed);
       return 0;
     }
   return -1;
@@ -2573,7 +2619,7 @@ KVX_API int kvx_b200_set_option(const char *name, int64_t value) {
 KVX_API int64_t kvx_b200_get_option(const char *name) {
   if (name == nullptr) return -1;
   for (const OptionName &o : kOptionNames)
-    if (strcmp(o.name, name) == 0) return g_opt.*(o.field);
+    if (strcmp(o.name, name) == 0) return (g_opt.*(o.field)).load(std::memory_order_relaxed);
   return -1;
 }
 

@@ -16,6 +16,7 @@
  * kvx_paged_kv.cu.
  */
 #include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
 #include <torch/library.h>
 #include <torch/types.h>
 
@@ -138,7 +139,13 @@ void reshape_and_cache_flash_kvx(torch::Tensor &key, torch::Tensor &value, torch
   TORCH_CHECK(io != KVX_DTYPE_INVALID, "KVX cache write unsupported dtype");
   const kvx_dtype_t slot_dtype = index_code(slot_mapping.scalar_type());
   TORCH_CHECK(slot_dtype != KVX_DTYPE_INVALID && slot_mapping.dim() == 1, "slot_mapping must be 1-D int32 or int64");
+  TORCH_CHECK(slot_mapping.is_cuda() && slot_mapping.is_contiguous(), "slot_mapping must be a contiguous CUDA tensor");
   const int64_t tokens = slot_mapping.size(0), heads = key.size(1), dim = key.size(2);
+  // the batch is sized by slot_mapping (as in the operator this one stands in for), so key and
+  // value must hold at least that many token rows
+  TORCH_CHECK(key.size(0) >= tokens && value.size(0) >= tokens, "key/value hold fewer tokens than slot_mapping");
+  TORCH_CHECK(key_cache.is_cuda() && value_cache.is_cuda(), "cache tensors must be CUDA tensors");
+  const at::cuda::OptionalCUDAGuard guard(at::device_of(key_cache));  // launch on the tensors' device and its stream
 
   kvx_cache_desc_t cache;
   const kvx_dtype_t cache_code = describe_cache(&cache, key_cache, value_cache, kv_cache_dtype, heads, dim);
@@ -180,6 +187,12 @@ void gather_kv(torch::Tensor &key_cache, torch::Tensor &value_cache, torch::Tens
   TORCH_CHECK(idx != KVX_DTYPE_INVALID && seq_lens.scalar_type() == block_table.scalar_type(),
               "block_table and seq_lens must share an int32 or int64 dtype");
   const int64_t seqs = key_out.size(0), max_len = key_out.size(1), heads = key_out.size(2), dim = key_out.size(3);
+  TORCH_CHECK(block_table.is_cuda() && seq_lens.is_cuda() && seq_lens.is_contiguous(),
+              "block_table and seq_lens must be contiguous CUDA tensors");
+  TORCH_CHECK(seq_lens.dim() == 1 && seq_lens.numel() == block_table.size(0),
+              "seq_lens must have one entry per row of block_table");
+  TORCH_CHECK(key_cache.is_cuda() && value_cache.is_cuda(), "cache tensors must be CUDA tensors");
+  const at::cuda::OptionalCUDAGuard guard(at::device_of(key_cache));
 
   kvx_cache_desc_t cache;
   const kvx_dtype_t cache_code = describe_cache(&cache, key_cache, value_cache, kv_cache_dtype, heads, dim);
@@ -236,6 +249,12 @@ void paged_attention_decode(torch::Tensor &out, torch::Tensor &query, torch::Ten
   TORCH_CHECK(idx != KVX_DTYPE_INVALID && seq_lens.scalar_type() == block_table.scalar_type(),
               "block_table and seq_lens must share an int32 or int64 dtype");
   const int64_t q_heads = query.size(1), dim = query.size(2);
+  TORCH_CHECK(block_table.is_cuda() && seq_lens.is_cuda() && seq_lens.is_contiguous(),
+              "block_table and seq_lens must be contiguous CUDA tensors");
+  TORCH_CHECK(seq_lens.dim() == 1 && seq_lens.numel() == block_table.size(0),
+              "seq_lens must have one entry per row of block_table");
+  TORCH_CHECK(key_cache.is_cuda() && value_cache.is_cuda(), "cache tensors must be CUDA tensors");
+  const at::cuda::OptionalCUDAGuard guard(at::device_of(key_cache));
   // KV heads: given, or read off the cache with the reference's stride rule (axis 2 when it is
   // contiguous over head_dim or the tensor is a permuted view, else axis 1)
   TORCH_CHECK(key_cache.dim() == 4, "cache tensors must be 4-D");

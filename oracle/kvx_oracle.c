@@ -319,6 +319,8 @@ static void gather_one(const kvx_cache_desc_t *c, const kvx_tensor_desc_t *pages
         const int64_t first = read_index(g->block_table.indptr, g->block_table.indptr_dtype, s);
         const int64_t count = read_index(g->block_table.indptr, g->block_table.indptr_dtype, s + 1) - first;
         if (tok >= count) continue;
+        /* a damaged indptr must not lead outside the index array: such tokens are skipped */
+        if (first < 0 || first + tok >= (int64_t)g->block_table.indices_count) continue;
         block = read_index(g->block_table.indices, g->block_table.index_dtype, first + tok);
       } else {
         if (lb >= mb) continue;

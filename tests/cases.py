@@ -181,6 +181,22 @@ def to_ragged(case: Case, indptr_dtype=np.int32, truncate=()) -> Case:
     return dataclasses.replace(case, ragged=np.array(ids, dtype=case.table.dtype), indptr=indptr)
 
 
+def damage_indptr(case: Case, seed: int) -> Case:
+    """A RAGGED case whose indptr no longer fits its index array: one entry negative, one beyond
+    the end of the array.  Tokens whose entry would lie outside the array must be skipped."""
+    import dataclasses
+    rng = np.random.default_rng(seed)
+    indptr = case.indptr.copy()
+    n = indptr.shape[0]
+    total = int(case.ragged.shape[0])
+    if n > 2:
+        indptr[int(rng.integers(1, n - 1))] = -3
+    indptr[n - 1] = total + 1000        # the last sequence claims more entries than exist
+    if n > 3:
+        indptr[int(rng.integers(1, n - 1))] = total + 7
+    return dataclasses.replace(case, indptr=indptr)
+
+
 def expected_gather_ragged_numpy(case: Case, cache_k: np.ndarray, cache_v: np.ndarray):
     """Independent numpy statement of the RAGGED gather (NHD / HND canonical pools)."""
     g = case.geom
@@ -191,6 +207,8 @@ def expected_gather_ragged_numpy(case: Case, cache_k: np.ndarray, cache_v: np.nd
         for s in range(case.indptr.shape[0] - 1):
             first, count = int(case.indptr[s]), int(case.indptr[s + 1] - case.indptr[s])
             for tok in range(min(int(case.lens[s]), case.max_seq_len, count)):
+                if first < 0 or first + tok >= case.ragged.shape[0]:
+                    continue  # damaged indptr: the entry would lie outside the index array
                 b = int(case.ragged[first + tok])
                 if b < 0 or b >= g.num_blocks:
                     continue

@@ -10,9 +10,9 @@ import pytest
 
 from kvx_b200 import abi
 from kvx_b200._lib import EXPORTS
+from oracle.build import REFERENCE_ROOT  # the KVX_REFERENCE_ROOT environment variable, or the usual place
 
 OK, INVALID, UNSUPPORTED = abi.STATUS_OK, abi.STATUS_INVALID_ARGUMENT, abi.STATUS_UNSUPPORTED
-REFERENCE_ROOT = "/root/reference"
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 

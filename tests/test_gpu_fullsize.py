@@ -137,3 +137,50 @@ def test_config5_fp8_full_size_round_trip_within_quantisation_error():
     torch.cuda.synchronize()
     same = (pages == dw.layer_pages(0)[0]).float().mean()
     assert float(same) > 0.999
+
+
+def test_bench_byte_check_accepts_good_buffers_and_sees_damage():
+    """The byte check the benchmark runs on its timed buffers (bench_support.verify_layer): green on
+    a written and gathered layer, red as soon as one page byte, one gathered byte or one byte past
+    a sequence's end is changed.  Small pool so the run is short; c2 (padded slots) and c3 (decode
+    write, pages that keep their fill pattern are gathered)."""
+    import torch
+
+    from kvx_b200 import bench_support as bs, workloads
+
+    for name in ("c2", "c3"):
+        spec = workloads.SPECS[name]
+        if name == "c3":
+            import dataclasses
+            spec = dataclasses.replace(spec, seqs=24)
+        dw = bs.setup_device_workload(spec, layers=2, pool_gb=1.0)
+        stream = torch.cuda.current_stream().cuda_stream
+        bs.fill_sentinel(dw)
+        for l in range(dw.layers):
+            bs.launch_write(dw, l, stream)
+            bs.launch_gather(dw, l, stream)
+        torch.cuda.synchronize()
+        res = bs.verify_layer(dw, dw.layers - 1)
+        assert res["ok"], (name, res)
+        kp, _ = dw.layer_pages(dw.layers - 1)
+        flat = kp.view(torch.uint8).view(-1)
+        slot = int(dw.slots[dw.slots >= 0][0])
+        row = dw.heads * spec.dim * 2
+        flat[slot * row + 5] ^= 1                              # a written row
+        assert not bs.verify_layer(dw, dw.layers - 1)["write_rows"]
+        flat[slot * row + 5] ^= 1
+        untouched = int((~torch.isin(torch.arange(flat.shape[0] // row, device="cuda"), dw.slots)).nonzero()[0])
+        flat[untouched * row + 9] ^= 1                         # a row no slot names
+        assert not bs.verify_layer(dw, dw.layers - 1)["untouched_pages"]
+        flat[untouched * row + 9] ^= 1
+        out = dw.out_v.view(torch.uint8).view(spec.seqs, -1)
+        out[1, 3] ^= 1                                         # a gathered byte
+        assert not bs.verify_layer(dw, dw.layers - 1)["gather_live"]
+        out[1, 3] ^= 1
+        s_short = int(dw.lens.argmin())
+        if int(dw.lens[s_short]) < dw.meta.max_seq_len:
+            out[s_short, -1] ^= 1                              # a byte past the end of a sequence
+            assert not bs.verify_layer(dw, dw.layers - 1)["gather_dead"]
+            out[s_short, -1] ^= 1
+        assert bs.verify_layer(dw, dw.layers - 1)["ok"]
+        del dw

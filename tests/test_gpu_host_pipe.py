@@ -77,3 +77,36 @@ def test_host_pipeline_fp8():
     k, v, ok_, ov_, _, _ = _run(case, 1 << 16, device_scales=scales)
     assert np.array_equal(k, ek) and np.array_equal(v, ev)
     assert np.array_equal(ok_, eok) and np.array_equal(ov_, eov)
+
+
+def test_host_pipeline_takes_pitched_host_rows():
+    """key / value in host memory whose token rows are further apart than heads * dim (slices of
+    a fused projection output): the rows are copied with a pitched copy and staged densely, so
+    the result equals the checker's on the same pitched descriptors; a row that is not dense
+    inside is refused before anything is staged."""
+    import kvx_b200
+    L = kvx_b200.lib()
+    base = cases.make_case(960, dtype=abi.DTYPE_BF16, heads=4, dim=64, block_size=16, num_blocks=40,
+                           lens=[120, 9, 77], pad_frac=0.1)
+    case = cases.to_pitched(base, 2 * 4 * 64, 24, seed=3)   # K rows 3x as far apart, V rows oddly so
+    _, ek, ev = oracle_write(case)
+    _, eok, eov = oracle_gather(case, ek, ev)
+    k, v, ok_, ov_, h2d, _ = _run(case, 1 << 14)
+    assert np.array_equal(k, ek) and np.array_equal(v, ev)
+    assert np.array_equal(ok_, eok) and np.array_equal(ov_, eov)
+    assert h2d < 2 * case.T * (3 * 4 * 64 * 2)              # only the rows themselves crossed the bus
+
+    import torch
+    hb = host_buffers(case)
+    dev = torch.zeros(case.cache_k.nbytes, dtype=torch.uint8, device="cuda")
+    cache, write, _, _, _ = descriptors(case, dict(hb, cache_k=dev, cache_v=dev), abi.MEMORY_HOST)
+    cache.k.memory = cache.v.memory = abi.MEMORY_DEVICE
+    write.io.key.stride[1] = 2 * 64                          # heads no longer adjacent inside a row
+    pipe = C.c_void_p()
+    assert L.kvx_host_pipe_create(1 << 14, 3, case.table.shape[1], C.byref(pipe)) == OK
+    try:
+        assert L.kvx_host_write_kv(pipe, C.byref(cache), C.byref(write)) == abi.STATUS_UNSUPPORTED
+        assert L.kvx_host_pipe_sync(pipe) == OK
+    finally:
+        L.kvx_host_pipe_destroy(pipe)
+    assert int(dev.max()) == 0

@@ -220,6 +220,9 @@ def test_ragged_block_table_gather(layout, dtype):
             rag.note = f"ragged {i}"
             check_gather(rag, k, v)
             check_gather(rag, k, v, "typed")
+            bad = cases.damage_indptr(rag, i)   # entries outside the index array are skipped, never read
+            bad.note = f"ragged {i}, damaged indptr"
+            check_gather(bad, k, v)
 
 
 def test_ragged_block_table_gather_fp8():

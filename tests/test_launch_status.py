@@ -11,6 +11,7 @@ import numpy as np
 import pytest
 
 from kvx_b200 import abi
+from oracle.build import REFERENCE_ROOT
 
 OK, INVALID, UNSUPPORTED = abi.STATUS_OK, abi.STATUS_INVALID_ARGUMENT, abi.STATUS_UNSUPPORTED
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -282,7 +283,7 @@ print("compared", n)
 """
 
 
-@pytest.mark.skipif(not os.path.exists("/root/reference/kernels/kvx_paged_kv.cu"),
+@pytest.mark.skipif(not os.path.exists(os.path.join(REFERENCE_ROOT, "kernels", "kvx_paged_kv.cu")),
                     reason="reference checkout not present")
 def test_launcher_statuses_agree_with_reference(built_lib):
     """Thousands of randomly corrupted descriptor sets through this launch layer and through

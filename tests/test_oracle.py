@@ -108,6 +108,11 @@ def test_ragged_table_gather_matches_numpy_statement(layout):
             assert np.array_equal(rk, ek) and np.array_equal(rv, ev)
             if not trunc and packed.table.shape[1] * packed.geom.block_size >= packed.max_seq_len:
                 assert np.array_equal(rk, pk) and np.array_equal(rv, pv)
+            bad = cases.damage_indptr(rag, seed)
+            st, rk, rv = oracle_gather(bad, k, v)
+            assert st == abi.STATUS_OK
+            ek, ev = cases.expected_gather_ragged_numpy(bad, k, v)
+            assert np.array_equal(rk, ek) and np.array_equal(rv, ev)
 
 
 @pytest.mark.parametrize("layout", [abi.LAYOUT_NHD, abi.LAYOUT_HND])
