@@ -62,7 +62,7 @@ def parse_args():
     ap.add_argument("--layout", default="nhd", choices=["nhd", "hnd", "packed", "paged"],
                     help="page layout of the headline workload: NHD (default), HND, HND_PACKED with 16-byte pack "
                          "groups for K and V, or 'paged' = packed K + [blocks, heads, dim, block_size] V")
-    ap.add_argument("--configs", default="c4,c5,c3,c4:packed,c2:packed",
+    ap.add_argument("--configs", default="c4,c5,c3,c4:packed,c2:packed,c4:paged",
                     help="other configurations (name or name:layout) timed on a few layers each and verified after "
                          "the headline workload; '' = none")
     ap.add_argument("--no-reference-kernels", action="store_true")
@@ -385,7 +385,7 @@ def all_ranks_true(flag: bool, dist) -> bool:
 CONFIG_LEG_LAYERS = {"c1": 22, "c2": 2, "c3": 2, "c4": 4, "c5": 4}
 
 
-def run_config_leg(name: str, rank: int, world: int, dist, peak: float, verify: bool = True, reps: int = 5) -> dict:
+def run_config_leg(name: str, rank: int, world: int, dist, peak: float, verify: bool = True, min_reps: int = 5) -> dict:
     """One of the other configurations on a few layers (each on its own pages), sharded by KV head
     over the job's ranks like the headline workload: writes and gathers timed separately with CUDA
     events (max over ranks), then the last layer byte-checked on every rank.  The fp8 configuration
@@ -422,17 +422,14 @@ def run_config_leg(name: str, rank: int, world: int, dist, peak: float, verify: 
             if st != abi.STATUS_OK:
                 raise RuntimeError(f"kvx_launch_kv_scales status {st}")
         legs.insert(0, ("scales", scales, 2 * dw.key.numel() * dw.key.element_size()))
-    for _ in range(2):  # warm-up
-        for _n, fn, _b in legs:
-            for l in range(dw.layers):
-                fn(l)
-    for leg, fn, nbytes in legs:
+
+    def timed(fn, rounds):
         torch.cuda.synchronize()
         if dist is not None:
             dist.barrier()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        for _ in range(reps):
+        for _ in range(rounds):
             for l in range(dw.layers):
                 fn(l)
         b.record()
@@ -440,10 +437,21 @@ def run_config_leg(name: str, rank: int, world: int, dist, peak: float, verify: 
         t = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device="cuda")
         if dist is not None:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        us = float(t.item()) * 1e3 / (reps * dw.layers)
+        return float(t.item())
+
+    # Warm-up: at least 3 rounds and about 0.15 s of the leg's own work, so that the clocks, which
+    # drop while the device waits for the set-up above, are back up when the timing starts.
+    for leg, fn, nbytes in legs:
+        spent, rounds = 0.0, 0
+        while rounds < 3 or (spent < 150.0 and rounds < 2000):
+            spent += timed(fn, 1)
+            rounds += 1
+        per_round = spent / rounds
+        reps = int(min(500, max(min_reps, 60.0 / max(per_round, 1e-3))))  # a timed region of about 60 ms
+        us = timed(fn, reps) * 1e3 / (reps * dw.layers)
         gbs = nbytes / us / 1e3
         out[leg] = {"us_per_launch": round(us, 2), "gbs_per_gpu": round(gbs, 1), "frac_of_peak": round(gbs / peak, 4),
-                    "bytes_per_launch": int(nbytes)}
+                    "bytes_per_launch": int(nbytes), "launches_timed": reps * dw.layers}
     out["layers"] = dw.layers
     out["heads_per_gpu"] = dw.heads
     out["tokens"] = {"write": dw.meta.write_tokens, "valid": dw.meta.valid_tokens, "gathered": dw.meta.gather_tokens}

@@ -155,29 +155,108 @@ __device__ __forceinline__ void pdl_prologue() {
 constexpr int kAttnWarps = 4;
 constexpr int kAttnThreads = kAttnWarps * 32;
 
-// Work items are (sequence, chunk, KV head) triples of chunks that exist.  The lengths live on
-// the device, so every CTA builds the same exclusive prefix sum of chunks per sequence in shared
-// memory (sm_prefix[0..S]); with too many sequences for that it enumerates the padded
-// (sequence, chunk) rectangle and meets chunks that do not exist.  Returns the item count.
+// Work items are (sequence, chunk, KV head) triples of chunks that exist, ordered longest first:
+// all full chunks (sequence-major), then the sequences' last, shorter chunks in kRemClasses
+// classes of falling length.  CTAs claim items in that order, so the last round of a launch is
+// made of the shortest items and the tail, when some CTAs have run out of work, is short.
+// The lengths live on the device, so every CTA builds the same lists in shared memory:
+// sm_prefix[0..S] = exclusive prefix sum of full chunks per sequence, sm_rem[] = the sequences
+// that have a shorter last chunk, by class (the order inside a class is the sequences' order:
+// every CTA must arrive at the same list).  With too many sequences for that the CTAs enumerate
+// the padded (sequence, chunk) rectangle in its natural order and meet chunks that do not
+// exist.  Returns the item count.
+constexpr int kRemClasses = 4;
+constexpr int kListCounts = 1 + kRemClasses;
+
+struct WorkList {
+  int32_t *prefix;    // [S + 1]
+  uint16_t *rem;      // [S]
+  int32_t full, rems;  // totals
+};
+
+// Full chunks of sequence s and the class of its shorter last chunk (-1 = none).
 template <typename IdxT>
-__device__ int64_t build_work_list(const AttnParams &p, int32_t *sm_prefix, int32_t *sm_scan) {
+__device__ __forceinline__ void chunk_counts(const AttnParams &p, int32_t s, int32_t *full, int32_t *rem_class) {
+  int64_t len = read_idx<IdxT>(p.lens, s);
+  if (len > p.max_seq_len) len = p.max_seq_len;
+  if (len <= 0) {
+    *full = 0, *rem_class = -1;
+    return;
+  }
+  const int32_t f = static_cast<int32_t>(len / p.chunk);
+  const int32_t r = static_cast<int32_t>(len - static_cast<int64_t>(f) * p.chunk);
+  *full = f;
+  *rem_class = r == 0 ? -1 : kRemClasses - 1 - (r - 1) * kRemClasses / p.chunk;  // class 0 = the longest
+}
+
+// `scratch`: kListCounts * kAttnWarps ints of shared memory, free to overwrite afterwards.
+template <typename IdxT>
+__device__ int64_t build_work_list(const AttnParams &p, WorkList *wl, int32_t *scratch) {
+  wl->full = wl->rems = 0;
   if (!p.use_prefix) return static_cast<int64_t>(p.seq_count) * p.splits * p.heads_kv;
   const int S = p.seq_count;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int per = (S + kAttnThreads - 1) / kAttnThreads;
-  const int begin = min(static_cast<int>(threadIdx.x) * per, S), end = min(begin + per, S);
-  int32_t local = 0;
-  for (int s = begin; s < end; ++s) local += chunks_of<IdxT>(p, s);
-  sm_scan[threadIdx.x] = local;
-  __syncthreads();
-  int32_t run = 0;
-  for (int t = 0; t < static_cast<int>(threadIdx.x); ++t) run += sm_scan[t];
+  const int begin = min(tid * per, S), end = min(begin + per, S);
+  int32_t local[kListCounts];
+#pragma unroll
+  for (int c = 0; c < kListCounts; ++c) local[c] = 0;
   for (int s = begin; s < end; ++s) {
-    sm_prefix[s] = run;
-    run += chunks_of<IdxT>(p, s);
+    int32_t f, rc;
+    chunk_counts<IdxT>(p, s, &f, &rc);
+    local[0] += f;
+#pragma unroll
+    for (int c = 0; c < kRemClasses; ++c) local[1 + c] += (rc == c);
   }
-  if (threadIdx.x == kAttnThreads - 1) sm_prefix[S] = run;
+  // exclusive scan of every count over the CTA's threads: inside the warps by shuffles, across
+  // them through shared memory
+  int32_t incl[kListCounts];
+#pragma unroll
+  for (int c = 0; c < kListCounts; ++c) {
+    int32_t v = local[c];
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int32_t n = __shfl_up_sync(0xFFFFFFFFu, v, d);
+      if (lane >= d) v += n;
+    }
+    incl[c] = v;
+    if (lane == 31) scratch[c * kAttnWarps + warp] = v;
+  }
   __syncthreads();
-  return static_cast<int64_t>(sm_prefix[S]) * p.heads_kv;
+  int32_t start[kListCounts], total[kListCounts];
+#pragma unroll
+  for (int c = 0; c < kListCounts; ++c) {
+    int32_t before = 0, all = 0;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) {
+      const int32_t t = scratch[c * kAttnWarps + w];
+      if (w < warp) before += t;
+      all += t;
+    }
+    start[c] = before + incl[c] - local[c];
+    total[c] = all;
+  }
+  // classes follow one another in the remainder list
+  int32_t class_base = 0;
+#pragma unroll
+  for (int c = 0; c < kRemClasses; ++c) {
+    start[1 + c] += class_base;
+    class_base += total[1 + c];
+  }
+  for (int s = begin; s < end; ++s) {
+    int32_t f, rc;
+    chunk_counts<IdxT>(p, s, &f, &rc);
+    wl->prefix[s] = start[0];
+    start[0] += f;
+#pragma unroll
+    for (int c = 0; c < kRemClasses; ++c)
+      if (rc == c) wl->rem[start[1 + c]++] = static_cast<uint16_t>(s);
+  }
+  if (tid == kAttnThreads - 1) wl->prefix[S] = start[0];
+  __syncthreads();
+  wl->full = total[0];
+  wl->rems = class_base;
+  return static_cast<int64_t>(total[0] + class_base) * p.heads_kv;
 }
 
 struct WorkItem {
@@ -194,27 +273,37 @@ __device__ __forceinline__ unsigned long long claim_item(const AttnParams &p, un
 
 // (sequence, chunk, KV head) and token range of item `item` of the work list.
 template <typename IdxT>
-__device__ __forceinline__ WorkItem locate_item(const AttnParams &p, int64_t item, const int32_t *sm_prefix) {
+__device__ __forceinline__ WorkItem locate_item(const AttnParams &p, int64_t item, const WorkList &wl) {
   WorkItem w;
   w.kvh = static_cast<int>(item % p.heads_kv);
   const int64_t ci = item / p.heads_kv;
+  int64_t len;
   if (p.use_prefix) {
-    int lo = 0, hi = p.seq_count;  // last s with prefix[s] <= ci
-    while (hi - lo > 1) {
-      const int mid = (lo + hi) >> 1;
-      if (sm_prefix[mid] <= ci)
-        lo = mid;
-      else
-        hi = mid;
+    if (ci < wl.full) {
+      int lo = 0, hi = p.seq_count;  // last s with prefix[s] <= ci
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (wl.prefix[mid] <= ci)
+          lo = mid;
+        else
+          hi = mid;
+      }
+      w.seq = lo;
+      w.split = static_cast<int>(ci - wl.prefix[lo]);
+      len = read_idx<IdxT>(p.lens, w.seq);
+      if (len > p.max_seq_len) len = p.max_seq_len;
+    } else {  // a sequence's shorter last chunk
+      w.seq = wl.rem[ci - wl.full];
+      len = read_idx<IdxT>(p.lens, w.seq);
+      if (len > p.max_seq_len) len = p.max_seq_len;
+      w.split = static_cast<int>(len / p.chunk);
     }
-    w.seq = lo;
-    w.split = static_cast<int>(ci - sm_prefix[lo]);
   } else {
     w.seq = static_cast<int>(ci / p.splits);
     w.split = static_cast<int>(ci - static_cast<int64_t>(w.seq) * p.splits);
+    len = read_idx<IdxT>(p.lens, w.seq);
+    if (len > p.max_seq_len) len = p.max_seq_len;
   }
-  int64_t len = read_idx<IdxT>(p.lens, w.seq);
-  if (len > p.max_seq_len) len = p.max_seq_len;
   w.begin = static_cast<int64_t>(w.split) * p.chunk;
   w.end = min(len, w.begin + p.chunk);
   return w;
@@ -339,12 +428,15 @@ __global__ void __launch_bounds__(kAttnThreads, attn_ctas_per_sm(kD, kNt))
   __shared__ float sm_m[kAttnWarps][8 * kNt];
   __shared__ float sm_l[kAttnWarps][8 * kNt];
   __shared__ int32_t sm_page[kAttnWarps][kTStages];
-  __shared__ int32_t sm_scan[kAttnThreads];
+  __shared__ int32_t sm_scan[kListCounts * kAttnWarps];
   __shared__ unsigned long long sm_item[2];  // this item and the next, claimed one item ahead
   char *ring = reinterpret_cast<char *>(sm_dyn);
   // merge buffer of the epilogue: lives in the ring, which is idle by then
   float (*sm_o)[kD + 8] = reinterpret_cast<float (*)[kD + 8]>(ring);  // [8 * kNt][kD + 8]
-  int32_t *sm_prefix = reinterpret_cast<int32_t *>(ring + kAttnWarps * kTStages * 2 * kTile);
+  // behind the ring: the work list ([S + 1] prefix of full chunks, [S] sequences with a shorter last chunk)
+  WorkList wl;
+  wl.prefix = reinterpret_cast<int32_t *>(ring + kAttnWarps * kTStages * 2 * kTile);
+  wl.rem = reinterpret_cast<uint16_t *>(wl.prefix + p.seq_count + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, j = lane & 3;
   const int G = p.group;
@@ -364,7 +456,7 @@ __global__ void __launch_bounds__(kAttnThreads, attn_ctas_per_sm(kD, kNt))
       asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const char *>(p.lens) + at));
   }
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  const int64_t items = build_work_list<IdxT>(p, sm_prefix, sm_scan);
+  const int64_t items = build_work_list<IdxT>(p, &wl, sm_scan);
 
   zero_empty_sequences<IdxT>(p);
 
@@ -386,7 +478,7 @@ __global__ void __launch_bounds__(kAttnThreads, attn_ctas_per_sm(kD, kNt))
   for (int parity = 0;; parity ^= 1) {
     const int64_t item = static_cast<int64_t>(sm_item[parity]);
     if (item >= items) break;
-    const WorkItem w = locate_item<IdxT>(p, item, sm_prefix);
+    const WorkItem w = locate_item<IdxT>(p, item, wl);
     const int seq = w.seq, split = w.split, kvh = w.kvh;
     const int64_t cbeg = w.begin, cend = w.end;
     const int64_t q_row0 = static_cast<int64_t>(seq) * p.heads_q + static_cast<int64_t>(kvh) * G;
@@ -1007,7 +1099,8 @@ KVX_API kvx_status_t kvx_launch_paged_attention_decode(const kvx_cache_desc_t *c
     const int per_sm = attn_ctas_per_sm(static_cast<int>(D), p.group <= 8 ? 1 : 2);  // the kernels' launch bounds
     // K and V steps of 16 rows, each row padded by 16 bytes
     const size_t ring = static_cast<size_t>(kAttnWarps) * kTStages * 2 * 16 * (D * elem + 16);
-    const size_t smem = ring + (p.use_prefix ? static_cast<size_t>(S + 1) * sizeof(int32_t) : 0);
+    // behind the ring: the prefix of full chunks and the list of sequences with a shorter last chunk
+    const size_t smem = ring + (p.use_prefix ? static_cast<size_t>(S + 1) * sizeof(int32_t) + (static_cast<size_t>(S) * 2 + 15) / 16 * 16 : 0);
     const int64_t most = S * p.splits * H;  // work items if every context had max_seq_len tokens
     const int64_t grid = std::max<int64_t>(1, std::min<int64_t>(most, static_cast<int64_t>(sm_count()) * per_sm));
     if (most <= grid)

@@ -63,6 +63,9 @@ struct Options {
   std::atomic<int64_t> wide{1};                   // 1 = 256-bit accesses where alignment allows
   std::atomic<int64_t> gather_rect_items{40000};  // padded (sequence, page, part, K|V) rectangles up to this size are walked as they are
   std::atomic<int64_t> write_prefetch_waves{2};   // leading write CTAs (in units of 8 per SM) that prefetch their rows into the L2
+  std::atomic<int64_t> f8_tile_mult{8};           // fp8 wide write: bytes per CTA relative to the copy write
+  std::atomic<int64_t> f8_unroll{1};              // fp8 wide write: 32-byte vectors of K and of V in flight per thread
+  std::atomic<int64_t> packed_tiles{1};           // 1 = transposing tile kernels for HND_PACKED pages where they apply
   std::atomic<int64_t> bulk_wait_us{1000000};     // a bulk-path wait on a copy is abandoned after this long
   std::atomic<int64_t> bulk_test_stall{0};        // test hook: pipe 0 of CTA 0 first waits on a barrier nothing completes
 };
@@ -91,6 +94,9 @@ const OptionName kOptionNames[] = {
     {"force_generic", &Options::force_generic},
     {"pdl", &Options::pdl},
     {"wide", &Options::wide},
+    {"f8_tile_mult", &Options::f8_tile_mult},
+    {"f8_unroll", &Options::f8_unroll},
+    {"packed_tiles", &Options::packed_tiles},
     {"bulk_wait_us", &Options::bulk_wait_us},
     {"bulk_test_stall", &Options::bulk_test_stall},
 };
@@ -160,6 +166,33 @@ bool view_packed16(const PageView &v, int64_t elem, int64_t dim) {
   return v.pack > 1 && v.pack != dim && v.pack * elem == 16 && v.dlo == elem && aligned(v.base, 16) &&
          v.blk % 16 == 0 && v.tok % 16 == 0 && v.head % 16 == 0 && v.dhi % 16 == 0 && v.blk >= 0 && v.tok >= 0 &&
          v.head >= 0 && v.dhi >= 0;
+}
+
+// One packed page tensor as the tile kernels see it (device code reads it too).
+struct PackedSide {
+  int64_t dhi;      // bytes between consecutive pack groups of one head
+  int32_t n_shift;  // log2(16 / u): 0 for 16-byte units ... 3 for 2-byte units
+  int32_t runs;     // 32-byte units per group row (block_size * u / 32)
+  int32_t runs_shift;
+};
+
+// HND_PACKED pages the transposing tile kernels take: pack groups of u = 2, 4, 8 or 16 bytes,
+// the groups of consecutive tokens adjacent (tok == u), a group row (block_size * u bytes) made
+// of whole 32-byte units, everything 32-byte aligned.  pack = 1 is the [blocks, heads, dim,
+// block_size] tensor vLLM's and TGI's non-flash attention keep V in.
+bool view_packed_tile(const PageView &v, int64_t elem, int64_t dim, int64_t block_size, PackedSide *out) {
+  const int64_t u = v.pack * elem;
+  if (u != 2 && u != 4 && u != 8 && u != 16) return false;
+  if (v.pack == dim && dim > 1) return false;  // dim contiguous: an ordinary HND tensor
+  if (v.pack > 1 && v.dlo != elem) return false;
+  if (v.tok != u || (block_size * u) % 32 != 0 || v.dhi < block_size * u) return false;
+  if (!aligned(v.base, 32) || v.blk % 32 != 0 || v.head % 32 != 0 || v.dhi % 32 != 0 || v.blk < 0 || v.head < 0)
+    return false;
+  out->dhi = v.dhi;
+  out->n_shift = shift_of(16 / u);
+  out->runs = static_cast<int32_t>(block_size * u / 32);
+  out->runs_shift = shift_of(out->runs);
+  return true;
 }
 
 // ------------------------------------------------------------------ device helpers ----
@@ -443,6 +476,19 @@ __device__ __forceinline__ uint32_t quant2_fast_unsigned_zero(float lo, float hi
   return c;
 }
 
+// The same for a pair of elements at once with the packed f32x2 arithmetic of sm_100 (one issue
+// slot for two products or two fused multiply-adds; each half rounds exactly like the scalar
+// instruction, denormals are kept): half the float-pipe instructions of the scalar chain.
+// neg_s = {-s, -s}, r = {RN(1 / s), RN(1 / s)}.
+__device__ __forceinline__ uint32_t quant2_packed_unsigned_zero(float2 x, float2 neg_s, float2 r) {
+  const float2 q0 = __fmul2_rn(x, r);
+  const float2 q1 = __ffma2_rn(__ffma2_rn(neg_s, q0, x), r, q0);
+  const float2 q2 = __ffma2_rn(__ffma2_rn(neg_s, q1, x), r, q1);
+  uint16_t c;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(c) : "f"(q2.y), "f"(q2.x));
+  return c;
+}
+
 // Two E4M3 bytes (bits 0-15) -> two f32, exact.
 __device__ __forceinline__ float2 e4m3x2_to_f32(uint32_t q) {
   uint32_t h2;
@@ -526,8 +572,9 @@ __device__ __forceinline__ uint2 quant_vec(const uint4 &x, float scale, float r,
     // 16-bit inputs: the sign of element i is the top bit of byte 2 i + 1 of the vector, so one
     // byte permute gathers four sign bytes and one logic operation puts them on four results
     // (instead of one sign copy per element inside the quotient).
+    const float2 neg_s = make_float2(-scale, -scale), r2 = make_float2(r, r);
 #pragma unroll
-    for (int i = 0; i < kPairs; ++i) q[i] = quant2_fast_unsigned_zero(f[2 * i], f[2 * i + 1], scale, r);
+    for (int i = 0; i < kPairs; ++i) q[i] = quant2_packed_unsigned_zero(make_float2(f[2 * i], f[2 * i + 1]), neg_s, r2);
     const uint32_t lo = q[0] | (q[1] << 16), hi = q[2] | (q[3] << 16);
     out.x = (lo & 0x7F7F7F7Fu) | (__byte_perm(x.x, x.y, 0x7531) & 0x80808080u);
     out.y = (hi & 0x7F7F7F7Fu) | (__byte_perm(x.z, x.w, 0x7531) & 0x80808080u);
@@ -687,7 +734,7 @@ __global__ void __launch_bounds__(kWriteThreads) kvx_write_f8_kernel(const Write
 // bytes of K and 32 bytes of V (16 + 16 elements of one head) into two 16-byte stores, which
 // halves the index arithmetic per element -- the kernel is bound by instruction issue.
 // p.vpr / p.vps count 32-byte input vectors here.
-template <typename IoT, typename SlotT>
+template <typename IoT, typename SlotT, int kUnroll>
 __global__ void __launch_bounds__(kWriteThreads) kvx_write_f8_wide_kernel(const WriteF8Params q) {
   const WriteRowsParams &p = q.w;
   __shared__ int64_t s_k[kMaxTokTile];
@@ -721,22 +768,35 @@ __global__ void __launch_bounds__(kWriteThreads) kvx_write_f8_wide_kernel(const 
   const char *ksrc = p.key + tok0 * p.row_bytes;
   const char *vsrc = p.value + tok0 * p.row_bytes;
   const int nvec = ntok * p.vpr;
-  for (int f = tid; f < nvec; f += kWriteThreads) {
-    const int tok = f >> p.vpr_shift;
-    const int64_t ko = s_k[tok];
-    if (ko < 0) continue;
-    const int v = f - (tok << p.vpr_shift);
-    const int h = v >> p.vps_shift;
-    const int w = (v - (h << p.vps_shift)) * 16;  // cache bytes into the head
-    const Vec32 kr = load_stream32(ksrc + static_cast<int64_t>(f) * 32);
-    const Vec32 vr = load_stream32(vsrc + static_cast<int64_t>(f) * 32);
-    const float4 sc = s_scale[h];
-    const uint2 a0 = quant_vec(make_uint4(kr.w[0], kr.w[1], kr.w[2], kr.w[3]), sc.x, sc.y, IoT{});
-    const uint2 a1 = quant_vec(make_uint4(kr.w[4], kr.w[5], kr.w[6], kr.w[7]), sc.x, sc.y, IoT{});
-    const uint2 b0 = quant_vec(make_uint4(vr.w[0], vr.w[1], vr.w[2], vr.w[3]), sc.z, sc.w, IoT{});
-    const uint2 b1 = quant_vec(make_uint4(vr.w[4], vr.w[5], vr.w[6], vr.w[7]), sc.z, sc.w, IoT{});
-    *reinterpret_cast<uint4 *>(p.k_base + ko + (h * k_head32 + w)) = make_uint4(a0.x, a0.y, a1.x, a1.y);
-    *reinterpret_cast<uint4 *>(p.v_base + s_v[tok] + (h * v_head32 + w)) = make_uint4(b0.x, b0.y, b1.x, b1.y);
+  for (int f0 = tid; f0 < nvec; f0 += kWriteThreads * kUnroll) {
+    Vec32 kr[kUnroll], vr[kUnroll];
+    int64_t ko[kUnroll];
+    // all loads of the round first, so that kUnroll x 64 bytes per thread are in flight
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int f = f0 + u * kWriteThreads;
+      ko[u] = f < nvec ? s_k[f >> p.vpr_shift] : -1;
+      if (ko[u] >= 0) {
+        kr[u] = load_stream32(ksrc + static_cast<int64_t>(f) * 32);
+        vr[u] = load_stream32(vsrc + static_cast<int64_t>(f) * 32);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      if (ko[u] < 0) continue;
+      const int f = f0 + u * kWriteThreads;
+      const int tok = f >> p.vpr_shift;
+      const int v = f - (tok << p.vpr_shift);
+      const int h = v >> p.vps_shift;
+      const int w = (v - (h << p.vps_shift)) * 16;  // cache bytes into the head
+      const float4 sc = s_scale[h];
+      const uint2 a0 = quant_vec(make_uint4(kr[u].w[0], kr[u].w[1], kr[u].w[2], kr[u].w[3]), sc.x, sc.y, IoT{});
+      const uint2 a1 = quant_vec(make_uint4(kr[u].w[4], kr[u].w[5], kr[u].w[6], kr[u].w[7]), sc.x, sc.y, IoT{});
+      const uint2 b0 = quant_vec(make_uint4(vr[u].w[0], vr[u].w[1], vr[u].w[2], vr[u].w[3]), sc.z, sc.w, IoT{});
+      const uint2 b1 = quant_vec(make_uint4(vr[u].w[4], vr[u].w[5], vr[u].w[6], vr[u].w[7]), sc.z, sc.w, IoT{});
+      *reinterpret_cast<uint4 *>(p.k_base + ko[u] + (h * k_head32 + w)) = make_uint4(a0.x, a0.y, a1.x, a1.y);
+      *reinterpret_cast<uint4 *>(p.v_base + s_v[tok] + (h * v_head32 + w)) = make_uint4(b0.x, b0.y, b1.x, b1.y);
+    }
   }
 }
 
@@ -1196,6 +1256,384 @@ __global__ void __launch_bounds__(kGatherThreads) kvx_gather_pages_wide_kernel(c
       }
     }
   }
+}
+
+// ------------------------------------------------------------------ packed pages -------
+// HND_PACKED pages ([blocks, heads, dim / pack, block_size, pack]): inside a (page, head) tile
+// the unit of `pack` elements (u = pack * elem bytes, 2 / 4 / 8 / 16) of token t and group g
+// lies at g * dhi + t * u, while a dense token row holds its groups side by side -- the tile is
+// the transpose, in units of u bytes, of the dense [token][group] block.  Both sides are
+// accessed with full 16- or 32-byte vectors: a 16-byte page vector holds the unit of ONE group
+// for n = 16 / u consecutive tokens, a 16-byte dense vector the units of n consecutive groups
+// for ONE token, so n lanes that hold the page vectors of n consecutive groups exchange units
+// (an n x n transposition of u-byte units by shuffles, log2 n steps) and end up with the dense
+// vectors of n consecutive tokens, or the other way round for the write.  u = 16 needs no
+// exchange at all.
+
+// `upper` = this lane has the step's lane bit set; the partner is lane ^ d.
+__device__ __forceinline__ void exchange_pairs(uint32_t (&w)[4], bool upper, int d) {  // units of 8 bytes
+  uint32_t a = upper ? w[0] : w[2], b = upper ? w[1] : w[3];
+  a = __shfl_xor_sync(0xFFFFFFFFu, a, d);
+  b = __shfl_xor_sync(0xFFFFFFFFu, b, d);
+  if (upper)
+    w[0] = a, w[1] = b;
+  else
+    w[2] = a, w[3] = b;
+}
+__device__ __forceinline__ void exchange_words(uint32_t (&w)[4], bool upper, int d) {  // units of 4 bytes
+  uint32_t a = upper ? w[0] : w[1], b = upper ? w[2] : w[3];
+  a = __shfl_xor_sync(0xFFFFFFFFu, a, d);
+  b = __shfl_xor_sync(0xFFFFFFFFu, b, d);
+  if (upper)
+    w[0] = a, w[2] = b;
+  else
+    w[1] = a, w[3] = b;
+}
+__device__ __forceinline__ void exchange_halves(uint32_t (&w)[4], bool upper) {  // units of 2 bytes, d = 1
+  const uint32_t pick = upper ? 0x5410u : 0x7632u;  // the lower lane sends its odd units, the upper its even ones
+  uint32_t a = __byte_perm(w[0], w[1], pick), b = __byte_perm(w[2], w[3], pick);
+  a = __shfl_xor_sync(0xFFFFFFFFu, a, 1);
+  b = __shfl_xor_sync(0xFFFFFFFFu, b, 1);
+  if (upper) {
+    w[0] = __byte_perm(a, w[0], 0x7610u), w[1] = __byte_perm(a, w[1], 0x7632u);
+    w[2] = __byte_perm(b, w[2], 0x7610u), w[3] = __byte_perm(b, w[3], 0x7632u);
+  } else {
+    w[0] = __byte_perm(w[0], a, 0x5410u), w[1] = __byte_perm(w[1], a, 0x7610u);
+    w[2] = __byte_perm(w[2], b, 0x5410u), w[3] = __byte_perm(w[3], b, 0x7610u);
+  }
+}
+
+// Lane i of each aligned group of kN lanes holds the vector [x(i,0) .. x(i,kN-1)] of kN units;
+// afterwards it holds [x(0,i) .. x(kN-1,i)].  Every lane of the warp must take part.
+template <int kN>
+__device__ __forceinline__ void transpose_units(uint32_t (&w)[4], int lane) {
+  if constexpr (kN == 2) {
+    exchange_pairs(w, lane & 1, 1);
+  } else if constexpr (kN == 4) {
+    exchange_pairs(w, lane & 2, 2);
+    exchange_words(w, lane & 1, 1);
+  } else if constexpr (kN == 8) {
+    exchange_pairs(w, lane & 4, 4);
+    exchange_words(w, lane & 2, 2);
+    exchange_halves(w, lane & 1);
+  }
+}
+
+// A piece (up to kUnroll * 32 of the 32-byte units) of one (page, head) tile, page -> dense rows.
+// Lane slot j covers group g = (q / runs) * kN + j % kN and tokens [a * 2 kN, (a + 1) * 2 kN) with
+// q = j / kN, a = q % runs: the kN lanes of a group share a and hold consecutive groups.
+template <int kN, int kUnroll>
+__device__ __forceinline__ void gather_packed_piece(const char *src, char *dst, int64_t out_row_bytes,
+                                                    const PackedSide &side, int first_slot, int slots, int tokens,
+                                                    int lane) {
+  Vec32 x[kUnroll];
+  int tok_a[kUnroll], vec[kUnroll];
+#pragma unroll
+  for (int u = 0; u < kUnroll; ++u) {
+    const int j = first_slot + u * 32 + lane;
+    const int q = j / kN, i = j & (kN - 1);
+    const int gb = div_by(q, side.runs, side.runs_shift);
+    const int a = q - gb * side.runs;
+    tok_a[u] = j < slots ? a * 2 * kN + i : tokens;  // >= tokens: nothing to store
+    vec[u] = gb;
+    if (j < slots && a * 2 * kN < tokens) {
+      x[u] = load_stream32(src + static_cast<int64_t>(gb * kN + i) * side.dhi + a * 32);
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) x[u].w[k] = 0u;
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < kUnroll; ++u) {
+    uint32_t lo[4] = {x[u].w[0], x[u].w[1], x[u].w[2], x[u].w[3]};
+    uint32_t hi[4] = {x[u].w[4], x[u].w[5], x[u].w[6], x[u].w[7]};
+    transpose_units<kN>(lo, lane);
+    transpose_units<kN>(hi, lane);
+    char *row = dst + static_cast<int64_t>(tok_a[u]) * out_row_bytes + vec[u] * 16;
+    if (tok_a[u] < tokens) store_stream(row, make_uint4(lo[0], lo[1], lo[2], lo[3]));
+    if (tok_a[u] + kN < tokens) store_stream(row + kN * out_row_bytes, make_uint4(hi[0], hi[1], hi[2], hi[3]));
+  }
+}
+
+// 16-byte units (kN = 1), whole 128-byte lines on both sides and whole token rows per warp.  One
+// item = 8 consecutive tokens (4 token pairs = one 128-byte line of every group row) of one page,
+// all heads: the warp reads, head by head, 8 group rows x 128 bytes per instruction (a lane takes
+// 32 bytes of group 8 gh + lane / 4 at token pair 4 ah + lane % 4) and writes 4 token rows x 128
+// bytes with each of its two store instructions, so that the 8 output rows, which are contiguous,
+// are filled by this one warp.  Needs runs % 4 == 0 and a multiple of 8 groups per head.
+template <int kUnroll>
+__device__ __forceinline__ void gather_packed16_rows(const char *src, int64_t head_bytes, char *dst,
+                                                     int64_t out_row_bytes, int64_t head_out_bytes,
+                                                     const PackedSide &side, int ah, int g_blocks, int steps,
+                                                     int tokens, int lane) {
+  const int a = ah * 4 + (lane & 3), g_lo = lane >> 2;
+  if (8 * ah >= tokens) return;  // warp-uniform: none of the item's tokens exists
+  const bool live = 2 * a < tokens;
+  char *row = dst + static_cast<int64_t>(2 * a) * out_row_bytes;
+  for (int t0 = 0; t0 < steps; t0 += kUnroll) {  // a step = 8 groups of one head
+    Vec32 x[kUnroll];
+    int at[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int t = t0 + u;
+      const int h = t / g_blocks, gh = t - h * g_blocks;
+      const int g = gh * 8 + g_lo;
+      at[u] = t < steps ? static_cast<int>(h * head_out_bytes) + g * 16 : -1;
+      if (t < steps && live) x[u] = load_stream32(src + h * head_bytes + static_cast<int64_t>(g) * side.dhi + a * 32);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      if (at[u] < 0 || !live) continue;
+      store_stream(row + at[u], make_uint4(x[u].w[0], x[u].w[1], x[u].w[2], x[u].w[3]));
+      if (2 * a + 1 < tokens)
+        store_stream(row + out_row_bytes + at[u], make_uint4(x[u].w[4], x[u].w[5], x[u].w[6], x[u].w[7]));
+    }
+  }
+}
+
+struct GatherPackedParams {
+  GatherPagesParams g;  // parts = heads * pieces per head; k_vec / v_vec unused
+  PackedSide k, v;
+  int32_t slots;   // 32-byte units of one (page, head) tile: block_size * head_dim * elem / 32
+  int32_t pieces;  // work items per head
+  int32_t rows;    // 1: K and V in 16-byte units, items of 8 token rows (gather_packed16_rows); then
+                   // g.parts = 128-byte lines per group row and pieces = 8-group blocks per head
+  int64_t head_out_bytes;  // head_dim * elem
+};
+
+// Gather from packed pages: same work list as kvx_gather_pages_kernel (compacted (sequence,
+// page) chunks, warp-granular items), an item being one piece of one head's tile of K or of V.
+template <typename IdxT, int kUnroll, bool kRows>
+__global__ void __launch_bounds__(kGatherThreads) kvx_gather_packed_kernel(const GatherPackedParams pp) {
+  const GatherPagesParams &p = pp.g;
+  gather_prologue<IdxT>(p);
+  extern __shared__ int32_t s_prefix[];
+  __shared__ int32_t s_warp_tot[kGatherWarps];
+  int64_t chunks;
+  if (p.use_prefix)
+    chunks = build_page_prefix<IdxT>(p, s_prefix, s_warp_tot);
+  else
+    chunks = static_cast<int64_t>(p.s.seq_count) * p.s.max_blocks;
+
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = static_cast<int64_t>(blockIdx.x) * kGatherWarps + (threadIdx.x >> 5);
+  const int64_t warps = static_cast<int64_t>(gridDim.x) * kGatherWarps;
+  const int64_t items = chunks * p.parts * 2;
+
+  for (int64_t item = warp; item < items; item += warps) {
+    const int kv = static_cast<int>(item & 1);
+    const int64_t rest = item >> 1;
+    const int64_t c = rest / p.parts;
+    const int part = static_cast<int>(rest - c * p.parts);
+    ChunkRef ref;
+    if (p.use_prefix) {
+      ref = find_chunk(s_prefix, p.s.seq_count, static_cast<int32_t>(c));
+    } else {
+      ref.seq = static_cast<int32_t>(c / p.s.max_blocks);
+      ref.lb = static_cast<int32_t>(c - static_cast<int64_t>(ref.seq) * p.s.max_blocks);
+    }
+    const ChunkInfo ci = resolve_chunk<IdxT>(p, ref.seq, ref.lb);
+    if (ci.block < 0) continue;  // warp-uniform: every lane stays for the shuffles below
+    if constexpr (kRows) {
+      gather_packed16_rows<kUnroll>(kv ? p.v_base + ci.block * p.v_blk : p.k_base + ci.block * p.k_blk,
+                                    kv ? p.v_head : p.k_head, (kv ? p.value_out : p.key_out) + ci.out_off,
+                                    p.out_row_bytes, pp.head_out_bytes, kv ? pp.v : pp.k, part, pp.pieces,
+                                    pp.pieces * (p.vpr / p.vps), ci.tokens, lane);
+      continue;
+    }
+    const int h = part / pp.pieces;
+    const int first_slot = (part - h * pp.pieces) * (32 * kUnroll);
+    const char *src = (kv ? p.v_base + ci.block * p.v_blk + h * p.v_head : p.k_base + ci.block * p.k_blk + h * p.k_head);
+    char *dst = (kv ? p.value_out : p.key_out) + ci.out_off + h * pp.head_out_bytes;
+    const PackedSide &side = kv ? pp.v : pp.k;
+    switch (side.n_shift) {
+      case 0: gather_packed_piece<1, kUnroll>(src, dst, p.out_row_bytes, side, first_slot, pp.slots, ci.tokens, lane); break;
+      case 1: gather_packed_piece<2, kUnroll>(src, dst, p.out_row_bytes, side, first_slot, pp.slots, ci.tokens, lane); break;
+      case 2: gather_packed_piece<4, kUnroll>(src, dst, p.out_row_bytes, side, first_slot, pp.slots, ci.tokens, lane); break;
+      default: gather_packed_piece<8, kUnroll>(src, dst, p.out_row_bytes, side, first_slot, pp.slots, ci.tokens, lane); break;
+    }
+  }
+}
+
+// ---- write into packed pages ----------------------------------------------------------
+// Tokens arrive in any order and with holes (padding), but a page vector needs the units of
+// n = 16 / u consecutive slots.  So the tile's tokens are first cut into FRAGMENTS: maximal
+// runs of consecutive tokens whose slots are consecutive inside one aligned window of
+// W = 2 n = 32 / u slots (the slots of one 32-byte unit of a group row).  A fragment belongs to
+// the CTA that holds its first token, which reads up to W - 1 tokens past its tile's end to
+// complete it; a tile's leading tokens that continue a fragment begun in the previous tile are
+// left to that CTA.  Fragments never overlap, so every valid token is written exactly once.
+// A fragment that fills its window is stored as one 32-byte unit per group, one that fills an
+// aligned half as a 16-byte vector, anything else unit by unit.
+constexpr int kPackedTile = 64;              // most tokens per CTA
+constexpr int kPackedSlots = kPackedTile + 17;  // + the token before the tile + up to W - 1 = 15 after it
+
+struct WritePackedParams {
+  const char *key, *value;  // dense (or pitched) [T, heads * dim] rows
+  int64_t k_pitch, v_pitch;
+  char *k_base, *v_base;
+  int64_t k_blk, k_head, v_blk, v_head;
+  PackedSide k, v;
+  const void *slots;
+  int32_t num_tokens, num_blocks, block_size, bs_shift;
+  int32_t vpr;             // 16-byte vectors per dense token row
+  int32_t vph, vph_shift;  // ... per head
+  int32_t tok_tile;        // power of two <= kPackedTile
+};
+
+// Stores the units of `w` (positions 0 .. kN-1 of a half window) whose bit is set in `mask`.
+template <int kN>
+__device__ __forceinline__ void store_units(char *dst, const uint32_t (&w)[4], uint32_t mask) {
+  if constexpr (kN == 1) {
+    if (mask & 1u) store_stream(dst, make_uint4(w[0], w[1], w[2], w[3]));
+  } else if constexpr (kN == 2) {
+    if (mask & 1u) *reinterpret_cast<uint2 *>(dst) = make_uint2(w[0], w[1]);
+    if (mask & 2u) *reinterpret_cast<uint2 *>(dst + 8) = make_uint2(w[2], w[3]);
+  } else if constexpr (kN == 4) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      if (mask & (1u << k)) *reinterpret_cast<uint32_t *>(dst + 4 * k) = w[k];
+  } else {
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (mask & (1u << k))
+        *reinterpret_cast<uint16_t *>(dst + 2 * k) = static_cast<uint16_t>(w[k >> 1] >> (16 * (k & 1)));
+  }
+}
+
+// One tensor (K or V) of one token tile.  s_slot[1 + p] is the slot of tile token p (or -1),
+// for p = -1 .. tok_tile + 2 kN - 2.
+template <int kN>
+__device__ __forceinline__ void write_packed_tensor(const WritePackedParams &p, const char *rows, int64_t pitch,
+                                                    char *base, int64_t blk, int64_t head, const PackedSide &side,
+                                                    const int64_t *s_slot, int32_t *s_frag, int64_t *s_win,
+                                                    int *s_count, int ntok) {
+  constexpr int kW = 2 * kN;
+  const int tid = threadIdx.x, lane = tid & 31;
+  if (tid == 0) *s_count = 0;
+  __syncthreads();
+  if (tid < ntok) {
+    const int64_t sl = s_slot[1 + tid];
+    const int64_t before = s_slot[tid];
+    const int pos0 = static_cast<int>(sl & (kW - 1));
+    const bool continues = sl >= 0 && before >= 0 && sl == before + 1 && pos0 != 0;
+    if (sl >= 0 && !continues) {
+      int len = 1;
+      while (pos0 + len < kW && s_slot[1 + tid + len] == sl + len) ++len;
+      const int at = atomicAdd(s_count, 1);
+      s_frag[at] = tid | (pos0 << 8) | (len << 16);
+      int64_t b, o;
+      split_slot(sl - pos0, p.block_size, p.bs_shift, &b, &o);
+      s_win[at] = b * blk + o * (16 / kN);  // the window's first unit (group 0 of head 0)
+    }
+  }
+  __syncthreads();
+  const int nfrag = *s_count;
+  const int i = lane & (kN - 1);
+  const int groups = 32 / kN;  // (fragment, dense vector) pairs one warp instruction covers
+  const int total = nfrag * p.vpr;
+  const int64_t tok0 = static_cast<int64_t>(blockIdx.x) * p.tok_tile;
+  // Every lane of a warp runs the same number of rounds (the exchanges need all 32 lanes); a
+  // round takes kRound (fragment, vector) pairs per lane group, all loads first.
+  constexpr int kRound = 4;
+  const int warp_stride = (kWriteThreads / 32) * groups;
+  for (int e0 = (tid >> 5) * groups; e0 < total; e0 += warp_stride * kRound) {
+    uint32_t lo[kRound][4], hi[kRound][4];
+    int at[kRound];           // fragment, or -1
+    int vec[kRound];
+    uint32_t window[kRound];  // slots of the window the fragment fills
+#pragma unroll
+    for (int r = 0; r < kRound; ++r) {
+      const int e = e0 + r * warp_stride + lane / kN;
+      const bool live = e < total;
+      int frag = 0, v = 0;
+      if (live) {
+        frag = e / p.vpr;
+        v = e - frag * p.vpr;
+      }
+      const int32_t info = live ? s_frag[frag] : 0;
+      const int first = info & 0xFF, pos0 = (info >> 8) & 0xFF, len = live ? (info >> 16) : 0;
+      at[r] = live ? frag : -1;
+      vec[r] = v;
+      window[r] = ((1u << len) - 1u) << pos0;
+      // window position i (lower half) and kN + i (upper half) -> token of the fragment, if any
+      const int ra = i - pos0, rb = kN + i - pos0;
+      const char *from = rows + (tok0 + first) * pitch + static_cast<int64_t>(v) * 16;
+      uint4 x = make_uint4(0u, 0u, 0u, 0u), y = make_uint4(0u, 0u, 0u, 0u);
+      if (ra >= 0 && ra < len) x = load_stream(from + ra * pitch);
+      if (rb >= 0 && rb < len) y = load_stream(from + rb * pitch);
+      lo[r][0] = x.x, lo[r][1] = x.y, lo[r][2] = x.z, lo[r][3] = x.w;
+      hi[r][0] = y.x, hi[r][1] = y.y, hi[r][2] = y.z, hi[r][3] = y.w;
+    }
+#pragma unroll
+    for (int r = 0; r < kRound; ++r) {
+      transpose_units<kN>(lo[r], lane);
+      transpose_units<kN>(hi[r], lane);
+      if (at[r] < 0) continue;
+      const int h = div_by(vec[r], p.vph, p.vph_shift);
+      const int gb = vec[r] - h * p.vph;
+      char *dst = base + s_win[at[r]] + h * head + static_cast<int64_t>(gb * kN + i) * side.dhi;
+      const uint32_t half = (1u << kN) - 1u;
+      const uint32_t ma = window[r] & half, mb = (window[r] >> kN) & half;
+      if (ma == half && mb == half) {
+        Vec32 y;
+        y.w[0] = lo[r][0], y.w[1] = lo[r][1], y.w[2] = lo[r][2], y.w[3] = lo[r][3];
+        y.w[4] = hi[r][0], y.w[5] = hi[r][1], y.w[6] = hi[r][2], y.w[7] = hi[r][3];
+        store_stream32(dst, y);
+      } else {
+        if (ma == half)
+          store_stream(dst, make_uint4(lo[r][0], lo[r][1], lo[r][2], lo[r][3]));
+        else if (ma)
+          store_units<kN>(dst, lo[r], ma);
+        if (mb == half)
+          store_stream(dst + 16, make_uint4(hi[r][0], hi[r][1], hi[r][2], hi[r][3]));
+        else if (mb)
+          store_units<kN>(dst + 16, hi[r], mb);
+      }
+    }
+  }
+}
+
+template <typename SlotT>
+__global__ void __launch_bounds__(kWriteThreads) kvx_write_packed_kernel(const WritePackedParams p) {
+  __shared__ int64_t s_slot[kPackedSlots];
+  __shared__ int64_t s_win[kPackedTile];
+  __shared__ int32_t s_frag[kPackedTile];
+  __shared__ int s_count;
+  pdl_prologue();
+  const int tid = threadIdx.x;
+  const int64_t tok0 = static_cast<int64_t>(blockIdx.x) * p.tok_tile;
+  const int ntok = static_cast<int>(min(static_cast<int64_t>(p.tok_tile), p.num_tokens - tok0));
+  if (tid < p.tok_tile + 17) {
+    const int64_t t = tok0 - 1 + tid;
+    int64_t sl = -1;
+    if (t >= 0 && t < p.num_tokens) {
+      sl = static_cast<int64_t>(static_cast<const SlotT *>(p.slots)[t]);
+      if (sl >= 0) {  // a slot beyond the pool is skipped like padding
+        int64_t b, o;
+        split_slot(sl, p.block_size, p.bs_shift, &b, &o);
+        if (b >= p.num_blocks) sl = -1;
+      }
+    }
+    s_slot[tid] = sl < 0 ? -1 : sl;
+  }
+  // (write_packed_tensor begins with a barrier)
+#define KVX_PACKED_TENSOR(N, rows, pitch, base, blk, head, side) \
+  write_packed_tensor<N>(p, rows, pitch, base, blk, head, side, s_slot, s_frag, s_win, &s_count, ntok)
+  switch (p.k.n_shift) {
+    case 0: KVX_PACKED_TENSOR(1, p.key, p.k_pitch, p.k_base, p.k_blk, p.k_head, p.k); break;
+    case 1: KVX_PACKED_TENSOR(2, p.key, p.k_pitch, p.k_base, p.k_blk, p.k_head, p.k); break;
+    case 2: KVX_PACKED_TENSOR(4, p.key, p.k_pitch, p.k_base, p.k_blk, p.k_head, p.k); break;
+    default: KVX_PACKED_TENSOR(8, p.key, p.k_pitch, p.k_base, p.k_blk, p.k_head, p.k); break;
+  }
+  __syncthreads();  // the fragment list is rebuilt for V (its window may differ)
+  switch (p.v.n_shift) {
+    case 0: KVX_PACKED_TENSOR(1, p.value, p.v_pitch, p.v_base, p.v_blk, p.v_head, p.v); break;
+    case 1: KVX_PACKED_TENSOR(2, p.value, p.v_pitch, p.v_base, p.v_blk, p.v_head, p.v); break;
+    case 2: KVX_PACKED_TENSOR(4, p.value, p.v_pitch, p.v_base, p.v_blk, p.v_head, p.v); break;
+    default: KVX_PACKED_TENSOR(8, p.value, p.v_pitch, p.v_base, p.v_blk, p.v_head, p.v); break;
+  }
+#undef KVX_PACKED_TENSOR
 }
 
 // CTA-granular variant: one work item = one part of a page chunk, K AND V, moved by the
@@ -1861,6 +2299,40 @@ kvx_status_t write_impl(const kvx_cache_desc_t *cache, const kvx_write_desc_t *w
   const bool k_packed = !fp8 && view_packed16(gp.k, elem, D), v_packed = !fp8 && view_packed16(gp.v, elem, D);
   const int64_t k_pitch = write->io.key.stride[0] * io_elem, v_pitch = write->io.value.stride[0] * io_elem;
   const bool pitched = k_pitch != row_bytes || v_pitch != row_bytes;  // token rows further apart than dense
+  // ---- packed pages with pack groups below 16 bytes (or mixed): fragment / transposition tier --
+  PackedSide k_side{}, v_side{};
+  const int64_t tiles_knob = opt(g_opt.packed_tiles);
+  if (!fp8 && !opt(g_opt.force_generic) && tiles_knob != 0 && (D * io_elem) % 16 == 0 && k_pitch % 16 == 0 &&
+      v_pitch % 16 == 0 && aligned(write->io.key.data, 16) && aligned(write->io.value.data, 16) &&
+      row_bytes / 16 <= (1 << 20) && view_packed_tile(gp.k, elem, D, cache->block_size, &k_side) &&
+      view_packed_tile(gp.v, elem, D, cache->block_size, &v_side) &&
+      // K and V both in 16-byte groups: the token-fastest row kernel below is the faster one
+      (k_side.n_shift != 0 || v_side.n_shift != 0 || tiles_knob == 2)) {
+    WritePackedParams q;
+    q.key = static_cast<const char *>(write->io.key.data);
+    q.value = static_cast<const char *>(write->io.value.data);
+    q.k_pitch = k_pitch, q.v_pitch = v_pitch;
+    q.k_base = gp.k.base, q.k_blk = gp.k.blk, q.k_head = gp.k.head;
+    q.v_base = gp.v.base, q.v_blk = gp.v.blk, q.v_head = gp.v.head;
+    q.k = k_side, q.v = v_side;
+    q.slots = write->slots.slots;
+    q.num_tokens = static_cast<int32_t>(T);
+    q.num_blocks = gp.g.num_blocks;
+    q.block_size = gp.g.block_size;
+    q.bs_shift = shift_of(q.block_size);
+    q.vpr = static_cast<int32_t>(row_bytes / 16);
+    q.vph = static_cast<int32_t>(D * io_elem / 16);
+    q.vph_shift = shift_of(q.vph);
+    int tile = kPackedTile;
+    while (tile > 1 && (T + tile - 1) / tile < static_cast<int64_t>(dev.sm_count) * 4) tile >>= 1;
+    q.tok_tile = tile;
+    const int grid = static_cast<int>((T + tile - 1) / tile);
+    if (s32)
+      launch_streaming(kvx_write_packed_kernel<int32_t>, grid, kWriteThreads, 0, cs, q);
+    else
+      launch_streaming(kvx_write_packed_kernel<int64_t>, grid, kWriteThreads, 0, cs, q);
+    return finish_launch();
+  }
   const bool vec_ok = !opt(g_opt.force_generic) && (D * io_elem) % 16 == 0 && k_pitch % 16 == 0 && v_pitch % 16 == 0 &&
                       !(pitched && (k_packed || v_packed)) &&
                       (!fp8 || (gp.k.head * H < INT32_MAX && gp.v.head * H < INT32_MAX)) &&  // 32-bit in-page offsets
@@ -1917,19 +2389,32 @@ kvx_status_t write_impl(const kvx_cache_desc_t *cache, const kvx_write_desc_t *w
           gp.k.tok % 16 == 0 && gp.v.tok % 16 == 0 && gp.k.head % 16 == 0 && gp.v.head % 16 == 0) {
         q.w.vpr = static_cast<int32_t>(row32), q.w.vpr_shift = shift_of(row32);
         q.w.vps = static_cast<int32_t>(head32), q.w.vps_shift = shift_of(head32);
-        q.w.tok_tile = pick_tok_tile(T, 2 * q.w.vpr, dev.sm_count);  // same bytes per CTA as the 128-bit form
+        // 32-byte vectors per CTA: f8_tile_mult x the bytes per CTA of the 128-bit form
+        const int64_t want = std::max<int64_t>(1, opt(g_opt.f8_tile_mult)) * opt(g_opt.write_vecs_per_cta) / 2;
+        int64_t tile = std::min<int64_t>(kMaxTokTile, std::max<int64_t>(1, want / q.w.vpr));
+        while (tile > 1 && (T + tile - 1) / tile < static_cast<int64_t>(dev.sm_count) * 4) tile >>= 1;
+        q.w.tok_tile = static_cast<int32_t>(tile);
         const int wgrid = static_cast<int>((T + q.w.tok_tile - 1) / q.w.tok_tile);
+        const bool two = opt(g_opt.f8_unroll) >= 2;
+#define KVX_F8_WIDE(IoT, SlotT)                                                                   \
+  do {                                                                                            \
+    if (two)                                                                                      \
+      launch_streaming(kvx_write_f8_wide_kernel<IoT, SlotT, 2>, wgrid, kWriteThreads, 0, cs, q);  \
+    else                                                                                          \
+      launch_streaming(kvx_write_f8_wide_kernel<IoT, SlotT, 1>, wgrid, kWriteThreads, 0, cs, q);  \
+  } while (0)
         if (io_dtype == KVX_DTYPE_BF16) {
           if (s32)
-            launch_streaming(kvx_write_f8_wide_kernel<BF16, int32_t>, wgrid, kWriteThreads, 0, cs, q);
+            KVX_F8_WIDE(BF16, int32_t);
           else
-            launch_streaming(kvx_write_f8_wide_kernel<BF16, int64_t>, wgrid, kWriteThreads, 0, cs, q);
+            KVX_F8_WIDE(BF16, int64_t);
         } else {
           if (s32)
-            launch_streaming(kvx_write_f8_wide_kernel<F16, int32_t>, wgrid, kWriteThreads, 0, cs, q);
+            KVX_F8_WIDE(F16, int32_t);
           else
-            launch_streaming(kvx_write_f8_wide_kernel<F16, int64_t>, wgrid, kWriteThreads, 0, cs, q);
+            KVX_F8_WIDE(F16, int64_t);
         }
+#undef KVX_F8_WIDE
         return finish_launch();
       }
 #define KVX_F8_WRITE(IoT)                                                                                     \
@@ -2148,9 +2633,16 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
   const bool k_packed = !fp8 && !ragged && view_packed16(gp.k, elem, D);
   const bool v_packed = !fp8 && !ragged && view_packed16(gp.v, elem, D);
   const bool packed = k_packed || v_packed;
+  PackedSide k_side{}, v_side{};
+  const int64_t tiles_knob = opt(g_opt.packed_tiles);
+  const bool tiles = !fp8 && !ragged && !offsets && tiles_knob != 0 &&
+                     view_packed_tile(gp.k, elem, D, cache->block_size, &k_side) &&
+                     view_packed_tile(gp.v, elem, D, cache->block_size, &v_side);
   const bool vec_ok = !opt(g_opt.force_generic) && (D * io_elem) % 16 == 0 && aligned(gather->io.key.data, 16) &&
-                      aligned(gather->io.value.data, 16) && (k_packed || view_vectorisable(gp.k, elem, D, in_vec)) &&
-                      (v_packed || view_vectorisable(gp.v, elem, D, in_vec)) && chunk_vecs < (int64_t{1} << 30) &&
+                      aligned(gather->io.value.data, 16) &&
+                      (tiles || ((k_packed || view_vectorisable(gp.k, elem, D, in_vec)) &&
+                                 (v_packed || view_vectorisable(gp.v, elem, D, in_vec)))) &&
+                      chunk_vecs < (int64_t{1} << 30) &&
                       S * static_cast<int64_t>(gs.max_blocks) < (int64_t{1} << 31) &&
                       (!offsets || (aligned(gs.pool[0], in_vec) && aligned(gs.pool[1], in_vec) &&
                                     gs.pool_block_bytes % in_vec == 0));
@@ -2193,6 +2685,41 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
           cudaLaunchKernelEx(&cfg, kvx_gather_ragged_kernel<int64_t, 4>, p);
         return finish_launch();
       }
+    }
+    if (tiles) {
+      // ---- packed pages: transposing tiles (one item = up to 4 KB of one head's tile) ----
+      GatherPackedParams pp;
+      pp.g = p;
+      pp.k = k_side, pp.v = v_side;
+      pp.slots = static_cast<int32_t>(static_cast<int64_t>(cache->block_size) * D * elem / 32);
+      pp.pieces = (pp.slots + 127) / 128;
+      pp.head_out_bytes = D * elem;
+      pp.g.parts = static_cast<int32_t>(H) * pp.pieces;
+      pp.rows = tiles_knob != 3 && k_side.n_shift == 0 && v_side.n_shift == 0 && k_side.runs % 4 == 0 &&
+                (D * elem) % 128 == 0 && H * D * elem < (int64_t{1} << 30);
+      if (pp.rows) {  // items of 8 token rows, all heads
+        pp.g.parts = k_side.runs / 4;
+        pp.pieces = static_cast<int32_t>(D * elem / 128);
+      }
+      const int64_t max_items = S * gs.max_blocks * pp.g.parts * 2;
+      if (max_items <= opt(g_opt.gather_rect_items)) pp.g.use_prefix = 0;
+      const int64_t need = (max_items + kGatherWarps - 1) / kGatherWarps;
+      const int64_t per_sm = std::max<int64_t>(1, opt(g_opt.gather_ctas_per_sm));
+      const int64_t grid = std::max<int64_t>(1, std::min(static_cast<int64_t>(dev.sm_count) * per_sm, (need + 1) / 2));
+      const size_t smem = pp.g.use_prefix ? static_cast<size_t>(S + 1) * sizeof(int32_t) : 0;
+      const unsigned ug = static_cast<unsigned>(grid);
+      if (pp.rows) {
+        if (s32)
+          launch_streaming(kvx_gather_packed_kernel<int32_t, 4, true>, ug, kGatherThreads, smem, cs, pp);
+        else
+          launch_streaming(kvx_gather_packed_kernel<int64_t, 4, true>, ug, kGatherThreads, smem, cs, pp);
+      } else {
+        if (s32)
+          launch_streaming(kvx_gather_packed_kernel<int32_t, 4, false>, ug, kGatherThreads, smem, cs, pp);
+        else
+          launch_streaming(kvx_gather_packed_kernel<int64_t, 4, false>, ug, kGatherThreads, smem, cs, pp);
+      }
+      return finish_launch();
     }
     const bool contiguous_pages = !fp8 && !packed && gp.k.head == D * elem && gp.v.head == D * elem &&
                                   gp.k.tok == H * D * elem && gp.v.tok == H * D * elem;

@@ -19,14 +19,16 @@ def make_case(seed: int, *, layout=abi.LAYOUT_NHD, dtype=abi.DTYPE_BF16, num_blo
               heads=2, dim=8, pack=1, seqs=2, lens=None, max_seq_len=None, max_blocks=None,
               slot_dtype=np.int64, index_dtype=np.int32, pad_frac=0.0, oob_slots=0, bad_blocks=0,
               stride_pad=None, real_values=False, cache_dtype=None, scale_gran=abi.SCALE_NONE,
-              write_all=True, tokens=None) -> Case:
+              write_all=True, tokens=None, v_pack=0) -> Case:
     """One case.  Sequences own disjoint pages drawn from a seeded permutation; the write
     batch holds every token of every sequence (sequence-major) unless ``tokens`` caps it.
 
     pad_frac    fraction of slots replaced by -1 (and a few by other negatives)
     oob_slots   slots pointing past the pool (block >= num_blocks): must be skipped
     bad_blocks  block-table entries replaced by -1 / >= num_blocks inside valid ranges
-    stride_pad  (blk, tok, head) extra elements added to those strides (non-canonical pool)
+    stride_pad  (blk, tok, head) extra elements added to those strides (non-canonical pool); for
+                HND_PACKED pools: (blk, group row, head)
+    v_pack      pack factor of the V tensor of an HND_PACKED pool when it differs from K's
     """
     rng = np.random.default_rng(seed)
     geom = abi.CacheGeometry(num_blocks, block_size, heads, dim, layout, pack)
@@ -76,10 +78,11 @@ def make_case(seed: int, *, layout=abi.LAYOUT_NHD, dtype=abi.DTYPE_BF16, num_blo
 
     k_stride = v_stride = None
     n_elems = geom.elems
+    geom_v = abi.CacheGeometry(num_blocks, block_size, heads, dim, layout, v_pack) if v_pack else geom
     if stride_pad is not None:
         k_stride = _padded_strides(geom, stride_pad)
-        v_stride = _padded_strides(geom, tuple(2 * x for x in stride_pad))
-        n_k, n_v = extent(geom.shape, k_stride), extent(geom.shape, v_stride)
+        v_stride = _padded_strides(geom_v, tuple(2 * x for x in stride_pad))
+        n_k, n_v = extent(geom.shape, k_stride), extent(geom_v.shape, v_stride)
     else:
         n_k = n_v = n_elems
     case = Case(geom=geom, cache_dtype=cache_dtype, io_dtype=dtype, key=key, value=value, slots=slots,
@@ -87,7 +90,8 @@ def make_case(seed: int, *, layout=abi.LAYOUT_NHD, dtype=abi.DTYPE_BF16, num_blo
                 k_stride=k_stride, v_stride=v_stride, table=table,
                 lens=np.array(lens, dtype=index_dtype), max_seq_len=max_seq_len,
                 out_k=sentinel_fill(seqs * max_seq_len * heads * dim, dtype).reshape(seqs, max_seq_len, heads, dim),
-                out_v=sentinel_fill(seqs * max_seq_len * heads * dim, dtype).reshape(seqs, max_seq_len, heads, dim))
+                out_v=sentinel_fill(seqs * max_seq_len * heads * dim, dtype).reshape(seqs, max_seq_len, heads, dim),
+                v_pack=v_pack)
     if cache_dtype == abi.DTYPE_F8_E4M3:
         n = heads if scale_gran == abi.SCALE_PER_HEAD else 1
         case.scale_gran = scale_gran
@@ -111,7 +115,12 @@ def _padded_strides(geom: abi.CacheGeometry, pad) -> list[int]:
         s_head = bs * s_tok + head_pad
         s_blk = H * s_head + blk_pad
         return [s_blk, s_head, s_tok, 1]
-    raise ValueError("padded strides: NHD / HND only")
+    if geom.layout == abi.LAYOUT_HND_PACKED:
+        s_row = bs * geom.pack + tok_pad          # one pack group of every token of the page
+        s_head = (D // geom.pack) * s_row + head_pad
+        s_blk = H * s_head + blk_pad
+        return [s_blk, s_head, s_row, geom.pack, 1]
+    raise ValueError("padded strides: unknown layout")
 
 
 def expected_write_numpy(case: Case):
@@ -327,3 +336,12 @@ def to_pitched(case: Case, key_extra: int, value_extra: int, seed: int = 0) -> C
         out[name] = wide
         out[name + "_pitch"] = hd + extra
     return dataclasses.replace(case, **out)
+
+
+def reorder_tokens(case: Case, order: np.ndarray) -> Case:
+    """The same case with the write batch's tokens taken in ``order`` (a permutation or a
+    selection): rows and slots move together, so the pages end up the same for a permutation."""
+    import dataclasses
+    order = np.asarray(order, dtype=np.int64)
+    return dataclasses.replace(case, key=case.key[order].copy(), value=case.value[order].copy(),
+                               slots=case.slots[order].copy())

@@ -92,6 +92,9 @@ class Case:
     # arrays whose first heads * dim columns are the row (elements; 0 = dense [T, H, D])
     key_pitch: int = 0
     value_pitch: int = 0
+    # HND_PACKED pools whose V tensor has a pack factor of its own (vLLM / TGI "paged" caches: K in
+    # 16-byte pack groups, V [blocks, heads, dim, block_size] = pack 1); 0 = the geometry's pack
+    v_pack: int = 0
     note: str = ""
     keep: list = field(default_factory=list)
 
@@ -131,6 +134,10 @@ def descriptors(case: Case, bufs: dict, memory: int):
     else:
         cache = abi.cache_desc(g, case.cache_dtype, _addr(bufs["cache_k"]), _addr(bufs["cache_v"]), memory,
                                case.k_stride, case.v_stride)
+        if case.v_pack:
+            import dataclasses
+            gv = dataclasses.replace(g, pack=case.v_pack)
+            cache.v = abi.tensor_desc(_addr(bufs["cache_v"]), case.cache_dtype, gv.shape, case.v_stride, g.layout, memory)
     ks, vs = _scale(case, bufs.get("k_scale"), "k"), _scale(case, bufs.get("v_scale"), "v")
     write = abi.write_desc(case.T, g.num_kv_heads, g.head_dim, case.io_dtype, _addr(bufs["key"]),
                            _addr(bufs["value"]), index_code(case.slots), _addr(bufs["slots"]), memory, ks, vs)

@@ -91,7 +91,7 @@ def test_host_pipeline_takes_pitched_host_rows():
     case = cases.to_pitched(base, 2 * 4 * 64, 24, seed=3)   # K rows 3x as far apart, V rows oddly so
     _, ek, ev = oracle_write(case)
     _, eok, eov = oracle_gather(case, ek, ev)
-    k, v, ok_, ov_, h2d, _ = _run(case, 1 << 14)
+    k, v, ok_, ov_, h2d, _ = _run(case, 1 << 16)   # a chunk holds one padded sequence
     assert np.array_equal(k, ek) and np.array_equal(v, ev)
     assert np.array_equal(ok_, eok) and np.array_equal(ov_, eov)
     assert h2d < 2 * case.T * (3 * 4 * 64 * 2)              # only the rows themselves crossed the bus
@@ -103,7 +103,7 @@ def test_host_pipeline_takes_pitched_host_rows():
     cache.k.memory = cache.v.memory = abi.MEMORY_DEVICE
     write.io.key.stride[1] = 2 * 64                          # heads no longer adjacent inside a row
     pipe = C.c_void_p()
-    assert L.kvx_host_pipe_create(1 << 14, 3, case.table.shape[1], C.byref(pipe)) == OK
+    assert L.kvx_host_pipe_create(1 << 16, 3, case.table.shape[1], C.byref(pipe)) == OK
     try:
         assert L.kvx_host_write_kv(pipe, C.byref(cache), C.byref(write)) == abi.STATUS_UNSUPPORTED
         assert L.kvx_host_pipe_sync(pipe) == OK

@@ -1,0 +1,139 @@
+"""HND_PACKED pages ([blocks, heads, dim / pack, block_size, pack]) through the transposing
+kernels: every pack size whose group is 2, 4, 8 or 16 bytes, K and V with different packs (the
+"paged" caches of vLLM and TGI: K in 16-byte groups, V [blocks, heads, dim, block_size]), page
+sizes and strides that do and do not qualify, padding, out-of-range slots and page ids, partial
+last pages, pitched key / value rows -- byte for byte against the CPU checker, and against the
+one-element-per-thread tier of the library itself."""
+import numpy as np
+import pytest
+
+import kvx_b200
+from kvx_b200 import abi
+
+import cases
+from harness import gpu_gather, gpu_write, oracle_gather, oracle_write
+
+pytestmark = pytest.mark.gpu
+OK = abi.STATUS_OK
+PACKED = abi.LAYOUT_HND_PACKED
+
+
+@pytest.fixture(autouse=True)
+def _defaults():
+    saved = {n: kvx_b200.get_option(n) for n in ("packed_tiles", "force_generic", "gather_rect_items")}
+    yield
+    for n, v in saved.items():
+        kvx_b200.set_option(n, v)
+
+
+def _check(case, knobs=(1,)):
+    """knobs: values of the packed_tiles tuning knob to run with: 1 = the library's choice, 2 = the
+    fragment write kernel also where K and V are both in 16-byte groups, 3 = the gather without its
+    whole-line lane order, 0 = the older tiers (row kernel for 16-byte groups, one element per thread
+    otherwise)."""
+    st, ek, ev = oracle_write(case)
+    assert st == OK
+    st, eok, eov = oracle_gather(case, ek, ev)
+    assert st == OK
+    for knob in knobs:
+        kvx_b200.set_option("packed_tiles", knob)
+        st, k, v = gpu_write(case)
+        assert st == OK
+        assert np.array_equal(k, ek), f"K pages differ ({case.note}, packed_tiles {knob})"
+        assert np.array_equal(v, ev), f"V pages differ ({case.note}, packed_tiles {knob})"
+        for rect in (0, 1 << 40):
+            kvx_b200.set_option("gather_rect_items", rect)
+            st, gk, gv = gpu_gather(case, ek, ev)
+            assert st == OK
+            assert np.array_equal(gk, eok), f"K out differs ({case.note}, packed_tiles {knob}, rect {rect})"
+            assert np.array_equal(gv, eov), f"V out differs ({case.note}, packed_tiles {knob}, rect {rect})"
+
+
+@pytest.mark.parametrize("dtype,packs", [(abi.DTYPE_BF16, (1, 2, 4, 8)), (abi.DTYPE_F16, (8,)), (abi.DTYPE_F32, (1, 2, 4))])
+def test_every_pack_size(dtype, packs):
+    """Units of 2 / 4 / 8 / 16 bytes; lengths that leave partial pages; slots with holes."""
+    for i, pack in enumerate(packs):
+        for j, kw in enumerate([
+            dict(heads=8, dim=128, block_size=16, num_blocks=64, lens=[100, 17, 256, 1, 0, 333], pad_frac=0.1, bad_blocks=3),
+            dict(heads=2, dim=64, block_size=32, num_blocks=24, lens=[31, 33, 160], oob_slots=3, index_dtype=np.int64),
+            dict(heads=3, dim=48, block_size=16, num_blocks=20, lens=[50, 70, 9], max_seq_len=60, slot_dtype=np.int32),
+        ]):
+            case = cases.make_case(2000 + 10 * i + j, layout=PACKED, pack=pack, dtype=dtype, **kw)
+            case.note = f"pack {pack} case {j}"
+            _check(case, knobs=(1, 2, 3, 0))
+
+
+@pytest.mark.parametrize("dtype", [abi.DTYPE_BF16, abi.DTYPE_F16])
+def test_paged_attention_cache_k_packed_v_transposed(dtype):
+    """K [blocks, heads, dim / 8, block_size, 8], V [blocks, heads, dim, block_size] (pack 1)."""
+    for j, kw in enumerate([
+        dict(heads=8, dim=128, block_size=16, num_blocks=80, lens=[300, 77, 512, 9, 130], pad_frac=0.1),
+        dict(heads=4, dim=64, block_size=32, num_blocks=20, lens=[64, 1, 200], bad_blocks=2),
+        dict(heads=1, dim=256, block_size=16, num_blocks=12, lens=[16, 16, 47]),
+    ]):
+        case = cases.make_case(2100 + j, layout=PACKED, pack=8, v_pack=1, dtype=dtype, **kw)
+        case.note = f"paged {j}"
+        _check(case, knobs=(1, 0))
+
+
+def test_decode_sized_batches_and_scattered_slots():
+    """One token per sequence (every fragment a single slot), slots in reverse order, repeated
+    windows met from two sides."""
+    case = cases.make_case(2200, layout=PACKED, pack=1, dtype=abi.DTYPE_BF16, heads=4, dim=64, block_size=16,
+                           num_blocks=64, lens=[33] * 20)
+    rng = np.random.default_rng(5)
+    order = rng.permutation(case.T)
+    shuffled = cases.reorder_tokens(case, order)
+    shuffled.note = "shuffled tokens"
+    _check(shuffled)
+    backwards = cases.reorder_tokens(case, np.arange(case.T)[::-1])
+    backwards.note = "tokens backwards"
+    _check(backwards)
+    one = cases.reorder_tokens(case, np.array([t for t in range(case.T) if t % 33 == 32]))
+    one.note = "last token of every sequence"
+    _check(one)
+
+
+def test_shapes_that_do_not_qualify_fall_back():
+    """Group rows that are not whole 32-byte units, padded group rows, a head_dim whose rows are not
+    whole vectors: still exact (other tiers)."""
+    for j, kw in enumerate([
+        dict(pack=1, heads=2, dim=64, block_size=8, num_blocks=16, lens=[20, 9]),        # 8 tokens x 2 bytes = 16-byte rows
+        dict(pack=2, heads=2, dim=20, block_size=16, num_blocks=16, lens=[40, 9]),       # 40-byte heads
+        dict(pack=4, heads=2, dim=64, block_size=5, num_blocks=16, lens=[13, 9]),
+    ]):
+        case = cases.make_case(2300 + j, layout=PACKED, dtype=abi.DTYPE_BF16, **kw)
+        case.note = f"fallback {j}"
+        _check(case)
+
+
+def test_padded_strides_and_pitched_rows():
+    """Group rows, heads and blocks further apart than dense (multiples of 32 bytes: the tile
+    kernels; other multiples: the other tiers), and key / value rows with a token pitch."""
+    for j, (pad, pack, vp) in enumerate([((32, 16, 48), 8, 0), ((16, 32, 0), 1, 0), ((64, 16, 16), 8, 1), ((3, 5, 7), 2, 0)]):
+        case = cases.make_case(2400 + j, layout=PACKED, pack=pack, v_pack=vp, dtype=abi.DTYPE_BF16, heads=4, dim=64,
+                               block_size=16, num_blocks=24, lens=[100, 40, 7], stride_pad=pad, pad_frac=0.05)
+        case.note = f"padded strides {j}"
+        _check(case)
+    base = cases.make_case(2450, layout=PACKED, pack=8, v_pack=1, dtype=abi.DTYPE_BF16, heads=4, dim=64,
+                           block_size=16, num_blocks=24, lens=[100, 40, 7], pad_frac=0.1)
+    pitched = cases.to_pitched(base, 2 * 4 * 64, 64, seed=1)
+    pitched.note = "pitched rows"
+    _check(pitched)
+
+
+def test_full_size_round_trip_paged_layout():
+    """The Llama-3-70B shape with the paged-attention cache layout at its full token count:
+    write, gather, and the benchmark's own byte check."""
+    import torch
+    from kvx_b200 import bench_support as bs, workloads
+    for layout in ("packed", "paged"):
+        dw = bs.setup_device_workload(workloads.SPECS["c4"], layers=1, layout=layout)
+        stream = torch.cuda.current_stream().cuda_stream
+        bs.fill_sentinel(dw)
+        bs.launch_write(dw, 0, stream)
+        bs.launch_gather(dw, 0, stream)
+        torch.cuda.synchronize()
+        res = bs.verify_layer(dw, 0)
+        assert res["ok"], (layout, res)
+        del dw
