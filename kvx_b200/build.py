@@ -93,6 +93,30 @@ def build_torch_ops(force: bool = False, verbose: bool = False) -> str:
     return TORCH_OPS_PATH
 
 
+PROGRAMS = {  # native programs over the C ABI: source -> binary under build/
+    "kvx_bench": os.path.join(ROOT, "benchmarks", "kvx_bench.cu"),
+    "kvx_kernel_test": os.path.join(ROOT, "tests", "kvx_kernel_test.cu"),
+}
+
+
+def build_programs(force: bool = False, verbose: bool = False) -> dict:
+    """Compile the native benchmark and the native kernel test against ``libkvx_b200.so``
+    (found at run time through an rpath relative to the binary).  Returns name -> path."""
+    build(force=False, verbose=verbose)
+    headers = [os.path.join(INCLUDE, f) for f in os.listdir(INCLUDE)]
+    out = {}
+    for name, src in PROGRAMS.items():
+        exe = os.path.join(BUILD_DIR, name)
+        out[name] = exe
+        if not force and not _stale(exe, [src, LIB_PATH] + headers):
+            continue
+        cmd = [_nvcc(), "-std=c++17", "-O2", "-gencode", "arch=compute_100a,code=sm_100a", "-I" + INCLUDE, src, "-o", exe,
+               "-L" + LIB_DIR, "-lkvx_b200", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../kvx_b200/lib", "-lpthread"]
+        subprocess.run(cmd, check=True, stdout=None if verbose else subprocess.PIPE, stderr=subprocess.STDOUT)
+    return out
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose=True))
+    print(build_programs(force="--force" in sys.argv, verbose=True))
     print(build_torch_ops(force="--force" in sys.argv, verbose=True))
