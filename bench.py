@@ -578,6 +578,8 @@ def run_e2e(args, dw, dist) -> dict:
     # the last layer's gathered bytes must equal what the device-resident path produces
     check = bool(torch.equal(hok[0, : int(meta.lens[0])].cuda(), dw.out_k[0, : int(meta.lens[0])])) if dw.layers else True
     L.kvx_host_pipe_destroy(pipe)
+    del hk, hv, hok, hov
+    ceiling = pcie_ceiling(dist)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     bytes_all = (meta.write_bytes(spec.heads) + meta.gather_bytes(spec.heads)) * dw.layers * steps
     return {"value": round(bytes_all / dt / 1e9, 2), "unit": "GB/s", "steps": steps,
@@ -585,8 +587,51 @@ def run_e2e(args, dw, dist) -> dict:
             "h2d_bytes_per_step": int((h1.value - h0.value) // steps),
             "d2h_bytes_per_step": int((d1.value - d0.value) // steps),
             "pcie_gbs_per_gpu": round(((h1.value - h0.value) + (d1.value - d0.value)) / dt / 1e9, 2),
+            "pcie_ceiling": ceiling,
             "matches_device_path": check, "n_gpus": world,
             "api": "kvx_host_write_kv + kvx_host_gather_kv (pinned host buffers, staged in chunks)"}
+
+
+def pcie_ceiling(dist, chunk_mb: int = 64, chunks: int = 16) -> dict:
+    """What the box gives plain pinned copies: every rank at once moves `chunks` chunks of `chunk_mb` MB
+    host -> device, then device -> host, then both directions at the same time (two streams, one
+    asynchronous copy per chunk), wall-clock timed from a barrier to the last rank's completion.
+    The host-buffer leg above cannot beat the 'both' figure; it is reported next to it."""
+    import torch
+    n = chunk_mb << 20
+    host_in = torch.empty(n, dtype=torch.uint8).pin_memory()
+    host_out = torch.empty(n, dtype=torch.uint8).pin_memory()
+    host_in.fill_(1)
+    host_out.fill_(0)  # first touch by this process
+    dev_in = torch.empty(n, dtype=torch.uint8, device="cuda")
+    dev_out = torch.ones(n, dtype=torch.uint8, device="cuda")
+    up, down = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def run(h2d: bool, d2h: bool) -> float:
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(chunks):
+            if h2d:
+                with torch.cuda.stream(up):
+                    dev_in.copy_(host_in, non_blocking=True)
+            if d2h:
+                with torch.cuda.stream(down):
+                    host_out.copy_(dev_out, non_blocking=True)
+        torch.cuda.synchronize()
+        t = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device="cuda")
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    run(True, True)  # warm-up
+    gb = n * chunks / 1e9
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    t_up, t_down, t_both = run(True, False), run(False, True), run(True, True)
+    return {"h2d_gbs_per_gpu": round(gb / t_up, 1), "d2h_gbs_per_gpu": round(gb / t_down, 1),
+            "both_gbs_per_gpu": round(2 * gb / t_both, 1), "both_gbs_all_gpus": round(2 * gb * world / t_both, 1),
+            "how": f"{chunks} x {chunk_mb} MB pinned copies per direction and rank, all {world} ranks at once"}
 
 
 def time_reference_kernels(dw, peak: float) -> dict:

@@ -38,6 +38,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <numeric>
 
 namespace {
 
@@ -1479,6 +1480,7 @@ struct WritePackedParams {
   int32_t vpr;             // 16-byte vectors per dense token row
   int32_t vph, vph_shift;  // ... per head
   int32_t tok_tile;        // power of two <= kPackedTile
+  int32_t lines;           // 1: K and V in 16-byte units through write_packed16_lines
 };
 
 // Stores the units of `w` (positions 0 .. kN-1 of a half window) whose bit is set in `mask`.
@@ -1594,6 +1596,78 @@ __device__ __forceinline__ void write_packed_tensor(const WritePackedParams &p, 
   }
 }
 
+// 16-byte units with whole 128-byte lines on both sides (the mirror of gather_packed16_rows): the
+// window is the 8 slots of one line of a group row; a lane takes token pair a = lane % 4 of the
+// window and group 8 gh + lane / 4, so that each of its two loads reads 4 token rows x 128 bytes
+// per warp instruction and its 32-byte store fills, with the three other pairs, one line of each
+// of 8 group rows.  Needs a multiple of 8 groups per head and block sizes that are multiples of 8.
+// (K and V in one loop over a shared fragment list measured 2-4 % slower than one pass each.)
+__device__ __forceinline__ void write_packed16_lines(const WritePackedParams &p, const char *rows, int64_t pitch,
+                                                     char *base, int64_t blk, int64_t head, const PackedSide &side,
+                                                     const int64_t *s_slot, int32_t *s_frag, int64_t *s_win,
+                                                     int *s_count, int ntok) {
+  constexpr int kW = 8;
+  const int tid = threadIdx.x, lane = tid & 31;
+  if (tid == 0) *s_count = 0;
+  __syncthreads();
+  if (tid < ntok) {
+    const int64_t sl = s_slot[1 + tid];
+    const int64_t before = s_slot[tid];
+    const int pos0 = static_cast<int>(sl & (kW - 1));
+    const bool continues = sl >= 0 && before >= 0 && sl == before + 1 && pos0 != 0;
+    if (sl >= 0 && !continues) {
+      int len = 1;
+      while (pos0 + len < kW && s_slot[1 + tid + len] == sl + len) ++len;
+      const int at = atomicAdd(s_count, 1);
+      s_frag[at] = tid | (pos0 << 8) | (len << 16);
+      int64_t b, o;
+      split_slot(sl - pos0, p.block_size, p.bs_shift, &b, &o);
+      s_win[at] = b * blk + o * 16;
+    }
+  }
+  __syncthreads();
+  const int nfrag = *s_count;
+  const int a = lane & 3, g_lo = lane >> 2;
+  const int blocks_per_row = p.vpr >> 3;  // 8-group blocks of one token row (all heads)
+  const int blocks_per_head = p.vph >> 3;
+  const int total = nfrag * blocks_per_row;
+  const int64_t tok0 = static_cast<int64_t>(blockIdx.x) * p.tok_tile;
+  constexpr int kRound = 4;
+  for (int e0 = tid >> 5; e0 < total; e0 += (kWriteThreads / 32) * kRound) {
+    uint4 x[kRound], y[kRound];
+    int64_t to[kRound];
+    uint32_t have[kRound];  // bit 0: the pair's first token exists, bit 1: its second
+#pragma unroll
+    for (int r = 0; r < kRound; ++r) {
+      const int e = e0 + r * (kWriteThreads / 32);
+      have[r] = 0u;
+      if (e >= total) continue;
+      const int frag = e / blocks_per_row, blk8 = e - frag * blocks_per_row;
+      const int32_t info = s_frag[frag];
+      const int first = info & 0xFF, pos0 = (info >> 8) & 0xFF, len = info >> 16;
+      const int h = blk8 / blocks_per_head, gh = blk8 - h * blocks_per_head;
+      const int ra = 2 * a - pos0, rb = ra + 1;
+      const char *from = rows + (tok0 + first) * pitch + static_cast<int64_t>(blk8 * 8 + g_lo) * 16;
+      if (ra >= 0 && ra < len) x[r] = load_stream(from + ra * pitch), have[r] |= 1u;
+      if (rb >= 0 && rb < len) y[r] = load_stream(from + rb * pitch), have[r] |= 2u;
+      to[r] = s_win[frag] + h * head + static_cast<int64_t>(gh * 8 + g_lo) * side.dhi + a * 32;
+    }
+#pragma unroll
+    for (int r = 0; r < kRound; ++r) {
+      if (have[r] == 3u) {
+        Vec32 v;
+        v.w[0] = x[r].x, v.w[1] = x[r].y, v.w[2] = x[r].z, v.w[3] = x[r].w;
+        v.w[4] = y[r].x, v.w[5] = y[r].y, v.w[6] = y[r].z, v.w[7] = y[r].w;
+        store_stream32(base + to[r], v);
+      } else if (have[r] == 1u) {
+        store_stream(base + to[r], x[r]);
+      } else if (have[r] == 2u) {
+        store_stream(base + to[r] + 16, y[r]);
+      }
+    }
+  }
+}
+
 template <typename SlotT>
 __global__ void __launch_bounds__(kWriteThreads) kvx_write_packed_kernel(const WritePackedParams p) {
   __shared__ int64_t s_slot[kPackedSlots];
@@ -1616,6 +1690,12 @@ __global__ void __launch_bounds__(kWriteThreads) kvx_write_packed_kernel(const W
       }
     }
     s_slot[tid] = sl < 0 ? -1 : sl;
+  }
+  if (p.lines) {
+    write_packed16_lines(p, p.key, p.k_pitch, p.k_base, p.k_blk, p.k_head, p.k, s_slot, s_frag, s_win, &s_count, ntok);
+    __syncthreads();
+    write_packed16_lines(p, p.value, p.v_pitch, p.v_base, p.v_blk, p.v_head, p.v, s_slot, s_frag, s_win, &s_count, ntok);
+    return;
   }
   // (write_packed_tensor begins with a barrier)
 #define KVX_PACKED_TENSOR(N, rows, pitch, base, blk, head, side) \
@@ -2078,7 +2158,11 @@ __device__ __forceinline__ uint32_t absmax_vec(const uint4 &x, F32) {
   return max(max(x.x & 0x7FFFFFFFu, x.y & 0x7FFFFFFFu), max(x.z & 0x7FFFFFFFu, x.w & 0x7FFFFFFFu));
 }
 
-template <typename IoT>
+// kFixedHead: the grid's stride over the vectors is a multiple of the vectors per token row, so a
+// thread meets the same place of a token row -- the same head -- in every iteration: it keeps
+// its maxima in registers, four loads of K and of V in flight, and joins the other lanes of its
+// head once, after the loop (the kernel is otherwise bound by instruction issue, not by memory).
+template <typename IoT, bool kFixedHead>
 __global__ void __launch_bounds__(kScaleThreads) kvx_kv_scales_kernel(const ScalesParams p) {
   extern __shared__ uint32_t s_max[];  // [2 * heads]
   __shared__ int s_last;
@@ -2087,25 +2171,60 @@ __global__ void __launch_bounds__(kScaleThreads) kvx_kv_scales_kernel(const Scal
   __syncthreads();
 
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kScaleThreads;
-  // total_vecs is rounded up to a multiple of the CTA size by the loop bound so that every
-  // lane of a warp takes part in the shuffles.
-  const int64_t bound = (p.total_vecs + kScaleThreads - 1) / kScaleThreads * kScaleThreads;
-  for (int64_t f = static_cast<int64_t>(blockIdx.x) * kScaleThreads + tid; f < bound; f += stride) {
+  if constexpr (kFixedHead) {
+    const int64_t first = static_cast<int64_t>(blockIdx.x) * kScaleThreads + tid;
     uint32_t mk = 0, mv = 0;
-    int h = 0;
-    if (f < p.total_vecs) {
-      mk = absmax_vec(load_stream(p.key + f * 16), IoT{});
-      mv = absmax_vec(load_stream(p.value + f * 16), IoT{});
-      const int v = static_cast<int>(p.vpr_shift >= 0 ? (f & (p.vpr - 1)) : (f % p.vpr));
-      h = div_by(v, p.vps, p.vps_shift);
+    int64_t f = first;
+    for (; f + 3 * stride < p.total_vecs; f += 4 * stride) {
+      uint4 a[4], b[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        a[u] = load_stream(p.key + (f + u * stride) * 16);
+        b[u] = load_stream(p.value + (f + u * stride) * 16);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        mk = max(mk, absmax_vec(a[u], IoT{}));
+        mv = max(mv, absmax_vec(b[u], IoT{}));
+      }
     }
+    for (; f < p.total_vecs; f += stride) {
+      mk = max(mk, absmax_vec(load_stream(p.key + f * 16), IoT{}));
+      mv = max(mv, absmax_vec(load_stream(p.value + f * 16), IoT{}));
+    }
+    // lanes of one group share a head (the group divides the vectors per head, and the CTA's
+    // first vector is a multiple of the CTA size): fold them, then one shared-memory update each
     for (int d = 1; d < p.group; d <<= 1) {
       mk = max(mk, __shfl_xor_sync(0xFFFFFFFFu, mk, d));
       mv = max(mv, __shfl_xor_sync(0xFFFFFFFFu, mv, d));
     }
-    if ((tid & (p.group - 1)) == 0 && f < p.total_vecs) {
+    if ((tid & (p.group - 1)) == 0 && first < p.total_vecs) {
+      const int v = static_cast<int>(p.vpr_shift >= 0 ? (first & (p.vpr - 1)) : (first % p.vpr));
+      const int h = div_by(v, p.vps, p.vps_shift);
       if (mk) atomicMax(&s_max[h], mk);
       if (mv) atomicMax(&s_max[p.heads + h], mv);
+    }
+  } else {
+    // total_vecs is rounded up to a multiple of the CTA size by the loop bound so that every
+    // lane of a warp takes part in the shuffles.
+    const int64_t bound = (p.total_vecs + kScaleThreads - 1) / kScaleThreads * kScaleThreads;
+    for (int64_t f = static_cast<int64_t>(blockIdx.x) * kScaleThreads + tid; f < bound; f += stride) {
+      uint32_t mk = 0, mv = 0;
+      int h = 0;
+      if (f < p.total_vecs) {
+        mk = absmax_vec(load_stream(p.key + f * 16), IoT{});
+        mv = absmax_vec(load_stream(p.value + f * 16), IoT{});
+        const int v = static_cast<int>(p.vpr_shift >= 0 ? (f & (p.vpr - 1)) : (f % p.vpr));
+        h = div_by(v, p.vps, p.vps_shift);
+      }
+      for (int d = 1; d < p.group; d <<= 1) {
+        mk = max(mk, __shfl_xor_sync(0xFFFFFFFFu, mk, d));
+        mv = max(mv, __shfl_xor_sync(0xFFFFFFFFu, mv, d));
+      }
+      if ((tid & (p.group - 1)) == 0 && f < p.total_vecs) {
+        if (mk) atomicMax(&s_max[h], mk);
+        if (mv) atomicMax(&s_max[p.heads + h], mv);
+      }
     }
   }
   __syncthreads();
@@ -2306,8 +2425,10 @@ kvx_status_t write_impl(const kvx_cache_desc_t *cache, const kvx_write_desc_t *w
       v_pitch % 16 == 0 && aligned(write->io.key.data, 16) && aligned(write->io.value.data, 16) &&
       row_bytes / 16 <= (1 << 20) && view_packed_tile(gp.k, elem, D, cache->block_size, &k_side) &&
       view_packed_tile(gp.v, elem, D, cache->block_size, &v_side) &&
-      // K and V both in 16-byte groups: the token-fastest row kernel below is the faster one
-      (k_side.n_shift != 0 || v_side.n_shift != 0 || tiles_knob == 2)) {
+      // K and V both in 16-byte groups: whole-line fragments when the shape allows (a multiple of 8
+      // groups per head, pages of a multiple of 8 tokens), else the token-fastest row kernel below
+      (k_side.n_shift != 0 || v_side.n_shift != 0 || tiles_knob == 2 ||
+       (tiles_knob != 3 && (D * io_elem) % 128 == 0 && cache->block_size % 8 == 0))) {
     WritePackedParams q;
     q.key = static_cast<const char *>(write->io.key.data);
     q.value = static_cast<const char *>(write->io.value.data);
@@ -2326,6 +2447,8 @@ kvx_status_t write_impl(const kvx_cache_desc_t *cache, const kvx_write_desc_t *w
     int tile = kPackedTile;
     while (tile > 1 && (T + tile - 1) / tile < static_cast<int64_t>(dev.sm_count) * 4) tile >>= 1;
     q.tok_tile = tile;
+    q.lines = k_side.n_shift == 0 && v_side.n_shift == 0 && tiles_knob != 2 && tiles_knob != 3 &&
+              (D * io_elem) % 128 == 0 && cache->block_size % 8 == 0;
     const int grid = static_cast<int>((T + tile - 1) / tile);
     if (s32)
       launch_streaming(kvx_write_packed_kernel<int32_t>, grid, kWriteThreads, 0, cs, q);
@@ -3063,12 +3186,26 @@ static kvx_status_t kv_scales_impl(const kvx_kv_io_desc_t *io, kvx_scale_granula
   if (grid < 1) grid = 1;
   const size_t smem = 2 * static_cast<size_t>(H) * sizeof(uint32_t);
   const cudaStream_t cs = as_stream(stream);
+  // A stride that is a multiple of the vectors per token row fixes every thread's head: round
+  // the grid down to a multiple of vpr / gcd(vpr, CTA size) when that leaves enough CTAs.
+  int64_t unit = p.vpr / std::gcd<int64_t, int64_t>(p.vpr, kScaleThreads);
+  bool fixed = p.total_vecs >= 4 * grid * kScaleThreads && grid >= unit && unit <= cap;
+  if (fixed) grid = grid / unit * unit;
+  const unsigned ug = static_cast<unsigned>(grid);
+#define KVX_SCALES(IoT)                                                    \
+  do {                                                                     \
+    if (fixed)                                                             \
+      kvx_kv_scales_kernel<IoT, true><<<ug, kScaleThreads, smem, cs>>>(p);  \
+    else                                                                   \
+      kvx_kv_scales_kernel<IoT, false><<<ug, kScaleThreads, smem, cs>>>(p); \
+  } while (0)
   if (io->key.dtype == KVX_DTYPE_BF16)
-    kvx_kv_scales_kernel<BF16><<<static_cast<unsigned>(grid), kScaleThreads, smem, cs>>>(p);
+    KVX_SCALES(BF16);
   else if (io->key.dtype == KVX_DTYPE_F16)
-    kvx_kv_scales_kernel<F16><<<static_cast<unsigned>(grid), kScaleThreads, smem, cs>>>(p);
+    KVX_SCALES(F16);
   else
-    kvx_kv_scales_kernel<F32><<<static_cast<unsigned>(grid), kScaleThreads, smem, cs>>>(p);
+    KVX_SCALES(F32);
+#undef KVX_SCALES
   return finish_launch();
 }
 
