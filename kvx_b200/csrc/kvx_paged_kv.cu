@@ -66,6 +66,7 @@ struct Options {
   std::atomic<int64_t> write_prefetch_waves{2};   // leading write CTAs (in units of 8 per SM) that prefetch their rows into the L2
   std::atomic<int64_t> f8_tile_mult{8};           // fp8 wide write: bytes per CTA relative to the copy write
   std::atomic<int64_t> f8_unroll{1};              // fp8 wide write: 32-byte vectors of K and of V in flight per thread
+  std::atomic<int64_t> packed_tile_tokens{32};    // tokens per CTA of the packed-page write
   std::atomic<int64_t> packed_tiles{1};           // 1 = transposing tile kernels for HND_PACKED pages where they apply
   std::atomic<int64_t> bulk_wait_us{1000000};     // a bulk-path wait on a copy is abandoned after this long
   std::atomic<int64_t> bulk_test_stall{0};        // test hook: pipe 0 of CTA 0 first waits on a barrier nothing completes
@@ -97,6 +98,7 @@ const OptionName kOptionNames[] = {
     {"wide", &Options::wide},
     {"f8_tile_mult", &Options::f8_tile_mult},
     {"f8_unroll", &Options::f8_unroll},
+    {"packed_tile_tokens", &Options::packed_tile_tokens},
     {"packed_tiles", &Options::packed_tiles},
     {"bulk_wait_us", &Options::bulk_wait_us},
     {"bulk_test_stall", &Options::bulk_test_stall},
@@ -1466,7 +1468,7 @@ __global__ void __launch_bounds__(kGatherThreads) kvx_gather_packed_kernel(const
 // left to that CTA.  Fragments never overlap, so every valid token is written exactly once.
 // A fragment that fills its window is stored as one 32-byte unit per group, one that fills an
 // aligned half as a 16-byte vector, anything else unit by unit.
-constexpr int kPackedTile = 64;              // most tokens per CTA
+constexpr int kPackedTile = 128;             // most tokens per CTA
 constexpr int kPackedSlots = kPackedTile + 17;  // + the token before the tile + up to W - 1 = 15 after it
 
 struct WritePackedParams {
@@ -1692,6 +1694,51 @@ __global__ void __launch_bounds__(kWriteThreads) kvx_write_packed_kernel(const W
     s_slot[tid] = sl < 0 ? -1 : sl;
   }
   if (p.lines) {
+    // A tile without a hole (no padded or out-of-range slot) needs no fragments: 16 consecutive
+    // tokens x one 16-byte group are one 256-byte run of a page wherever a page begins, so the
+    // threads run over tokens fastest (sub-tiles of 16) and store 16 bytes each -- measured 2-3 %
+    // faster than the fragment route, which pays for itself only where holes cut the runs
+    // (padded slots: 3.4 against 2.9 TB/s).
+    __shared__ int64_t s_win_v[kPackedTile];
+    __syncthreads();
+    const bool whole = __syncthreads_and(tid >= ntok || s_slot[1 + tid] >= 0);
+    if (whole) {
+      if (tid < ntok) {
+        int64_t b, o;
+        split_slot(s_slot[1 + tid], p.block_size, p.bs_shift, &b, &o);
+        s_win[tid] = b * p.k_blk + o * 16;
+        s_win_v[tid] = b * p.v_blk + o * 16;
+      }
+      __syncthreads();
+      const int per_sub = 16 * p.vpr;
+      const int nvec = ((ntok + 15) >> 4) * per_sub;
+      for (int f0 = tid; f0 < nvec; f0 += kWriteThreads * 4) {
+        uint4 kr[4], vr[4];
+        int64_t kd[4], vd[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int f = f0 + u * kWriteThreads;
+          kd[u] = -1;
+          if (f >= nvec) continue;
+          const int sub = f / per_sub, r = f - sub * per_sub;
+          const int v = r >> 4, tok = sub * 16 + (r & 15);
+          if (tok >= ntok) continue;
+          const int h = div_by(v, p.vph, p.vph_shift);
+          const int w = v - h * p.vph;
+          kd[u] = s_win[tok] + h * p.k_head + w * p.k.dhi;
+          vd[u] = s_win_v[tok] + h * p.v_head + w * p.v.dhi;
+          kr[u] = load_stream(p.key + (tok0 + tok) * p.k_pitch + static_cast<int64_t>(v) * 16);
+          vr[u] = load_stream(p.value + (tok0 + tok) * p.v_pitch + static_cast<int64_t>(v) * 16);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (kd[u] < 0) continue;
+          store_stream(p.k_base + kd[u], kr[u]);
+          store_stream(p.v_base + vd[u], vr[u]);
+        }
+      }
+      return;
+    }
     write_packed16_lines(p, p.key, p.k_pitch, p.k_base, p.k_blk, p.k_head, p.k, s_slot, s_frag, s_win, &s_count, ntok);
     __syncthreads();
     write_packed16_lines(p, p.value, p.v_pitch, p.v_base, p.v_blk, p.v_head, p.v, s_slot, s_frag, s_win, &s_count, ntok);
@@ -2444,7 +2491,8 @@ kvx_status_t write_impl(const kvx_cache_desc_t *cache, const kvx_write_desc_t *w
     q.vpr = static_cast<int32_t>(row_bytes / 16);
     q.vph = static_cast<int32_t>(D * io_elem / 16);
     q.vph_shift = shift_of(q.vph);
-    int tile = kPackedTile;
+    int tile = static_cast<int>(std::min<int64_t>(kPackedTile, std::max<int64_t>(1, opt(g_opt.packed_tile_tokens))));
+    while ((tile & (tile - 1)) != 0) tile &= tile - 1;  // a power of two
     while (tile > 1 && (T + tile - 1) / tile < static_cast<int64_t>(dev.sm_count) * 4) tile >>= 1;
     q.tok_tile = tile;
     q.lines = k_side.n_shift == 0 && v_side.n_shift == 0 && tiles_knob != 2 && tiles_knob != 3 &&
