@@ -2205,10 +2205,10 @@ __device__ __forceinline__ uint32_t absmax_vec(const uint4 &x, F32) {
   return max(max(x.x & 0x7FFFFFFFu, x.y & 0x7FFFFFFFu), max(x.z & 0x7FFFFFFFu, x.w & 0x7FFFFFFFu));
 }
 
-// kFixedHead: the grid's stride over the vectors is a multiple of the vectors per token row, so a
-// thread meets the same place of a token row -- the same head -- in every iteration: it keeps
-// its maxima in registers, four loads of K and of V in flight, and joins the other lanes of its
-// head once, after the loop (the kernel is otherwise bound by instruction issue, not by memory).
+// kFixedHead (token rows of a power-of-two number of vectors): a thread keeps its place in the
+// token row -- the same head -- in every iteration, so it keeps its maxima in registers, four
+// loads of K and of V in flight, and joins the other lanes of its head once, after the loop
+// (the kernel is otherwise bound by instruction issue, not by memory).
 template <typename IoT, bool kFixedHead>
 __global__ void __launch_bounds__(kScaleThreads) kvx_kv_scales_kernel(const ScalesParams p) {
   extern __shared__ uint32_t s_max[];  // [2 * heads]
@@ -2219,15 +2219,27 @@ __global__ void __launch_bounds__(kScaleThreads) kvx_kv_scales_kernel(const Scal
 
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kScaleThreads;
   if constexpr (kFixedHead) {
-    const int64_t first = static_cast<int64_t>(blockIdx.x) * kScaleThreads + tid;
+    // A CTA owns a contiguous range of token rows and, of each row, either all of it (rows of up
+    // to 256 vectors: 256 / vpr rows per iteration) or one block of 256 vectors (longer rows):
+    // a thread keeps its place in the row, memory is walked front to back.
+    const int col_blocks = p.vpr > kScaleThreads ? p.vpr / kScaleThreads : 1;
+    const int rows_per_iter = p.vpr < kScaleThreads ? kScaleThreads / p.vpr : 1;
+    const int col = static_cast<int>(blockIdx.x % col_blocks) * kScaleThreads + (p.vpr < kScaleThreads ? tid % p.vpr : tid);
+    const int64_t chunks = gridDim.x / col_blocks;  // the launcher makes the grid a multiple of col_blocks
+    const int64_t rows = p.total_vecs / p.vpr;
+    const int64_t per_chunk = (rows + chunks - 1) / chunks;
+    const int64_t chunk = blockIdx.x / col_blocks;
+    const int64_t end = min(rows, (chunk + 1) * per_chunk);
     uint32_t mk = 0, mv = 0;
-    int64_t f = first;
-    for (; f + 3 * stride < p.total_vecs; f += 4 * stride) {
+    int64_t r = chunk * per_chunk + (p.vpr < kScaleThreads ? tid / p.vpr : 0);
+    const int64_t step = static_cast<int64_t>(rows_per_iter) * p.vpr;  // vectors between a thread's iterations
+    int64_t f = r * p.vpr + col;
+    for (; r + 3 * rows_per_iter < end; r += 4 * rows_per_iter, f += 4 * step) {
       uint4 a[4], b[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        a[u] = load_stream(p.key + (f + u * stride) * 16);
-        b[u] = load_stream(p.value + (f + u * stride) * 16);
+        a[u] = load_stream(p.key + (f + u * step) * 16);
+        b[u] = load_stream(p.value + (f + u * step) * 16);
       }
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
@@ -2235,19 +2247,18 @@ __global__ void __launch_bounds__(kScaleThreads) kvx_kv_scales_kernel(const Scal
         mv = max(mv, absmax_vec(b[u], IoT{}));
       }
     }
-    for (; f < p.total_vecs; f += stride) {
+    for (; r < end; r += rows_per_iter, f += step) {
       mk = max(mk, absmax_vec(load_stream(p.key + f * 16), IoT{}));
       mv = max(mv, absmax_vec(load_stream(p.value + f * 16), IoT{}));
     }
-    // lanes of one group share a head (the group divides the vectors per head, and the CTA's
-    // first vector is a multiple of the CTA size): fold them, then one shared-memory update each
+    // lanes of one group share a head (the group divides the vectors per head and a warp's
+    // columns are consecutive and aligned): fold them, then one shared-memory update each
     for (int d = 1; d < p.group; d <<= 1) {
       mk = max(mk, __shfl_xor_sync(0xFFFFFFFFu, mk, d));
       mv = max(mv, __shfl_xor_sync(0xFFFFFFFFu, mv, d));
     }
-    if ((tid & (p.group - 1)) == 0 && first < p.total_vecs) {
-      const int v = static_cast<int>(p.vpr_shift >= 0 ? (first & (p.vpr - 1)) : (first % p.vpr));
-      const int h = div_by(v, p.vps, p.vps_shift);
+    if ((tid & (p.group - 1)) == 0) {
+      const int h = div_by(col, p.vps, p.vps_shift);
       if (mk) atomicMax(&s_max[h], mk);
       if (mv) atomicMax(&s_max[p.heads + h], mv);
     }
@@ -3234,10 +3245,10 @@ static kvx_status_t kv_scales_impl(const kvx_kv_io_desc_t *io, kvx_scale_granula
   if (grid < 1) grid = 1;
   const size_t smem = 2 * static_cast<size_t>(H) * sizeof(uint32_t);
   const cudaStream_t cs = as_stream(stream);
-  // A stride that is a multiple of the vectors per token row fixes every thread's head: round
-  // the grid down to a multiple of vpr / gcd(vpr, CTA size) when that leaves enough CTAs.
-  int64_t unit = p.vpr / std::gcd<int64_t, int64_t>(p.vpr, kScaleThreads);
-  bool fixed = p.total_vecs >= 4 * grid * kScaleThreads && grid >= unit && unit <= cap;
+  // Token rows of a power-of-two number of vectors let every thread keep its place in the row:
+  // the grid is then a multiple of the 256-vector blocks of a row.
+  const int64_t unit = p.vpr > kScaleThreads ? p.vpr / kScaleThreads : 1;
+  const bool fixed = p.vpr_shift >= 0 && p.total_vecs >= 4 * grid * kScaleThreads && grid >= unit;
   if (fixed) grid = grid / unit * unit;
   const unsigned ug = static_cast<unsigned>(grid);
 #define KVX_SCALES(IoT)                                                    \
