@@ -1616,10 +1616,12 @@ __device__ __forceinline__ void write_packed16_lines(const WritePackedParams &p,
     const int64_t sl = s_slot[1 + tid];
     const int64_t before = s_slot[tid];
     const int pos0 = static_cast<int>(sl & (kW - 1));
-    const bool continues = sl >= 0 && before >= 0 && sl == before + 1 && pos0 != 0;
+    // Fragments end at the tile's borders here: the neighbouring tiles may have taken the route
+    // for tiles without holes, which writes a tile's own tokens and nothing else.
+    const bool continues = tid > 0 && sl >= 0 && before >= 0 && sl == before + 1 && pos0 != 0;
     if (sl >= 0 && !continues) {
       int len = 1;
-      while (pos0 + len < kW && s_slot[1 + tid + len] == sl + len) ++len;
+      while (pos0 + len < kW && tid + len < ntok && s_slot[1 + tid + len] == sl + len) ++len;
       const int at = atomicAdd(s_count, 1);
       s_frag[at] = tid | (pos0 << 8) | (len << 16);
       int64_t b, o;

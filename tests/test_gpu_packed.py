@@ -94,6 +94,21 @@ def test_decode_sized_batches_and_scattered_slots():
     _check(one)
 
 
+@pytest.mark.parametrize("pad", [0.0, 0.02, 0.3])
+def test_batches_large_enough_for_full_token_tiles(pad):
+    """Tens of thousands of tokens, so that a CTA takes a full tile of tokens: tiles without a hole
+    and tiles with holes then lie next to each other and take different routes through the write
+    kernel; every token must be written by exactly one of them.  16-byte groups (both routes), the
+    paged pairing and 4-byte groups (fragments that continue across tile borders)."""
+    for j, kw in enumerate([dict(pack=8), dict(pack=8, v_pack=1), dict(pack=2)]):
+        case = cases.make_case(2500 + j, layout=PACKED, dtype=abi.DTYPE_BF16, heads=2, dim=64, block_size=16,
+                               num_blocks=1400, lens=[2000, 1999, 2001, 2500, 1500, 2000, 2040, 1960, 2000, 2000, 1000],
+                               pad_frac=pad, **kw)
+        case.note = f"large batch {j}, pad {pad}"
+        assert case.T > 148 * 4 * 32   # CTAs take full 32-token tiles
+        _check(case)
+
+
 def test_shapes_that_do_not_qualify_fall_back():
     """Group rows that are not whole 32-byte units, padded group rows, a head_dim whose rows are not
     whole vectors: still exact (other tiers)."""
