@@ -162,13 +162,18 @@ bool view_vectorisable(const PageView &v, int64_t elem, int64_t dim, int64_t vec
          v.head >= 0;
 }
 
-// HND_PACKED pages whose pack group is exactly one 16-byte vector (pack * elem == 16, the
-// packing vLLM's and TGI's non-flash paged attention use): the 16-byte vectors of one head
-// are then `dhi` bytes apart instead of adjacent, and a token's vectors 16 bytes apart.
-bool view_packed16(const PageView &v, int64_t elem, int64_t dim) {
-  return v.pack > 1 && v.pack != dim && v.pack * elem == 16 && v.dlo == elem && aligned(v.base, 16) &&
-         v.blk % 16 == 0 && v.tok % 16 == 0 && v.head % 16 == 0 && v.dhi % 16 == 0 && v.blk >= 0 && v.tok >= 0 &&
-         v.head >= 0 && v.dhi >= 0;
+// HND_PACKED pages whose pack group is one 16-byte vector (pack * elem == 16, the packing vLLM's
+// and TGI's non-flash paged attention use) or 2^k of them (32, 64 ... bytes): the groups of one
+// head are then `dhi` bytes apart instead of adjacent, and a token's groups pack * elem bytes
+// apart.  *sub = k: vector w of a head lies at (w >> k) * dhi + (w & (2^k - 1)) * 16.
+bool view_packed16(const PageView &v, int64_t elem, int64_t dim, int32_t *sub) {
+  const int64_t u = v.pack * elem;
+  *sub = 0;
+  if (!(v.pack > 1 && v.pack != dim && u % 16 == 0 && is_pow2(u / 16) && v.dlo == elem && aligned(v.base, 16) &&
+        v.blk % 16 == 0 && v.tok % 16 == 0 && v.tok >= u && v.head % 16 == 0 && v.dhi % 16 == 0 && v.blk >= 0 && v.head >= 0 && v.dhi >= 0))
+    return false;
+  *sub = shift_of(u / 16);
+  return true;
 }
 
 // One packed page tensor as the tile kernels see it (device code reads it too).
@@ -255,6 +260,12 @@ __device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.lau
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void prefetch_l2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 
+// Byte offset of 16-byte vector w of a head whose pack groups (2^sub vectors each) are `step`
+// bytes apart; step = 16, sub = 0 for a head that is contiguous.
+__device__ __forceinline__ int64_t group_vec_offset(int w, int64_t step, int sub) {
+  return static_cast<int64_t>(w >> sub) * step + ((w & ((1 << sub) - 1)) << 4);
+}
+
 // n / d and n % d for a runtime d with a known power-of-two shift (or -1).
 __device__ __forceinline__ int div_by(int n, int d, int shift) {
   return shift >= 0 ? (n >> shift) : (n / d);
@@ -286,7 +297,8 @@ struct WriteRowsParams {
   char *k_base, *v_base;
   int64_t k_blk, k_tok, k_head;  // bytes
   int64_t v_blk, v_tok, v_head;
-  int64_t k_vec, v_vec;  // bytes between consecutive 16-byte vectors of one head (16 unless packed)
+  int64_t k_vec, v_vec;  // bytes between consecutive pack groups of one head (16 unless packed)
+  int32_t k_sub, v_sub;  // log2 of the 16-byte vectors per pack group (0 unless the groups are 32 bytes or more)
   int64_t k_pitch, v_pitch;  // bytes between consecutive token rows of key / value (row_bytes when dense)
   const void *slots;
   int64_t row_bytes;
@@ -372,8 +384,8 @@ __global__ void __launch_bounds__(kWriteThreads) kvx_write_rows_kernel(const Wri
           if (kSeg) {
             const int h = div_by(v, p.vps, p.vps_shift);
             const int64_t w = v - h * p.vps;
-            kd[u] = ko + h * p.k_head + w * p.k_vec;
-            vd[u] = s_v[tok] + h * p.v_head + w * p.v_vec;
+            kd[u] = ko + h * p.k_head + group_vec_offset(w, p.k_vec, p.k_sub);
+            vd[u] = s_v[tok] + h * p.v_head + group_vec_offset(w, p.v_vec, p.v_sub);
           } else {
             kd[u] = ko + static_cast<int64_t>(v) * 16;
             vd[u] = s_v[tok] + static_cast<int64_t>(v) * 16;
@@ -999,7 +1011,8 @@ struct GatherPagesParams {
   const char *k_base, *v_base;
   int64_t k_blk, k_tok, k_head;  // bytes
   int64_t v_blk, v_tok, v_head;
-  int64_t k_vec, v_vec;  // bytes between consecutive 16-byte vectors of one head (16 unless packed)
+  int64_t k_vec, v_vec;  // bytes between consecutive pack groups of one head (16 unless packed)
+  int32_t k_sub, v_sub;  // log2 of the 16-byte vectors per pack group
   char *key_out, *value_out;
   GatherShape s;
   int64_t out_row_bytes;  // bytes of one output token row
@@ -1162,6 +1175,7 @@ __global__ void __launch_bounds__(kGatherThreads) kvx_gather_pages_kernel(const 
     const int64_t tok_b = kv ? p.v_tok : p.k_tok;
     const int64_t head_b = kv ? p.v_head : p.k_head;
     const int64_t vec_b = kv ? p.v_vec : p.k_vec;
+    const int vec_sub = kv ? p.v_sub : p.k_sub;
 
     for (int f0 = vbeg + lane; f0 < vend; f0 += 32 * kUnroll) {
       uint4 r[kUnroll];
@@ -1174,7 +1188,7 @@ __global__ void __launch_bounds__(kGatherThreads) kvx_gather_pages_kernel(const 
             const int tok = div_by(f, p.vpr, p.vpr_shift);
             const int v = f - tok * p.vpr;
             const int h = div_by(v, p.vps, p.vps_shift);
-            so = tok * tok_b + h * head_b + (v - h * p.vps) * vec_b;
+            so = tok * tok_b + h * head_b + group_vec_offset(v - h * p.vps, vec_b, vec_sub);
           } else {
             so = static_cast<int64_t>(f) * 16;
           }
@@ -1399,8 +1413,9 @@ struct GatherPackedParams {
   PackedSide k, v;
   int32_t slots;   // 32-byte units of one (page, head) tile: block_size * head_dim * elem / 32
   int32_t pieces;  // work items per head
-  int32_t rows;    // 1: K and V in 16-byte units, items of 8 token rows (gather_packed16_rows); then
+  int32_t rows;    // 1: 16-byte units, items of 8 token rows (gather_packed16_rows); then
                    // g.parts = 128-byte lines per group row and pieces = 8-group blocks per head
+  int32_t only;    // -1: K and V; 0: K only; 1: V only (K and V of different kinds take a launch each)
   int64_t head_out_bytes;  // head_dim * elem
 };
 
@@ -1421,11 +1436,11 @@ __global__ void __launch_bounds__(kGatherThreads) kvx_gather_packed_kernel(const
   const int lane = threadIdx.x & 31;
   const int64_t warp = static_cast<int64_t>(blockIdx.x) * kGatherWarps + (threadIdx.x >> 5);
   const int64_t warps = static_cast<int64_t>(gridDim.x) * kGatherWarps;
-  const int64_t items = chunks * p.parts * 2;
+  const int64_t items = chunks * p.parts * (pp.only < 0 ? 2 : 1);
 
   for (int64_t item = warp; item < items; item += warps) {
-    const int kv = static_cast<int>(item & 1);
-    const int64_t rest = item >> 1;
+    const int kv = pp.only < 0 ? static_cast<int>(item & 1) : pp.only;
+    const int64_t rest = pp.only < 0 ? (item >> 1) : item;
     const int64_t c = rest / p.parts;
     const int part = static_cast<int>(rest - c * p.parts);
     ChunkRef ref;
@@ -1997,6 +2012,82 @@ __global__ void __launch_bounds__(kGatherThreads) kvx_gather_f8_kernel(const Gat
   }
 }
 
+// The dequantising gather with 256-bit stores: 16-bit outputs whose head rows are whole 32-byte
+// vectors.  A lane turns 16 cache bytes (16 elements of one head) into one 32-byte store: half
+// the memory instructions and half the index arithmetic per element of the kernel above.
+// part_vecs, vpr and vps still count 16-byte output vectors (all even here).
+template <typename IoT, typename IdxT, int kUnroll>
+__global__ void __launch_bounds__(kGatherThreads) kvx_gather_f8_wide_kernel(const GatherPagesParams p) {
+  gather_prologue<IdxT>(p);
+  extern __shared__ int32_t s_prefix[];
+  __shared__ int32_t s_warp_tot[kGatherWarps];
+  int64_t chunks;
+  if (p.use_prefix)
+    chunks = build_page_prefix<IdxT>(p, s_prefix, s_warp_tot);
+  else
+    chunks = static_cast<int64_t>(p.s.seq_count) * p.s.max_blocks;
+
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = static_cast<int64_t>(blockIdx.x) * kGatherWarps + (threadIdx.x >> 5);
+  const int64_t warps = static_cast<int64_t>(gridDim.x) * kGatherWarps;
+  const int64_t items = chunks * p.parts * 2;
+  const int part_units = p.part_vecs >> 1, row_units = p.vpr >> 1, seg_units = p.vps >> 1;
+  const int row_shift = p.vpr_shift >= 0 ? p.vpr_shift - 1 : -1, seg_shift = p.vps_shift >= 0 ? p.vps_shift - 1 : -1;
+
+  for (int64_t item = warp; item < items; item += warps) {
+    const int kv = static_cast<int>(item & 1);
+    const int64_t rest = item >> 1;
+    const int64_t c = rest / p.parts;
+    const int part = static_cast<int>(rest - c * p.parts);
+    ChunkRef ref;
+    if (p.use_prefix) {
+      ref = find_chunk(s_prefix, p.s.seq_count, static_cast<int32_t>(c));
+    } else {
+      ref.seq = static_cast<int32_t>(c / p.s.max_blocks);
+      ref.lb = static_cast<int32_t>(c - static_cast<int64_t>(ref.seq) * p.s.max_blocks);
+    }
+    const ChunkInfo ci = resolve_chunk<IdxT>(p, ref.seq, ref.lb);
+    if (ci.block < 0) continue;
+    const int nunit = ci.tokens * row_units;
+    const int ubeg = part * part_units;
+    const int uend = min(ubeg + part_units, nunit);
+    const char *src = kv ? p.v_base + ci.block * p.v_blk : p.k_base + ci.block * p.k_blk;
+    char *dst = (kv ? p.value_out : p.key_out) + ci.out_off;
+    const int64_t tok_b = kv ? p.v_tok : p.k_tok;
+    const int64_t head_b = kv ? p.v_head : p.k_head;
+    const ScaleView sc = kv ? p.vs : p.ks;
+
+    for (int f0 = ubeg + lane; f0 < uend; f0 += 32 * kUnroll) {
+      uint4 r[kUnroll];
+      int hh[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int f = f0 + u * 32;
+        if (f < uend) {
+          const int tok = div_by(f, row_units, row_shift);
+          const int v = f - tok * row_units;
+          const int h = div_by(v, seg_units, seg_shift);
+          hh[u] = h;
+          r[u] = *reinterpret_cast<const uint4 *>(src + tok * tok_b + h * head_b + static_cast<int64_t>(v - h * seg_units) * 16);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int f = f0 + u * 32;
+        if (f < uend) {
+          const float scale = __ldg(sc.base + hh[u] * sc.stride);
+          const uint4 lo = dequant_vec(make_uint2(r[u].x, r[u].y), scale, IoT{});
+          const uint4 hi = dequant_vec(make_uint2(r[u].z, r[u].w), scale, IoT{});
+          Vec32 out;
+          out.w[0] = lo.x, out.w[1] = lo.y, out.w[2] = lo.z, out.w[3] = lo.w;
+          out.w[4] = hi.x, out.w[5] = hi.y, out.w[6] = hi.z, out.w[7] = hi.w;
+          store_stream32(dst + static_cast<int64_t>(f) * 32, out);
+        }
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------ gather: bulk tier --
 // cp.async.bulk staging of contiguous page chunks: global -> shared (completion on an
 // mbarrier) -> global (bulk group).  One elected thread ("pipe") owns a ring of stages and
@@ -2475,7 +2566,8 @@ kvx_status_t write_impl(const kvx_cache_desc_t *cache, const kvx_write_desc_t *w
   // ---- vector tier: 16-byte input vectors, each inside one head -------------------------
   const int64_t row_bytes = H * D * io_elem;
   const int64_t out_vec = fp8 ? 16 / io_elem : 16;  // cache bytes produced per input vector
-  const bool k_packed = !fp8 && view_packed16(gp.k, elem, D), v_packed = !fp8 && view_packed16(gp.v, elem, D);
+  int32_t k_sub = 0, v_sub = 0;
+  const bool k_packed = !fp8 && view_packed16(gp.k, elem, D, &k_sub), v_packed = !fp8 && view_packed16(gp.v, elem, D, &v_sub);
   const int64_t k_pitch = write->io.key.stride[0] * io_elem, v_pitch = write->io.value.stride[0] * io_elem;
   const bool pitched = k_pitch != row_bytes || v_pitch != row_bytes;  // token rows further apart than dense
   // ---- packed pages with pack groups below 16 bytes (or mixed): fragment / transposition tier --
@@ -2530,6 +2622,7 @@ kvx_status_t write_impl(const kvx_cache_desc_t *cache, const kvx_write_desc_t *w
     p.k_base = gp.k.base, p.k_blk = gp.k.blk, p.k_tok = gp.k.tok, p.k_head = gp.k.head;
     p.v_base = gp.v.base, p.v_blk = gp.v.blk, p.v_tok = gp.v.tok, p.v_head = gp.v.head;
     p.k_vec = k_packed ? gp.k.dhi : 16, p.v_vec = v_packed ? gp.v.dhi : 16;
+    p.k_sub = k_sub, p.v_sub = v_sub;
     p.slots = write->slots.slots;
     p.row_bytes = row_bytes;
     p.k_pitch = k_pitch, p.v_pitch = v_pitch;
@@ -2814,8 +2907,9 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
   const int64_t out_row = H * D * io_elem;
   const int64_t in_vec = fp8 ? 16 / io_elem : 16;  // cache bytes consumed per output vector
   const int64_t chunk_vecs = static_cast<int64_t>(cache->block_size) * (out_row / 16);
-  const bool k_packed = !fp8 && !ragged && view_packed16(gp.k, elem, D);
-  const bool v_packed = !fp8 && !ragged && view_packed16(gp.v, elem, D);
+  int32_t k_sub = 0, v_sub = 0;
+  const bool k_packed = !fp8 && !ragged && view_packed16(gp.k, elem, D, &k_sub);
+  const bool v_packed = !fp8 && !ragged && view_packed16(gp.v, elem, D, &v_sub);
   const bool packed = k_packed || v_packed;
   PackedSide k_side{}, v_side{};
   const int64_t tiles_knob = opt(g_opt.packed_tiles);
@@ -2835,6 +2929,7 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
     p.k_base = gp.k.base, p.k_blk = gp.k.blk, p.k_tok = gp.k.tok, p.k_head = gp.k.head;
     p.v_base = gp.v.base, p.v_blk = gp.v.blk, p.v_tok = gp.v.tok, p.v_head = gp.v.head;
     p.k_vec = k_packed ? gp.k.dhi : 16, p.v_vec = v_packed ? gp.v.dhi : 16;
+    p.k_sub = k_sub, p.v_sub = v_sub;
     p.key_out = static_cast<char *>(gather->io.key.data);
     p.value_out = static_cast<char *>(gather->io.value.data);
     p.s = gs;
@@ -2871,37 +2966,52 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
       }
     }
     if (tiles) {
-      // ---- packed pages: transposing tiles (one item = up to 4 KB of one head's tile) ----
+      // ---- packed pages: transposing tiles.  A tensor in 16-byte groups whose shape allows it is
+      // gathered in items of 8 token rows (all heads), any other in items of up to 4 KB of one
+      // head's tile; K and V of different kinds take a launch each when the batch is large.
       GatherPackedParams pp;
       pp.g = p;
       pp.k = k_side, pp.v = v_side;
       pp.slots = static_cast<int32_t>(static_cast<int64_t>(cache->block_size) * D * elem / 32);
-      pp.pieces = (pp.slots + 127) / 128;
       pp.head_out_bytes = D * elem;
-      pp.g.parts = static_cast<int32_t>(H) * pp.pieces;
-      pp.rows = tiles_knob != 3 && k_side.n_shift == 0 && v_side.n_shift == 0 && k_side.runs % 4 == 0 &&
-                (D * elem) % 128 == 0 && H * D * elem < (int64_t{1} << 30);
-      if (pp.rows) {  // items of 8 token rows, all heads
-        pp.g.parts = k_side.runs / 4;
-        pp.pieces = static_cast<int32_t>(D * elem / 128);
-      }
-      const int64_t max_items = S * gs.max_blocks * pp.g.parts * 2;
-      if (max_items <= opt(g_opt.gather_rect_items)) pp.g.use_prefix = 0;
-      const int64_t need = (max_items + kGatherWarps - 1) / kGatherWarps;
-      const int64_t per_sm = std::max<int64_t>(1, opt(g_opt.gather_ctas_per_sm));
-      const int64_t grid = std::max<int64_t>(1, std::min(static_cast<int64_t>(dev.sm_count) * per_sm, (need + 1) / 2));
-      const size_t smem = pp.g.use_prefix ? static_cast<size_t>(S + 1) * sizeof(int32_t) : 0;
-      const unsigned ug = static_cast<unsigned>(grid);
-      if (pp.rows) {
-        if (s32)
-          launch_streaming(kvx_gather_packed_kernel<int32_t, 4, true>, ug, kGatherThreads, smem, cs, pp);
-        else
-          launch_streaming(kvx_gather_packed_kernel<int64_t, 4, true>, ug, kGatherThreads, smem, cs, pp);
+      const bool rows_shape = tiles_knob != 3 && (D * elem) % 128 == 0 && H * D * elem < (int64_t{1} << 30);
+      const bool k_rows = rows_shape && k_side.n_shift == 0 && k_side.runs % 4 == 0;
+      const bool v_rows = rows_shape && v_side.n_shift == 0 && v_side.runs % 4 == 0;
+      auto launch = [&](bool rows, int only) {
+        pp.rows = rows, pp.only = only;
+        if (rows) {
+          pp.g.parts = (only == 1 ? v_side.runs : k_side.runs) / 4;
+          pp.pieces = static_cast<int32_t>(D * elem / 128);
+        } else {
+          pp.pieces = (pp.slots + 127) / 128;
+          pp.g.parts = static_cast<int32_t>(H) * pp.pieces;
+        }
+        const int64_t max_items = S * gs.max_blocks * pp.g.parts * (only < 0 ? 2 : 1);
+        pp.g.use_prefix = p.use_prefix && max_items > opt(g_opt.gather_rect_items);
+        const int64_t need = (max_items + kGatherWarps - 1) / kGatherWarps;
+        const int64_t per_sm = std::max<int64_t>(1, opt(g_opt.gather_ctas_per_sm));
+        const unsigned ug = static_cast<unsigned>(
+            std::max<int64_t>(1, std::min(static_cast<int64_t>(dev.sm_count) * per_sm, (need + 1) / 2)));
+        const size_t smem = pp.g.use_prefix ? static_cast<size_t>(S + 1) * sizeof(int32_t) : 0;
+        if (rows) {
+          if (s32)
+            launch_streaming(kvx_gather_packed_kernel<int32_t, 4, true>, ug, kGatherThreads, smem, cs, pp);
+          else
+            launch_streaming(kvx_gather_packed_kernel<int64_t, 4, true>, ug, kGatherThreads, smem, cs, pp);
+        } else {
+          if (s32)
+            launch_streaming(kvx_gather_packed_kernel<int32_t, 4, false>, ug, kGatherThreads, smem, cs, pp);
+          else
+            launch_streaming(kvx_gather_packed_kernel<int64_t, 4, false>, ug, kGatherThreads, smem, cs, pp);
+        }
+      };
+      const int64_t piece_items = S * gs.max_blocks * H * ((pp.slots + 127) / 128) * 2;
+      if (k_rows == v_rows || piece_items <= opt(g_opt.gather_rect_items)) {
+        launch(k_rows && v_rows, -1);
       } else {
-        if (s32)
-          launch_streaming(kvx_gather_packed_kernel<int32_t, 4, false>, ug, kGatherThreads, smem, cs, pp);
-        else
-          launch_streaming(kvx_gather_packed_kernel<int64_t, 4, false>, ug, kGatherThreads, smem, cs, pp);
+        launch(k_rows, 0);
+        g_launches.fetch_add(1, std::memory_order_relaxed);  // two kernels for this call
+        launch(v_rows, 1);
       }
       return finish_launch();
     }
@@ -2969,6 +3079,24 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
     int64_t grid = static_cast<int64_t>(dev.sm_count) * per_sm;
     grid = std::max<int64_t>(1, std::min(grid, fp8 ? need : (need + 1) / 2));
     const unsigned ug = static_cast<unsigned>(grid);
+    if (fp8 && !offsets && io_elem == 2 && opt(g_opt.wide) && (p.vps % 2) == 0 && (p.part_vecs % 2) == 0 &&
+        aligned(p.key_out, 32) && aligned(p.value_out, 32) && aligned(p.k_base, 16) && aligned(p.v_base, 16) &&
+        p.k_blk % 16 == 0 && p.v_blk % 16 == 0 && p.k_tok % 16 == 0 && p.v_tok % 16 == 0 && p.k_head % 16 == 0 &&
+        p.v_head % 16 == 0) {
+      // 256-bit stores: 16 cache bytes -> 32 output bytes per lane
+      if (io_dtype == KVX_DTYPE_BF16) {
+        if (s32)
+          launch_streaming(kvx_gather_f8_wide_kernel<BF16, int32_t, 4>, ug, kGatherThreads, prefix_bytes, cs, p);
+        else
+          launch_streaming(kvx_gather_f8_wide_kernel<BF16, int64_t, 4>, ug, kGatherThreads, prefix_bytes, cs, p);
+      } else {
+        if (s32)
+          launch_streaming(kvx_gather_f8_wide_kernel<F16, int32_t, 4>, ug, kGatherThreads, prefix_bytes, cs, p);
+        else
+          launch_streaming(kvx_gather_f8_wide_kernel<F16, int64_t, 4>, ug, kGatherThreads, prefix_bytes, cs, p);
+      }
+      return finish_launch();
+    }
     if (fp8) {
 #define KVX_F8_GATHER(IoT)                                                                     \
   do {                                                                                         \

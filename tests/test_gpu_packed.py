@@ -49,15 +49,19 @@ def _check(case, knobs=(1,)):
             assert np.array_equal(gv, eov), f"V out differs ({case.note}, packed_tiles {knob}, rect {rect})"
 
 
-@pytest.mark.parametrize("dtype,packs", [(abi.DTYPE_BF16, (1, 2, 4, 8)), (abi.DTYPE_F16, (8,)), (abi.DTYPE_F32, (1, 2, 4))])
+@pytest.mark.parametrize("dtype,packs", [(abi.DTYPE_BF16, (1, 2, 4, 8, 16, 32)), (abi.DTYPE_F16, (8,)),
+                                         (abi.DTYPE_F32, (1, 2, 4, 8, 16))])
 def test_every_pack_size(dtype, packs):
-    """Units of 2 / 4 / 8 / 16 bytes; lengths that leave partial pages; slots with holes."""
+    """Units of 2 / 4 / 8 / 16 bytes (the transposing kernels) and of 32 / 64 bytes (the vector tier
+    with group-wise addressing); lengths that leave partial pages; slots with holes."""
     for i, pack in enumerate(packs):
         for j, kw in enumerate([
             dict(heads=8, dim=128, block_size=16, num_blocks=64, lens=[100, 17, 256, 1, 0, 333], pad_frac=0.1, bad_blocks=3),
             dict(heads=2, dim=64, block_size=32, num_blocks=24, lens=[31, 33, 160], oob_slots=3, index_dtype=np.int64),
             dict(heads=3, dim=48, block_size=16, num_blocks=20, lens=[50, 70, 9], max_seq_len=60, slot_dtype=np.int32),
         ]):
+            if kw["dim"] % pack:
+                continue
             case = cases.make_case(2000 + 10 * i + j, layout=PACKED, pack=pack, dtype=dtype, **kw)
             case.note = f"pack {pack} case {j}"
             _check(case, knobs=(1, 2, 3, 0))
