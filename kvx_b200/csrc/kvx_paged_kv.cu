@@ -1618,7 +1618,10 @@ __device__ __forceinline__ void write_packed_tensor(const WritePackedParams &p, 
 // window and group 8 gh + lane / 4, so that each of its two loads reads 4 token rows x 128 bytes
 // per warp instruction and its 32-byte store fills, with the three other pairs, one line of each
 // of 8 group rows.  Needs a multiple of 8 groups per head and block sizes that are multiples of 8.
-// (K and V in one loop over a shared fragment list measured 2-4 % slower than one pass each.)
+// (K and V in one loop over a shared fragment list measured 2-4 % slower than one pass each.  A
+// tokens-fastest route without fragments for tiles without a hole is 1-2 % faster in a short
+// burst and 1-2 % slower once the device sits at its power limit, which back-to-back packed
+// writes reach -- about 950 W -- so there is one route.)
 __device__ __forceinline__ void write_packed16_lines(const WritePackedParams &p, const char *rows, int64_t pitch,
                                                      char *base, int64_t blk, int64_t head, const PackedSide &side,
                                                      const int64_t *s_slot, int32_t *s_frag, int64_t *s_win,
@@ -1631,8 +1634,8 @@ __device__ __forceinline__ void write_packed16_lines(const WritePackedParams &p,
     const int64_t sl = s_slot[1 + tid];
     const int64_t before = s_slot[tid];
     const int pos0 = static_cast<int>(sl & (kW - 1));
-    // Fragments end at the tile's borders here: the neighbouring tiles may have taken the route
-    // for tiles without holes, which writes a tile's own tokens and nothing else.
+    // Fragments end at the tile's borders here (a window is 8 slots, a tile 32 tokens: little is
+    // lost, and no tile depends on what its neighbour does).
     const bool continues = tid > 0 && sl >= 0 && before >= 0 && sl == before + 1 && pos0 != 0;
     if (sl >= 0 && !continues) {
       int len = 1;
@@ -1711,51 +1714,6 @@ __global__ void __launch_bounds__(kWriteThreads) kvx_write_packed_kernel(const W
     s_slot[tid] = sl < 0 ? -1 : sl;
   }
   if (p.lines) {
-    // A tile without a hole (no padded or out-of-range slot) needs no fragments: 16 consecutive
-    // tokens x one 16-byte group are one 256-byte run of a page wherever a page begins, so the
-    // threads run over tokens fastest (sub-tiles of 16) and store 16 bytes each -- measured 2-3 %
-    // faster than the fragment route, which pays for itself only where holes cut the runs
-    // (padded slots: 3.4 against 2.9 TB/s).
-    __shared__ int64_t s_win_v[kPackedTile];
-    __syncthreads();
-    const bool whole = __syncthreads_and(tid >= ntok || s_slot[1 + tid] >= 0);
-    if (whole) {
-      if (tid < ntok) {
-        int64_t b, o;
-        split_slot(s_slot[1 + tid], p.block_size, p.bs_shift, &b, &o);
-        s_win[tid] = b * p.k_blk + o * 16;
-        s_win_v[tid] = b * p.v_blk + o * 16;
-      }
-      __syncthreads();
-      const int per_sub = 16 * p.vpr;
-      const int nvec = ((ntok + 15) >> 4) * per_sub;
-      for (int f0 = tid; f0 < nvec; f0 += kWriteThreads * 4) {
-        uint4 kr[4], vr[4];
-        int64_t kd[4], vd[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int f = f0 + u * kWriteThreads;
-          kd[u] = -1;
-          if (f >= nvec) continue;
-          const int sub = f / per_sub, r = f - sub * per_sub;
-          const int v = r >> 4, tok = sub * 16 + (r & 15);
-          if (tok >= ntok) continue;
-          const int h = div_by(v, p.vph, p.vph_shift);
-          const int w = v - h * p.vph;
-          kd[u] = s_win[tok] + h * p.k_head + w * p.k.dhi;
-          vd[u] = s_win_v[tok] + h * p.v_head + w * p.v.dhi;
-          kr[u] = load_stream(p.key + (tok0 + tok) * p.k_pitch + static_cast<int64_t>(v) * 16);
-          vr[u] = load_stream(p.value + (tok0 + tok) * p.v_pitch + static_cast<int64_t>(v) * 16);
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          if (kd[u] < 0) continue;
-          store_stream(p.k_base + kd[u], kr[u]);
-          store_stream(p.v_base + vd[u], vr[u]);
-        }
-      }
-      return;
-    }
     write_packed16_lines(p, p.key, p.k_pitch, p.k_base, p.k_blk, p.k_head, p.k, s_slot, s_frag, s_win, &s_count, ntok);
     __syncthreads();
     write_packed16_lines(p, p.value, p.v_pitch, p.v_base, p.v_blk, p.v_head, p.v, s_slot, s_frag, s_win, &s_count, ntok);
