@@ -1408,20 +1408,80 @@ __device__ __forceinline__ void gather_packed16_rows(const char *src, int64_t he
   }
 }
 
+// 2-byte units (kN = 8: a [dims, tokens] tile of 16-bit elements, the V tensor of the paged
+// attention caches) with whole token rows per warp.  One item = the 16 tokens of one 32-byte unit
+// of the group rows, all heads.  A lane reads two group rows (dims d and d + 32 of a block of 64
+// dims), 8 lanes transpose 8 dims x 8 tokens twice each, and one more exchange between the lanes
+// i and i ^ 4 puts the two blocks of 32 dims side by side, so that every store instruction
+// writes 4 token rows x 128 bytes (64 dims) instead of 8 rows x 64 bytes.
+template <int kPairs>
+__device__ __forceinline__ void gather_packed2_rows(const char *src, int64_t head_bytes, char *dst,
+                                                    int64_t out_row_bytes, int64_t head_out_bytes,
+                                                    const PackedSide &side, int a, int blocks, int steps,
+                                                    int tokens, int lane) {
+  const int i = lane & 7, q = lane >> 3;
+  const int t0 = a * 16;
+  if (t0 >= tokens) return;  // warp-uniform
+  const bool low = i < 4;
+  char *row = dst + static_cast<int64_t>(t0 + (i & 3)) * out_row_bytes + (low ? 0 : 64) + q * 16;
+  for (int s0 = 0; s0 < steps; s0 += kPairs) {  // a step = 64 dims of one head
+    Vec32 x[kPairs], y[kPairs];
+    int at[kPairs];
+#pragma unroll
+    for (int u = 0; u < kPairs; ++u) {
+      const int s = s0 + u;
+      const int h = s / blocks, b64 = s - h * blocks;
+      at[u] = s < steps ? static_cast<int>(h * head_out_bytes) + b64 * 128 : -1;
+      if (s < steps) {
+        const char *from = src + h * head_bytes + static_cast<int64_t>(b64 * 64 + q * 8 + i) * side.dhi + a * 32;
+        x[u] = load_stream32(from);
+        y[u] = load_stream32(from + 32 * side.dhi);
+      } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) x[u].w[k] = y[u].w[k] = 0u;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kPairs; ++u) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {  // tokens t0 .. t0 + 7, then t0 + 8 .. t0 + 15
+        uint32_t a0[4] = {x[u].w[4 * half], x[u].w[4 * half + 1], x[u].w[4 * half + 2], x[u].w[4 * half + 3]};
+        uint32_t a1[4] = {y[u].w[4 * half], y[u].w[4 * half + 1], y[u].w[4 * half + 2], y[u].w[4 * half + 3]};
+        transpose_units<8>(a0, lane);  // lane i: token i of the half, dims 8 q .. 8 q + 7 of the first 32
+        transpose_units<8>(a1, lane);  // ... of the second 32
+        uint32_t first[4], second[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint32_t got = __shfl_xor_sync(0xFFFFFFFFu, low ? a1[k] : a0[k], 4);
+          first[k] = low ? a0[k] : got;    // token i & 3:     lanes 0-3 their first 32 dims, lanes 4-7 the partner's second 32
+          second[k] = low ? got : a1[k];   // token 4 + i & 3: lanes 0-3 the partner's first 32, lanes 4-7 their second 32
+        }
+        if (at[u] < 0) continue;
+        const int tok = t0 + 8 * half + (i & 3);
+        char *to = row + static_cast<int64_t>(8 * half) * out_row_bytes + at[u];
+        if (tok < tokens) store_stream(to, make_uint4(first[0], first[1], first[2], first[3]));
+        if (tok + 4 < tokens) store_stream(to + 4 * out_row_bytes, make_uint4(second[0], second[1], second[2], second[3]));
+      }
+    }
+  }
+}
+
 struct GatherPackedParams {
   GatherPagesParams g;  // parts = heads * pieces per head; k_vec / v_vec unused
   PackedSide k, v;
   int32_t slots;   // 32-byte units of one (page, head) tile: block_size * head_dim * elem / 32
   int32_t pieces;  // work items per head
   int32_t rows;    // 1: 16-byte units, items of 8 token rows (gather_packed16_rows); then
-                   // g.parts = 128-byte lines per group row and pieces = 8-group blocks per head
+                   // g.parts = 128-byte lines per group row and pieces = 8-group blocks per head.
+                   // 2: 2-byte units, items of 16 token rows (gather_packed2_rows); then g.parts =
+                   // 32-byte units per group row and pieces = 64-dim blocks per head
   int32_t only;    // -1: K and V; 0: K only; 1: V only (K and V of different kinds take a launch each)
   int64_t head_out_bytes;  // head_dim * elem
 };
 
 // Gather from packed pages: same work list as kvx_gather_pages_kernel (compacted (sequence,
 // page) chunks, warp-granular items), an item being one piece of one head's tile of K or of V.
-template <typename IdxT, int kUnroll, bool kRows>
+template <typename IdxT, int kUnroll, int kRows>
 __global__ void __launch_bounds__(kGatherThreads) kvx_gather_packed_kernel(const GatherPackedParams pp) {
   const GatherPagesParams &p = pp.g;
   gather_prologue<IdxT>(p);
@@ -1452,11 +1512,18 @@ __global__ void __launch_bounds__(kGatherThreads) kvx_gather_packed_kernel(const
     }
     const ChunkInfo ci = resolve_chunk<IdxT>(p, ref.seq, ref.lb);
     if (ci.block < 0) continue;  // warp-uniform: every lane stays for the shuffles below
-    if constexpr (kRows) {
+    if constexpr (kRows == 1) {
       gather_packed16_rows<kUnroll>(kv ? p.v_base + ci.block * p.v_blk : p.k_base + ci.block * p.k_blk,
                                     kv ? p.v_head : p.k_head, (kv ? p.value_out : p.key_out) + ci.out_off,
                                     p.out_row_bytes, pp.head_out_bytes, kv ? pp.v : pp.k, part, pp.pieces,
                                     pp.pieces * (p.vpr / p.vps), ci.tokens, lane);
+      continue;
+    }
+    if constexpr (kRows == 2) {
+      gather_packed2_rows<2>(kv ? p.v_base + ci.block * p.v_blk : p.k_base + ci.block * p.k_blk,
+                             kv ? p.v_head : p.k_head, (kv ? p.value_out : p.key_out) + ci.out_off, p.out_row_bytes,
+                             pp.head_out_bytes, kv ? pp.v : pp.k, part, pp.pieces, pp.pieces * (p.vpr / p.vps),
+                             ci.tokens, lane);
       continue;
     }
     const int h = part / pp.pieces;
@@ -2933,12 +3000,22 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
       pp.slots = static_cast<int32_t>(static_cast<int64_t>(cache->block_size) * D * elem / 32);
       pp.head_out_bytes = D * elem;
       const bool rows_shape = tiles_knob != 3 && (D * elem) % 128 == 0 && H * D * elem < (int64_t{1} << 30);
-      const bool k_rows = rows_shape && k_side.n_shift == 0 && k_side.runs % 4 == 0;
-      const bool v_rows = rows_shape && v_side.n_shift == 0 && v_side.runs % 4 == 0;
-      auto launch = [&](bool rows, int only) {
-        pp.rows = rows, pp.only = only;
-        if (rows) {
-          pp.g.parts = (only == 1 ? v_side.runs : k_side.runs) / 4;
+      // item kind per tensor: 1 = rows of 16-byte units, 2 = rows of 2-byte units, 0 = pieces
+      auto kind_of = [&](const PackedSide &side) {
+        if (!rows_shape) return 0;
+        if (side.n_shift == 0 && side.runs % 4 == 0) return 1;
+        if (side.n_shift == 3) return 2;
+        return 0;
+      };
+      const int k_kind = kind_of(k_side), v_kind = kind_of(v_side);
+      auto launch = [&](int kind, int only) {
+        pp.rows = kind, pp.only = only;
+        const PackedSide &side = only == 1 ? v_side : k_side;
+        if (kind == 1) {
+          pp.g.parts = side.runs / 4;
+          pp.pieces = static_cast<int32_t>(D * elem / 128);
+        } else if (kind == 2) {
+          pp.g.parts = side.runs;
           pp.pieces = static_cast<int32_t>(D * elem / 128);
         } else {
           pp.pieces = (pp.slots + 127) / 128;
@@ -2951,25 +3028,30 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
         const unsigned ug = static_cast<unsigned>(
             std::max<int64_t>(1, std::min(static_cast<int64_t>(dev.sm_count) * per_sm, (need + 1) / 2)));
         const size_t smem = pp.g.use_prefix ? static_cast<size_t>(S + 1) * sizeof(int32_t) : 0;
-        if (rows) {
-          if (s32)
-            launch_streaming(kvx_gather_packed_kernel<int32_t, 4, true>, ug, kGatherThreads, smem, cs, pp);
-          else
-            launch_streaming(kvx_gather_packed_kernel<int64_t, 4, true>, ug, kGatherThreads, smem, cs, pp);
-        } else {
-          if (s32)
-            launch_streaming(kvx_gather_packed_kernel<int32_t, 4, false>, ug, kGatherThreads, smem, cs, pp);
-          else
-            launch_streaming(kvx_gather_packed_kernel<int64_t, 4, false>, ug, kGatherThreads, smem, cs, pp);
-        }
+#define KVX_GATHER_PACKED(KIND)                                                                       \
+  do {                                                                                                \
+    if (s32)                                                                                          \
+      launch_streaming(kvx_gather_packed_kernel<int32_t, 4, KIND>, ug, kGatherThreads, smem, cs, pp); \
+    else                                                                                              \
+      launch_streaming(kvx_gather_packed_kernel<int64_t, 4, KIND>, ug, kGatherThreads, smem, cs, pp); \
+  } while (0)
+        if (kind == 1)
+          KVX_GATHER_PACKED(1);
+        else if (kind == 2)
+          KVX_GATHER_PACKED(2);
+        else
+          KVX_GATHER_PACKED(0);
+#undef KVX_GATHER_PACKED
       };
       const int64_t piece_items = S * gs.max_blocks * H * ((pp.slots + 127) / 128) * 2;
-      if (k_rows == v_rows || piece_items <= opt(g_opt.gather_rect_items)) {
-        launch(k_rows && v_rows, -1);
+      if (piece_items <= opt(g_opt.gather_rect_items)) {
+        launch(0, -1);  // a small batch: one launch of the piece kind for both tensors
+      } else if (k_kind == v_kind) {
+        launch(k_kind, -1);
       } else {
-        launch(k_rows, 0);
+        launch(k_kind, 0);
         g_launches.fetch_add(1, std::memory_order_relaxed);  // two kernels for this call
-        launch(v_rows, 1);
+        launch(v_kind, 1);
       }
       return finish_launch();
     }
