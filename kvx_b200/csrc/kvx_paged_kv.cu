@@ -1564,7 +1564,7 @@ struct WritePackedParams {
   int32_t vpr;             // 16-byte vectors per dense token row
   int32_t vph, vph_shift;  // ... per head
   int32_t tok_tile;        // power of two <= kPackedTile
-  int32_t lines;           // 1: K and V in 16-byte units through write_packed16_lines
+  int32_t k_lines, v_lines;  // 1: that tensor (16-byte units) through write_packed16_lines
 };
 
 // Stores the units of `w` (positions 0 .. kN-1 of a half window) whose bit is set in `mask`.
@@ -1780,27 +1780,29 @@ __global__ void __launch_bounds__(kWriteThreads) kvx_write_packed_kernel(const W
     }
     s_slot[tid] = sl < 0 ? -1 : sl;
   }
-  if (p.lines) {
-    write_packed16_lines(p, p.key, p.k_pitch, p.k_base, p.k_blk, p.k_head, p.k, s_slot, s_frag, s_win, &s_count, ntok);
-    __syncthreads();
-    write_packed16_lines(p, p.value, p.v_pitch, p.v_base, p.v_blk, p.v_head, p.v, s_slot, s_frag, s_win, &s_count, ntok);
-    return;
-  }
-  // (write_packed_tensor begins with a barrier)
+  // (both tensor routines begin with a barrier)
 #define KVX_PACKED_TENSOR(N, rows, pitch, base, blk, head, side) \
   write_packed_tensor<N>(p, rows, pitch, base, blk, head, side, s_slot, s_frag, s_win, &s_count, ntok)
-  switch (p.k.n_shift) {
-    case 0: KVX_PACKED_TENSOR(1, p.key, p.k_pitch, p.k_base, p.k_blk, p.k_head, p.k); break;
-    case 1: KVX_PACKED_TENSOR(2, p.key, p.k_pitch, p.k_base, p.k_blk, p.k_head, p.k); break;
-    case 2: KVX_PACKED_TENSOR(4, p.key, p.k_pitch, p.k_base, p.k_blk, p.k_head, p.k); break;
-    default: KVX_PACKED_TENSOR(8, p.key, p.k_pitch, p.k_base, p.k_blk, p.k_head, p.k); break;
+  if (p.k_lines) {
+    write_packed16_lines(p, p.key, p.k_pitch, p.k_base, p.k_blk, p.k_head, p.k, s_slot, s_frag, s_win, &s_count, ntok);
+  } else {
+    switch (p.k.n_shift) {
+      case 0: KVX_PACKED_TENSOR(1, p.key, p.k_pitch, p.k_base, p.k_blk, p.k_head, p.k); break;
+      case 1: KVX_PACKED_TENSOR(2, p.key, p.k_pitch, p.k_base, p.k_blk, p.k_head, p.k); break;
+      case 2: KVX_PACKED_TENSOR(4, p.key, p.k_pitch, p.k_base, p.k_blk, p.k_head, p.k); break;
+      default: KVX_PACKED_TENSOR(8, p.key, p.k_pitch, p.k_base, p.k_blk, p.k_head, p.k); break;
+    }
   }
   __syncthreads();  // the fragment list is rebuilt for V (its window may differ)
-  switch (p.v.n_shift) {
-    case 0: KVX_PACKED_TENSOR(1, p.value, p.v_pitch, p.v_base, p.v_blk, p.v_head, p.v); break;
-    case 1: KVX_PACKED_TENSOR(2, p.value, p.v_pitch, p.v_base, p.v_blk, p.v_head, p.v); break;
-    case 2: KVX_PACKED_TENSOR(4, p.value, p.v_pitch, p.v_base, p.v_blk, p.v_head, p.v); break;
-    default: KVX_PACKED_TENSOR(8, p.value, p.v_pitch, p.v_base, p.v_blk, p.v_head, p.v); break;
+  if (p.v_lines) {
+    write_packed16_lines(p, p.value, p.v_pitch, p.v_base, p.v_blk, p.v_head, p.v, s_slot, s_frag, s_win, &s_count, ntok);
+  } else {
+    switch (p.v.n_shift) {
+      case 0: KVX_PACKED_TENSOR(1, p.value, p.v_pitch, p.v_base, p.v_blk, p.v_head, p.v); break;
+      case 1: KVX_PACKED_TENSOR(2, p.value, p.v_pitch, p.v_base, p.v_blk, p.v_head, p.v); break;
+      case 2: KVX_PACKED_TENSOR(4, p.value, p.v_pitch, p.v_base, p.v_blk, p.v_head, p.v); break;
+      default: KVX_PACKED_TENSOR(8, p.value, p.v_pitch, p.v_base, p.v_blk, p.v_head, p.v); break;
+    }
   }
 #undef KVX_PACKED_TENSOR
 }
@@ -2625,8 +2627,10 @@ kvx_status_t write_impl(const kvx_cache_desc_t *cache, const kvx_write_desc_t *w
     while ((tile & (tile - 1)) != 0) tile &= tile - 1;  // a power of two
     while (tile > 1 && (T + tile - 1) / tile < static_cast<int64_t>(dev.sm_count) * 4) tile >>= 1;
     q.tok_tile = tile;
-    q.lines = k_side.n_shift == 0 && v_side.n_shift == 0 && tiles_knob != 2 && tiles_knob != 3 &&
-              (D * io_elem) % 128 == 0 && cache->block_size % 8 == 0;
+    const bool lines_shape = tiles_knob != 2 && tiles_knob != 3 && (D * io_elem) % 128 == 0 && cache->block_size % 8 == 0;
+    // (K alone through the whole-line routine next to a V of 2-byte units measured slower than K
+    // as two-slot fragments: 5.28 against 5.61 TB/s on the paged Llama-3-70B shape)
+    q.k_lines = q.v_lines = lines_shape && k_side.n_shift == 0 && v_side.n_shift == 0;
     const int grid = static_cast<int>((T + tile - 1) / tile);
     if (s32)
       launch_streaming(kvx_write_packed_kernel<int32_t>, grid, kWriteThreads, 0, cs, q);
