@@ -113,6 +113,24 @@ def test_batches_large_enough_for_full_token_tiles(pad):
         _check(case)
 
 
+def test_unpadded_output_from_packed_pages():
+    """kvx_launch_gather_kv_varlen over packed pages: rows of a sequence start at out_indptr[s];
+    sequences given fewer rows than they have tokens stop there, rows cut off the end stay unwritten."""
+    for j, kw in enumerate([dict(pack=8), dict(pack=8, v_pack=1), dict(pack=1), dict(pack=4)]):
+        base = cases.make_case(2600 + j, layout=PACKED, dtype=abi.DTYPE_BF16, heads=4, dim=64, block_size=16,
+                               num_blocks=48, lens=[100, 17, 256, 1, 0, 90], bad_blocks=2, **kw)
+        _, k, v = oracle_write(base)
+        for variant in (dict(), dict(indptr_dtype=np.int64, gap=3, short=(0, 2)), dict(rows_cut=37)):
+            case = cases.to_varlen(base, **variant)
+            st, ek, ev = oracle_gather(case, k, v)
+            assert st == OK
+            for rect in (0, 1 << 40):
+                kvx_b200.set_option("gather_rect_items", rect)
+                st, gk, gv = gpu_gather(case, k, v)
+                assert st == OK
+                assert np.array_equal(gk, ek) and np.array_equal(gv, ev), (j, variant, rect)
+
+
 def test_shapes_that_do_not_qualify_fall_back():
     """Group rows that are not whole 32-byte units, padded group rows, a head_dim whose rows are not
     whole vectors: still exact (other tiers)."""
