@@ -18,10 +18,16 @@
  *   gather, bulk tier    kvx_gather_bulk_kernel    same decomposition, but a page chunk is
  *                        staged global -> shared -> global with cp.async.bulk (the TMA
  *                        engine), one elected thread per ring of stages.
- *   fp8-e4m3             quantise-on-write / dequantise-on-gather variants of the above
+ *   packed pages         kvx_write_packed_kernel / kvx_gather_packed_kernel: HND_PACKED pages whose
+ *                        pack group is 2 .. 16 bytes (K and V each with its own pack factor)
+ *                        are a transposition, in units of the group, of the dense token rows;
+ *                        it is done in registers with warp shuffles between full 16- and
+ *                        32-byte accesses on both sides, the write after cutting its tokens
+ *                        into runs of consecutive slots.
+ *   fp8-e4m3             quantise-on-write / dequantise-on-gather variants of the vector tiers
  *                        plus the absmax -> scale reduction.
  *   generic tier         one element per thread for layouts, head sizes or alignments the
- *                        vector tiers cannot take (HND_PACKED, odd head_dim, ...).
+ *                        other tiers cannot take (odd head_dim, misaligned tensors, ...).
  *
  * Semantics (which element goes where, what is skipped) follow the reference kernels:
  * kernels/kvx_paged_kv.cu:54-75 (offsets), :98-123 (write), :232-266 (gather).
