@@ -71,6 +71,16 @@ def parse_args():
     return ap.parse_args()
 
 
+def config_dict(spec, meta, layers: int, heads_rank: int, pool_gb: float, world: int, layout: str) -> dict:
+    """The `config` object of the JSON line; both arms print the same one for the same workload."""
+    return {"workload": spec.name, "layout": layout, "layers": layers, "heads_global": spec.heads,
+            "heads_per_gpu": heads_rank, "head_dim": spec.dim, "block_size": spec.block_size, "seqs": spec.seqs,
+            "write_tokens": meta.write_tokens, "valid_tokens": meta.valid_tokens, "gather_tokens": meta.gather_tokens,
+            "pool_blocks_per_tensor": meta.num_blocks, "pool_gb_per_gpu": pool_gb,
+            "parallelism": f"kv_head_shard{world}",
+            "l2": "inputs (K+V batch, page pool) larger than L2; every layer has its own pages"}
+
+
 def dist_env():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -151,14 +161,29 @@ def reference_arm(args) -> None:
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": res.get("ms_per_layer"), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-            "config": {"workload": spec.name, "layers_per_step": 1, "heads": spec.heads, "head_dim": spec.dim,
-                       "block_size": spec.block_size, "seqs": spec.seqs, "l2": "inputs larger than host caches"},
+            # the workload of the other arm at this many GPUs (the same object it prints); what a step
+            # of THIS arm samples of it is said in cpu_baseline.sample
+            "config": reference_config(spec, args),
             "cpu_baseline": res,
             "e2e": {"value": res["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "wall_s": round(time.perf_counter() - t0, 1)}
     if not args.no_reference_kernels:
         line["reference_cuda"] = reference_cuda_column(args, spec)
     print(json.dumps(line), flush=True)
+
+
+def reference_config(spec, args) -> dict:
+    """The `config` the GPU arm prints for the same command line (the page pool at its stated
+    size, which a B200 holds; the layers and layout of the command line)."""
+    from kvx_b200 import workloads
+    world = max(1, args.gpus)
+    layers = spec.layers if args.layers is None else args.layers
+    budget = None if args.pool_gb is None else args.pool_gb * 1e9 * spec.layers / layers
+    meta = workloads.build_metadata(spec, pool_budget_bytes=budget, shards=world)
+    heads_rank = spec.heads // world
+    page_local = spec.block_size * heads_rank * spec.dim * workloads.ELEM[spec.cache_dtype]
+    pool_gb = round(2 * layers * meta.num_blocks * page_local / 1e9, 2)
+    return config_dict(spec, meta, layers, heads_rank, pool_gb, world, args.layout)
 
 
 def reference_cuda_column(args, spec) -> dict:
@@ -325,12 +350,7 @@ def main() -> None:
         "metric": "kv_write_gather_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
         "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": round(total_ms / steps, 4),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-        "config": {"workload": spec.name, "layout": args.layout, "layers": layers, "heads_global": spec.heads, "heads_per_gpu": heads_rank,
-                   "head_dim": spec.dim, "block_size": spec.block_size, "seqs": spec.seqs,
-                   "write_tokens": meta.write_tokens, "valid_tokens": meta.valid_tokens,
-                   "gather_tokens": meta.gather_tokens, "pool_blocks_per_tensor": meta.num_blocks,
-                   "pool_gb_per_gpu": pool_gb_used, "parallelism": f"kv_head_shard{world}",
-                   "l2": "inputs (K+V batch, page pool) larger than L2; every layer has its own pages"},
+        "config": config_dict(spec, meta, layers, heads_rank, pool_gb_used, world, args.layout),
         "pct_of_nominal_8tbs": round(100 * value / world / NOMINAL_HBM_GBS, 1),
         "write": {"gbs_per_gpu": round(write_gbs_rank, 1), "us_per_launch": round(write_ms * 1e3 / (layers * steps), 2),
                   "tokens_per_s": round(meta.valid_tokens * layers * steps / (write_ms * 1e-3)),

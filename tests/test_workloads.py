@@ -71,3 +71,23 @@ def test_seeds_are_reproducible_and_distinct():
     c = workloads.build_metadata(workloads.SPECS["c2"], num_blocks=20000, seed=5)
     assert np.array_equal(a.slots, b.slots) and np.array_equal(a.table, b.table)
     assert not np.array_equal(a.lens, c.lens)
+
+
+def test_reference_arm_prints_the_gpu_arms_config():
+    """`bench.py --impl reference` must describe the same workload as the other arm: the full
+    configuration at its stated pool size, whatever bounded sample of it a CPU step runs."""
+    import argparse
+    import importlib.util
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench", os.path.join(root, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    from kvx_b200 import workloads
+    c = bench.reference_config(workloads.SPECS["c2"], argparse.Namespace(gpus=1, layers=None, pool_gb=None, layout="nhd"))
+    assert (c["workload"], c["layers"], c["heads_per_gpu"], c["pool_blocks_per_tensor"], c["pool_gb_per_gpu"]) == \
+        ("c2_llama3_8b_prefill", 32, 8, 71525, 150.0)
+    assert (c["write_tokens"], c["valid_tokens"], c["gather_tokens"]) == (142060, 127653, 142060)
+    c8 = bench.reference_config(workloads.SPECS["c2"], argparse.Namespace(gpus=8, layers=None, pool_gb=None, layout="nhd"))
+    assert (c8["heads_per_gpu"], c8["pool_gb_per_gpu"], c8["parallelism"]) == (1, 18.75, "kv_head_shard8")
+    assert set(c) == set(c8)
