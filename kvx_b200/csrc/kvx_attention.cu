@@ -25,6 +25,7 @@
  * Nothing here allocates; split partials live in caller-provided scratch.
  */
 #include "kvx_attention.h"
+#include "kvx_paged_kv.h"
 
 #include "kvx_pages.h"
 
@@ -85,9 +86,11 @@ __device__ __forceinline__ int64_t read_idx(const void *p, int64_t i) {
 #ifndef KVX_ATTN_MIN_ITEMS
 #define KVX_ATTN_MIN_ITEMS 2048
 #endif
-__host__ __device__ inline int32_t choose_chunk(int64_t seq_count, int64_t heads_kv, int64_t max_seq_len) {
+inline int32_t choose_chunk(int64_t seq_count, int64_t heads_kv, int64_t max_seq_len) {
+  int64_t want = kvx_b200_get_option("attn_min_items");  // tuning knob; 0 = the built-in value
+  if (want <= 0) want = KVX_ATTN_MIN_ITEMS;
   int64_t chunk = 2048;
-  while (chunk > 256 && seq_count * heads_kv * ((max_seq_len + chunk - 1) / chunk) < KVX_ATTN_MIN_ITEMS) chunk >>= 1;
+  while (chunk > 256 && seq_count * heads_kv * ((max_seq_len + chunk - 1) / chunk) < want) chunk >>= 1;
   return static_cast<int32_t>(chunk);
 }
 

@@ -70,6 +70,7 @@ struct Options {
   std::atomic<int64_t> wide{1};                   // 1 = 256-bit accesses where alignment allows
   std::atomic<int64_t> gather_rect_items{40000};  // padded (sequence, page, part, K|V) rectangles up to this size are walked as they are
   std::atomic<int64_t> write_prefetch_waves{2};   // leading write CTAs (in units of 8 per SM) that prefetch their rows into the L2
+  std::atomic<int64_t> attn_min_items{0};         // decode attention: work items wanted before chunks stop halving (0 = built in)
   std::atomic<int64_t> f8_tile_mult{8};           // fp8 wide write: bytes per CTA relative to the copy write
   std::atomic<int64_t> f8_unroll{1};              // fp8 wide write: 32-byte vectors of K and of V in flight per thread
   std::atomic<int64_t> packed_tile_tokens{32};    // tokens per CTA of the packed-page write
@@ -102,6 +103,7 @@ const OptionName kOptionNames[] = {
     {"force_generic", &Options::force_generic},
     {"pdl", &Options::pdl},
     {"wide", &Options::wide},
+    {"attn_min_items", &Options::attn_min_items},
     {"f8_tile_mult", &Options::f8_tile_mult},
     {"f8_unroll", &Options::f8_unroll},
     {"packed_tile_tokens", &Options::packed_tile_tokens},
@@ -2629,7 +2631,12 @@ kvx_status_t write_impl(const kvx_cache_desc_t *cache, const kvx_write_desc_t *w
     q.vpr = static_cast<int32_t>(row_bytes / 16);
     q.vph = static_cast<int32_t>(D * io_elem / 16);
     q.vph_shift = shift_of(q.vph);
-    int tile = static_cast<int>(std::min<int64_t>(kPackedTile, std::max<int64_t>(1, opt(g_opt.packed_tile_tokens))));
+    // Tokens per CTA: the knob's value for token rows of 2 KB (8 heads x 128 x 16 bits) and more,
+    // proportionally more tokens for shorter rows (a shard of the heads), so that a CTA's set-up
+    // (slots, fragment lists) is spread over about as many bytes.
+    int64_t want = std::max<int64_t>(1, opt(g_opt.packed_tile_tokens));
+    if (row_bytes < 2048) want = want * 2048 / std::max<int64_t>(row_bytes, 16);
+    int tile = static_cast<int>(std::min<int64_t>(kPackedTile, want));
     while ((tile & (tile - 1)) != 0) tile &= tile - 1;  // a power of two
     while (tile > 1 && (T + tile - 1) / tile < static_cast<int64_t>(dev.sm_count) * 4) tile >>= 1;
     q.tok_tile = tile;
