@@ -72,6 +72,7 @@ struct AttnParams {
   int32_t heads_q, heads_kv, group, dim;
   int32_t chunk, splits;
   int32_t use_prefix;  // 1: the fast kernel compacts its work list with a prefix sum in shared memory
+  int32_t carry;       // 1: the fast kernel starts an item's first loads ahead of the previous item's epilogue
 };
 
 template <typename IdxT>
@@ -432,10 +433,14 @@ __global__ void __launch_bounds__(kAttnThreads, attn_ctas_per_sm(kD, kNt))
   __shared__ float sm_l[kAttnWarps][8 * kNt];
   __shared__ int32_t sm_page[kAttnWarps][kTStages];
   __shared__ int32_t sm_scan[kListCounts * kAttnWarps];
-  __shared__ unsigned long long sm_item[2];  // this item and the next, claimed one item ahead
+  __shared__ unsigned long long sm_item[3];  // this item and the next two: items are claimed two ahead
   char *ring = reinterpret_cast<char *>(sm_dyn);
-  // merge buffer of the epilogue: lives in the ring, which is idle by then
-  float (*sm_o)[kD + 8] = reinterpret_cast<float (*)[kD + 8]>(ring);  // [8 * kNt][kD + 8]
+  // Merge buffer of the epilogue, [8 * kNt][kD + 8]: it lives in the ring, in the last stage of
+  // warp 0, which is idle by then -- the other stages may already hold the first steps of the
+  // next item (see "carried" below).  Where it does not fit one stage nothing is carried.
+  constexpr bool kCanCarry = 8 * kNt * (kD + 8) * 4 <= 2 * kTile;
+  float (*sm_o)[kD + 8] = reinterpret_cast<float (*)[kD + 8]>(ring + (kCanCarry ? (kTStages - 1) * 2 * kTile : 0));
+  const bool carry = kCanCarry && p.carry != 0;
   // behind the ring: the work list ([S + 1] prefix of full chunks, [S] sequences with a shorter last chunk)
   WorkList wl;
   wl.prefix = reinterpret_cast<int32_t *>(ring + kAttnWarps * kTStages * 2 * kTile);
@@ -475,20 +480,62 @@ __global__ void __launch_bounds__(kAttnThreads, attn_ctas_per_sm(kD, kNt))
   // ldmatrix.trans (V^T as A operand): matrix i -> tokens 8 (i >> 1) + lane % 8, chunk 2 mt + (i & 1)
   const uint32_t lv_at = kTile + ((lane & 7) + 8 * (lane >> 4)) * kPitch + ((lane >> 3) & 1) * 16;
 
-  unsigned long long round = 0;
-  if (threadIdx.x == 0) sm_item[0] = claim_item(p, &round);
-  __syncthreads();
-  for (int parity = 0;; parity ^= 1) {
-    const int64_t item = static_cast<int64_t>(sm_item[parity]);
-    if (item >= items) break;
-    const WorkItem w = locate_item<IdxT>(p, item, wl);
-    const int seq = w.seq, split = w.split, kvh = w.kvh;
-    const int64_t cbeg = w.begin, cend = w.end;
-    const int64_t q_row0 = static_cast<int64_t>(seq) * p.heads_q + static_cast<int64_t>(kvh) * G;
+  // One 16-token step of an item into stage i % kTStages of the warp's ring (an empty copy
+  // group beyond the warp's steps, so that the group count stays one per call).
+  auto issue = [&](int seq, int64_t cbeg, int64_t cend, int kvh, int mine, int i) {
+    if (i < mine) {
+      const uint32_t t0 = static_cast<uint32_t>(cbeg) + static_cast<uint32_t>(warp + i * kAttnWarps) * 16u;
+      const uint32_t lb = p.bs_shift >= 0 ? (t0 >> p.bs_shift) : (t0 / static_cast<uint32_t>(p.block_size));
+      const uint32_t o0 = t0 - lb * static_cast<uint32_t>(p.block_size);  // a step never straddles pages
+      int64_t b = -1;
+      if (lb < static_cast<uint32_t>(p.max_blocks)) {
+        b = read_idx<IdxT>(p.table, static_cast<int64_t>(seq) * p.max_blocks + lb);
+        if (b < 0 || b >= p.num_blocks) b = -1;  // as the gather: skipped
+      }
+      const int stage = i % kTStages;
+      sm_page[warp][stage] = static_cast<int32_t>(b);  // every lane writes the same value
+      if (b >= 0) {
+        const int left = static_cast<int>(min(static_cast<int64_t>(16), cend - t0));  // valid rows
+        // this lane's first row of the step; later rows are cp_rows_per_it rows further on
+        const char *kp = p.k.base + b * p.k.blk + static_cast<int64_t>(kvh) * p.k.head +
+                         (static_cast<int64_t>(o0) + cp_row0) * p.k.tok + 16 * cp_chunk;
+        const char *vp = p.v.base + b * p.v.blk + static_cast<int64_t>(kvh) * p.v.head +
+                         (static_cast<int64_t>(o0) + cp_row0) * p.v.tok + 16 * cp_chunk;
+        const uint32_t kd = my_ring + stage * (2 * kTile) + cp_at0, vd = kd + kTile;
+        if (left == 16) {
+#pragma unroll
+          for (int it = 0; it < kPerLane; ++it) {
+            cp_async16_s(kd + it * cp_rows_per_it * kPitch, kp + it * k_step);
+            cp_async16_s(vd + it * cp_rows_per_it * kPitch, vp + it * v_step);
+          }
+        } else {
+#pragma unroll
+          for (int it = 0; it < kPerLane; ++it) {
+            if (it * cp_rows_per_it + cp_row0 < left) {
+              cp_async16_s(kd + it * cp_rows_per_it * kPitch, kp + it * k_step);
+              cp_async16_s(vd + it * cp_rows_per_it * kPitch, vp + it * v_step);
+            } else {  // beyond the chunk: zeros, so that a zero weight never meets what the page holds there
+              st_shared_zero16(kd + it * cp_rows_per_it * kPitch);
+              st_shared_zero16(vd + it * cp_rows_per_it * kPitch);
+            }
+          }
+        }
+      }
+    }
+    cp_async_commit();
+  };
+  // This warp's steps of a chunk: every kAttnWarps-th, starting at its own number.
+  auto steps_of = [&](int64_t cbeg, int64_t cend) {
+    const int nsteps = cend > cbeg ? static_cast<int>((cend - cbeg + 15) >> 4) : 0;
+    return nsteps > warp ? (nsteps - warp + kAttnWarps - 1) / kAttnWarps : 0;
+  };
 
-    // Q^T as B operands: column g of tile nt = query head 8 nt + g of the group (zero beyond the
-    // group), b0 = dims 16 kk + 2j, +1; b1 = dims 16 kk + 8 + 2j, +1.
-    uint32_t qb[kNt][kKs][2];
+  // Q^T as B operands: column g of tile nt = query head 8 nt + g of the group (zero beyond the
+  // group), b0 = dims 16 kk + 2j, +1; b1 = dims 16 kk + 8 + 2j, +1.  An item's rows are asked
+  // for before the previous item's epilogue, which needs none of these registers.
+  uint32_t qb[kNt][kKs][2];
+  auto load_query = [&](int seq, int kvh) {
+    const int64_t q_row0 = static_cast<int64_t>(seq) * p.heads_q + static_cast<int64_t>(kvh) * G;
 #pragma unroll
     for (int nt = 0; nt < kNt; ++nt) {
 #pragma unroll
@@ -507,6 +554,33 @@ __global__ void __launch_bounds__(kAttnThreads, attn_ctas_per_sm(kD, kNt))
         }
       }
     }
+  };
+
+  // Items are claimed two ahead (by one thread, behind an item's first loads, so that the round
+  // trip of the atomic is off the path between two items): the barrier that ends an item makes
+  // the number of the item after the next one visible, and every warp knows the next item while
+  // it works on this one.  "Carried": after its last step of an item a warp issues its first
+  // kTStages - 1 steps of the next item, so that the lookups and the first rows of that item
+  // travel while the CTA merges and writes this item's result.
+  unsigned long long round = 0;
+  if (threadIdx.x == 0) {
+    sm_item[0] = claim_item(p, &round);
+    sm_item[1] = claim_item(p, &round);
+  }
+  __syncthreads();
+  WorkItem w;
+  bool have = static_cast<int64_t>(sm_item[0]) < items;
+  if (have) {
+    w = locate_item<IdxT>(p, static_cast<int64_t>(sm_item[0]), wl);
+    load_query(w.seq, w.kvh);
+  }
+  bool carried = false;
+  for (int n = 0; have; n = n == 2 ? 0 : n + 1) {
+    const int n1 = n == 2 ? 0 : n + 1, n2 = n1 == 2 ? 0 : n1 + 1;
+    const int seq = w.seq, split = w.split, kvh = w.kvh;
+    const int64_t cbeg = w.begin, cend = w.end;
+    const int64_t q_row0 = static_cast<int64_t>(seq) * p.heads_q + static_cast<int64_t>(kvh) * G;
+
     const float score_mul = kFp8 ? p.scale_log2 * p.ks.base[kvh * p.ks.stride] : p.scale_log2;
 
     // out^T: tile mt = dims 16 mt ..; c0, c1 = (dim g, heads 8 nt + 2j, + 1), c2, c3 = (dim g + 8, ..)
@@ -520,58 +594,14 @@ __global__ void __launch_bounds__(kAttnThreads, attn_ctas_per_sm(kD, kNt))
       l0[nt] = l1[nt] = 0.f;
     }
 
-    const int nsteps = cend > cbeg ? static_cast<int>((cend - cbeg + 15) >> 4) : 0;
-    const int mine = nsteps > warp ? (nsteps - warp + kAttnWarps - 1) / kAttnWarps : 0;
-    const int64_t head_k = static_cast<int64_t>(kvh) * p.k.head, head_v = static_cast<int64_t>(kvh) * p.v.head;
-
-    auto issue = [&](int i) {
-      if (i < mine) {
-        const uint32_t t0 = static_cast<uint32_t>(cbeg) + static_cast<uint32_t>(warp + i * kAttnWarps) * 16u;
-        const uint32_t lb = p.bs_shift >= 0 ? (t0 >> p.bs_shift) : (t0 / static_cast<uint32_t>(p.block_size));
-        const uint32_t o0 = t0 - lb * static_cast<uint32_t>(p.block_size);  // a step never straddles pages
-        int64_t b = -1;
-        if (lb < static_cast<uint32_t>(p.max_blocks)) {
-          b = read_idx<IdxT>(p.table, static_cast<int64_t>(seq) * p.max_blocks + lb);
-          if (b < 0 || b >= p.num_blocks) b = -1;  // as the gather: skipped
-        }
-        const int stage = i % kTStages;
-        sm_page[warp][stage] = static_cast<int32_t>(b);  // every lane writes the same value
-        if (b >= 0) {
-          const int left = static_cast<int>(min(static_cast<int64_t>(16), cend - t0));  // valid rows
-          // this lane's first row of the step; later rows are cp_rows_per_it rows further on
-          const char *kp = p.k.base + b * p.k.blk + head_k + (static_cast<int64_t>(o0) + cp_row0) * p.k.tok + 16 * cp_chunk;
-          const char *vp = p.v.base + b * p.v.blk + head_v + (static_cast<int64_t>(o0) + cp_row0) * p.v.tok + 16 * cp_chunk;
-          const uint32_t kd = my_ring + stage * (2 * kTile) + cp_at0, vd = kd + kTile;
-          if (left == 16) {
+    const int mine = steps_of(cbeg, cend);
+    if (!carried) {
 #pragma unroll
-            for (int it = 0; it < kPerLane; ++it) {
-              cp_async16_s(kd + it * cp_rows_per_it * kPitch, kp + it * k_step);
-              cp_async16_s(vd + it * cp_rows_per_it * kPitch, vp + it * v_step);
-            }
-          } else {
-#pragma unroll
-            for (int it = 0; it < kPerLane; ++it) {
-              if (it * cp_rows_per_it + cp_row0 < left) {
-                cp_async16_s(kd + it * cp_rows_per_it * kPitch, kp + it * k_step);
-                cp_async16_s(vd + it * cp_rows_per_it * kPitch, vp + it * v_step);
-              } else {  // beyond the chunk: zeros, so that a zero weight never meets what the page holds there
-                st_shared_zero16(kd + it * cp_rows_per_it * kPitch);
-                st_shared_zero16(vd + it * cp_rows_per_it * kPitch);
-              }
-            }
-          }
-        }
-      }
-      cp_async_commit();
-    };
-
-#pragma unroll
-    for (int i = 0; i < kTStages - 1; ++i) issue(i);
-    // The next item is claimed now, behind this item's first loads, so that the round trip of
-    // the atomic is off the path between two items.
-    if (threadIdx.x == 0) sm_item[parity ^ 1] = claim_item(p, &round);
+      for (int i = 0; i < kTStages - 1; ++i) issue(seq, cbeg, cend, kvh, mine, i);
+    }
+    if (threadIdx.x == 0) sm_item[n2] = claim_item(p, &round);
     for (int i = 0; i < mine; ++i) {
-      issue(i + kTStages - 1);
+      issue(seq, cbeg, cend, kvh, mine, i + kTStages - 1);
       cp_async_wait<kTStages - 1>();
       __syncwarp();  // every lane's chunks of step i are in place
       const int stage = i % kTStages;
@@ -672,6 +702,20 @@ __global__ void __launch_bounds__(kAttnThreads, attn_ctas_per_sm(kD, kNt))
     }
     cp_async_wait<0>();
 
+    // The next item, and its first steps on their way before this item's epilogue.
+    have = static_cast<int64_t>(sm_item[n1]) < items;
+    carried = false;
+    if (have) {
+      w = locate_item<IdxT>(p, static_cast<int64_t>(sm_item[n1]), wl);
+      load_query(w.seq, w.kvh);
+      if (carry) {
+        const int next_mine = steps_of(w.begin, w.end);
+#pragma unroll
+        for (int i = 0; i < kTStages - 1; ++i) issue(w.seq, w.begin, w.end, w.kvh, next_mine, i);
+        carried = true;
+      }
+    }
+
     // Denominators were kept per lane (its two tokens per step): complete them over g.
 #pragma unroll
     for (int nt = 0; nt < kNt; ++nt) {
@@ -734,7 +778,7 @@ __global__ void __launch_bounds__(kAttnThreads, attn_ctas_per_sm(kD, kNt))
         }
       }
     }
-    __syncthreads();  // the next item's id is visible; merge buffers and the ring are free again
+    __syncthreads();  // the number of the item after the next is visible; merge buffers and the ring are free again
   }
 }
 
@@ -1067,6 +1111,7 @@ KVX_API kvx_status_t kvx_launch_paged_attention_decode(const kvx_cache_desc_t *c
   p.part_o = nullptr;
   p.part_ml = nullptr;
   p.counter = nullptr;
+  p.carry = 0;
   p.scale_log2 = attn->scale * 1.4426950408889634f;
   p.seq_count = static_cast<int32_t>(S);
   p.max_blocks = static_cast<int32_t>(attn->block_table.max_blocks_per_seq);
@@ -1099,6 +1144,7 @@ KVX_API kvx_status_t kvx_launch_paged_attention_decode(const kvx_cache_desc_t *c
       p.part_ml = p.part_o + S * Hq * p.splits * D;
     }
     p.use_prefix = S <= kMaxPrefixSeqs ? 1 : 0;
+    p.carry = kvx_b200_get_option("attn_carry") != 0 ? 1 : 0;  // tuning knob; on unless set to 0
     const int per_sm = attn_ctas_per_sm(static_cast<int>(D), p.group <= 8 ? 1 : 2);  // the kernels' launch bounds
     // K and V steps of 16 rows, each row padded by 16 bytes
     const size_t ring = static_cast<size_t>(kAttnWarps) * kTStages * 2 * 16 * (D * elem + 16);

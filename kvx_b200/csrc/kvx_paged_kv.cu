@@ -71,6 +71,7 @@ struct Options {
   std::atomic<int64_t> gather_rect_items{40000};  // padded (sequence, page, part, K|V) rectangles up to this size are walked as they are
   std::atomic<int64_t> write_prefetch_waves{2};   // leading write CTAs (in units of 8 per SM) that prefetch their rows into the L2
   std::atomic<int64_t> attn_min_items{0};         // decode attention: work items wanted before chunks stop halving (0 = built in)
+  std::atomic<int64_t> attn_carry{1};             // decode attention: first loads of the next work item ahead of an item's epilogue (0 = off)
   std::atomic<int64_t> f8_tile_mult{8};           // fp8 wide write: bytes per CTA relative to the copy write
   std::atomic<int64_t> f8_unroll{1};              // fp8 wide write: 32-byte vectors of K and of V in flight per thread
   std::atomic<int64_t> packed_tile_tokens{32};    // tokens per CTA of the packed-page write
@@ -104,6 +105,7 @@ const OptionName kOptionNames[] = {
     {"pdl", &Options::pdl},
     {"wide", &Options::wide},
     {"attn_min_items", &Options::attn_min_items},
+    {"attn_carry", &Options::attn_carry},
     {"f8_tile_mult", &Options::f8_tile_mult},
     {"f8_unroll", &Options::f8_unroll},
     {"packed_tile_tokens", &Options::packed_tile_tokens},

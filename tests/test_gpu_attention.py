@@ -23,6 +23,16 @@ pytestmark = pytest.mark.gpu
 TOL = {abi.DTYPE_BF16: (1.5e-2, 1.6e-2), abi.DTYPE_F16: (2e-3, 2e-3), abi.DTYPE_F32: (2e-5, 2e-5)}
 
 
+@pytest.fixture(autouse=True, params=["carried_first_loads", "no_carry"])
+def item_hand_over(request):
+    """Every test runs with the fast kernel's two ways of going from one work item to the next:
+    the next item's first loads issued ahead of the epilogue (the default), or after it."""
+    saved = kvx_b200.get_option("attn_carry")
+    kvx_b200.set_option("attn_carry", 1 if request.param == "carried_first_loads" else 0)
+    yield request.param
+    kvx_b200.set_option("attn_carry", saved)
+
+
 def _query(case, group, seed):
     rng = np.random.default_rng(seed)
     S, Hq, D = case.table.shape[0], case.geom.num_kv_heads * group, case.geom.head_dim
