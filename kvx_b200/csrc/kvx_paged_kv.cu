@@ -1388,32 +1388,36 @@ __device__ __forceinline__ void gather_packed_piece(const char *src, char *dst, 
 // 32 bytes of group 8 gh + lane / 4 at token pair 4 ah + lane % 4) and writes 4 token rows x 128
 // bytes with each of its two store instructions, so that the 8 output rows, which are contiguous,
 // are filled by this one warp.  Needs runs % 4 == 0 and a multiple of 8 groups per head.
+// With few heads (a shard of them) such an item is too little to keep a warp's loads in flight
+// between two table lookups, so an item then spans 2^span_shift neighbouring lines of the group
+// rows (octets of tokens), walked fastest: a group row gives up 2^span_shift x 128 contiguous bytes.
 template <int kUnroll>
 __device__ __forceinline__ void gather_packed16_rows(const char *src, int64_t head_bytes, char *dst,
                                                      int64_t out_row_bytes, int64_t head_out_bytes,
-                                                     const PackedSide &side, int ah, int g_blocks, int steps,
-                                                     int tokens, int lane) {
-  const int a = ah * 4 + (lane & 3), g_lo = lane >> 2;
-  if (8 * ah >= tokens) return;  // warp-uniform: none of the item's tokens exists
-  const bool live = 2 * a < tokens;
-  char *row = dst + static_cast<int64_t>(2 * a) * out_row_bytes;
-  for (int t0 = 0; t0 < steps; t0 += kUnroll) {  // a step = 8 groups of one head
+                                                     const PackedSide &side, int ah0, int span_shift, int g_blocks,
+                                                     int steps, int tokens, int lane) {
+  const int g_lo = lane >> 2;
+  if (8 * ah0 >= tokens) return;  // warp-uniform: none of the item's tokens exists
+  const int total = steps << span_shift, span_mask = (1 << span_shift) - 1;
+  for (int t0 = 0; t0 < total; t0 += kUnroll) {  // a step = 8 groups of one head, for one octet of tokens
     Vec32 x[kUnroll];
-    int at[kUnroll];
+    int at[kUnroll], first[kUnroll];  // byte offset inside a token row; the lane's first token (-1: nothing)
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-      const int t = t0 + u;
-      const int h = t / g_blocks, gh = t - h * g_blocks;
+      const int t = t0 + u, st = t >> span_shift;
+      const int a = (ah0 + (t & span_mask)) * 4 + (lane & 3);
+      const int h = st / g_blocks, gh = st - h * g_blocks;
       const int g = gh * 8 + g_lo;
-      at[u] = t < steps ? static_cast<int>(h * head_out_bytes) + g * 16 : -1;
-      if (t < steps && live) x[u] = load_stream32(src + h * head_bytes + static_cast<int64_t>(g) * side.dhi + a * 32);
+      at[u] = static_cast<int>(h * head_out_bytes) + g * 16;
+      first[u] = t < total && 2 * a < tokens ? 2 * a : -1;
+      if (first[u] >= 0) x[u] = load_stream32(src + h * head_bytes + static_cast<int64_t>(g) * side.dhi + a * 32);
     }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-      if (at[u] < 0 || !live) continue;
-      store_stream(row + at[u], make_uint4(x[u].w[0], x[u].w[1], x[u].w[2], x[u].w[3]));
-      if (2 * a + 1 < tokens)
-        store_stream(row + out_row_bytes + at[u], make_uint4(x[u].w[4], x[u].w[5], x[u].w[6], x[u].w[7]));
+      if (first[u] < 0) continue;
+      char *row = dst + static_cast<int64_t>(first[u]) * out_row_bytes + at[u];
+      store_stream(row, make_uint4(x[u].w[0], x[u].w[1], x[u].w[2], x[u].w[3]));
+      if (first[u] + 1 < tokens) store_stream(row + out_row_bytes, make_uint4(x[u].w[4], x[u].w[5], x[u].w[6], x[u].w[7]));
     }
   }
 }
@@ -1485,6 +1489,7 @@ struct GatherPackedParams {
                    // g.parts = 128-byte lines per group row and pieces = 8-group blocks per head.
                    // 2: 2-byte units, items of 16 token rows (gather_packed2_rows); then g.parts =
                    // 32-byte units per group row and pieces = 64-dim blocks per head
+  int32_t span_shift;  // rows == 1: an item spans 2^span_shift lines of the group rows (g.parts counts items)
   int32_t only;    // -1: K and V; 0: K only; 1: V only (K and V of different kinds take a launch each)
   int64_t head_out_bytes;  // head_dim * elem
 };
@@ -1525,8 +1530,8 @@ __global__ void __launch_bounds__(kGatherThreads) kvx_gather_packed_kernel(const
     if constexpr (kRows == 1) {
       gather_packed16_rows<kUnroll>(kv ? p.v_base + ci.block * p.v_blk : p.k_base + ci.block * p.k_blk,
                                     kv ? p.v_head : p.k_head, (kv ? p.value_out : p.key_out) + ci.out_off,
-                                    p.out_row_bytes, pp.head_out_bytes, kv ? pp.v : pp.k, part, pp.pieces,
-                                    pp.pieces * (p.vpr / p.vps), ci.tokens, lane);
+                                    p.out_row_bytes, pp.head_out_bytes, kv ? pp.v : pp.k, part << pp.span_shift,
+                                    pp.span_shift, pp.pieces, pp.pieces * (p.vpr / p.vps), ci.tokens, lane);
       continue;
     }
     if constexpr (kRows == 2) {
@@ -3030,9 +3035,16 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
       auto launch = [&](int kind, int only) {
         pp.rows = kind, pp.only = only;
         const PackedSide &side = only == 1 ? v_side : k_side;
+        pp.span_shift = 0;
         if (kind == 1) {
-          pp.g.parts = side.runs / 4;
           pp.pieces = static_cast<int32_t>(D * elem / 128);
+          // Few heads (a shard of them): an item of 8 tokens is little per table lookup, so it
+          // takes more octets of tokens, up to 16 steps of loads.  (Measured on shards of 1, 2 and
+          // 4 heads of 256 bytes: 16 % to 40 % faster than one octet; K and V under one lookup on top
+          // of it changed nothing.)
+          int lines = side.runs / 4;
+          while (lines % 2 == 0 && (H * pp.pieces << (pp.span_shift + 1)) <= 16) lines /= 2, ++pp.span_shift;
+          pp.g.parts = lines;
         } else if (kind == 2) {
           pp.g.parts = side.runs;
           pp.pieces = static_cast<int32_t>(D * elem / 128);
@@ -3063,10 +3075,10 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
 #undef KVX_GATHER_PACKED
       };
       const int64_t piece_items = S * gs.max_blocks * H * ((pp.slots + 127) / 128) * 2;
-      if (piece_items <= opt(g_opt.gather_rect_items)) {
-        launch(0, -1);  // a small batch: one launch of the piece kind for both tensors
-      } else if (k_kind == v_kind) {
+      if (k_kind == v_kind) {
         launch(k_kind, -1);
+      } else if (piece_items <= opt(g_opt.gather_rect_items)) {
+        launch(0, -1);  // a small batch: one launch of the piece kind for both tensors
       } else {
         launch(k_kind, 0);
         g_launches.fetch_add(1, std::memory_order_relaxed);  // two kernels for this call

@@ -113,6 +113,22 @@ def test_batches_large_enough_for_full_token_tiles(pad):
         _check(case)
 
 
+@pytest.mark.parametrize("heads", [1, 2, 4])
+def test_a_shard_of_the_heads(heads):
+    """One, two or four KV heads (what a rank of a head-sharded cache holds): a gather item then
+    spans two, four or eight octets of a page's tokens instead of one.  Pages of 16 to 128 tokens,
+    last pages that end inside an octet, inside a span and on its border; batches past the size up
+    to which the gather takes another route."""
+    lens = [1, 7, 8, 9, 15, 16, 17, 31, 33, 63, 64, 65, 100, 127, 128, 129, 200, 255, 300, 0, 5]
+    for j, bs in enumerate([16, 32, 64, 128]):
+        for dim in (64, 128):
+            case = cases.make_case(2700 + 10 * j + dim // 64, layout=PACKED, pack=8, dtype=abi.DTYPE_BF16, heads=heads,
+                                   dim=dim, block_size=bs, num_blocks=sum(-(-n // bs) for n in lens) + 4, lens=lens,
+                                   pad_frac=0.05, bad_blocks=2)
+            case.note = f"{heads} heads, pages of {bs}, dim {dim}"
+            _check(case, knobs=(1, 3))
+
+
 def test_unpadded_output_from_packed_pages():
     """kvx_launch_gather_kv_varlen over packed pages: rows of a sequence start at out_indptr[s];
     sequences given fewer rows than they have tokens stop there, rows cut off the end stay unwritten."""
