@@ -435,11 +435,13 @@ __global__ void __launch_bounds__(kAttnThreads, attn_ctas_per_sm(kD, kNt))
   __shared__ int32_t sm_scan[kListCounts * kAttnWarps];
   __shared__ unsigned long long sm_item[3];  // this item and the next two: items are claimed two ahead
   char *ring = reinterpret_cast<char *>(sm_dyn);
-  // Merge buffer of the epilogue, [8 * kNt][kD + 8]: it lives in the ring, in the last stage of
-  // warp 0, which is idle by then -- the other stages may already hold the first steps of the
-  // next item (see "carried" below).  Where it does not fit one stage nothing is carried.
+  // Merge buffers of the epilogue, [8 * kNt][kD + 8] floats: they live in the ring, which is
+  // idle by then.  Where one fits a stage, every warp uses the last stage of its own ring -- the
+  // other stages may already hold the first steps of the next item (see "carried" below).
+  // Where it does not (e4m3 pages with 9 to 16 query heads per KV head), the warps add into one
+  // buffer at the start of the ring and nothing is carried.
   constexpr bool kCanCarry = 8 * kNt * (kD + 8) * 4 <= 2 * kTile;
-  float (*sm_o)[kD + 8] = reinterpret_cast<float (*)[kD + 8]>(ring + (kCanCarry ? (kTStages - 1) * 2 * kTile : 0));
+  float (*sm_o)[kD + 8] = reinterpret_cast<float (*)[kD + 8]>(ring);
   const bool carry = kCanCarry && p.carry != 0;
   // behind the ring: the work list ([S + 1] prefix of full chunks, [S] sequences with a shorter last chunk)
   WorkList wl;
@@ -728,6 +730,50 @@ __global__ void __launch_bounds__(kAttnThreads, attn_ctas_per_sm(kD, kNt))
         sm_m[warp][8 * nt + 2 * j] = m0[nt], sm_m[warp][8 * nt + 2 * j + 1] = m1[nt];
         sm_l[warp][8 * nt + 2 * j] = l0[nt], sm_l[warp][8 * nt + 2 * j + 1] = l1[nt];
       }
+    }
+    if constexpr (kCanCarry) {
+      // Every warp lays its own (unscaled) result down in the last stage of its own ring -- no
+      // zeroing, no atomics -- and after one barrier the CTA sums the four with their weights.
+      constexpr int kWarpRing = kTStages * 2 * kTile;
+      float (*my_o)[kD + 8] = reinterpret_cast<float (*)[kD + 8]>(ring + warp * kWarpRing + (kTStages - 1) * 2 * kTile);
+#pragma unroll
+      for (int nt = 0; nt < kNt; ++nt) {
+        const int h0 = 8 * nt + 2 * j;
+#pragma unroll
+        for (int mt = 0; mt < kKs; ++mt) {
+          const int d_lo = kFp8 ? 16 * mt + 2 * g : 16 * mt + g, d_hi = kFp8 ? d_lo + 1 : d_lo + 8;
+          my_o[h0][d_lo] = o[nt][mt][0], my_o[h0][d_hi] = o[nt][mt][2];
+          my_o[h0 + 1][d_lo] = o[nt][mt][1], my_o[h0 + 1][d_hi] = o[nt][mt][3];
+        }
+      }
+      __syncthreads();
+      for (int i = threadIdx.x; i < G * kD; i += kAttnThreads) {
+        const int row = i / kD, d = i - row * kD;
+        float M = -INFINITY, L = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, sm_m[w][row]);
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) {
+          const float f = exp2_diff(sm_m[w][row], M);
+          L += sm_l[w][row] * f;
+          acc += reinterpret_cast<const float (*)[kD + 8]>(ring + w * kWarpRing + (kTStages - 1) * 2 * kTile)[row][d] * f;
+        }
+        float val = L > 0.f ? acc / L : 0.f;
+        if (kFp8) val *= p.vs.base[kvh * p.vs.stride];
+        const int64_t q = q_row0 + row;
+        if (p.splits == 1) {
+          reinterpret_cast<uint16_t *>(p.out)[q * kD + d] = QT::round1(val);
+        } else {
+          const int64_t at = q * p.splits + split;
+          p.part_o[at * kD + d] = val;
+          if (d == 0) {
+            p.part_ml[at * 2] = M;
+            p.part_ml[at * 2 + 1] = L;
+          }
+        }
+      }
+      __syncthreads();  // the number of the item after the next is visible; merge buffers and the ring are free again
+      continue;
     }
     __syncthreads();  // every warp is done with its part of the ring
     for (int i = threadIdx.x; i < 8 * kNt * (kD + 8); i += kAttnThreads) (&sm_o[0][0])[i] = 0.f;
