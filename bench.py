@@ -616,42 +616,51 @@ def pcie_ceiling(dist, chunk_mb: int = 64, chunks: int = 16) -> dict:
     """What the box gives plain pinned copies: every rank at once moves `chunks` chunks of `chunk_mb` MB
     host -> device, then device -> host, then both directions at the same time (two streams, one
     asynchronous copy per chunk), wall-clock timed from a barrier to the last rank's completion.
-    The host-buffer leg above cannot beat the 'both' figure; it is reported next to it."""
+    Twice: with one host chunk per direction used over and over (it stays in the host's caches: the
+    most the links give), and with every chunk at its own place in `chunks` x `chunk_mb` MB of pinned
+    memory per direction (streamed from and to host DRAM, as the host-buffer leg's data is).  The
+    host-buffer leg above cannot beat the 'both' figures; it is reported next to them."""
     import torch
     n = chunk_mb << 20
-    host_in = torch.empty(n, dtype=torch.uint8).pin_memory()
-    host_out = torch.empty(n, dtype=torch.uint8).pin_memory()
+    host_in = torch.empty(n * chunks, dtype=torch.uint8).pin_memory()
+    host_out = torch.empty(n * chunks, dtype=torch.uint8).pin_memory()
     host_in.fill_(1)
     host_out.fill_(0)  # first touch by this process
     dev_in = torch.empty(n, dtype=torch.uint8, device="cuda")
     dev_out = torch.ones(n, dtype=torch.uint8, device="cuda")
     up, down = torch.cuda.Stream(), torch.cuda.Stream()
 
-    def run(h2d: bool, d2h: bool) -> float:
+    def run(h2d: bool, d2h: bool, streamed: bool) -> float:
         torch.cuda.synchronize()
         if dist is not None:
             dist.barrier()
         t0 = time.perf_counter()
-        for _ in range(chunks):
+        for i in range(chunks):
+            at = i * n if streamed else 0
             if h2d:
                 with torch.cuda.stream(up):
-                    dev_in.copy_(host_in, non_blocking=True)
+                    dev_in.copy_(host_in[at:at + n], non_blocking=True)
             if d2h:
                 with torch.cuda.stream(down):
-                    host_out.copy_(dev_out, non_blocking=True)
+                    host_out[at:at + n].copy_(dev_out, non_blocking=True)
         torch.cuda.synchronize()
         t = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device="cuda")
         if dist is not None:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    run(True, True)  # warm-up
+    run(True, True, True)  # warm-up
     gb = n * chunks / 1e9
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    t_up, t_down, t_both = run(True, False), run(False, True), run(True, True)
+    t_up, t_down, t_both = run(True, False, False), run(False, True, False), run(True, True, False)
+    s_up, s_down, s_both = run(True, False, True), run(False, True, True), run(True, True, True)
     return {"h2d_gbs_per_gpu": round(gb / t_up, 1), "d2h_gbs_per_gpu": round(gb / t_down, 1),
             "both_gbs_per_gpu": round(2 * gb / t_both, 1), "both_gbs_all_gpus": round(2 * gb * world / t_both, 1),
-            "how": f"{chunks} x {chunk_mb} MB pinned copies per direction and rank, all {world} ranks at once"}
+            "streamed": {"h2d_gbs_per_gpu": round(gb / s_up, 1), "d2h_gbs_per_gpu": round(gb / s_down, 1),
+                         "both_gbs_per_gpu": round(2 * gb / s_both, 1),
+                         "both_gbs_all_gpus": round(2 * gb * world / s_both, 1)},
+            "how": f"{chunks} x {chunk_mb} MB pinned copies per direction and rank, all {world} ranks at once; "
+                   f"'streamed': every chunk at its own place in {chunks * chunk_mb} MB per direction"}
 
 
 def time_reference_kernels(dw, peak: float) -> dict:
