@@ -122,6 +122,22 @@ def test_split_contexts_and_merge():
     check(case, k, v, 4, max_seq_len=100)
 
 
+def test_many_items_per_cta_from_the_compacted_list():
+    """Thousands of work items for a few hundred persistent CTAs: every CTA takes many items in a
+    row (claimed two ahead, the next item's first rows issued before an item's epilogue), full
+    chunks first, then last chunks of every length class; sequences without tokens in between."""
+    rng = np.random.default_rng(79)
+    lens = [int(x) for x in rng.choice([0, 1, 15, 16, 17, 40, 63, 64, 65, 130, 255, 256, 257, 300, 511, 520, 700],
+                                       size=500)]
+    lens[7], lens[250], lens[499] = 2049, 4100, 5000  # contexts of several chunks: partial results and the merge
+    for i, (dtype, group, dim) in enumerate(((abi.DTYPE_BF16, 4, 128), (abi.DTYPE_F16, 12, 64))):
+        case = cases.make_case(2170 + i, dtype=dtype, real_values=True, heads=8, dim=dim, block_size=16,
+                               num_blocks=sum(-(-n // 16) for n in lens) + 8, lens=lens)
+        case.note = f"many items, group {group}"
+        _, k, v = oracle_write(case)
+        check(case, k, v, group, seed=i)
+
+
 def test_more_sequences_than_the_shared_memory_prefix_holds():
     """Beyond 8 192 sequences the tensor-core kernels enumerate the padded (sequence, chunk)
     rectangle instead of a compacted list; both forms (heads in columns / in rows)."""
