@@ -466,6 +466,13 @@ __global__ void __launch_bounds__(kAttnThreads, attn_ctas_per_sm(kD, kNt))
       asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const char *>(p.lens) + at));
   }
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  // The first two items are claimed at once (see below): the atomics travel while the work
+  // list is built.
+  unsigned long long round = 0;
+  if (threadIdx.x == 0) {
+    sm_item[0] = claim_item(p, &round);
+    sm_item[1] = claim_item(p, &round);
+  }
   const int64_t items = build_work_list<IdxT>(p, &wl, sm_scan);
 
   zero_empty_sequences<IdxT>(p);
@@ -564,11 +571,6 @@ __global__ void __launch_bounds__(kAttnThreads, attn_ctas_per_sm(kD, kNt))
   // it works on this one.  "Carried": after its last step of an item a warp issues its first
   // kTStages - 1 steps of the next item, so that the lookups and the first rows of that item
   // travel while the CTA merges and writes this item's result.
-  unsigned long long round = 0;
-  if (threadIdx.x == 0) {
-    sm_item[0] = claim_item(p, &round);
-    sm_item[1] = claim_item(p, &round);
-  }
   __syncthreads();
   WorkItem w;
   bool have = static_cast<int64_t>(sm_item[0]) < items;
@@ -837,25 +839,61 @@ __global__ void kvx_attention_reset_kernel(unsigned long long *counter) {
 // ------------------------------------------------------------------ merge of chunks ----
 
 // One CTA per (sequence, query head): out = sum_s w_s O_s / sum_s w_s over the chunks the
-// sequence really has, w_s = L_s * exp2(M_s - max M).
+// sequence really has, w_s = L_s * exp2(M_s - max M).  The loads are laid out so that few of
+// them wait for one another: a lane per chunk asks for (M_s, L_s), the weights go through shared
+// memory (each warp keeps its own copy: no barrier), and a thread's partial outputs are asked
+// for four at a time.
 template <typename IdxT>
 __global__ void __launch_bounds__(128) kvx_attention_merge_kernel(const AttnParams p, int out_code) {
   pdl_prologue();
+  __shared__ float s_w[4][32];
   const int64_t q = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int seq = static_cast<int>(q / p.heads_q);
   int64_t len = read_idx<IdxT>(p.lens, seq);
   if (len > p.max_seq_len) len = p.max_seq_len;
   const int live = len <= 0 ? 0 : static_cast<int>(min(static_cast<int64_t>(p.splits), (len + p.chunk - 1) / p.chunk));
-  float M = -INFINITY, W = 0.f;
-  for (int s = 0; s < live; ++s) M = fmaxf(M, p.part_ml[(q * p.splits + s) * 2]);
-  for (int s = 0; s < live; ++s)
-    W += p.part_ml[(q * p.splits + s) * 2 + 1] * exp2_diff(p.part_ml[(q * p.splits + s) * 2], M);
-  for (int d = threadIdx.x; d < p.dim; d += blockDim.x) {
-    float acc = 0.f;
-    for (int s = 0; s < live; ++s) {
-      const float w = p.part_ml[(q * p.splits + s) * 2 + 1] * exp2_diff(p.part_ml[(q * p.splits + s) * 2], M);
-      acc += w * p.part_o[(q * p.splits + s) * p.dim + d];
+  const float2 *ml = reinterpret_cast<const float2 *>(p.part_ml) + q * p.splits;  // (M_s, L_s)
+  const float *po = p.part_o + q * p.splits * p.dim;
+  float M = -INFINITY;
+  for (int s = lane; s < live; s += 32) M = fmaxf(M, ml[s].x);
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) M = fmaxf(M, __shfl_xor_sync(0xFFFFFFFFu, M, d));
+  // a thread owns dims threadIdx.x and threadIdx.x + 128 (the fast tier's head_dim is at most 256)
+  const int d0 = threadIdx.x, d1 = threadIdx.x + 128;
+  float W = 0.f, acc0 = 0.f, acc1 = 0.f;
+  for (int s0 = 0; s0 < live; s0 += 32) {
+    float w = 0.f;
+    if (s0 + lane < live) {
+      const float2 v = ml[s0 + lane];
+      w = v.y * exp2_diff(v.x, M);
     }
+    W += w;
+    __syncwarp();
+    s_w[warp][lane] = w;
+    __syncwarp();
+    const int n = min(32, live - s0);
+    const float *from = po + static_cast<int64_t>(s0) * p.dim;
+    for (int k0 = 0; k0 < n; k0 += 4) {
+      float x0[4], x1[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const bool in = k0 + k < n;
+        x0[k] = in && d0 < p.dim ? from[static_cast<int64_t>(k0 + k) * p.dim + d0] : 0.f;
+        x1[k] = in && d1 < p.dim ? from[static_cast<int64_t>(k0 + k) * p.dim + d1] : 0.f;
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float wk = k0 + k < n ? s_w[warp][k0 + k] : 0.f;
+        acc0 += wk * x0[k];
+        acc1 += wk * x1[k];
+      }
+    }
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) W += __shfl_xor_sync(0xFFFFFFFFu, W, d);
+  auto put = [&](int d, float acc) {
+    if (d >= p.dim) return;
     const float val = W > 0.f ? acc / W : 0.f;
     const int64_t at = q * p.dim + d;
     if (out_code == KVX_DTYPE_BF16)
@@ -864,7 +902,9 @@ __global__ void __launch_bounds__(128) kvx_attention_merge_kernel(const AttnPara
       reinterpret_cast<uint16_t *>(p.out)[at] = Fp16::round1(val);
     else
       reinterpret_cast<float *>(p.out)[at] = val;
-  }
+  };
+  put(d0, acc0);
+  put(d1, acc1);
 }
 
 // ------------------------------------------------------------------ generic tier -------
