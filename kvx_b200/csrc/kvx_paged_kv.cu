@@ -72,6 +72,8 @@ struct Options {
   std::atomic<int64_t> write_prefetch_waves{2};   // leading write CTAs (in units of 8 per SM) that prefetch their rows into the L2
   std::atomic<int64_t> attn_min_items{0};         // decode attention: work items wanted before chunks stop halving (0 = built in)
   std::atomic<int64_t> attn_carry{1};             // decode attention: first loads of the next work item ahead of an item's epilogue (0 = off)
+  std::atomic<int64_t> packed_fill_halves{1};     // packed write: prefetch the sector a lone half-sector store goes to (0 = off)
+  std::atomic<int64_t> packed_lines_variant{0};   // packed write, whole-line kernel: 0 = 2 load rounds per thread, 6 CTAs per SM; 1 = 4 rounds, 4 CTAs
   std::atomic<int64_t> f8_tile_mult{8};           // fp8 wide write: bytes per CTA relative to the copy write
   std::atomic<int64_t> f8_unroll{1};              // fp8 wide write: 32-byte vectors of K and of V in flight per thread
   std::atomic<int64_t> packed_tile_tokens{32};    // tokens per CTA of the packed-page write
@@ -106,6 +108,8 @@ const OptionName kOptionNames[] = {
     {"wide", &Options::wide},
     {"attn_min_items", &Options::attn_min_items},
     {"attn_carry", &Options::attn_carry},
+    {"packed_fill_halves", &Options::packed_fill_halves},
+    {"packed_lines_variant", &Options::packed_lines_variant},
     {"f8_tile_mult", &Options::f8_tile_mult},
     {"f8_unroll", &Options::f8_unroll},
     {"packed_tile_tokens", &Options::packed_tile_tokens},
@@ -1580,6 +1584,7 @@ struct WritePackedParams {
   int32_t vph, vph_shift;  // ... per head
   int32_t tok_tile;        // power of two <= kPackedTile
   int32_t k_lines, v_lines;  // 1: that tensor (16-byte units) through write_packed16_lines
+  int32_t fill_halves;       // whole-line routine: prefetch the sector that a lone 16-byte store goes to
 };
 
 // Stores the units of `w` (positions 0 .. kN-1 of a half window) whose bit is set in `mask`.
@@ -1695,66 +1700,93 @@ __device__ __forceinline__ void write_packed_tensor(const WritePackedParams &p, 
   }
 }
 
-// 16-byte units with whole 128-byte lines on both sides (the mirror of gather_packed16_rows): the
-// window is the 8 slots of one line of a group row; a lane takes token pair a = lane % 4 of the
-// window and group 8 gh + lane / 4, so that each of its two loads reads 4 token rows x 128 bytes
-// per warp instruction and its 32-byte store fills, with the three other pairs, one line of each
+// K and V both in 16-byte units with whole 128-byte lines on both sides (the mirror of
+// gather_packed16_rows).  The window is the 8 slots of one line of a group row.  Here the tile's
+// tokens are not cut into fragments but sorted into WINDOWS: a table says, for every window the
+// tile touches, which token of the tile (if any) goes to each of its 8 slots.  Holes in the
+// slots (padding) then cost nothing but the lanes they leave idle, where every hole used to
+// start a new fragment and with it another pass of a warp over all group rows: with 10 % of
+// the slots padded the tile has 1.5 times the fragments of a tile without holes, and the
+// kernel, which keeps the load-store path 87 % busy without them, slowed down by as much.
+// Windows end at the tile's borders (no tile depends on what its neighbour does), and tokens
+// that lie far apart but share a window simply get a window entry each.
+//
+// Building the table: a valid token LEADS a window unless the nearest valid token among the 7
+// before it lies in the same window.  Every valid token walks back to its leader (over holes and
+// over members of its own window) and enters itself at its slot's position in the leader's table
+// row, which is the row with the leader's own number in the tile (rows are cleared while the
+// slots are loaded); leaders also add themselves to the list of windows.  One barrier.
+// Work items are then (window, block of 8 groups): a lane takes slot pair a = lane % 4 of the
+// window and group 8 gh + lane / 4, each of its two loads reads 4 token rows x 128 bytes per
+// warp instruction and its 32-byte store fills, with the three other pairs, one line of each
 // of 8 group rows.  Needs a multiple of 8 groups per head and block sizes that are multiples of 8.
-// (K and V in one loop over a shared fragment list measured 2-4 % slower than one pass each.  A
-// tokens-fastest route without fragments for tiles without a hole is 1-2 % faster in a short
-// burst and 1-2 % slower once the device sits at its power limit, which back-to-back packed
-// writes reach -- about 950 W -- so there is one route.)
-__device__ __forceinline__ void write_packed16_lines(const WritePackedParams &p, const char *rows, int64_t pitch,
-                                                     char *base, int64_t blk, int64_t head, const PackedSide &side,
-                                                     const int64_t *s_slot, int32_t *s_frag, int64_t *s_win,
-                                                     int *s_count, int ntok) {
-  constexpr int kW = 8;
-  const int tid = threadIdx.x, lane = tid & 31;
-  if (tid == 0) *s_count = 0;
-  __syncthreads();
-  if (tid < ntok) {
-    const int64_t sl = s_slot[1 + tid];
-    const int64_t before = s_slot[tid];
-    const int pos0 = static_cast<int>(sl & (kW - 1));
-    // Fragments end at the tile's borders here (a window is 8 slots, a tile 32 tokens: little is
-    // lost, and no tile depends on what its neighbour does).
-    const bool continues = tid > 0 && sl >= 0 && before >= 0 && sl == before + 1 && pos0 != 0;
-    if (sl >= 0 && !continues) {
-      int len = 1;
-      while (pos0 + len < kW && tid + len < ntok && s_slot[1 + tid + len] == sl + len) ++len;
-      const int at = atomicAdd(s_count, 1);
-      s_frag[at] = tid | (pos0 << 8) | (len << 16);
+// (A tokens-fastest route for tiles without a hole is 1-2 % faster in a short burst and 1-2 %
+// slower once the device sits at its power limit, which back-to-back packed writes reach --
+// about 950 W -- so there is one route.)
+struct PackedWindows {
+  int64_t *k_at, *v_at;  // [windows] byte offset of the window's first unit in the K / V pool (group 0, head 0)
+  int32_t *leader;       // [windows] the leading token of the window = its row in `token`
+  int16_t *token;        // [tokens][8] for a leader: the token of the tile at each slot of its window, -1 = none
+  int *count;
+};
+
+// (the caller has cleared `token` and *count and put a barrier behind that and the slots)
+__device__ __forceinline__ void build_packed_windows(const WritePackedParams &p, const int64_t *s_slot, const PackedWindows &w,
+                                                     int ntok) {
+  for (int t = threadIdx.x; t < ntok; t += kWriteThreads) {
+    const int64_t sl = s_slot[1 + t];
+    if (sl < 0) continue;
+    int lead = t;
+    for (;;) {  // does the nearest valid token among the 7 before `lead` share the window?
+      int j = lead - 1;
+      while (j >= 0 && j >= lead - 7 && s_slot[1 + j] < 0) --j;
+      if (j < 0 || j < lead - 7 || (s_slot[1 + j] >> 3) != (sl >> 3)) break;
+      lead = j;
+    }
+    w.token[8 * lead + static_cast<int>(sl & 7)] = static_cast<int16_t>(t);
+    if (lead == t) {
+      const int at = atomicAdd(w.count, 1);
       int64_t b, o;
-      split_slot(sl - pos0, p.block_size, p.bs_shift, &b, &o);
-      s_win[at] = b * blk + o * 16;
+      split_slot(sl & ~int64_t{7}, p.block_size, p.bs_shift, &b, &o);
+      w.leader[at] = t;
+      w.k_at[at] = b * p.k_blk + o * 16;
+      w.v_at[at] = b * p.v_blk + o * 16;
     }
   }
-  __syncthreads();
-  const int nfrag = *s_count;
+}
+
+template <int kRound>
+__device__ __forceinline__ void write_packed16_windows(const WritePackedParams &p, const char *rows, int64_t pitch,
+                                                       char *base, int64_t head, const PackedSide &side,
+                                                       const int64_t *s_at, const int32_t *s_leader,
+                                                       const int16_t *s_token, int windows) {
+  const int tid = threadIdx.x, lane = tid & 31;
   const int a = lane & 3, g_lo = lane >> 2;
   const int blocks_per_row = p.vpr >> 3;  // 8-group blocks of one token row (all heads)
   const int blocks_per_head = p.vph >> 3;
-  const int total = nfrag * blocks_per_row;
+  const int total = windows * blocks_per_row;
   const int64_t tok0 = static_cast<int64_t>(blockIdx.x) * p.tok_tile;
-  constexpr int kRound = 4;
   for (int e0 = tid >> 5; e0 < total; e0 += (kWriteThreads / 32) * kRound) {
     uint4 x[kRound], y[kRound];
     int64_t to[kRound];
-    uint32_t have[kRound];  // bit 0: the pair's first token exists, bit 1: its second
+    uint32_t have[kRound];  // bit 0: the pair's first slot gets a token, bit 1: its second
 #pragma unroll
     for (int r = 0; r < kRound; ++r) {
       const int e = e0 + r * (kWriteThreads / 32);
       have[r] = 0u;
       if (e >= total) continue;
-      const int frag = e / blocks_per_row, blk8 = e - frag * blocks_per_row;
-      const int32_t info = s_frag[frag];
-      const int first = info & 0xFF, pos0 = (info >> 8) & 0xFF, len = info >> 16;
+      const int win = e / blocks_per_row, blk8 = e - win * blocks_per_row;
+      const uint32_t pair = *reinterpret_cast<const uint32_t *>(s_token + 8 * s_leader[win] + 2 * a);
+      const int ta = static_cast<int16_t>(pair & 0xFFFFu), tb = static_cast<int16_t>(pair >> 16);
       const int h = blk8 / blocks_per_head, gh = blk8 - h * blocks_per_head;
-      const int ra = 2 * a - pos0, rb = ra + 1;
-      const char *from = rows + (tok0 + first) * pitch + static_cast<int64_t>(blk8 * 8 + g_lo) * 16;
-      if (ra >= 0 && ra < len) x[r] = load_stream(from + ra * pitch), have[r] |= 1u;
-      if (rb >= 0 && rb < len) y[r] = load_stream(from + rb * pitch), have[r] |= 2u;
-      to[r] = s_win[frag] + h * head + static_cast<int64_t>(gh * 8 + g_lo) * side.dhi + a * 32;
+      const char *from = rows + tok0 * pitch + static_cast<int64_t>(blk8 * 8 + g_lo) * 16;
+      if (ta >= 0) x[r] = load_stream(from + ta * pitch), have[r] |= 1u;
+      if (tb >= 0) y[r] = load_stream(from + tb * pitch), have[r] |= 2u;
+      to[r] = s_at[win] + h * head + static_cast<int64_t>(gh * 8 + g_lo) * side.dhi + a * 32;
+      // Half a sector (the pair's other slot gets nothing from this tile): ask for the sector
+      // now, so that the 16 bytes meet it in the L2 and it leaves as a whole sector, instead of
+      // the memory completing it with a read-modify-write of its own when it is evicted.
+      if (p.fill_halves && (have[r] == 1u || have[r] == 2u)) prefetch_l2(base + to[r]);
     }
 #pragma unroll
     for (int r = 0; r < kRound; ++r) {
@@ -1772,22 +1804,17 @@ __device__ __forceinline__ void write_packed16_lines(const WritePackedParams &p,
   }
 }
 
+// Slots of the tile's tokens, of the token before it and of up to 16 after it (-1: padding, or
+// beyond the pool, which is skipped like padding): s_slot[1 + t] for token t of the tile.
 template <typename SlotT>
-__global__ void __launch_bounds__(kWriteThreads) kvx_write_packed_kernel(const WritePackedParams p) {
-  __shared__ int64_t s_slot[kPackedSlots];
-  __shared__ int64_t s_win[kPackedTile];
-  __shared__ int32_t s_frag[kPackedTile];
-  __shared__ int s_count;
-  pdl_prologue();
+__device__ __forceinline__ void load_tile_slots(const WritePackedParams &p, int64_t tok0, int64_t *s_slot) {
   const int tid = threadIdx.x;
-  const int64_t tok0 = static_cast<int64_t>(blockIdx.x) * p.tok_tile;
-  const int ntok = static_cast<int>(min(static_cast<int64_t>(p.tok_tile), p.num_tokens - tok0));
   if (tid < p.tok_tile + 17) {
     const int64_t t = tok0 - 1 + tid;
     int64_t sl = -1;
     if (t >= 0 && t < p.num_tokens) {
       sl = static_cast<int64_t>(static_cast<const SlotT *>(p.slots)[t]);
-      if (sl >= 0) {  // a slot beyond the pool is skipped like padding
+      if (sl >= 0) {
         int64_t b, o;
         split_slot(sl, p.block_size, p.bs_shift, &b, &o);
         if (b >= p.num_blocks) sl = -1;
@@ -1795,12 +1822,48 @@ __global__ void __launch_bounds__(kWriteThreads) kvx_write_packed_kernel(const W
     }
     s_slot[tid] = sl < 0 ? -1 : sl;
   }
+}
+
+// K and V both in 16-byte units, whole lines: one window table serves both tensors.
+template <typename SlotT, int kRound, int kMinCtas>
+__global__ void __launch_bounds__(kWriteThreads, kMinCtas) kvx_write_packed_lines_kernel(const WritePackedParams p) {
+  __shared__ int64_t s_slot[kPackedSlots];
+  __shared__ int64_t s_win[kPackedTile];
+  __shared__ int64_t s_win_v[kPackedTile];
+  __shared__ __align__(16) int16_t s_token[kPackedTile * 8];
+  __shared__ int32_t s_leader[kPackedTile];
+  __shared__ int s_count;
+  pdl_prologue();
+  const int tid = threadIdx.x;
+  const int64_t tok0 = static_cast<int64_t>(blockIdx.x) * p.tok_tile;
+  const int ntok = static_cast<int>(min(static_cast<int64_t>(p.tok_tile), p.num_tokens - tok0));
+  load_tile_slots<SlotT>(p, tok0, s_slot);
+  for (int t = tid; t < ntok; t += kWriteThreads)
+    *reinterpret_cast<uint4 *>(s_token + 8 * t) = make_uint4(0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu);
+  if (tid == 0) s_count = 0;
+  __syncthreads();
+  const PackedWindows w{s_win, s_win_v, s_leader, s_token, &s_count};
+  build_packed_windows(p, s_slot, w, ntok);
+  __syncthreads();
+  const int windows = s_count;
+  write_packed16_windows<kRound>(p, p.key, p.k_pitch, p.k_base, p.k_head, p.k, s_win, s_leader, s_token, windows);
+  write_packed16_windows<kRound>(p, p.value, p.v_pitch, p.v_base, p.v_head, p.v, s_win_v, s_leader, s_token, windows);
+}
+
+template <typename SlotT>
+__global__ void __launch_bounds__(kWriteThreads) kvx_write_packed_kernel(const WritePackedParams p) {
+  __shared__ int64_t s_slot[kPackedSlots];
+  __shared__ int64_t s_win[kPackedTile];
+  __shared__ int32_t s_frag[kPackedTile];
+  __shared__ int s_count;
+  pdl_prologue();
+  const int64_t tok0 = static_cast<int64_t>(blockIdx.x) * p.tok_tile;
+  const int ntok = static_cast<int>(min(static_cast<int64_t>(p.tok_tile), p.num_tokens - tok0));
+  load_tile_slots<SlotT>(p, tok0, s_slot);
   // (both tensor routines begin with a barrier)
 #define KVX_PACKED_TENSOR(N, rows, pitch, base, blk, head, side) \
   write_packed_tensor<N>(p, rows, pitch, base, blk, head, side, s_slot, s_frag, s_win, &s_count, ntok)
-  if (p.k_lines) {
-    write_packed16_lines(p, p.key, p.k_pitch, p.k_base, p.k_blk, p.k_head, p.k, s_slot, s_frag, s_win, &s_count, ntok);
-  } else {
+  {
     switch (p.k.n_shift) {
       case 0: KVX_PACKED_TENSOR(1, p.key, p.k_pitch, p.k_base, p.k_blk, p.k_head, p.k); break;
       case 1: KVX_PACKED_TENSOR(2, p.key, p.k_pitch, p.k_base, p.k_blk, p.k_head, p.k); break;
@@ -1809,9 +1872,7 @@ __global__ void __launch_bounds__(kWriteThreads) kvx_write_packed_kernel(const W
     }
   }
   __syncthreads();  // the fragment list is rebuilt for V (its window may differ)
-  if (p.v_lines) {
-    write_packed16_lines(p, p.value, p.v_pitch, p.v_base, p.v_blk, p.v_head, p.v, s_slot, s_frag, s_win, &s_count, ntok);
-  } else {
+  {
     switch (p.v.n_shift) {
       case 0: KVX_PACKED_TENSOR(1, p.value, p.v_pitch, p.v_base, p.v_blk, p.v_head, p.v); break;
       case 1: KVX_PACKED_TENSOR(2, p.value, p.v_pitch, p.v_base, p.v_blk, p.v_head, p.v); break;
@@ -2651,7 +2712,28 @@ kvx_status_t write_impl(const kvx_cache_desc_t *cache, const kvx_write_desc_t *w
     // (K alone through the whole-line routine next to a V of 2-byte units measured slower than K
     // as two-slot fragments: 5.28 against 5.61 TB/s on the paged Llama-3-70B shape)
     q.k_lines = q.v_lines = lines_shape && k_side.n_shift == 0 && v_side.n_shift == 0;
+    q.fill_halves = opt(g_opt.packed_fill_halves) != 0;
     const int grid = static_cast<int>((T + tile - 1) / tile);
+    if (q.k_lines && q.v_lines) {
+      const int64_t variant = opt(g_opt.packed_lines_variant);
+#define KVX_LINES(ROUND, CTAS)                                                                                  \
+  do {                                                                                                          \
+    if (s32)                                                                                                    \
+      launch_streaming(kvx_write_packed_lines_kernel<int32_t, ROUND, CTAS>, grid, kWriteThreads, 0, cs, q);     \
+    else                                                                                                        \
+      launch_streaming(kvx_write_packed_lines_kernel<int64_t, ROUND, CTAS>, grid, kWriteThreads, 0, cs, q);     \
+  } while (0)
+      // Two rounds of loads per thread at 40 registers and 6 CTAs per SM, or four at 64 and 4:
+      // measured equal within 2 % on full batches (5.92-5.97 against 5.81-5.96 TB/s unpadded, 4.04
+      // against 4.08 TB/s with 10 % padded slots), the first 5 % ahead on a one-head shard.  With
+      // spills to reach 5 or 8 CTAs per SM it is 10-20 % slower.
+      if (variant == 1)
+        KVX_LINES(4, 4);
+      else
+        KVX_LINES(2, 6);
+#undef KVX_LINES
+      return finish_launch();
+    }
     if (s32)
       launch_streaming(kvx_write_packed_kernel<int32_t>, grid, kWriteThreads, 0, cs, q);
     else

@@ -20,7 +20,8 @@ PACKED = abi.LAYOUT_HND_PACKED
 
 @pytest.fixture(autouse=True)
 def _defaults():
-    saved = {n: kvx_b200.get_option(n) for n in ("packed_tiles", "force_generic", "gather_rect_items")}
+    saved = {n: kvx_b200.get_option(n) for n in ("packed_tiles", "force_generic", "gather_rect_items",
+                                                 "packed_lines_variant", "packed_fill_halves")}
     yield
     for n, v in saved.items():
         kvx_b200.set_option(n, v)
@@ -111,6 +112,12 @@ def test_batches_large_enough_for_full_token_tiles(pad):
         case.note = f"large batch {j}, pad {pad}"
         assert case.T > 148 * 4 * 32   # CTAs take full 32-token tiles
         _check(case)
+        if j == 0:  # the whole-line kernel's other shape, and without the sector prefetch of lone halves
+            kvx_b200.set_option("packed_lines_variant", 1)
+            kvx_b200.set_option("packed_fill_halves", 0)
+            _check(case)
+            kvx_b200.set_option("packed_lines_variant", 0)
+            kvx_b200.set_option("packed_fill_halves", 1)
 
 
 @pytest.mark.parametrize("heads", [1, 2, 4])
