@@ -23,7 +23,9 @@
  *                        are a transposition, in units of the group, of the dense token rows;
  *                        it is done in registers with warp shuffles between full 16- and
  *                        32-byte accesses on both sides, the write after cutting its tokens
- *                        into runs of consecutive slots.
+ *                        into runs of consecutive slots -- or, with K and V in 16-byte groups
+ *                        (kvx_write_packed_lines_kernel), after sorting them into the 8-slot
+ *                        windows of the pages' 128-byte lines.
  *   fp8-e4m3             quantise-on-write / dequantise-on-gather variants of the vector tiers
  *                        plus the absmax -> scale reduction.
  *   generic tier         one element per thread for layouts, head sizes or alignments the
