@@ -131,7 +131,8 @@ def test_a_shard_of_the_heads(heads):
         for dim in (64, 128):
             case = cases.make_case(2700 + 10 * j + dim // 64, layout=PACKED, pack=8, dtype=abi.DTYPE_BF16, heads=heads,
                                    dim=dim, block_size=bs, num_blocks=sum(-(-n // bs) for n in lens) + 4, lens=lens,
-                                   pad_frac=0.05, bad_blocks=2)
+                                   pad_frac=0.05 + 0.1 * (j % 2), bad_blocks=2, oob_slots=j,
+                                   slot_dtype=np.int32 if j % 2 else np.int64)
             case.note = f"{heads} heads, pages of {bs}, dim {dim}"
             _check(case, knobs=(1, 3))
 
