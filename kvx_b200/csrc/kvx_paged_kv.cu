@@ -2597,6 +2597,24 @@ kvx_status_t launch_write_generic(const kvx_write_desc_t *w, const GenericParams
 
 // Tokens per CTA: aim at `write_vecs_per_cta` vectors of K per CTA, but never fewer CTAs
 // than fill the machine twice when the batch is small.
+// CTAs of a warp-item gather kernel.  Work items are small (one unrolled iteration of a warp)
+// and there are many more CTAs than fit at once, so the hardware scheduler balances the tail;
+// measured best at up to `per_sm` = 256 CTAs per SM, but never more than half a CTA-slot per item
+// of the padded (sequence, page) rectangle: beyond that most CTAs would only run their prefix
+// scan.  A rectangle of more than 65 536 (sequence, page) pairs is a batch of contexts padded to
+// the longest one, mostly holes (a decode batch of 512 contexts of 1 to 1 024 pages is 9 % full):
+// it is counted as 65 536 pairs and given four items per warp, not two, because every CTA pays
+// the scan over all sequences before its first item (one head of 8, full contexts of that
+// batch: 285 us with 256 CTAs per SM, 233 us with 64).
+int64_t gather_item_grid(int64_t seq_count, int64_t max_blocks, int64_t items_per_chunk, int sm_count, int64_t per_sm,
+                         int warps_per_cta) {
+  const int64_t rect = seq_count * max_blocks;
+  const bool sparse = rect > 65536;
+  const int64_t items = (sparse ? int64_t{65536} : rect) * items_per_chunk;
+  const int64_t ctas = (items + warps_per_cta - 1) / warps_per_cta;
+  return std::max<int64_t>(1, std::min(static_cast<int64_t>(sm_count) * per_sm, (ctas + 1) / (sparse ? 4 : 2)));
+}
+
 int pick_tok_tile(int64_t tokens, int64_t vpr, int sm_count) {
   int64_t tile = opt(g_opt.write_vecs_per_cta) / vpr;
   if (tile < 1) tile = 1;
@@ -3138,10 +3156,9 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
         }
         const int64_t max_items = S * gs.max_blocks * pp.g.parts * (only < 0 ? 2 : 1);
         pp.g.use_prefix = p.use_prefix && max_items > opt(g_opt.gather_rect_items);
-        const int64_t need = (max_items + kGatherWarps - 1) / kGatherWarps;
         const int64_t per_sm = std::max<int64_t>(1, opt(g_opt.gather_ctas_per_sm));
-        const unsigned ug = static_cast<unsigned>(
-            std::max<int64_t>(1, std::min(static_cast<int64_t>(dev.sm_count) * per_sm, (need + 1) / 2)));
+        const unsigned ug = static_cast<unsigned>(gather_item_grid(S, gs.max_blocks, pp.g.parts * (only < 0 ? 2 : 1),
+                                                                   dev.sm_count, per_sm, kGatherWarps));
         const size_t smem = pp.g.use_prefix ? static_cast<size_t>(S + 1) * sizeof(int32_t) : 0;
 #define KVX_GATHER_PACKED(KIND)                                                                       \
   do {                                                                                                \
@@ -3217,10 +3234,7 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
     if (part_vecs > chunk_vecs) part_vecs = chunk_vecs;
     p.part_vecs = static_cast<int32_t>(part_vecs);
     p.parts = static_cast<int32_t>((chunk_vecs + part_vecs - 1) / part_vecs);
-    // Grid.  Work items are small (one unrolled iteration of a warp) and there are many more
-    // CTAs than fit at once (4 per SM), so the hardware scheduler balances the tail; measured
-    // best at up to 256 CTAs per SM.  But never more than half a CTA-slot per item of the padded
-    // (sequence, page) rectangle: beyond that most CTAs would only run their prefix scan.
+    // Grid: see gather_item_grid.
     const int64_t max_items = S * gs.max_blocks * p.parts * 2;
     const int64_t need = (max_items + kGatherWarps - 1) / kGatherWarps;
     // A small rectangle is walked as it is: without the scan a warp asks for its length and its
@@ -3232,7 +3246,8 @@ kvx_status_t gather_impl(const kvx_cache_desc_t *cache, const kvx_gather_desc_t 
     int64_t per_sm = opt(g_opt.gather_ctas_per_sm) < 1 ? 1 : opt(g_opt.gather_ctas_per_sm);
     if (fp8) per_sm = std::min<int64_t>(per_sm, 8);
     int64_t grid = static_cast<int64_t>(dev.sm_count) * per_sm;
-    grid = std::max<int64_t>(1, std::min(grid, fp8 ? need : (need + 1) / 2));
+    grid = fp8 ? std::max<int64_t>(1, std::min(grid, need))
+               : gather_item_grid(S, gs.max_blocks, static_cast<int64_t>(p.parts) * 2, dev.sm_count, per_sm, kGatherWarps);
     const unsigned ug = static_cast<unsigned>(grid);
     if (fp8 && !offsets && io_elem == 2 && opt(g_opt.wide) && (p.vps % 2) == 0 && (p.part_vecs % 2) == 0 &&
         aligned(p.key_out, 32) && aligned(p.value_out, 32) && aligned(p.k_base, 16) && aligned(p.v_base, 16) &&
