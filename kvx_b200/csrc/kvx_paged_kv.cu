@@ -1598,14 +1598,40 @@ __device__ __forceinline__ void store_units(char *dst, const uint32_t (&w)[4], u
     if (mask & 1u) *reinterpret_cast<uint2 *>(dst) = make_uint2(w[0], w[1]);
     if (mask & 2u) *reinterpret_cast<uint2 *>(dst + 8) = make_uint2(w[2], w[3]);
   } else if constexpr (kN == 4) {
+    // aligned pairs of units go out as one 8-byte store
 #pragma unroll
-    for (int k = 0; k < 4; ++k)
-      if (mask & (1u << k)) *reinterpret_cast<uint32_t *>(dst + 4 * k) = w[k];
+    for (int k = 0; k < 4; k += 2) {
+      const uint32_t m = (mask >> k) & 3u;
+      if (m == 3u)
+        *reinterpret_cast<uint2 *>(dst + 4 * k) = make_uint2(w[k], w[k + 1]);
+      else if (m & 1u)
+        *reinterpret_cast<uint32_t *>(dst + 4 * k) = w[k];
+      else if (m & 2u)
+        *reinterpret_cast<uint32_t *>(dst + 4 * k + 4) = w[k + 1];
+    }
   } else {
+    // aligned runs of four and of two units go out as 8- and 4-byte stores (a half window with
+    // one hole: three stores, not seven)
 #pragma unroll
-    for (int k = 0; k < 8; ++k)
-      if (mask & (1u << k))
-        *reinterpret_cast<uint16_t *>(dst + 2 * k) = static_cast<uint16_t>(w[k >> 1] >> (16 * (k & 1)));
+    for (int q = 0; q < 2; ++q) {  // units 4 q .. 4 q + 3 = words 2 q, 2 q + 1
+      const uint32_t m = (mask >> (4 * q)) & 0xFu;
+      if (m == 0xFu) {
+        *reinterpret_cast<uint2 *>(dst + 8 * q) = make_uint2(w[2 * q], w[2 * q + 1]);
+        continue;
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {  // units 4 q + 2 j, + 1 = word 2 q + j
+        const uint32_t mm = (m >> (2 * j)) & 3u;
+        const uint32_t word = w[2 * q + j];
+        char *at = dst + 8 * q + 4 * j;
+        if (mm == 3u)
+          *reinterpret_cast<uint32_t *>(at) = word;
+        else if (mm & 1u)
+          *reinterpret_cast<uint16_t *>(at) = static_cast<uint16_t>(word);
+        else if (mm & 2u)
+          *reinterpret_cast<uint16_t *>(at + 2) = static_cast<uint16_t>(word >> 16);
+      }
+    }
   }
 }
 
