@@ -553,8 +553,10 @@ def run_e2e(args, dw, dist) -> dict:
     hs = torch.from_numpy(meta.slots).pin_memory()
     ht = torch.from_numpy(meta.table).pin_memory()
     hl = torch.from_numpy(meta.lens).pin_memory()
-    hok = torch.empty(dw.out_k.shape, dtype=dw.out_k.dtype).pin_memory()
-    hov = torch.empty(dw.out_v.shape, dtype=dw.out_v.dtype).pin_memory()
+    # one pinned array for both outputs: V a fixed distance behind K, which lets the pipeline bring
+    # a sequence's K run and V run back as one 2-D copy
+    hout = torch.empty((2, *dw.out_k.shape), dtype=dw.out_k.dtype).pin_memory()
+    hok, hov = hout[0], hout[1]
     seq_bytes = dw.out_k[0].numel() * dw.out_k.element_size()
     chunk = max(args.e2e_chunk_mb << 20, seq_bytes)
     pipe = C.c_void_p()

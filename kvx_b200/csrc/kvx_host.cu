@@ -96,8 +96,10 @@ KVX_API kvx_status_t kvx_host_pipe_create(size_t chunk_bytes, uint32_t max_seqs,
   p->max_seqs = max_seqs;
   bool good = true;
   for (int i = 0; i < kRings * kSets && good; ++i) {
-    good = cudaMalloc(&p->k_stage[i], p->chunk_bytes) == cudaSuccess &&
-           cudaMalloc(&p->v_stage[i], p->chunk_bytes) == cudaSuccess &&
+    // K and V staging of a set are one allocation, V one chunk behind K: a K run and the V run
+    // of the same rows are then the two rows of one 2-D copy
+    good = cudaMalloc(&p->k_stage[i], 2 * p->chunk_bytes) == cudaSuccess &&
+           (p->v_stage[i] = p->k_stage[i] + p->chunk_bytes) != nullptr &&
            (i >= kSets || cudaMalloc(&p->slot_stage[i], p->slot_cap) == cudaSuccess) &&
            cudaEventCreateWithFlags(&p->ready[i], cudaEventDisableTiming) == cudaSuccess &&
            cudaEventCreateWithFlags(&p->freed[i], cudaEventDisableTiming) == cudaSuccess;
@@ -127,8 +129,7 @@ KVX_API void kvx_host_pipe_destroy(kvx_host_pipe_t *p) {
   if (p->d2h) cudaStreamSynchronize(p->d2h);
   if (p->d2h_v) cudaStreamSynchronize(p->d2h_v);
   for (int i = 0; i < kRings * kSets; ++i) {
-    cudaFree(p->k_stage[i]);
-    cudaFree(p->v_stage[i]);
+    cudaFree(p->k_stage[i]);  // (V staging is its second half)
     if (i < kSets) cudaFree(p->slot_stage[i]);
     if (p->ready[i]) cudaEventDestroy(p->ready[i]);
     if (p->freed[i]) cudaEventDestroy(p->freed[i]);
@@ -265,7 +266,13 @@ KVX_API kvx_status_t kvx_host_gather_kv(kvx_host_pipe_t *p, const kvx_cache_desc
     ok(p, cudaStreamWaitEvent(p->d2h, p->ready[set], 0));
     ok(p, cudaStreamWaitEvent(p->d2h_v, p->ready[set], 0));
 
-    // Copy back runs of consecutive defined pages, never a byte more.
+    // Copy back runs of consecutive defined pages, never a byte more.  Under load from the other
+    // direction a device->host copy costs about 20 us whatever its size, and a sequence's runs are
+    // a few MB, so where the caller's K and V outputs lie a fixed distance apart that a 2-D copy
+    // can use as its pitch (V behind K, less than 2 GB: one allocation for both, say), the K run
+    // and the V run go back as the two rows of ONE copy.
+    const int64_t kv_apart = static_cast<char *>(gather->io.value.data) - static_cast<char *>(gather->io.key.data);
+    const bool paired = kvx_b200_get_option("host_pair_kv") != 0 && kv_apart >= S * seq_bytes && kv_apart <= INT32_MAX;
     for (int64_t i = 0; i < n && status == KVX_STATUS_OK; ++i) {
       const int64_t s = s0 + i;
       int64_t len = index_at(gather->seq_lens.lengths, bt.index_dtype, s);
@@ -284,8 +291,13 @@ KVX_API kvx_status_t kvx_host_gather_kv(kvx_host_pipe_t *p, const kvx_cache_desc
           const int64_t off = tok0 * row, bytes = (tok1 - tok0) * row;
           char *hk = static_cast<char *>(gather->io.key.data) + s * seq_bytes + off;
           char *hv = static_cast<char *>(gather->io.value.data) + s * seq_bytes + off;
-          ok(p, cudaMemcpyAsync(hk, p->k_stage[set] + i * seq_bytes + off, bytes, cudaMemcpyDeviceToHost, p->d2h));
-          ok(p, cudaMemcpyAsync(hv, p->v_stage[set] + i * seq_bytes + off, bytes, cudaMemcpyDeviceToHost, p->d2h_v));
+          if (paired) {
+            ok(p, cudaMemcpy2DAsync(hk, static_cast<size_t>(kv_apart), p->k_stage[set] + i * seq_bytes + off, p->chunk_bytes,
+                                    static_cast<size_t>(bytes), 2, cudaMemcpyDeviceToHost, p->d2h));
+          } else {
+            ok(p, cudaMemcpyAsync(hk, p->k_stage[set] + i * seq_bytes + off, bytes, cudaMemcpyDeviceToHost, p->d2h));
+            ok(p, cudaMemcpyAsync(hv, p->v_stage[set] + i * seq_bytes + off, bytes, cudaMemcpyDeviceToHost, p->d2h_v));
+          }
           p->d2h_bytes += static_cast<uint64_t>(2 * bytes);
           run_begin = -1;
         }

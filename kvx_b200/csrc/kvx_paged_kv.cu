@@ -74,6 +74,7 @@ struct Options {
   std::atomic<int64_t> write_prefetch_waves{2};   // leading write CTAs (in units of 8 per SM) that prefetch their rows into the L2
   std::atomic<int64_t> attn_min_items{0};         // decode attention: work items wanted before chunks stop halving (0 = built in)
   std::atomic<int64_t> attn_carry{1};             // decode attention: first loads of the next work item ahead of an item's epilogue (0 = off)
+  std::atomic<int64_t> host_pair_kv{1};           // host-buffer gather: K and V run of a sequence as one 2-D copy where the outputs allow it (0 = two copies)
   std::atomic<int64_t> packed_fill_halves{1};     // packed write: prefetch the sector a lone half-sector store goes to (0 = off)
   std::atomic<int64_t> packed_lines_variant{0};   // packed write, whole-line kernel: 0 = 2 load rounds per thread, 6 CTAs per SM; 1 = 4 rounds, 4 CTAs
   std::atomic<int64_t> f8_tile_mult{8};           // fp8 wide write: bytes per CTA relative to the copy write
@@ -110,6 +111,7 @@ const OptionName kOptionNames[] = {
     {"wide", &Options::wide},
     {"attn_min_items", &Options::attn_min_items},
     {"attn_carry", &Options::attn_carry},
+    {"host_pair_kv", &Options::host_pair_kv},
     {"packed_fill_halves", &Options::packed_fill_halves},
     {"packed_lines_variant", &Options::packed_lines_variant},
     {"f8_tile_mult", &Options::f8_tile_mult},

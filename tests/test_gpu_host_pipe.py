@@ -16,11 +16,14 @@ pytestmark = pytest.mark.gpu
 OK = abi.STATUS_OK
 
 
-def _run(case, chunk_bytes, device_scales=None):
+def _run(case, chunk_bytes, device_scales=None, adjacent_outputs=False):
     import torch
     import kvx_b200
     L = kvx_b200.lib()
     hb = host_buffers(case)                      # numpy host buffers (inputs and outputs)
+    if adjacent_outputs:                         # V output right behind the K output, in one array
+        both = np.stack([hb["out_k"], hb["out_v"]])
+        hb["out_k"], hb["out_v"] = both[0], both[1]
     if device_scales is not None:                # quantisation scales are read by the kernels
         hb["k_scale"], hb["v_scale"] = device_scales
     dev_k = torch.from_numpy(case.cache_k.view(np.uint8).copy()).cuda()
@@ -65,6 +68,29 @@ def test_host_pipeline_matches_checker(dtype):
         assert np.array_equal(k, ek) and np.array_equal(v, ev), f"pages differ (case {i})"
         assert np.array_equal(ok_, eok) and np.array_equal(ov_, eov), f"host outputs differ (case {i})"
         assert h2d >= 2 * case.T * row and d2h > 0
+
+
+def test_host_pipeline_pairs_the_k_and_v_runs_of_a_sequence():
+    """Where the V output lies a fixed distance behind the K output (one array for both), a
+    sequence's K run and V run go back as the two rows of one 2-D copy; same bytes as with two
+    copies (the knob) and as the checker's, untouched rows included; damaged table entries cut
+    the runs."""
+    import kvx_b200
+    case = cases.make_case(950, dtype=abi.DTYPE_BF16, heads=8, dim=128, block_size=16, num_blocks=120,
+                           lens=[300, 77, 512, 9, 0, 130, 511], pad_frac=0.1, bad_blocks=4)
+    _, ek, ev = oracle_write(case)
+    _, eok, eov = oracle_gather(case, ek, ev)
+    row = case.geom.num_kv_heads * case.geom.head_dim * case.key.dtype.itemsize
+    saved = kvx_b200.get_option("host_pair_kv")
+    try:
+        for pair in (1, 0):
+            kvx_b200.set_option("host_pair_kv", pair)
+            k, v, ok_, ov_, _, d2h = _run(case, 3 * case.max_seq_len * row, adjacent_outputs=True)
+            assert np.array_equal(k, ek) and np.array_equal(v, ev)
+            assert np.array_equal(ok_, eok) and np.array_equal(ov_, eov), f"host outputs differ (paired copies {pair})"
+            assert d2h > 0
+    finally:
+        kvx_b200.set_option("host_pair_kv", saved)
 
 
 def test_host_pipeline_fp8():
