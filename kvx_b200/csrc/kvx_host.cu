@@ -17,6 +17,9 @@ namespace {
 
 constexpr int kSets = 3;   // staging sets in rotation, per ring
 constexpr int kRings = 2;  // ring 0 stages write batches, ring 1 stages gathered sequences
+// Longest K (or V) run that returns paired with the other tensor's as one 2-D copy: beyond it
+// a copy's set-up no longer shows, and 2-D copies with rows of 64 MB measured erratic.
+constexpr int64_t kPairedRunBytes = int64_t{16} << 20;
 
 int64_t elem_bytes(kvx_dtype_t t) {
   switch (t) {
@@ -291,7 +294,7 @@ KVX_API kvx_status_t kvx_host_gather_kv(kvx_host_pipe_t *p, const kvx_cache_desc
           const int64_t off = tok0 * row, bytes = (tok1 - tok0) * row;
           char *hk = static_cast<char *>(gather->io.key.data) + s * seq_bytes + off;
           char *hv = static_cast<char *>(gather->io.value.data) + s * seq_bytes + off;
-          if (paired) {
+          if (paired && bytes <= kPairedRunBytes) {
             ok(p, cudaMemcpy2DAsync(hk, static_cast<size_t>(kv_apart), p->k_stage[set] + i * seq_bytes + off, p->chunk_bytes,
                                     static_cast<size_t>(bytes), 2, cudaMemcpyDeviceToHost, p->d2h));
           } else {
