@@ -240,6 +240,11 @@ def test_options_and_counter(built_lib):
     kvx_b200.set_option("write_unroll", old)
     with pytest.raises(KeyError):
         kvx_b200.set_option("no_such_option", 1)
+    # the knobs the GPU tests and the benchmark switch, with their built-in values
+    for name, value in (("attn_carry", 1), ("attn_min_items", 0), ("packed_fill_halves", 1), ("packed_lines_variant", 0),
+                        ("packed_tiles", 1), ("packed_tile_tokens", 32), ("host_pair_kv", 1), ("gather_rect_items", 40000),
+                        ("gather_ctas_per_sm", 256), ("bulk_test_stall", 0)):
+        assert kvx_b200.get_option(name) == value, name
     built_lib.kvx_b200_reset_launch_count()
     assert built_lib.kvx_b200_launch_count() == 0
 
